@@ -1,0 +1,168 @@
+/*
+ * primitiv_b200 -- C ABI of the Blackwell (sm_100a) backend for primitiv's
+ * minibatch-broadcasting matrix product and the device operations around it.
+ *
+ * This is the only surface that crosses from host code into the CUDA kernels.
+ * primitiv::devices::B200 (primitiv_b200/device/) is written on top of it, and so
+ * is anything that binds the library from another language.
+ *
+ * Conventions
+ *   - Every function returns 0 on success, otherwise a non-zero B200_ERR_* /
+ *     cudaError code; b200_error_string() explains it.  Nothing throws.
+ *   - All tensors are primitiv tensors: column-major, densely packed, minibatch
+ *     outermost (primitiv/core/device.h:298-299).  Element (i, j, n) of a
+ *     Shape({r, c}, batch) tensor is at  i + j*r + n*r*c.
+ *   - Pointers are DEVICE pointers unless the parameter name ends in `_host`.
+ *   - `stream` is a cudaStream_t passed as void*; NULL is the legacy default
+ *     stream, which is what the reference CUDA device uses for every launch.
+ *   - Calls are asynchronous with respect to the host unless stated otherwise.
+ *   - One host thread at a time per context (the contract of primitiv::Device).
+ *   - There is no CPU fallback: if no sm_100 GPU is present, context creation fails.
+ */
+#ifndef PRIMITIV_B200_H_
+#define PRIMITIV_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_API __attribute__((visibility("default")))
+
+typedef struct b200_ctx b200_ctx;
+
+/* Numeric modes of the matrix product. */
+enum {
+  B200_MODE_FP32_3XTF32 = 0, /* fp32 storage; each product = 3 TF32 tensor-core passes on hi/lo splits; fp32 accuracy */
+  B200_MODE_TF32        = 1, /* fp32 storage; one TF32 pass */
+  B200_MODE_FP16        = 2  /* half storage, fp32 accumulation, one rounding on store (mirrors primitiv::devices::CUDA16) */
+};
+
+/* Error codes (values >= 1000; smaller non-zero values are cudaError_t). */
+enum {
+  B200_OK                 = 0,
+  B200_ERR_INVALID_ARG    = 1001,
+  B200_ERR_NO_DEVICE      = 1002, /* no CUDA device / not compute capability 10.x */
+  B200_ERR_OUT_OF_MEMORY  = 1003,
+  B200_ERR_KERNEL_TIMEOUT = 1004, /* a bounded device-side wait gave up; see b200_status_poll */
+  B200_ERR_DRIVER         = 1005, /* driver entry point for tensor-map encoding unavailable or failed */
+  B200_ERR_TOO_LARGE      = 1006  /* size beyond a documented maximum */
+};
+
+B200_API const char *b200_error_string(int code);
+
+/* ---- context ------------------------------------------------------------------
+ * Replaces primitiv::cuda::InternalState (primitiv/internal/cuda/utils.h:320-350):
+ * device properties, the caching memory pool and the kernels' status word.  No
+ * cuBLAS / cuRAND / cuDNN handle exists: every kernel is in this library. */
+B200_API int b200_ctx_create(int device_id, b200_ctx **ctx);
+B200_API int b200_ctx_destroy(b200_ctx *ctx);
+B200_API int b200_ctx_device(const b200_ctx *ctx, int *device_id, int *sm_count);
+
+/* Reads and clears the device status word written by a kernel whose bounded wait
+ * ran out.  Synchronises `stream`.  *code is 0 when no kernel reported anything. */
+B200_API int b200_status_poll(b200_ctx *ctx, void *stream, int *code);
+
+/* ---- caching memory pool --------------------------------------------------------
+ * Replaces primitiv::MemoryPool (primitiv/core/memory_pool.cc:35-94) as configured
+ * by the CUDA device (primitiv/internal/cuda/utils.h:327-342).  Blocks are 256-byte
+ * aligned; freed blocks are cached per size class (geometric classes with four
+ * steps per octave, so at most ~19% round-up instead of up to 100%); when
+ * cudaMalloc fails every cached block is released and the allocation retried once,
+ * as the reference pool does. */
+B200_API int b200_pool_alloc(b200_ctx *ctx, size_t bytes, void **ptr, size_t *allocated_bytes);
+B200_API int b200_pool_free(b200_ctx *ctx, void *ptr);
+B200_API int b200_pool_release_cached(b200_ctx *ctx);
+/* stats[0]=bytes in use, [1]=bytes cached, [2]=cudaMalloc calls, [3]=cache hits */
+B200_API int b200_pool_stats(const b200_ctx *ctx, uint64_t stats[4]);
+/* Pure host function: the block size a request of `bytes` is rounded up to. */
+B200_API size_t b200_pool_size_class(size_t bytes);
+/* Host-side fault injection for tests: a soft capacity in bytes (0 = none).  A
+ * request that would push in-use + cached bytes past it is treated exactly like
+ * a failed cudaMalloc (release cached blocks, retry once, then
+ * B200_ERR_OUT_OF_MEMORY), without touching the GPU's real memory limit. */
+B200_API int b200_pool_set_limit(b200_ctx *ctx, size_t bytes);
+
+/* ---- the hot path -----------------------------------------------------------------
+ * b200_matmul_fw replaces Device::matmul_fw_impl (primitiv/core/device.h:464;
+ * CUDA: primitiv/devices/cuda/ops/matmul.cu:26-65; CUDA16: cuda16/ops/matmul.cu:46-129):
+ *     y[n] = a[n or 0] . b[n or 0]                      (overwrite)
+ * a: Shape({di,dj}, ba), b: Shape({dj,dk}, bb), y: Shape({di,dk}, max(ba,bb));
+ * ba, bb in {1, N}; an operand with batch 1 is broadcast.
+ *
+ * b200_matmul_bw replaces Device::matmul_bw_impl (primitiv/core/device.h:481-483;
+ * CUDA: matmul.cu:67-138; CUDA16: cuda16/ops/matmul.cu:131-266):
+ *     ga[n or 0] += gy[n] . b[n or 0]^T ;   gb[n or 0] += a[n or 0]^T . gy[n]
+ * accumulating in place, and summing over the batch into a broadcast operand's
+ * gradient.  Either of ga / gb may be NULL to skip that product.
+ *
+ * Element type is float for the two fp32 modes and IEEE half for B200_MODE_FP16.
+ * The tensor-core path needs 16-byte aligned pointers and leading dimensions
+ * that are multiples of 16 bytes; anything else (e.g. 123x123, {10,1024}) runs
+ * on the CUDA-core kernel of this library, which computes in plain fp32 FMA. */
+B200_API int b200_matmul_fw(b200_ctx *ctx, int mode,
+                            const void *a, const void *b, void *y,
+                            uint32_t di, uint32_t dj, uint32_t dk,
+                            uint32_t ba, uint32_t bb, void *stream);
+
+B200_API int b200_matmul_bw(b200_ctx *ctx, int mode,
+                            const void *a, const void *b, const void *gy,
+                            void *ga, void *gb,
+                            uint32_t di, uint32_t dj, uint32_t dk,
+                            uint32_t ba, uint32_t bb, void *stream);
+
+/* Same two operations with HOST buffers: copies the operands to the device
+ * (pool memory), runs the kernels, copies the result back and synchronises.
+ * This is what a caller holding host data pays end to end
+ * (Device::new_tensor_by_array + matmul + Tensor::to_vector in primitiv terms). */
+B200_API int b200_matmul_fw_host(b200_ctx *ctx, int mode,
+                                 const void *a_host, const void *b_host, void *y_host,
+                                 uint32_t di, uint32_t dj, uint32_t dk,
+                                 uint32_t ba, uint32_t bb);
+
+B200_API int b200_matmul_bw_host(b200_ctx *ctx, int mode,
+                                 const void *a_host, const void *b_host, const void *gy_host,
+                                 void *ga_host, void *gb_host,
+                                 uint32_t di, uint32_t dj, uint32_t dk,
+                                 uint32_t ba, uint32_t bb);
+
+/* ---- the general contraction underneath (what cublasSgemm / SgemmBatched /
+ * Hgemm were to the reference devices) --------------------------------------------------
+ *   C[g] = (accumulate ? C[g] : 0) + sum_{r < red} opA(A[g*a_gs + r*a_rs]) . opB(B[g*b_gs + r*b_rs])
+ * for g < groups; all strides in ELEMENTS.  C is m x n, column-major, ld = m.
+ *   trans_a == 0: A is m x k column-major (ld m);  trans_a != 0: A is k x m (ld k), used transposed
+ *   trans_b == 0: B is k x n column-major (ld k);  trans_b != 0: B is n x k (ld n), used transposed
+ * `red` > 1 sums several operand pairs into one C without atomics (the
+ * "a batched, b broadcast" gradient that the reference computes with a serial
+ * loop of Sgemm calls, matmul.cu:113-123).
+ * force_path: 0 = choose; 1 = CUDA-core kernel; 2 = tensor-core kernel (error if ineligible). */
+B200_API int b200_gemm(b200_ctx *ctx, int mode, int trans_a, int trans_b,
+                       const void *A, const void *B, void *C,
+                       uint32_t m, uint32_t n, uint32_t k,
+                       uint32_t groups, uint32_t red,
+                       uint64_t a_gs, uint64_t a_rs, uint64_t b_gs, uint64_t b_rs, uint64_t c_gs,
+                       int accumulate, int force_path, void *stream);
+
+/* Kernel choice for b200_matmul_* and for b200_gemm calls with force_path == 0:
+ * 0 = per problem (default), 1 = always the CUDA-core kernel, 2 = the tensor-core
+ * kernel whenever the operands are eligible, however small the problem. */
+B200_API int b200_set_path_policy(b200_ctx *ctx, int policy);
+
+/* Optional per-launch timing.  While enabled, every kernel launch of this context is
+ * bracketed by a pair of CUDA events on its stream.  b200_profile_read synchronises the
+ * device, sums elapsed milliseconds and launch counts per kernel kind since the last
+ * read, and clears the records:
+ *   [0] tensor-core GEMM   [1] TF32 packing pre-pass   [2] CUDA-core GEMM   [3] elementwise */
+B200_API int b200_profile_enable(b200_ctx *ctx, int on);
+B200_API int b200_profile_read(b200_ctx *ctx, double ms[4], uint64_t launches[4]);
+
+/* Number of kernel launches this context has issued (all kernels of this library). */
+B200_API int b200_launch_count(const b200_ctx *ctx, uint64_t *launches);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif  /* PRIMITIV_B200_H_ */

@@ -1,0 +1,170 @@
+"""ctypes binding of include/primitiv_b200.h.
+
+Device memory and streams come from the caller (raw integer addresses, e.g.
+``torch.Tensor.data_ptr()``); this module never allocates through torch and has
+no compute of its own.
+"""
+import ctypes
+import os
+
+MODE_FP32_3XTF32 = 0
+MODE_TF32 = 1
+MODE_FP16 = 2
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+_u32 = ctypes.c_uint32
+_u64 = ctypes.c_uint64
+_vp = ctypes.c_void_p
+_int = ctypes.c_int
+
+# name -> (restype, argtypes); every symbol include/primitiv_b200.h declares
+SIGNATURES = {
+    "b200_error_string": (ctypes.c_char_p, [_int]),
+    "b200_ctx_create": (_int, [_int, ctypes.POINTER(_vp)]),
+    "b200_ctx_destroy": (_int, [_vp]),
+    "b200_ctx_device": (_int, [_vp, ctypes.POINTER(_int), ctypes.POINTER(_int)]),
+    "b200_status_poll": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
+    "b200_pool_alloc": (_int, [_vp, ctypes.c_size_t, ctypes.POINTER(_vp), ctypes.POINTER(ctypes.c_size_t)]),
+    "b200_pool_free": (_int, [_vp, _vp]),
+    "b200_pool_release_cached": (_int, [_vp]),
+    "b200_pool_stats": (_int, [_vp, ctypes.POINTER(_u64)]),
+    "b200_pool_set_limit": (_int, [_vp, ctypes.c_size_t]),
+    "b200_pool_size_class": (ctypes.c_size_t, [ctypes.c_size_t]),
+    "b200_matmul_fw": (_int, [_vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp]),
+    "b200_matmul_bw": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp]),
+    "b200_matmul_fw_host": (_int, [_vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32]),
+    "b200_matmul_bw_host": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32]),
+    "b200_gemm": (_int, [_vp, _int, _int, _int, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32,
+                         _u64, _u64, _u64, _u64, _u64, _int, _int, _vp]),
+    "b200_set_path_policy": (_int, [_vp, _int]),
+    "b200_profile_enable": (_int, [_vp, _int]),
+    "b200_profile_read": (_int, [_vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_u64)]),
+    "b200_launch_count": (_int, [_vp, ctypes.POINTER(_u64)]),
+}
+
+
+class B200Error(RuntimeError):
+    def __init__(self, code, what=""):
+        self.code = code
+        msg = lib().b200_error_string(code).decode() if _LIB is not None else str(code)
+        super().__init__("%s (code %d)%s" % (msg, code, (": " + what) if what else ""))
+
+
+def library_path():
+    return os.path.join(_PKG, "libprimitiv_b200.so")
+
+
+def lib():
+    """Loads libprimitiv_b200.so.  Raises if it has not been built: there is no fallback."""
+    global _LIB
+    if _LIB is None:
+        path = library_path()
+        if not os.path.exists(path):
+            raise ImportError(
+                "libprimitiv_b200.so is not built (run `python -m primitiv_b200.build`); "
+                "primitiv_b200 has no non-CUDA implementation")
+        handle = ctypes.CDLL(path)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _LIB = handle
+    return _LIB
+
+
+def _check(code, what=""):
+    if code != 0:
+        raise B200Error(code, what)
+
+
+class Context:
+    """One b200_ctx (one GPU).  Mirrors the lifetime of a primitiv::devices::B200 object."""
+
+    def __init__(self, device_id=0):
+        self._h = _vp()
+        _check(lib().b200_ctx_create(device_id, ctypes.byref(self._h)), "b200_ctx_create")
+        self.device_id = device_id
+
+    def close(self):
+        if self._h:
+            lib().b200_ctx_destroy(self._h)
+            self._h = _vp()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def sm_count(self):
+        d, n = _int(), _int()
+        _check(lib().b200_ctx_device(self._h, ctypes.byref(d), ctypes.byref(n)))
+        return n.value
+
+    def status_poll(self, stream=None):
+        c = _int()
+        _check(lib().b200_status_poll(self._h, stream, ctypes.byref(c)))
+        return c.value
+
+    def set_path_policy(self, policy):
+        _check(lib().b200_set_path_policy(self._h, policy), "set_path_policy")
+
+    def profile_enable(self, on=True):
+        _check(lib().b200_profile_enable(self._h, int(on)))
+
+    def profile_read(self):
+        """-> {kind: (milliseconds, launches)} since the last read."""
+        ms = (ctypes.c_double * 4)()
+        n = (_u64 * 4)()
+        _check(lib().b200_profile_read(self._h, ms, n))
+        names = ("gemm_tc", "pack", "gemm_simt", "elementwise")
+        return {k: (ms[i], n[i]) for i, k in enumerate(names)}
+
+    def launch_count(self):
+        n = _u64()
+        _check(lib().b200_launch_count(self._h, ctypes.byref(n)))
+        return n.value
+
+    # -- pool --
+    def pool_alloc(self, nbytes):
+        p, got = _vp(), ctypes.c_size_t()
+        _check(lib().b200_pool_alloc(self._h, nbytes, ctypes.byref(p), ctypes.byref(got)), "pool_alloc")
+        return p.value, got.value
+
+    def pool_free(self, ptr):
+        _check(lib().b200_pool_free(self._h, ptr), "pool_free")
+
+    def pool_release_cached(self):
+        _check(lib().b200_pool_release_cached(self._h))
+
+    def pool_set_limit(self, nbytes):
+        _check(lib().b200_pool_set_limit(self._h, nbytes))
+
+    def pool_stats(self):
+        arr = (_u64 * 4)()
+        _check(lib().b200_pool_stats(self._h, arr))
+        return dict(in_use=arr[0], cached=arr[1], mallocs=arr[2], hits=arr[3])
+
+    # -- hot path (device pointers as ints) --
+    def matmul_fw(self, mode, a, b, y, di, dj, dk, ba, bb, stream=None):
+        _check(lib().b200_matmul_fw(self._h, mode, a, b, y, di, dj, dk, ba, bb, stream), "matmul_fw")
+
+    def matmul_bw(self, mode, a, b, gy, ga, gb, di, dj, dk, ba, bb, stream=None):
+        _check(lib().b200_matmul_bw(self._h, mode, a, b, gy, ga, gb, di, dj, dk, ba, bb, stream),
+               "matmul_bw")
+
+    def matmul_fw_host(self, mode, a, b, y, di, dj, dk, ba, bb):
+        _check(lib().b200_matmul_fw_host(self._h, mode, a, b, y, di, dj, dk, ba, bb), "matmul_fw_host")
+
+    def matmul_bw_host(self, mode, a, b, gy, ga, gb, di, dj, dk, ba, bb):
+        _check(lib().b200_matmul_bw_host(self._h, mode, a, b, gy, ga, gb, di, dj, dk, ba, bb),
+               "matmul_bw_host")
+
+    def gemm(self, mode, trans_a, trans_b, A, B, C, m, n, k, groups=1, red=1,
+             a_gs=0, a_rs=0, b_gs=0, b_rs=0, c_gs=0, accumulate=False, force_path=0, stream=None):
+        _check(lib().b200_gemm(self._h, mode, int(trans_a), int(trans_b), A, B, C, m, n, k, groups, red,
+                               a_gs, a_rs, b_gs, b_rs, c_gs, int(accumulate), force_path, stream),
+               "gemm")

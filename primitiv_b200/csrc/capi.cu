@@ -1,0 +1,307 @@
+// extern "C" entry points of libprimitiv_b200.so: context, pool, and the mapping of
+// primitiv's matmul_fw / matmul_bw onto the general contraction.
+#include <cstring>
+#include <new>
+
+#include "ctx.h"
+
+using b200::DeviceGuard;
+using b200::GemmArgs;
+
+extern "C" {
+
+const char *b200_error_string(int code) {
+  switch (code) {
+    case B200_OK: return "ok";
+    case B200_ERR_INVALID_ARG: return "primitiv_b200: invalid argument";
+    case B200_ERR_NO_DEVICE: return "primitiv_b200: no CUDA device of compute capability 10.x (there is no CPU fallback)";
+    case B200_ERR_OUT_OF_MEMORY: return "primitiv_b200: device memory exhausted (after releasing the pool's cached blocks)";
+    case B200_ERR_KERNEL_TIMEOUT: return "primitiv_b200: a bounded device-side wait ran out";
+    case B200_ERR_DRIVER: return "primitiv_b200: tensor-map encoding failed or driver entry point missing";
+    case B200_ERR_TOO_LARGE: return "primitiv_b200: size beyond a documented maximum";
+    default: break;
+  }
+  if (code > 0 && code < 1000) return cudaGetErrorString(static_cast<cudaError_t>(code));
+  return "primitiv_b200: unknown error";
+}
+
+int b200_ctx_create(int device_id, b200_ctx **out) {
+  if (!out) return B200_ERR_INVALID_ARG;
+  *out = nullptr;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    return B200_ERR_NO_DEVICE;
+  }
+  if (device_id < 0 || device_id >= n) return B200_ERR_INVALID_ARG;
+  cudaDeviceProp prop;
+  B200_CUDA_TRY(cudaGetDeviceProperties(&prop, device_id));
+  if (prop.major != 10) return B200_ERR_NO_DEVICE;
+  b200_ctx *ctx = new (std::nothrow) b200_ctx();
+  if (!ctx) return B200_ERR_OUT_OF_MEMORY;
+  ctx->device = device_id;
+  ctx->sm_count = prop.multiProcessorCount;
+  ctx->cc_major = prop.major;
+  ctx->cc_minor = prop.minor;
+  ctx->smem_optin = prop.sharedMemPerBlockOptin;
+  DeviceGuard guard(device_id);
+  cudaError_t e = cudaMalloc(&ctx->d_status, 256);
+  if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, 256);
+  if (e != cudaSuccess) {
+    delete ctx;
+    return static_cast<int>(e);
+  }
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+      qres == cudaDriverEntryPointSuccess) {
+    ctx->encode_tiled = reinterpret_cast<b200::EncodeTiledFn>(fn);
+  } else {
+    cudaGetLastError();
+    cudaFree(ctx->d_status);
+    delete ctx;
+    return B200_ERR_DRIVER;
+  }
+  *out = ctx;
+  return B200_OK;
+}
+
+int b200_ctx_destroy(b200_ctx *ctx) {
+  if (!ctx) return B200_OK;
+  DeviceGuard guard(ctx->device);
+  cudaDeviceSynchronize();
+  cudaFree(ctx->d_status);
+  delete ctx;  // the pool's destructor returns cached blocks
+  return B200_OK;
+}
+
+int b200_ctx_device(const b200_ctx *ctx, int *device_id, int *sm_count) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  if (device_id) *device_id = ctx->device;
+  if (sm_count) *sm_count = ctx->sm_count;
+  return B200_OK;
+}
+
+int b200_status_poll(b200_ctx *ctx, void *stream, int *code) {
+  if (!ctx || !code) return B200_ERR_INVALID_ARG;
+  DeviceGuard guard(ctx->device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int host = 0;
+  B200_CUDA_TRY(cudaMemcpyAsync(&host, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
+  B200_CUDA_TRY(cudaStreamSynchronize(s));
+  if (host != 0) B200_CUDA_TRY(cudaMemsetAsync(ctx->d_status, 0, sizeof(int), s));
+  *code = host;
+  return B200_OK;
+}
+
+int b200_pool_alloc(b200_ctx *ctx, size_t bytes, void **ptr, size_t *allocated) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  DeviceGuard guard(ctx->device);
+  return ctx->pool.alloc(bytes, ptr, allocated);
+}
+
+int b200_pool_free(b200_ctx *ctx, void *ptr) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  return ctx->pool.free(ptr);
+}
+
+int b200_pool_release_cached(b200_ctx *ctx) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  DeviceGuard guard(ctx->device);
+  ctx->pool.release_cached();
+  return B200_OK;
+}
+
+int b200_pool_stats(const b200_ctx *ctx, uint64_t stats[4]) {
+  if (!ctx || !stats) return B200_ERR_INVALID_ARG;
+  ctx->pool.stats(stats);
+  return B200_OK;
+}
+
+size_t b200_pool_size_class(size_t bytes) { return b200::Pool::size_class(bytes ? bytes : 1); }
+
+int b200_pool_set_limit(b200_ctx *ctx, size_t bytes) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  ctx->pool.set_limit(bytes);
+  return B200_OK;
+}
+
+int b200_set_path_policy(b200_ctx *ctx, int policy) {
+  if (!ctx || policy < 0 || policy > 2) return B200_ERR_INVALID_ARG;
+  ctx->path_policy = policy;
+  return B200_OK;
+}
+
+int b200_profile_enable(b200_ctx *ctx, int on) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  ctx->profiling = on != 0;
+  return B200_OK;
+}
+
+int b200_profile_read(b200_ctx *ctx, double ms[4], uint64_t launches[4]) {
+  if (!ctx || !ms || !launches) return B200_ERR_INVALID_ARG;
+  DeviceGuard guard(ctx->device);
+  for (int i = 0; i < b200::kProfKinds; ++i) { ms[i] = 0.0; launches[i] = 0; }
+  B200_CUDA_TRY(cudaDeviceSynchronize());
+  for (auto &r : ctx->prof) {
+    float t = 0.f;
+    if (cudaEventElapsedTime(&t, r.start, r.stop) == cudaSuccess && r.kind >= 0 && r.kind < b200::kProfKinds) {
+      ms[r.kind] += t;
+      launches[r.kind] += 1;
+    }
+    cudaEventDestroy(r.start);
+    cudaEventDestroy(r.stop);
+  }
+  ctx->prof.clear();
+  return B200_OK;
+}
+
+int b200_launch_count(const b200_ctx *ctx, uint64_t *launches) {
+  if (!ctx || !launches) return B200_ERR_INVALID_ARG;
+  *launches = ctx->launches;
+  return B200_OK;
+}
+
+int b200_gemm(b200_ctx *ctx, int mode, int trans_a, int trans_b, const void *A, const void *B,
+              void *C, uint32_t m, uint32_t n, uint32_t k, uint32_t groups, uint32_t red,
+              uint64_t a_gs, uint64_t a_rs, uint64_t b_gs, uint64_t b_rs, uint64_t c_gs,
+              int accumulate, int force_path, void *stream) {
+  if (!ctx || !A || !B || !C) return B200_ERR_INVALID_ARG;
+  if (mode < B200_MODE_FP32_3XTF32 || mode > B200_MODE_FP16) return B200_ERR_INVALID_ARG;
+  if (m == 0 || n == 0 || groups == 0) return B200_OK;
+  if (k == 0 || red == 0) return B200_ERR_INVALID_ARG;
+  DeviceGuard guard(ctx->device);
+  GemmArgs g{mode, trans_a ? 1 : 0, trans_b ? 1 : 0, A, B, C, m, n, k, groups, red,
+             a_gs, a_rs, b_gs, b_rs, c_gs, accumulate ? 1 : 0};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool eligible = b200::gemm_tc_eligible(ctx, g);
+  if (force_path == 2) return eligible ? b200::gemm_tc(ctx, g, s) : B200_ERR_INVALID_ARG;
+  if (force_path == 1) return b200::gemm_simt(ctx, g, s);
+  if (ctx->path_policy == 2 && eligible) return b200::gemm_tc(ctx, g, s);
+  if (ctx->path_policy == 1) return b200::gemm_simt(ctx, g, s);
+  // A 128-row MMA tile on a problem this small is mostly padding; the CUDA-core
+  // kernel wins below roughly a tile's worth of work.
+  const double macs = static_cast<double>(m) * n * k * groups * red;
+  if (eligible && m >= 32 && n >= 16 && macs >= 2097152.0) return b200::gemm_tc(ctx, g, s);
+  return b200::gemm_simt(ctx, g, s);
+}
+
+static int check_matmul(const b200_ctx *ctx, int mode, uint32_t ba, uint32_t bb) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  if (mode < B200_MODE_FP32_3XTF32 || mode > B200_MODE_FP16) return B200_ERR_INVALID_ARG;
+  if (ba == 0 || bb == 0) return B200_ERR_INVALID_ARG;
+  if (ba != bb && ba != 1 && bb != 1) return B200_ERR_INVALID_ARG;  // Shape::has_compatible_batch
+  return B200_OK;
+}
+
+int b200_matmul_fw(b200_ctx *ctx, int mode, const void *a, const void *b, void *y, uint32_t di,
+                   uint32_t dj, uint32_t dk, uint32_t ba, uint32_t bb, void *stream) {
+  int rc = check_matmul(ctx, mode, ba, bb);
+  if (rc) return rc;
+  if (!a || !b || !y) return B200_ERR_INVALID_ARG;
+  const uint64_t na = (uint64_t)di * dj, nb = (uint64_t)dj * dk, ny = (uint64_t)di * dk;
+  if (ba == 1) {
+    // one product over the combined {dj, dk*bb} matrix: b's batches are adjacent columns
+    return b200_gemm(ctx, mode, 0, 0, a, b, y, di, dk * bb, dj, 1, 1, 0, 0, 0, 0, 0, 0, 0, stream);
+  }
+  return b200_gemm(ctx, mode, 0, 0, a, b, y, di, dk, dj, ba, 1, na, 0, bb > 1 ? nb : 0, 0, ny, 0, 0,
+                   stream);
+}
+
+int b200_matmul_bw(b200_ctx *ctx, int mode, const void *a, const void *b, const void *gy, void *ga,
+                   void *gb, uint32_t di, uint32_t dj, uint32_t dk, uint32_t ba, uint32_t bb,
+                   void *stream) {
+  int rc = check_matmul(ctx, mode, ba, bb);
+  if (rc) return rc;
+  if (!a || !b || !gy) return B200_ERR_INVALID_ARG;
+  const uint64_t na = (uint64_t)di * dj, nb = (uint64_t)dj * dk, ny = (uint64_t)di * dk;
+  if (ba == 1) {
+    const uint32_t dkb = dk * bb;
+    // ga += gy_all . b_all^T : the batch sum is the tail of one long contraction
+    if (ga) {
+      rc = b200_gemm(ctx, mode, 0, 1, gy, b, ga, di, dj, dkb, 1, 1, 0, 0, 0, 0, 0, 1, 0, stream);
+      if (rc) return rc;
+    }
+    // gb_all += a^T . gy_all
+    if (gb) rc = b200_gemm(ctx, mode, 1, 0, a, gy, gb, dj, dkb, di, 1, 1, 0, 0, 0, 0, 0, 1, 0, stream);
+    return rc;
+  }
+  // ga[n] += gy[n] . b[n or 0]^T
+  if (ga) {
+    rc = b200_gemm(ctx, mode, 0, 1, gy, b, ga, di, dj, dk, ba, 1, ny, 0, bb > 1 ? nb : 0, 0, na, 1, 0,
+                   stream);
+    if (rc) return rc;
+  }
+  if (gb) {
+    if (bb > 1) {
+      // gb[n] += a[n]^T . gy[n]
+      rc = b200_gemm(ctx, mode, 1, 0, a, gy, gb, dj, dk, di, ba, 1, na, 0, ny, 0, nb, 1, 0, stream);
+    } else {
+      // gb += sum_n a[n]^T . gy[n] : one launch, the batch is a second contraction axis
+      rc = b200_gemm(ctx, mode, 1, 0, a, gy, gb, dj, dk, di, 1, ba, 0, na, 0, ny, 0, 1, 0, stream);
+    }
+  }
+  return rc;
+}
+
+namespace {
+
+struct Scratch {
+  b200_ctx *ctx;
+  void *p = nullptr;
+  explicit Scratch(b200_ctx *c) : ctx(c) {}
+  ~Scratch() { if (p) ctx->pool.free(p); }
+  int get(size_t bytes) { return ctx->pool.alloc(bytes, &p, nullptr); }
+};
+
+}  // namespace
+
+int b200_matmul_fw_host(b200_ctx *ctx, int mode, const void *a_host, const void *b_host,
+                        void *y_host, uint32_t di, uint32_t dj, uint32_t dk, uint32_t ba,
+                        uint32_t bb) {
+  int rc = check_matmul(ctx, mode, ba, bb);
+  if (rc) return rc;
+  if (!a_host || !b_host || !y_host) return B200_ERR_INVALID_ARG;
+  DeviceGuard guard(ctx->device);
+  const size_t eb = b200::elem_bytes(mode);
+  const uint32_t bs = ba > bb ? ba : bb;
+  const size_t sa = (size_t)di * dj * ba * eb, sb = (size_t)dj * dk * bb * eb, sy = (size_t)di * dk * bs * eb;
+  Scratch da(ctx), db(ctx), dy(ctx);
+  if ((rc = da.get(sa)) || (rc = db.get(sb)) || (rc = dy.get(sy))) return rc;
+  B200_CUDA_TRY(cudaMemcpyAsync(da.p, a_host, sa, cudaMemcpyHostToDevice, 0));
+  B200_CUDA_TRY(cudaMemcpyAsync(db.p, b_host, sb, cudaMemcpyHostToDevice, 0));
+  rc = b200_matmul_fw(ctx, mode, da.p, db.p, dy.p, di, dj, dk, ba, bb, nullptr);
+  if (rc) return rc;
+  B200_CUDA_TRY(cudaMemcpyAsync(y_host, dy.p, sy, cudaMemcpyDeviceToHost, 0));
+  B200_CUDA_TRY(cudaStreamSynchronize(0));
+  return B200_OK;
+}
+
+int b200_matmul_bw_host(b200_ctx *ctx, int mode, const void *a_host, const void *b_host,
+                        const void *gy_host, void *ga_host, void *gb_host, uint32_t di, uint32_t dj,
+                        uint32_t dk, uint32_t ba, uint32_t bb) {
+  int rc = check_matmul(ctx, mode, ba, bb);
+  if (rc) return rc;
+  if (!a_host || !b_host || !gy_host || !ga_host || !gb_host) return B200_ERR_INVALID_ARG;
+  DeviceGuard guard(ctx->device);
+  const size_t eb = b200::elem_bytes(mode);
+  const uint32_t bs = ba > bb ? ba : bb;
+  const size_t sa = (size_t)di * dj * ba * eb, sb = (size_t)dj * dk * bb * eb, sy = (size_t)di * dk * bs * eb;
+  Scratch da(ctx), db(ctx), dgy(ctx), dga(ctx), dgb(ctx);
+  if ((rc = da.get(sa)) || (rc = db.get(sb)) || (rc = dgy.get(sy)) || (rc = dga.get(sa)) ||
+      (rc = dgb.get(sb)))
+    return rc;
+  B200_CUDA_TRY(cudaMemcpyAsync(da.p, a_host, sa, cudaMemcpyHostToDevice, 0));
+  B200_CUDA_TRY(cudaMemcpyAsync(db.p, b_host, sb, cudaMemcpyHostToDevice, 0));
+  B200_CUDA_TRY(cudaMemcpyAsync(dgy.p, gy_host, sy, cudaMemcpyHostToDevice, 0));
+  B200_CUDA_TRY(cudaMemcpyAsync(dga.p, ga_host, sa, cudaMemcpyHostToDevice, 0));
+  B200_CUDA_TRY(cudaMemcpyAsync(dgb.p, gb_host, sb, cudaMemcpyHostToDevice, 0));
+  rc = b200_matmul_bw(ctx, mode, da.p, db.p, dgy.p, dga.p, dgb.p, di, dj, dk, ba, bb, nullptr);
+  if (rc) return rc;
+  B200_CUDA_TRY(cudaMemcpyAsync(ga_host, dga.p, sa, cudaMemcpyDeviceToHost, 0));
+  B200_CUDA_TRY(cudaMemcpyAsync(gb_host, dgb.p, sb, cudaMemcpyDeviceToHost, 0));
+  B200_CUDA_TRY(cudaStreamSynchronize(0));
+  return B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,131 @@
+// Internal context shared by the translation units of libprimitiv_b200.so.
+#ifndef PRIMITIV_B200_CSRC_CTX_H_
+#define PRIMITIV_B200_CSRC_CTX_H_
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <map>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/primitiv_b200.h"
+
+namespace b200 {
+
+// Caching device-memory pool.  Size classes are geometric with four steps per
+// octave (1, 1.25, 1.5, 1.75 x 2^e), 256-byte granularity below 1 KiB.  All
+// blocks are handed out and reused in stream order on the caller's single
+// stream, so no event tracking is needed (the contract of primitiv::Device is
+// one host thread and one stream per device).
+class Pool {
+ public:
+  Pool() = default;
+  ~Pool();
+  int alloc(std::size_t bytes, void **ptr, std::size_t *allocated);
+  int free(void *ptr);
+  void release_cached();
+  void stats(std::uint64_t out[4]) const;
+  // Test hook: a soft capacity (0 = none).  Requests that would push
+  // in-use + cached bytes past it behave exactly like a failed cudaMalloc.
+  void set_limit(std::size_t bytes) { limit_ = bytes; }
+  static std::size_t size_class(std::size_t bytes);
+
+ private:
+  std::map<std::size_t, std::vector<void *>> cached_;
+  std::unordered_map<void *, std::size_t> in_use_;
+  std::size_t bytes_in_use_ = 0, bytes_cached_ = 0, limit_ = 0;
+  std::uint64_t n_malloc_ = 0, n_hit_ = 0;
+  int raw_alloc(std::size_t bytes, void **ptr);
+};
+
+typedef CUresult (*EncodeTiledFn)(
+    CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+}  // namespace b200
+
+struct b200_ctx {
+  int device = 0;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  std::size_t smem_optin = 0;
+  b200::Pool pool;
+  int *d_status = nullptr;       // device status word (bounded-wait failures)
+  b200::EncodeTiledFn encode_tiled = nullptr;
+  std::uint64_t launches = 0;
+  bool tc_smem_configured = false;
+  int path_policy = 0;           // 0 = choose per problem, 1 = CUDA-core kernel, 2 = tensor-core kernel when eligible
+  // optional per-launch timing (b200_profile_*): event pairs, summed when read
+  bool profiling = false;
+  struct ProfRec { cudaEvent_t start, stop; int kind; };
+  std::vector<ProfRec> prof;
+};
+
+namespace b200 {
+
+// RAII device guard: every entry point makes its context's device current, as
+// the reference does with cudaSetDevice at the top of every op
+// (primitiv/devices/cuda/ops/matmul.cu:33), and restores the previous one.
+struct DeviceGuard {
+  int prev = -1;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+  }
+  ~DeviceGuard() {
+    int cur = -1;
+    cudaGetDevice(&cur);
+    if (prev >= 0 && cur != prev) cudaSetDevice(prev);
+  }
+};
+
+// Kernel kinds for b200_profile_read.
+enum { kProfGemmTc = 0, kProfPack = 1, kProfGemmSimt = 2, kProfElementwise = 3, kProfKinds = 4 };
+
+// Brackets one kernel launch with CUDA events on its stream when profiling is on.
+struct ProfScope {
+  b200_ctx *ctx;
+  cudaStream_t stream;
+  cudaEvent_t stop = nullptr;
+  ProfScope(b200_ctx *c, int kind, cudaStream_t s) : ctx(c), stream(s) {
+    if (!c->profiling) return;
+    cudaEvent_t start;
+    if (cudaEventCreate(&start) != cudaSuccess) return;
+    if (cudaEventCreate(&stop) != cudaSuccess) { cudaEventDestroy(start); stop = nullptr; return; }
+    cudaEventRecord(start, s);
+    c->prof.push_back({start, stop, kind});
+  }
+  ~ProfScope() { if (stop) cudaEventRecord(stop, stream); }
+};
+
+struct GemmArgs {
+  int mode;
+  int trans_a, trans_b;
+  const void *A, *B;
+  void *C;
+  std::uint32_t m, n, k, groups, red;
+  std::uint64_t a_gs, a_rs, b_gs, b_rs, c_gs;
+  int accumulate;
+};
+
+// CUDA-core path: any shape, any alignment.
+int gemm_simt(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
+// tcgen05 path.  tc_eligible() says whether the operands meet TMA's alignment rules.
+bool gemm_tc_eligible(const b200_ctx *ctx, const GemmArgs &g);
+int gemm_tc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
+
+inline int elem_bytes(int mode) { return mode == B200_MODE_FP16 ? 2 : 4; }
+
+}  // namespace b200
+
+#define B200_CUDA_TRY(expr)                     \
+  do {                                          \
+    cudaError_t e__ = (expr);                   \
+    if (e__ != cudaSuccess) return (int)e__;    \
+  } while (0)
+
+#endif  // PRIMITIV_B200_CSRC_CTX_H_

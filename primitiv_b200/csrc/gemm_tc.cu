@@ -1,0 +1,810 @@
+// Tensor-core matrix product for sm_100a: tcgen05.mma with the accumulator in
+// tensor memory (TMEM), operands staged in shared memory by TMA, one persistent
+// CTA per SM walking a static tile list.
+//
+//   C[g] = (acc ? C[g] : 0) + sum_{r<red} opA(A[g*a_gs + r*a_rs]) . opB(B[g*b_gs + r*b_rs])
+//
+// primitiv tensors are column-major, so of the three contractions on the path
+//   forward     y  = a . b        A is MN-major (m contiguous), B is K-major
+//   backward-a  ga += gy . b^T    A and B are both MN-major
+//   backward-b  gb += a^T . gy    A and B are both K-major
+// every major-ness combination occurs.  The shared-memory matrix descriptors, the
+// instruction descriptor and the TMA boxes are computed on the host and passed in;
+// nothing about the operand layout is compiled into the kernel.
+//
+// fp16 operands, and fp32 operands in single-pass TF32 mode, are fed to the tensor
+// core in either major-ness straight from the caller's memory when they meet TMA's
+// 16-byte alignment rules (the tensor core ignores the 13 low mantissa bits of an
+// fp32 word).  Otherwise (unaligned fp32, or the 3xTF32 accuracy mode) a packing
+// pre-pass writes K-major planes [matrix][mn][k padded to 4] into pool scratch,
+// transposing if needed and rounding to TF32: hi = rn_tf32(x) and, for 3xTF32,
+// lo = rn_tf32(x - hi).  The main loop then runs one pass (hi,hi) or three passes
+// (lo,hi), (hi,lo), (hi,hi) per k-block into the same accumulator.
+//
+// Shared-memory layouts (stage bases 1024-aligned):
+//   K-major operand : [rows][128 B of k]              one TMA box {BK, rows}
+//   MN-major operand: [chunk][BK k-rows][128 B of mn] one TMA box {128 B, BK} per chunk
+// BK is 32 fp32 / 64 fp16 elements (128 bytes) per pipeline stage.  The swizzle is
+// the 128-byte pattern on 16-byte units, except for 32-bit MN-major operands:
+// kind::tf32 reads those correctly only under the 128-byte pattern on 32-byte
+// units (TMA SWIZZLE_128B_ATOM_32B, descriptor layout 1) with k-groups of 4 rows,
+// i.e. a stride-byte-offset of 512; under the plain pattern it returns zeros.
+//
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
+// owner, warps 2-9 = epilogue.  Output row i of the tile lives in TMEM lane i, so
+// for a fixed output column the 32 lanes of a warp hold 32 consecutive rows:
+// column-major C is written (and, for +=, read) with coalesced 128-byte accesses
+// straight from registers.
+//
+// Accumulation accuracy.  The tensor core truncates when it adds into its fp32
+// accumulator, which biases a long contraction (measured: 7e-6 normwise after
+// 384 accumulation steps).  In 3xTF32 mode the contraction is therefore cut into
+// chunks of kChunkKBlocks k-blocks; each chunk accumulates in TMEM from zero, and
+// the epilogue warps add finished chunks into fp32 registers with round-to-nearest
+// while the tensor core works on the next chunk (two TMEM buffers).  The error
+// then no longer grows with the contraction length.  The single-pass modes use one
+// chunk per tile, and the two TMEM buffers overlap a tile's epilogue with the next
+// tile's main loop.
+//
+// Every device-side wait is bounded (wall-clock, %globaltimer).  A wait that runs
+// out raises a CTA-wide abort flag, writes B200_ERR_KERNEL_TIMEOUT into the
+// context's status word, drains the CTA's own TMA copies and MMAs with bounded
+// waits, frees TMEM and returns.
+#include <cuda_fp16.h>
+
+#include <cstring>
+
+#include "ctx.h"
+
+namespace b200 {
+namespace {
+
+constexpr uint32_t kBM = 128;
+constexpr uint32_t kMaxStages = 8;
+constexpr uint32_t kThreads = 320;
+constexpr uint32_t kEpilogueWarps = 8;
+constexpr uint32_t kChunkKBlocks = 8;  // 3xTF32: promote to registers every 8 k-blocks (256 k)
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+
+struct alignas(64) TcParams {
+  CUtensorMap mapA[2];  // [0] = values (or hi plane), [1] = lo plane
+  CUtensorMap mapB[2];
+  void *C;
+  unsigned long long c_gs;
+  uint32_t m, n;
+  uint32_t kblocks, red, groups;
+  uint32_t tiles_m, tiles_n;
+  uint32_t bn, bk, stages;
+  uint32_t a_chunks, b_chunks;
+  uint32_t a_chunk_elems, b_chunk_elems;
+  uint32_t a_chunk_bytes, b_chunk_bytes;
+  uint32_t a_mn_major, b_mn_major;
+  uint32_t a_gmul, a_rmul, b_gmul, b_rmul;
+  uint32_t kstep_a_bytes, kstep_b_bytes, ksteps;
+  uint32_t lbo_a, sbo_a, lbo_b, sbo_b;
+  uint32_t layout_a, layout_b;  // descriptor swizzle field
+  uint32_t idesc;
+  uint32_t passes;
+  uint32_t chunk_kblocks;  // k-blocks per accumulation chunk
+  uint32_t accumulate, out_half, kind_f16;
+  uint32_t a_stage_bytes, stage_bytes;
+  uint32_t tmem_cols;
+  int *status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done;
+}
+
+// Bounded wait.  Returns false if the CTA is aborting or the limit ran out (in
+// which case it raises the abort flag itself).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *s_abort) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 31u) == 0u) {
+      if (*s_abort) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        *s_abort = 1;
+        return false;
+      }
+    }
+  }
+}
+
+// Wait used only on the abort path: never raises anything, just gives up.
+__device__ __forceinline__ void mbar_wait_quiet(uint32_t bar, uint32_t parity) {
+  const unsigned long long t0 = globaltimer_ns();
+  while (!mbar_try_wait(bar, parity)) {
+    if (globaltimer_ns() - t0 > kWaitLimitNs / 4) return;
+  }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<unsigned long long>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo,
+                                                   uint32_t layout) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
+  d |= static_cast<uint64_t>(1) << 46;  // descriptor version for sm_100
+  d |= static_cast<uint64_t>(layout & 7u) << 61;
+  return d;
+}
+
+__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Writes 32 consecutive output columns of one row (this lane's) to column-major C.
+template <typename T>
+__device__ __forceinline__ void store_cols(T *C, unsigned long long base, uint32_t m, uint32_t n,
+                                           uint32_t col0, const float (&x)[32], bool accumulate) {
+#pragma unroll
+  for (uint32_t j = 0; j < 32u; ++j) {
+    const uint32_t col = col0 + j;
+    if (col < n) {
+      T *q = C + base + static_cast<unsigned long long>(col) * m;
+      float v = x[j];
+      if constexpr (sizeof(T) == 2) {
+        if (accumulate) v += __half2float(*q);
+        *q = __float2half_rn(v);
+      } else {
+        if (accumulate) v += *q;
+        *q = v;
+      }
+    }
+  }
+}
+
+template <bool kChunked>
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t tmem_full_bar[2];
+  __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+  __shared__ __align__(8) uint64_t drain_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  volatile int *abort_flag = &s_abort;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (uint32_t s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (uint32_t b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&tmem_full_bar[b]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[b]), kEpilogueWarps);
+    }
+    mbar_init(smem_u32(&drain_bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_slot)),
+                 "r"(p.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  const uint32_t tiles_per_group = p.tiles_m * p.tiles_n;
+  const uint32_t total_tiles = tiles_per_group * p.groups;
+  const uint32_t kb_per_tile = p.red * p.kblocks;  // k-blocks of one tile, over both contraction axes
+  const uint32_t chunks_per_tile = (kb_per_tile + p.chunk_kblocks - 1) / p.chunk_kblocks;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t armed_mask = 0, armed_parity = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const uint32_t g = tile / tiles_per_group;
+        const uint32_t rem = tile - g * tiles_per_group;
+        const int m0 = static_cast<int>((rem % p.tiles_m) * kBM);
+        const int n0 = static_cast<int>((rem / p.tiles_m) * p.bn);
+        for (uint32_t r = 0; ok && r < p.red; ++r) {
+          const int za = static_cast<int>(g * p.a_gmul + r * p.a_rmul);
+          const int zb = static_cast<int>(g * p.b_gmul + r * p.b_rmul);
+          for (uint32_t kb = 0; ok && kb < p.kblocks; ++kb) {
+            const int k0 = static_cast<int>(kb * p.bk);
+            for (uint32_t ps = 0; ps < p.passes; ++ps) {
+              if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
+                ok = false;
+                break;
+              }
+              const uint32_t ia = (p.passes == 3u && ps == 0u) ? 1u : 0u;
+              const uint32_t ib = (p.passes == 3u && ps == 1u) ? 1u : 0u;
+              const uint32_t bar = smem_u32(&full_bar[stage]);
+              const uint32_t sa = smem_base + stage * p.stage_bytes;
+              const uint32_t sb = sa + p.a_stage_bytes;
+              mbar_arrive_expect_tx(bar, p.stage_bytes);
+              armed_mask |= 1u << stage;
+              armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+              if (p.a_mn_major) {
+                for (uint32_t c = 0; c < p.a_chunks; ++c)
+                  tma_load_3d(sa + c * p.a_chunk_bytes, &p.mapA[ia], bar,
+                              m0 + static_cast<int>(c * p.a_chunk_elems), k0, za);
+              } else {
+                tma_load_3d(sa, &p.mapA[ia], bar, k0, m0, za);
+              }
+              if (p.b_mn_major) {
+                for (uint32_t c = 0; c < p.b_chunks; ++c)
+                  tma_load_3d(sb + c * p.b_chunk_bytes, &p.mapB[ib], bar,
+                              n0 + static_cast<int>(c * p.b_chunk_elems), k0, zb);
+              } else {
+                tma_load_3d(sb, &p.mapB[ib], bar, k0, n0, zb);
+              }
+              if (++stage == p.stages) {
+                stage = 0;
+                phase ^= 1u;
+              }
+            }
+          }
+        }
+      }
+      if (*abort_flag) {
+        // let this CTA's own copies land before its shared memory is given up
+        for (uint32_t s = 0; s < p.stages; ++s)
+          if (armed_mask & (1u << s))
+            mbar_wait_quiet(smem_u32(&full_bar[s]), (armed_parity >> s) & 1u);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t chunk_no = 0;  // chunks this CTA has started, over all its tiles
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        uint32_t kb_left = kb_per_tile;
+        for (uint32_t c = 0; ok && c < chunks_per_tile; ++c, ++chunk_no) {
+          const uint32_t buf = chunk_no & 1u;
+          const uint32_t buf_phase = (chunk_no >> 1) & 1u;
+          if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * p.bn;
+          const uint32_t kbs = kb_left < p.chunk_kblocks ? kb_left : p.chunk_kblocks;
+          kb_left -= kbs;
+          const uint32_t iters = kbs * p.passes;
+          for (uint32_t it = 0; it < iters; ++it) {
+            if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t sa = smem_base + stage * p.stage_bytes;
+            const uint32_t sb = sa + p.a_stage_bytes;
+            for (uint32_t ks = 0; ks < p.ksteps; ++ks) {
+              const uint64_t da = make_smem_desc(sa + ks * p.kstep_a_bytes, p.lbo_a, p.sbo_a, p.layout_a);
+              const uint64_t db = make_smem_desc(sb + ks * p.kstep_b_bytes, p.lbo_b, p.sbo_b, p.layout_b);
+              const uint32_t acc = (it | ks) != 0u ? 1u : 0u;
+              if (p.kind_f16)
+                mma_f16(d_tmem, da, db, p.idesc, acc);
+              else
+                mma_tf32(d_tmem, da, db, p.idesc, acc);
+            }
+            mma_commit(smem_u32(&empty_bar[stage]));  // frees the stage when these MMAs retire
+            if (++stage == p.stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          if (ok) mma_commit(smem_u32(&tmem_full_bar[buf]));
+        }
+      }
+      if (*abort_flag) {
+        // retire whatever was issued before TMEM is freed
+        mma_commit(smem_u32(&drain_bar));
+        mbar_wait_quiet(smem_u32(&drain_bar), 0);
+      }
+    }
+    __syncwarp();
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const uint32_t quarter = warp & 3u;         // TMEM lanes this warp may touch
+    const uint32_t half = (warp - 2u) >> 2;     // which half of the tile's columns
+    const uint32_t cols_per = p.bn >> 1;        // 32, 64 or 128 columns per thread
+    const uint32_t col_base = half * cols_per;
+    const uint32_t row_in_tile = quarter * 32u + lane;
+    const uint32_t lane_addr = (quarter * 32u) << 16;
+    uint32_t chunk_no = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const uint32_t g = tile / tiles_per_group;
+      const uint32_t rem = tile - g * tiles_per_group;
+      const uint32_t m0 = (rem % p.tiles_m) * kBM;
+      const uint32_t n0 = (rem / p.tiles_m) * p.bn;
+      const uint32_t row = m0 + row_in_tile;
+      const bool row_ok = row < p.m;
+      const unsigned long long base =
+          static_cast<unsigned long long>(g) * p.c_gs + static_cast<unsigned long long>(row);
+      if constexpr (kChunked) {
+        float acc[4][32];
+        for (uint32_t c = 0; ok && c < chunks_per_tile; ++c, ++chunk_no) {
+          const uint32_t buf = chunk_no & 1u;
+          if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), (chunk_no >> 1) & 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (uint32_t j = 0; j < 4u; ++j) {
+            if (j * 32u < cols_per) {
+              uint32_t v[32];
+              tmem_ld32(tmem_base + lane_addr + buf * p.bn + col_base + j * 32u, v);
+              if (c == 0) {
+#pragma unroll
+                for (uint32_t i = 0; i < 32u; ++i) acc[j][i] = __uint_as_float(v[i]);
+              } else {
+#pragma unroll
+                for (uint32_t i = 0; i < 32u; ++i) acc[j][i] += __uint_as_float(v[i]);
+              }
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+        }
+        if (ok && row_ok) {
+#pragma unroll
+          for (uint32_t j = 0; j < 4u; ++j) {
+            const uint32_t col0 = n0 + col_base + j * 32u;
+            if (j * 32u < cols_per && col0 < p.n) {
+              if (p.out_half)
+                store_cols(static_cast<__half *>(p.C), base, p.m, p.n, col0, acc[j], p.accumulate != 0u);
+              else
+                store_cols(static_cast<float *>(p.C), base, p.m, p.n, col0, acc[j], p.accumulate != 0u);
+            }
+          }
+        }
+      } else {
+        const uint32_t buf = chunk_no & 1u;
+        if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), (chunk_no >> 1) & 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        ++chunk_no;
+        tc_fence_after();
+        for (uint32_t c0 = 0; c0 < cols_per; c0 += 32u) {
+          const uint32_t col0 = n0 + col_base + c0;
+          if (col0 >= p.n) break;  // warp-uniform
+          uint32_t v[32];
+          tmem_ld32(tmem_base + lane_addr + buf * p.bn + col_base + c0, v);
+          if (row_ok) {
+            float x[32];
+#pragma unroll
+            for (uint32_t i = 0; i < 32u; ++i) x[i] = __uint_as_float(v[i]);
+            if (p.out_half)
+              store_cols(static_cast<__half *>(p.C), base, p.m, p.n, col0, x, p.accumulate != 0u);
+            else
+              store_cols(static_cast<float *>(p.C), base, p.m, p.n, col0, x, p.accumulate != 0u);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && s_abort) atomicCAS(p.status, 0, B200_ERR_KERNEL_TIMEOUT);
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(p.tmem_cols)
+                 : "memory");
+  }
+}
+
+// ------------------------------ packing pre-pass ------------------------------
+
+// x rounded to TF32 (10 explicit mantissa bits), nearest with ties away from zero.
+// The result has its 13 low mantissa bits clear, so the tensor core sees it exactly.
+__device__ __forceinline__ float rn_tf32(float x) {
+  uint32_t u = __float_as_uint(x);
+  if ((u & 0x7f800000u) == 0x7f800000u) return x;  // inf / nan pass through
+  u = (u + 0x1000u) & 0xffffe000u;
+  return __uint_as_float(u);
+}
+
+// Packs one fp32 operand into K-major planes: dst[b][i][p], i < mn, p < k, row
+// stride k_pad (a multiple of 4 so TMA strides are 16-byte multiples).
+//   hi = rn_tf32(x), lo = rn_tf32(x - hi) (lo written only when lo != nullptr).
+// Source element (i, p) of matrix b is at src[b*src_bs + i*s_mn + p*s_k]:
+// (s_mn, s_k) = (1, mn) for an MN-major source (the kernel transposes through
+// shared memory), (k, 1) for a K-major source.  One 32x32 tile per CTA iteration,
+// flat 1-D grid so the batch can exceed 65535.
+template <bool kTranspose>
+__global__ void __launch_bounds__(256) pack_tf32_kernel(
+    const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo, uint32_t mn,
+    uint32_t k, uint32_t k_pad, unsigned long long src_bs, uint32_t tiles_mn, uint32_t tiles_k,
+    unsigned long long total_tiles) {
+  __shared__ float tile[32][33];
+  const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;  // 32 x 8
+  for (unsigned long long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    const unsigned long long per_b = static_cast<unsigned long long>(tiles_mn) * tiles_k;
+    const unsigned long long b = t / per_b;
+    const uint32_t rem = static_cast<uint32_t>(t - b * per_b);
+    const uint32_t i0 = (rem % tiles_mn) * 32u, p0 = (rem / tiles_mn) * 32u;
+    const float *s = src + b * src_bs;
+    const unsigned long long dst_b = b * static_cast<unsigned long long>(mn) * k_pad;
+    if (kTranspose) {
+      // read coalesced along mn, write coalesced along k
+#pragma unroll
+      for (uint32_t j = 0; j < 32u; j += 8u) {
+        const uint32_t i = i0 + tx, pp = p0 + ty + j;
+        tile[ty + j][tx] = (i < mn && pp < k) ? s[static_cast<unsigned long long>(pp) * mn + i] : 0.f;
+      }
+      __syncthreads();
+#pragma unroll
+      for (uint32_t j = 0; j < 32u; j += 8u) {
+        const uint32_t i = i0 + ty + j, pp = p0 + tx;
+        if (i < mn && pp < k) {
+          const float x = tile[tx][ty + j];
+          const float h = rn_tf32(x);
+          const unsigned long long o = dst_b + static_cast<unsigned long long>(i) * k_pad + pp;
+          hi[o] = h;
+          if (lo) lo[o] = rn_tf32(x - h);
+        }
+      }
+      __syncthreads();
+    } else {
+#pragma unroll
+      for (uint32_t j = 0; j < 32u; j += 8u) {
+        const uint32_t i = i0 + ty + j, pp = p0 + tx;
+        if (i < mn && pp < k) {
+          const float x = s[static_cast<unsigned long long>(i) * k + pp];
+          const float h = rn_tf32(x);
+          const unsigned long long o = dst_b + static_cast<unsigned long long>(i) * k_pad + pp;
+          hi[o] = h;
+          if (lo) lo[o] = rn_tf32(x - h);
+        }
+      }
+    }
+  }
+}
+
+struct OperandView {
+  const void *ptr;
+  uint32_t mn, k;         // extents
+  bool mn_major;          // true: mn contiguous; false: k contiguous
+  uint64_t ld;            // elements between consecutive lines of the slow axis
+  uint64_t batch_stride;  // elements between consecutive matrices
+  uint32_t nbatch;
+};
+
+int encode_map(const b200_ctx *ctx, CUtensorMap *map, const void *ptr, const OperandView &v,
+               int ebytes, uint32_t box_mn, uint32_t box_k, CUtensorMapSwizzle swz) {
+  const uint64_t d0 = v.mn_major ? v.mn : v.k;
+  const uint64_t d1 = v.mn_major ? v.k : v.mn;
+  const uint32_t nb = v.nbatch > 0 ? v.nbatch : 1;
+  cuuint64_t dims[3] = {d0, d1, nb};
+  cuuint64_t strides[2] = {v.ld * ebytes, (nb > 1 ? v.batch_stride : v.ld * d1) * ebytes};
+  cuuint32_t box[3] = {v.mn_major ? box_mn : box_k, v.mn_major ? box_k : box_mn, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt =
+      ebytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const CUresult r = ctx->encode_tiled(map, dt, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+                                       CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200_OK : B200_ERR_DRIVER;
+}
+
+// Batch-stride pattern of one operand: (g, r) -> matrix index g*gmul + r*rmul.
+bool stride_pattern(uint64_t gs, uint64_t rs, uint32_t groups, uint32_t red, uint64_t *stride,
+                    uint32_t *nbatch, uint32_t *gmul, uint32_t *rmul) {
+  const bool g_on = groups > 1 && gs != 0, r_on = red > 1 && rs != 0;
+  *gmul = g_on ? 1u : 0u;
+  *rmul = r_on ? 1u : 0u;
+  if (g_on && r_on) return false;  // two independent batch axes: not needed by primitiv's matmul
+  *stride = g_on ? gs : (r_on ? rs : 0);
+  *nbatch = g_on ? groups : (r_on ? red : 1u);
+  return true;
+}
+
+// Can this operand be handed to TMA as it lies in the caller's memory?
+bool direct_ok(const void *ptr, uint64_t ld, uint64_t bstride, uint32_t nbatch, int eb) {
+  const uint64_t al = 16 / eb;
+  if (reinterpret_cast<uintptr_t>(ptr) % 16) return false;
+  if (ld % al) return false;
+  if (nbatch > 1 && bstride % al) return false;
+  return true;
+}
+
+}  // namespace
+
+bool gemm_tc_eligible(const b200_ctx *ctx, const GemmArgs &g) {
+  if (!ctx->encode_tiled) return false;
+  if (g.m == 0 || g.n == 0 || g.k == 0 || g.groups == 0 || g.red == 0) return false;
+  uint64_t sta, stb;
+  uint32_t nba, nbb, gm, rm;
+  if (!stride_pattern(g.a_gs, g.a_rs, g.groups, g.red, &sta, &nba, &gm, &rm)) return false;
+  if (!stride_pattern(g.b_gs, g.b_rs, g.groups, g.red, &stb, &nbb, &gm, &rm)) return false;
+  if (g.mode == B200_MODE_FP16) {
+    // half operands are never repacked: they must satisfy TMA's alignment rules as they lie
+    const uint64_t lda = g.trans_a ? g.k : g.m, ldb = g.trans_b ? g.n : g.k;
+    return direct_ok(g.A, lda, sta, nba, 2) && direct_ok(g.B, ldb, stb, nbb, 2);
+  }
+  return true;  // fp32: whatever is not directly loadable goes through the packing pre-pass
+}
+
+int gemm_tc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream) {
+  if (!gemm_tc_eligible(ctx, g)) return B200_ERR_INVALID_ARG;
+  const int eb = elem_bytes(g.mode);
+  const bool f16 = g.mode == B200_MODE_FP16;
+  const uint32_t passes = g.mode == B200_MODE_FP32_3XTF32 ? 3u : 1u;
+
+  TcParams p;
+  memset(&p, 0, sizeof(p));
+  p.bk = 128u / eb;                       // 128 bytes of k per stage
+  const uint32_t umma_k = 32u / eb;       // 8 (tf32) or 16 (fp16)
+  const uint32_t chunk = 128u / eb;       // mn elements per 128-byte swizzle row
+  p.bn = g.n > 128 ? 256u : (g.n > 64 ? 128u : 64u);
+  p.m = g.m;
+  p.n = g.n;
+  p.kblocks = (g.k + p.bk - 1) / p.bk;
+  p.red = g.red;
+  p.groups = g.groups;
+  p.tiles_m = (g.m + kBM - 1) / kBM;
+  p.tiles_n = (g.n + p.bn - 1) / p.bn;
+  const uint64_t total_tiles = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * g.groups;
+  if (total_tiles > 0x7fffffffull) return B200_ERR_TOO_LARGE;
+
+  // ---- operand views, packing where needed ----
+  OperandView va, vb;
+  va.ptr = g.A; va.mn = g.m; va.k = g.k; va.mn_major = !g.trans_a; va.ld = g.trans_a ? g.k : g.m;
+  stride_pattern(g.a_gs, g.a_rs, g.groups, g.red, &va.batch_stride, &va.nbatch, &p.a_gmul, &p.a_rmul);
+  vb.ptr = g.B; vb.mn = g.n; vb.k = g.k; vb.mn_major = g.trans_b != 0; vb.ld = g.trans_b ? g.n : g.k;
+  stride_pattern(g.b_gs, g.b_rs, g.groups, g.red, &vb.batch_stride, &vb.nbatch, &p.b_gmul, &p.b_rmul);
+
+  const void *a_src[2] = {g.A, nullptr}, *b_src[2] = {g.B, nullptr};
+  void *scratch = nullptr;
+  if (!f16) {
+    OperandView *views[2] = {&va, &vb};
+    const void **srcs[2] = {a_src, b_src};
+    bool pack[2];
+    uint64_t plane_elems[2] = {0, 0};
+    uint32_t kpad[2] = {0, 0};
+    for (int o = 0; o < 2; ++o) {
+      const OperandView &v = *views[o];
+      const bool direct = direct_ok(v.ptr, v.ld, v.batch_stride, v.nbatch, 4);
+      pack[o] = passes == 3 || !direct;
+      if (pack[o]) {
+        kpad[o] = (v.k + 3u) & ~3u;
+        plane_elems[o] = (static_cast<uint64_t>(v.nbatch) * v.mn * kpad[o] + 63ull) & ~63ull;
+      }
+    }
+    const uint64_t planes = passes == 3 ? 2 : 1;
+    const uint64_t total = planes * (plane_elems[0] + plane_elems[1]);
+    if (total) {
+      int rc = ctx->pool.alloc(total * sizeof(float), &scratch, nullptr);
+      if (rc != B200_OK) return rc;
+    }
+    float *cursor = static_cast<float *>(scratch);
+    for (int o = 0; o < 2; ++o) {
+      if (!pack[o]) continue;
+      OperandView &v = *views[o];
+      float *hi = cursor;
+      float *lo = passes == 3 ? cursor + plane_elems[o] : nullptr;
+      cursor += planes * plane_elems[o];
+      const uint32_t tiles_mn = (v.mn + 31u) / 32u, tiles_k = (v.k + 31u) / 32u;
+      const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
+      const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
+      const unsigned blocks = static_cast<unsigned>(tt < cap ? tt : cap);
+      ProfScope prof(ctx, kProfPack, stream);
+      if (v.mn_major)
+        pack_tf32_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const float *>(v.ptr), hi, lo, v.mn, v.k,
+                                                          kpad[o], v.batch_stride, tiles_mn, tiles_k, tt);
+      else
+        pack_tf32_kernel<false><<<blocks, 256, 0, stream>>>(static_cast<const float *>(v.ptr), hi, lo, v.mn, v.k,
+                                                           kpad[o], v.batch_stride, tiles_mn, tiles_k, tt);
+      ++ctx->launches;
+      srcs[o][0] = hi;
+      srcs[o][1] = lo;
+      v.ptr = hi;
+      v.mn_major = false;
+      v.ld = kpad[o];
+      v.batch_stride = static_cast<uint64_t>(v.mn) * kpad[o];
+    }
+  }
+
+  p.a_mn_major = va.mn_major ? 1u : 0u;
+  p.b_mn_major = vb.mn_major ? 1u : 0u;
+  p.ksteps = p.bk / umma_k;
+  p.a_stage_bytes = kBM * 128u;
+  p.stage_bytes = (kBM + p.bn) * 128u;
+  p.layout_a = p.layout_b = 2u;  // 128-byte swizzle
+  CUtensorMapSwizzle swz_a = CU_TENSOR_MAP_SWIZZLE_128B, swz_b = CU_TENSOR_MAP_SWIZZLE_128B;
+  if (p.a_mn_major) {
+    p.a_chunks = kBM / chunk;
+    p.a_chunk_elems = chunk;
+    p.a_chunk_bytes = p.bk * 128u;
+    p.lbo_a = p.a_chunk_bytes;
+    p.sbo_a = 1024u;
+    p.kstep_a_bytes = (umma_k / 8u) * 1024u;
+    if (!f16) {  // 32-bit MN-major: 32-byte swizzle atoms, k-groups of 4 rows
+      swz_a = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+      p.layout_a = 1u;
+      p.sbo_a = 512u;
+    }
+  } else {
+    p.a_chunks = 1;
+    p.lbo_a = 0;
+    p.sbo_a = 1024u;
+    p.kstep_a_bytes = umma_k * eb;
+  }
+  if (p.b_mn_major) {
+    p.b_chunks = p.bn / chunk;
+    p.b_chunk_elems = chunk;
+    p.b_chunk_bytes = p.bk * 128u;
+    p.lbo_b = p.b_chunk_bytes;
+    p.sbo_b = 1024u;
+    p.kstep_b_bytes = (umma_k / 8u) * 1024u;
+    if (!f16) {
+      swz_b = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+      p.layout_b = 1u;
+      p.sbo_b = 512u;
+    }
+  } else {
+    p.b_chunks = 1;
+    p.lbo_b = 0;
+    p.sbo_b = 1024u;
+    p.kstep_b_bytes = umma_k * eb;
+  }
+  const uint32_t fmt = f16 ? 0u : 2u;  // F16 = 0 (kind::f16), TF32 = 2 (kind::tf32)
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (p.a_mn_major << 15) | (p.b_mn_major << 16) |
+            ((p.bn >> 3) << 17) | ((kBM >> 4) << 24);
+  p.passes = passes;
+  const bool chunked = passes == 3 && static_cast<uint64_t>(g.red) * p.kblocks > kChunkKBlocks;
+  p.chunk_kblocks = chunked ? kChunkKBlocks : g.red * p.kblocks;
+  p.accumulate = g.accumulate ? 1u : 0u;
+  p.out_half = f16 ? 1u : 0u;
+  p.kind_f16 = f16 ? 1u : 0u;
+  p.C = g.C;
+  p.c_gs = g.c_gs;
+  p.status = ctx->d_status;
+  p.tmem_cols = p.bn * 2u;  // 128, 256 or 512: powers of two
+
+  const size_t budget = ctx->smem_optin > 8192 ? ctx->smem_optin - 4096 : 0;
+  uint32_t stages = budget > 1024 ? static_cast<uint32_t>((budget - 1024) / p.stage_bytes) : 0;
+  if (stages > kMaxStages) stages = kMaxStages;
+  int rc = stages >= 2 ? B200_OK : B200_ERR_INVALID_ARG;
+  p.stages = stages;
+  const size_t smem_bytes = static_cast<size_t>(stages) * p.stage_bytes + 1024;
+
+  for (int i = 0; i < (passes == 3 ? 2 : 1) && rc == B200_OK; ++i) {
+    rc = encode_map(ctx, &p.mapA[i], a_src[i], va, eb, p.a_mn_major ? chunk : kBM, p.bk, swz_a);
+    if (rc == B200_OK)
+      rc = encode_map(ctx, &p.mapB[i], b_src[i], vb, eb, p.b_mn_major ? chunk : p.bn, p.bk, swz_b);
+  }
+  if (rc == B200_OK && !ctx->tc_smem_configured) {
+    const int max_dyn = static_cast<int>(ctx->smem_optin - 2048);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
+    if (e != cudaSuccess) rc = static_cast<int>(e);
+    ctx->tc_smem_configured = (e == cudaSuccess);
+  }
+  if (rc == B200_OK) {
+    const unsigned grid =
+        static_cast<unsigned>(total_tiles < (uint64_t)ctx->sm_count ? total_tiles : ctx->sm_count);
+    ProfScope prof(ctx, kProfGemmTc, stream);
+    if (chunked)
+      gemm_tc_kernel<true><<<grid, kThreads, smem_bytes, stream>>>(p);
+    else
+      gemm_tc_kernel<false><<<grid, kThreads, smem_bytes, stream>>>(p);
+    ++ctx->launches;
+    rc = static_cast<int>(cudaGetLastError());
+  }
+  if (scratch) ctx->pool.free(scratch);  // stream-ordered reuse: later work queues behind this GEMM
+  return rc;
+}
+
+}  // namespace b200

@@ -1,0 +1,193 @@
+"""GPU parity tests of the hot path, through the C ABI, against the CPU oracle.
+
+Tolerances: fp32 3xTF32 mode <= 1e-5 normwise relative error against the fp64
+oracle; TF32 and fp16 modes <= 2e-3.  The reference's own known-answer vectors
+are held to the reference's ULP bounds (4 ULP fp32; the CUDA16 bounds for fp16)."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle_lib as ol
+import primitiv_b200 as pb
+from gpu_util import MODES, TOL, matmul_bw, matmul_fw
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+with open(os.path.join(GOLDEN, "matmul_known_answers.json")) as _f:
+    KNOWN = json.load(_f)["cases"]
+
+
+def _dims(case):
+    di, dj = case["a_shape"]
+    return di, dj, case["b_shape"][1], case["a_batch"], case["b_batch"]
+
+
+@pytest.mark.parametrize("policy", [0, 2], ids=["auto", "tensorcore"])
+@pytest.mark.parametrize("mode", list(MODES))
+@pytest.mark.parametrize("case", KNOWN, ids=lambda c: c["name"])
+def test_reference_known_answers(ctx, case, mode, policy):
+    """test/tensor_forward_test.cc:1798-1905, test/tensor_backward_test.cc:1599-1668,
+    test/operator_impl_test.cc:1132-1144 of the reference, on this backend."""
+    m = MODES[mode]
+    di, dj, dk, ba, bb = _dims(case)
+    ulps = case["ulps_fp16"] if mode == "fp16" else case["ulps"]
+    a, b = np.array(case["a"], np.float32), np.array(case["b"], np.float32)
+    ctx.set_path_policy(policy)
+    try:
+        if case["kind"] == "fw":
+            y = matmul_fw(ctx, m, a, b, di, dj, dk, ba, bb)
+            assert ol.ulp_diff(y, np.array(case["y"], np.float32)).max() <= ulps
+        else:
+            gy = np.array(case["gy"], np.float32)
+            ga0 = np.full(di * dj * ba, case["prefill"], np.float32)
+            gb0 = np.full(dj * dk * bb, case["prefill"], np.float32)
+            ga, gb = matmul_bw(ctx, m, a, b, gy, ga0, gb0, di, dj, dk, ba, bb)
+            assert ol.ulp_diff(ga, np.array(case["ga"], np.float32)).max() <= ulps
+            assert ol.ulp_diff(gb, np.array(case["gb"], np.float32)).max() <= ulps
+    finally:
+        ctx.set_path_policy(0)
+
+
+def _check_all(ctx, mode, a, b, gy, di, dj, dk, ba, bb, prefill=0.5):
+    m = MODES[mode]
+    if mode == "fp16":  # the oracle sees the values the device stores
+        a, b, gy = ol.round_to_half(a), ol.round_to_half(b), ol.round_to_half(gy)
+    ga0 = np.full(di * dj * ba, prefill, np.float32)
+    gb0 = np.full(dj * dk * bb, prefill, np.float32)
+    y = matmul_fw(ctx, m, a, b, di, dj, dk, ba, bb)
+    ga, gb = matmul_bw(ctx, m, a, b, gy, ga0, gb0, di, dj, dk, ba, bb)
+    y64 = ol.fw_f64(a, b, di, dj, dk, ba, bb)
+    ga64, gb64 = ol.bw_f64(a, b, gy, ga0, gb0, di, dj, dk, ba, bb)
+    errs = (ol.rel_err(y, y64), ol.rel_err(ga, ga64), ol.rel_err(gb, gb64))
+    assert max(errs) <= TOL[mode], errs
+    return y, ga, gb
+
+
+_REF = np.load(os.path.join(GOLDEN, "matmul_ref_naive_cases.npz"))
+
+
+@pytest.mark.parametrize("policy", [0, 2], ids=["auto", "tensorcore"])
+@pytest.mark.parametrize("mode", list(MODES))
+@pytest.mark.parametrize("idx", range(len(_REF["cases"])))
+def test_against_reference_naive_fixtures(ctx, idx, mode, policy):
+    di, dj, dk, ba, bb = [int(v) for v in _REF["cases"][idx]]
+    a, b, gy = _REF["a_%d" % idx], _REF["b_%d" % idx], _REF["gy_%d" % idx]
+    ctx.set_path_policy(policy)
+    try:
+        y, ga, gb = _check_all(ctx, mode, a, b, gy, di, dj, dk, ba, bb)
+    finally:
+        ctx.set_path_policy(0)
+    if mode == "3xtf32":  # directly against what the reference's Naive device produced
+        for got, key in ((y, "y"), (ga, "ga"), (gb, "gb")):
+            want = _REF["%s_%d" % (key, idx)]
+            assert np.linalg.norm(got - want) <= 1e-5 * np.linalg.norm(want)
+
+
+# (di, dj, dk, ba, bb): every broadcast combination, tile-edge and ragged extents, a long
+# contraction, a batch-summed gradient with many batches.  Sized for the CPU oracle.
+SHAPES = [
+    (512, 384, 256, 1, 4), (384, 512, 320, 4, 4), (256, 768, 128, 3, 1), (1024, 1024, 1024, 1, 1),
+    (260, 132, 72, 2, 2), (128, 128, 128, 1, 1), (129, 257, 65, 1, 3), (130, 36, 520, 5, 1),
+    (64, 4096, 64, 1, 2), (256, 256, 64, 1, 16), (4096, 512, 64, 1, 1), (96, 200, 40, 7, 1),
+    (100, 1000, 8, 1, 64),
+]
+
+
+@pytest.mark.parametrize("mode", list(MODES))
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_random_shapes_against_fp64_oracle(ctx, shape, mode):
+    di, dj, dk, ba, bb = shape
+    rng = np.random.default_rng(hash(shape) % (2 ** 32))
+    a = rng.uniform(-1, 1, di * dj * ba).astype(np.float32)
+    b = rng.uniform(-1, 1, dj * dk * bb).astype(np.float32)
+    gy = rng.standard_normal(di * dk * max(ba, bb)).astype(np.float32)
+    _check_all(ctx, mode, a, b, gy, di, dj, dk, ba, bb)
+
+
+@pytest.mark.parametrize("mode", list(MODES))
+def test_plumbing_workload(ctx, mode):
+    """W {256,256} broadcast, X {256,64}x16, gy N(0,1), all from one mt19937(0); gradients pre-filled 0.5."""
+    c = ol.config1_inputs()
+    args = (c["di"], c["dj"], c["dk"], c["ba"], c["bb"])
+    y, ga, gb = _check_all(ctx, mode, c["a"], c["b"], c["gy"], *args, prefill=0.5)
+    if mode == "3xtf32" and ol.have_ref():
+        y_ref, _ = ol.ref_fw(c["a"], c["b"], *args)
+        ga_ref, gb_ref, _ = ol.ref_bw(c["a"], c["b"], c["gy"], c["ga0"], c["gb0"], *args)
+        for got, want in ((y, y_ref), (ga, ga_ref), (gb, gb_ref)):
+            assert np.linalg.norm(got - want) <= 1e-5 * np.linalg.norm(want)
+
+
+def test_accumulation_really_accumulates(ctx):
+    """Two backward calls into the same gradient add twice (beta = 1), and the forward overwrites."""
+    di, dj, dk, ba, bb = 192, 160, 96, 1, 3
+    rng = np.random.default_rng(5)
+    a = rng.uniform(-1, 1, di * dj).astype(np.float32)
+    b = rng.uniform(-1, 1, dj * dk * bb).astype(np.float32)
+    gy = rng.standard_normal(di * dk * bb).astype(np.float32)
+    m = pb.MODE_FP32_3XTF32
+    da, db, dgy = [torch.from_numpy(x).cuda() for x in (a, b, gy)]
+    ga = torch.full((di * dj,), 0.25, device="cuda")
+    gb = torch.full((dj * dk * bb,), -1.0, device="cuda")
+    for _ in range(2):
+        ctx.matmul_bw(m, da.data_ptr(), db.data_ptr(), dgy.data_ptr(), ga.data_ptr(), gb.data_ptr(),
+                      di, dj, dk, ba, bb)
+    z = np.zeros
+    ga64, gb64 = ol.bw_f64(a, b, gy, z(di * dj, np.float32), z(dj * dk * bb, np.float32), di, dj, dk, ba, bb)
+    assert ol.rel_err(ga.cpu().numpy(), 0.25 + 2 * ga64) < 1e-5
+    assert ol.rel_err(gb.cpu().numpy(), -1.0 + 2 * gb64) < 1e-5
+    y = torch.full((di * dk * bb,), 1e30, device="cuda")  # must be overwritten, not added to
+    ctx.matmul_fw(m, da.data_ptr(), db.data_ptr(), y.data_ptr(), di, dj, dk, ba, bb)
+    assert ol.rel_err(y.cpu().numpy(), ol.fw_f64(a, b, di, dj, dk, ba, bb)) < 1e-5
+
+
+def test_null_gradient_skips_that_product(ctx):
+    di, dj, dk = 64, 64, 64
+    rng = np.random.default_rng(6)
+    a, b, gy = [torch.from_numpy(rng.standard_normal(di * dj).astype(np.float32)).cuda() for _ in range(3)]
+    ga = torch.zeros(di * dj, device="cuda")
+    ctx.matmul_bw(pb.MODE_TF32, a.data_ptr(), b.data_ptr(), gy.data_ptr(), ga.data_ptr(), None, di, dj, dk, 1, 1)
+    torch.cuda.synchronize()
+    assert float(ga.abs().sum()) > 0
+
+
+@pytest.mark.parametrize("mode", list(MODES))
+def test_bitwise_deterministic(ctx, mode):
+    """No atomics anywhere on the path: the batch-summed gradient is the same bits every run."""
+    di, dj, dk, ba, bb = 256, 192, 128, 6, 1
+    rng = np.random.default_rng(7)
+    a = rng.uniform(-1, 1, di * dj * ba).astype(np.float32)
+    b = rng.uniform(-1, 1, dj * dk * bb).astype(np.float32)
+    gy = rng.standard_normal(di * dk * ba).astype(np.float32)
+    z = np.zeros
+    runs = [matmul_bw(ctx, MODES[mode], a, b, gy, z(di * dj * ba, np.float32), z(dj * dk, np.float32),
+                      di, dj, dk, ba, bb) for _ in range(3)]
+    for ga, gb in runs[1:]:
+        assert np.array_equal(ga, runs[0][0]) and np.array_equal(gb, runs[0][1])
+
+
+def test_invalid_arguments_are_rejected(ctx):
+    x = torch.zeros(64, device="cuda")
+    p = x.data_ptr()
+    with pytest.raises(pb.B200Error):  # incompatible batches (Shape::has_compatible_batch)
+        ctx.matmul_fw(pb.MODE_TF32, p, p, p, 2, 2, 2, 2, 3)
+    with pytest.raises(pb.B200Error):
+        ctx.matmul_fw(7, p, p, p, 2, 2, 2, 1, 1)
+    with pytest.raises(pb.B200Error):
+        ctx.matmul_fw(pb.MODE_TF32, None, p, p, 2, 2, 2, 1, 1)
+
+
+def test_host_buffer_entry_points(ctx):
+    c = ol.config1_inputs()
+    args = (c["di"], c["dj"], c["dk"], c["ba"], c["bb"])
+    y = np.empty(c["di"] * c["dk"] * c["bb"], np.float32)
+    ctx.matmul_fw_host(pb.MODE_FP32_3XTF32, c["a"].ctypes.data, c["b"].ctypes.data, y.ctypes.data, *args)
+    assert ol.rel_err(y, ol.fw_f64(c["a"], c["b"], *args)) < 1e-5
+    ga, gb = c["ga0"].copy(), c["gb0"].copy()
+    ctx.matmul_bw_host(pb.MODE_FP32_3XTF32, c["a"].ctypes.data, c["b"].ctypes.data, c["gy"].ctypes.data,
+                       ga.ctypes.data, gb.ctypes.data, *args)
+    ga64, gb64 = ol.bw_f64(c["a"], c["b"], c["gy"], c["ga0"], c["gb0"], *args)
+    assert ol.rel_err(ga, ga64) < 1e-5 and ol.rel_err(gb, gb64) < 1e-5
