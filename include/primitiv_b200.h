@@ -145,6 +145,33 @@ B200_API int b200_gemm(b200_ctx *ctx, int mode, int trans_a, int trans_b,
                        uint64_t a_gs, uint64_t a_rs, uint64_t b_gs, uint64_t b_rs, uint64_t c_gs,
                        int accumulate, int force_path, void *stream);
 
+/* ---- one product without any allocation (no counterpart in the reference) -----------------
+ * Some hosts of this library may not allocate device memory on the path that calls it: an
+ * application that handed the whole GPU to its own allocator at start-up, or a serving loop
+ * that forbids cudaMalloc / cudaFree between requests because both synchronise the device.
+ * For them this entry point computes one fp32 product in 3xTF32 mode,
+ *     C = (accumulate ? C : 0) + opA(A) . opB(B)        (same operand conventions as b200_gemm,
+ *                                                        groups = red = 1, tensor-core kernel)
+ * with the hi/lo packing planes, which b200_gemm takes from the pool, placed in a fixed
+ * 32 MiB array inside the library's device image (B200_NOALLOC_SCRATCH_BYTES; every GPU that
+ * loads the library holds it until the process exits).  It calls no cudaMalloc, cudaFree,
+ * pool routine or event creation, and gives bit-identical results to b200_gemm.
+ *
+ * Limit: 2 planes x (m + n) x round_up(k, 4) floats, each plane rounded up to 64 floats, must
+ * fit the array, i.e. roughly (m + n) * k <= 4 Mi elements (1024 x 1024 x 2048, 2048 x 2048 x
+ * 1024, ...).  Larger products return B200_ERR_TOO_LARGE and launch nothing.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress);
+ * make that first call outside any stream capture.  All calls share the one array: it keeps
+ * whatever the previous call packed, nothing in it needs clearing because the packing pass
+ * rewrites every element the product reads, and two calls whose kernels can overlap on the
+ * GPU (different streams, or different contexts on the same device) race on it. */
+#define B200_NOALLOC_SCRATCH_BYTES (32u << 20)
+B200_API int b200_gemm_3xtf32_noalloc(b200_ctx *ctx, int trans_a, int trans_b,
+                                      const void *A, const void *B, void *C,
+                                      uint32_t m, uint32_t n, uint32_t k,
+                                      int accumulate, void *stream);
+
 /* Kernel choice for b200_matmul_* and for b200_gemm calls with force_path == 0:
  * 0 = per problem (default), 1 = always the CUDA-core kernel, 2 = the tensor-core
  * kernel whenever the operands are eligible, however small the problem. */

@@ -38,6 +38,7 @@ SIGNATURES = {
     "b200_matmul_bw_host": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32]),
     "b200_gemm": (_int, [_vp, _int, _int, _int, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32,
                          _u64, _u64, _u64, _u64, _u64, _int, _int, _vp]),
+    "b200_gemm_3xtf32_noalloc": (_int, [_vp, _int, _int, _vp, _vp, _vp, _u32, _u32, _u32, _int, _vp]),
     "b200_set_path_policy": (_int, [_vp, _int]),
     "b200_profile_enable": (_int, [_vp, _int]),
     "b200_profile_read": (_int, [_vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_u64)]),
@@ -108,6 +109,11 @@ class Context:
         c = _int()
         _check(lib().b200_status_poll(self._h, stream, ctypes.byref(c)))
         return c.value
+
+    def gemm_3xtf32_noalloc(self, trans_a, trans_b, A, B, C, m, n, k, accumulate=False, stream=None):
+        """One 3xTF32 product whose scratch is a fixed array inside the library: allocates nothing."""
+        _check(lib().b200_gemm_3xtf32_noalloc(self._h, int(trans_a), int(trans_b), A, B, C, m, n, k,
+                                              int(accumulate), stream), "gemm_3xtf32_noalloc")
 
     def set_path_policy(self, policy):
         _check(lib().b200_set_path_policy(self._h, policy), "set_path_policy")

@@ -186,6 +186,17 @@ int b200_gemm(b200_ctx *ctx, int mode, int trans_a, int trans_b, const void *A, 
   return b200::gemm_simt(ctx, g, s);
 }
 
+int b200_gemm_3xtf32_noalloc(b200_ctx *ctx, int trans_a, int trans_b, const void *A, const void *B,
+                             void *C, uint32_t m, uint32_t n, uint32_t k, int accumulate,
+                             void *stream) {
+  if (!ctx || !A || !B || !C) return B200_ERR_INVALID_ARG;
+  if (m == 0 || n == 0 || k == 0) return B200_ERR_INVALID_ARG;
+  DeviceGuard guard(ctx->device);
+  GemmArgs g{B200_MODE_FP32_3XTF32, trans_a ? 1 : 0, trans_b ? 1 : 0, A, B, C, m, n, k, 1, 1,
+             0, 0, 0, 0, 0, accumulate ? 1 : 0};
+  return b200::gemm_3xtf32_noalloc(ctx, g, static_cast<cudaStream_t>(stream));
+}
+
 static int check_matmul(const b200_ctx *ctx, int mode, uint32_t ba, uint32_t bb) {
   if (!ctx) return B200_ERR_INVALID_ARG;
   if (mode < B200_MODE_FP32_3XTF32 || mode > B200_MODE_FP16) return B200_ERR_INVALID_ARG;

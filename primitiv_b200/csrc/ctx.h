@@ -117,6 +117,8 @@ int gemm_simt(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
 // tcgen05 path.  tc_eligible() says whether the operands meet TMA's alignment rules.
 bool gemm_tc_eligible(const b200_ctx *ctx, const GemmArgs &g);
 int gemm_tc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
+// 3xTF32 product whose packing planes live in a fixed device array: allocates nothing.
+int gemm_3xtf32_noalloc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
 
 inline int elem_bytes(int mode) { return mode == B200_MODE_FP16 ? 2 : 4; }
 

@@ -635,7 +635,14 @@ bool gemm_tc_eligible(const b200_ctx *ctx, const GemmArgs &g) {
   return true;  // fp32: whatever is not directly loadable goes through the packing pre-pass
 }
 
-int gemm_tc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream) {
+namespace {
+
+// Shared body of gemm_tc and of the allocation-free entry point.  With
+// fixed_scratch == nullptr the packing planes come from the context's pool; otherwise
+// they are laid out in the caller-supplied device buffer of fixed_elems floats and
+// nothing is allocated.
+int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fixed_scratch,
+                uint64_t fixed_elems) {
   if (!gemm_tc_eligible(ctx, g)) return B200_ERR_INVALID_ARG;
   const int eb = elem_bytes(g.mode);
   const bool f16 = g.mode == B200_MODE_FP16;
@@ -683,11 +690,15 @@ int gemm_tc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream) {
     }
     const uint64_t planes = passes == 3 ? 2 : 1;
     const uint64_t total = planes * (plane_elems[0] + plane_elems[1]);
-    if (total) {
+    float *cursor = nullptr;
+    if (total && fixed_scratch) {
+      if (total > fixed_elems) return B200_ERR_TOO_LARGE;
+      cursor = fixed_scratch;
+    } else if (total) {
       int rc = ctx->pool.alloc(total * sizeof(float), &scratch, nullptr);
       if (rc != B200_OK) return rc;
+      cursor = static_cast<float *>(scratch);
     }
-    float *cursor = static_cast<float *>(scratch);
     for (int o = 0; o < 2; ++o) {
       if (!pack[o]) continue;
       OperandView &v = *views[o];
@@ -804,6 +815,45 @@ int gemm_tc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream) {
     rc = static_cast<int>(cudaGetLastError());
   }
   if (scratch) ctx->pool.free(scratch);  // stream-ordered reuse: later work queues behind this GEMM
+  return rc;
+}
+
+}  // namespace
+
+int gemm_tc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream) {
+  return gemm_tc_run(ctx, g, stream, nullptr, 0);
+}
+
+// ---------------- allocation-free 3xTF32 product (b200_gemm_3xtf32_noalloc) ----------------
+//
+// The packing planes of this variant live in a file-scope device array instead of
+// pool memory.  Every GPU that loads the library carries the array until the process
+// exits, so it is kept modest: 8 Mi floats = 32 MiB, which holds the hi and lo planes
+// of both operands as long as  2 * (m + n) * round_up(k, 4) <= 8 Mi  (with 64-float
+// rounding per plane), e.g. 1024 x 1024 x 2048 or 2048 x 2048 x 1024.
+constexpr uint64_t kStaticScratchFloats = 8ull << 20;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not an address a
+// kernel can use; the device address is looked up once per device, with that device
+// current, and cached here.
+constexpr int kMaxDevices = 64;
+static float *g_static_scratch_addr[kMaxDevices] = {};
+
+int gemm_3xtf32_noalloc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream) {
+  if (ctx->device < 0 || ctx->device >= kMaxDevices) return B200_ERR_INVALID_ARG;
+  float *&addr = g_static_scratch_addr[ctx->device];
+  if (!addr) {
+    void *sym = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&sym, g_static_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    addr = static_cast<float *>(sym);
+  }
+  // Per-launch timing creates events, which is an allocation of sorts: keep it off here.
+  const bool was_profiling = ctx->profiling;
+  ctx->profiling = false;
+  const int rc = gemm_tc_run(ctx, g, stream, addr, kStaticScratchFloats);
+  ctx->profiling = was_profiling;
   return rc;
 }
 
