@@ -41,6 +41,12 @@ SAMPLE_DK = 64
 SAMPLE_FLOPS = 3 * 2 * N_DIM * N_DIM * SAMPLE_DK
 
 
+def set_batch(batch):
+    global BATCH, FLOPS_PER_STEP
+    BATCH = batch
+    FLOPS_PER_STEP = 3 * 2 * N_DIM ** 3 * BATCH
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -139,7 +145,7 @@ def run_reference(args, rank):
 
 
 def workload_config(n_gpus):
-    return {"workload": "batched_square_gemm_4096x4096x4096_batch8_fp32_3xtf32_fw_bw",
+    return {"workload": "batched_square_gemm_4096x4096x4096_batch%d_fp32_3xtf32_fw_bw" % BATCH,
             "shape": [N_DIM, N_DIM, N_DIM], "batch_per_gpu": BATCH, "global_batch": BATCH * n_gpus,
             "mode": "3xTF32", "flops_per_step_per_gpu": FLOPS_PER_STEP,
             "l2": "every operand (512 MiB) is larger than L2 (126 MB); no flush needed",
@@ -201,14 +207,33 @@ def run_ours(args, rank, local_rank, world):
     assert ctx.status_poll() == 0, "a kernel reported a bounded-wait timeout"
 
     # ---- end to end through the host-buffer entry points (pinned host memory) ----
+    e2e = None
+    if not args.skip_e2e:
+        e2e = run_e2e(args, ctx, mode, a, b, gy, barrier, dist, torch)
+    if dist is not None:
+        t = torch.tensor([ms, e2e["ms"] if e2e else 0.0], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        if e2e:
+            e2e["ms"] = float(t[1])
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+    emit(args, world, ms, prof, launches, sampler, e2e)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_e2e(args, ctx, mode, a, b, gy, barrier, dist, torch):
+    n, bs = N_DIM, BATCH
+    P = lambda t: t.data_ptr()
     e2e_steps = max(1, min(args.steps, 3))
     hb = lambda src: src.cpu().pin_memory()
     ha, hbm, hgy = hb(a), hb(b), hb(gy)
     hy = torch.empty(n * n * bs).pin_memory()
     hga = torch.zeros(n * n * bs).pin_memory()
     hgb = torch.zeros(n * n * bs).pin_memory()
-    del y, ga, gb
-    torch.cuda.empty_cache()
 
     def e2e_step():
         ctx.matmul_fw_host(mode, P(ha), P(hbm), P(hy), n, n, n, bs, bs)
@@ -223,20 +248,13 @@ def run_ours(args, rank, local_rank, world):
         e2e_step()
     f1.record()
     barrier()
-    e2e_ms = f0.elapsed_time(f1)
     tensor_bytes = n * n * bs * 4
-    h2d = (2 + 5) * tensor_bytes   # fw: a, b;  bw: a, b, gy, ga, gb (the gradients hold the values to add to)
-    d2h = (1 + 2) * tensor_bytes   # y; ga, gb
+    return {"ms": f0.elapsed_time(f1), "steps": e2e_steps,
+            "h2d": (2 + 5) * tensor_bytes,   # fw: a, b;  bw: a, b, gy, ga, gb (gradients hold the values added to)
+            "d2h": (1 + 2) * tensor_bytes}   # y; ga, gb
 
-    if dist is not None:
-        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
-    if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
-        return
 
+def emit(args, world, ms, prof, launches, sampler, e2e):
     peaks = measured_peaks()
     ms_per_step = ms / args.steps
     value = FLOPS_PER_STEP * world / (ms_per_step * 1e-3) / 1e9
@@ -259,19 +277,19 @@ def run_ours(args, rank, local_rank, world):
             "algorithmic_tflops_in_kernel": achieved / 3.0,
             "kernel_ms_per_step": tc_ms / args.steps, "pack_ms_per_step": prof["pack"][0] / args.steps,
         },
-        "e2e": {"value": FLOPS_PER_STEP * world / (e2e_ms / e2e_steps * 1e-3) / 1e9, "unit": "GFLOP/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                "ms_per_step": e2e_ms / e2e_steps},
         "gpu_launches": int(launches),
         "clocks": sampler.summary(),
     }
-    if world == 1:
+    if e2e:
+        per = e2e["ms"] / e2e["steps"]
+        line["e2e"] = {"value": FLOPS_PER_STEP * world / (per * 1e-3) / 1e9, "unit": "GFLOP/s",
+                       "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                       "steps": e2e["steps"], "ms_per_step": per}
+    if world == 1 and not args.skip_cpu:
         t, kind, cores = cpu_sample()
         line["cpu_baseline"] = {"value": SAMPLE_FLOPS / t / 1e9, "unit": "GFLOP/s", "cores": cores,
                                 "kind": kind, "sample": SAMPLE_TEXT}
     print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
 
 
 def main():
@@ -280,7 +298,13 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=BATCH,
+                    help="batch elements per GPU (default 8 = the benchmark workload; smaller values are for "
+                         "profiler captures and are marked in config.workload)")
+    ap.add_argument("--skip-e2e", action="store_true", help="leave out the host-buffer leg (profiler captures)")
+    ap.add_argument("--skip-cpu", action="store_true", help="leave out the CPU baseline leg (profiler captures)")
     args = ap.parse_args()
+    set_batch(args.batch)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
