@@ -47,6 +47,7 @@ def build(verbose=False, force=False):
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(os.path.dirname(PKG), "include", "primitiv_b200.h"))
+    headers.append(os.path.join(os.path.dirname(PKG), "include", "primitiv_b200_ops.h"))
     headers.append(os.path.abspath(__file__))
     jobs = []
     objs = []

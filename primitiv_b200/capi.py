@@ -43,6 +43,36 @@ SIGNATURES = {
     "b200_profile_enable": (_int, [_vp, _int]),
     "b200_profile_read": (_int, [_vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_u64)]),
     "b200_launch_count": (_int, [_vp, ctypes.POINTER(_u64)]),
+    # ---- include/primitiv_b200_ops.h ----
+    "b200_unary_fw": (_int, [_vp, _int, _int, _vp, _vp, _u64, ctypes.c_float, ctypes.c_int32, _vp]),
+    "b200_unary_bw": (_int, [_vp, _int, _int, _vp, _vp, _vp, _vp, _u64, ctypes.c_float, ctypes.c_int32, _vp]),
+    "b200_scalar_fw": (_int, [_vp, _int, _int, _vp, _vp, _vp, _u64, _u32, _int, _int, _vp]),
+    "b200_binary_fw": (_int, [_vp, _int, _int, _vp, _vp, _vp, _u64, _u32, _int, _int, _vp]),
+    "b200_binary_bw": (_int, [_vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _u32, _int, _int, _vp]),
+    "b200_inplace_add": (_int, [_vp, _int, _vp, _vp, _u64, _u32, _u32, ctypes.c_float, _vp]),
+    "b200_inplace_multiply_const": (_int, [_vp, _int, _vp, _u64, ctypes.c_float, _vp]),
+    "b200_fill": (_int, [_vp, _int, _vp, _u64, ctypes.c_float, _vp]),
+    "b200_identity": (_int, [_vp, _int, _vp, _u32, _vp]),
+    "b200_upload": (_int, [_vp, _int, _vp, _vp, _u64, _vp]),
+    "b200_download": (_int, [_vp, _int, _vp, _vp, _u64, _vp]),
+    "b200_copy": (_int, [_vp, _int, _vp, _int, _vp, _u64, _vp]),
+    "b200_slice_fw": (_int, [_vp, _int, _vp, _vp, _u64, _u32, _u32, _u32, _u64, _vp]),
+    "b200_slice_bw": (_int, [_vp, _int, _vp, _vp, _u64, _u32, _u32, _u32, _u64, _u32, _u32, _vp]),
+    "b200_concat_part": (_int, [_vp, _int, _vp, _vp, _u64, _u32, _u32, _u32, _u64, _u32, _int, _vp]),
+    "b200_pick_fw": (_int, [_vp, _int, _vp, _vp, _u32, _vp, _u64, _u32, _u64, _u32, _int, _vp]),
+    "b200_pick_bw": (_int, [_vp, _int, _vp, _vp, _u32, _vp, _u64, _u32, _u64, _u32, _int, _vp]),
+    "b200_broadcast_fw": (_int, [_vp, _int, _vp, _vp, _u64, _u64, _u32, _vp]),
+    "b200_batch_pick_fw": (_int, [_vp, _int, _vp, _vp, _u32, _vp, _u64, _vp]),
+    "b200_batch_pick_bw": (_int, [_vp, _int, _vp, _vp, _u32, _vp, _u64, _vp]),
+    "b200_transpose": (_int, [_vp, _int, _vp, _vp, _u32, _u32, _u32, _int, _vp]),
+    "b200_permute_dims": (_int, [_vp, _int, _vp, _vp, _u32, _vp, _vp, _u32, _int, _vp]),
+    "b200_flip": (_int, [_vp, _int, _vp, _vp, _u64, _u32, _u64, _int, _vp]),
+    "b200_reduce_fw": (_int, [_vp, _int, _int, _vp, _vp, _u32, _u64, _u64, _vp]),
+    "b200_minmax_bw": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _u32, _u64, _u64, _vp]),
+    "b200_argminmax": (_int, [_vp, _int, _int, _vp, _vp, _u32, _u64, _u64, _vp]),
+    "b200_batch_sum_fw": (_int, [_vp, _int, _vp, _vp, _u64, _u32, _vp]),
+    "b200_seed": (_int, [_vp, _u64]),
+    "b200_random": (_int, [_vp, _int, _int, ctypes.c_float, ctypes.c_float, _vp, _u64, _vp]),
 }
 
 
@@ -168,6 +198,10 @@ class Context:
     def matmul_bw_host(self, mode, a, b, gy, ga, gb, di, dj, dk, ba, bb):
         _check(lib().b200_matmul_bw_host(self._h, mode, a, b, gy, ga, gb, di, dj, dk, ba, bb),
                "matmul_bw_host")
+
+    def op(self, name, *args):
+        """Calls any other entry point by name (the elementwise / movement / reduction set)."""
+        _check(getattr(lib(), name)(self._h, *args), name)
 
     def gemm(self, mode, trans_a, trans_b, A, B, C, m, n, k, groups=1, red=1,
              a_gs=0, a_rs=0, b_gs=0, b_rs=0, c_gs=0, accumulate=False, force_path=0, stream=None):

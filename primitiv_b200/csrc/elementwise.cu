@@ -1,0 +1,514 @@
+// Elementwise kernels: unary (+ constant), scalar-operand, binary with batch
+// broadcasting, in-place add / scale, fill, identity, host I/O and copies.
+//
+// Flat kernels move 128 bits per thread per access (4 floats / 8 halves) when the
+// pointers are 16-byte aligned, with a scalar tail; arithmetic is fp32 for both storage
+// types.  A gradient that is not batched receives the sum over the batch: one thread
+// per element walks the batch in order, so results are deterministic and no kernel uses
+// atomics.
+#include "ops_common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr unsigned kBlock = 256;
+
+// ------------------------------- unary ---------------------------------------
+
+template <int OP>
+__device__ __forceinline__ float unary_f(float x, float k, int ik) {
+  if constexpr (OP == B200_OP_NEGATE) return -x;
+  else if constexpr (OP == B200_OP_ABS) return fabsf(x);
+  else if constexpr (OP == B200_OP_SQRT) return sqrtf(x);
+  else if constexpr (OP == B200_OP_EXP) return expf(x);
+  else if constexpr (OP == B200_OP_LOG) return logf(x);
+  else if constexpr (OP == B200_OP_TANH) return tanhf(x);
+  else if constexpr (OP == B200_OP_SIGMOID) return .5f + .5f * tanhf(.5f * x);
+  else if constexpr (OP == B200_OP_SOFTPLUS) return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));
+  else if constexpr (OP == B200_OP_SIN) return sinf(x);
+  else if constexpr (OP == B200_OP_COS) return cosf(x);
+  else if constexpr (OP == B200_OP_TAN) return tanf(x);
+  else if constexpr (OP == B200_OP_ADD_CONST) return x + k;
+  else if constexpr (OP == B200_OP_SUB_CONST_R) return x - k;
+  else if constexpr (OP == B200_OP_SUB_CONST_L) return k - x;
+  else if constexpr (OP == B200_OP_MUL_CONST) return x * k;
+  else if constexpr (OP == B200_OP_DIV_CONST_R) return x / k;
+  else if constexpr (OP == B200_OP_DIV_CONST_L) return k / x;
+  else if constexpr (OP == B200_OP_POW_CONST_R) return powf(x, k);
+  else if constexpr (OP == B200_OP_POW_CONST_L) return powf(k, x);
+  else if constexpr (OP == B200_OP_PRELU) return x > 0.f ? x : k * x;
+  else if constexpr (OP == B200_OP_ELU) return x > 0.f ? x : k * (expf(x) - 1.f);
+  else if constexpr (OP == B200_OP_POWN) {
+    // exponentiation by squaring on |ik|, reciprocal for negative exponents
+    unsigned r = ik < 0 ? 0u - static_cast<unsigned>(ik) : static_cast<unsigned>(ik);
+    float ret = 1.f, f = x;
+    while (r) {
+      if (r & 1u) ret *= f;
+      f *= f;
+      r >>= 1;
+    }
+    return ik >= 0 ? ret : 1.f / ret;
+  }
+  return 0.f;
+}
+
+// the amount added to gx
+template <int OP>
+__device__ __forceinline__ float unary_d(float x, float y, float gy, float k, int ik) {
+  if constexpr (OP == B200_OP_NEGATE) return -gy;
+  else if constexpr (OP == B200_OP_ABS) return ((x > 0.f) - (x < 0.f)) * gy;
+  else if constexpr (OP == B200_OP_SQRT) return .5f * gy / y;
+  else if constexpr (OP == B200_OP_EXP) return y * gy;
+  else if constexpr (OP == B200_OP_LOG) return gy / x;
+  else if constexpr (OP == B200_OP_TANH) return (1.f - y * y) * gy;
+  else if constexpr (OP == B200_OP_SIGMOID) return y * (1.f - y) * gy;
+  else if constexpr (OP == B200_OP_SOFTPLUS) return (.5f + .5f * tanhf(.5f * x)) * gy;
+  else if constexpr (OP == B200_OP_SIN) return cosf(x) * gy;
+  else if constexpr (OP == B200_OP_COS) return -sinf(x) * gy;
+  else if constexpr (OP == B200_OP_TAN) return (1.f + y * y) * gy;
+  else if constexpr (OP == B200_OP_ADD_CONST) return gy;
+  else if constexpr (OP == B200_OP_SUB_CONST_R) return gy;
+  else if constexpr (OP == B200_OP_SUB_CONST_L) return -gy;
+  else if constexpr (OP == B200_OP_MUL_CONST) return k * gy;
+  else if constexpr (OP == B200_OP_DIV_CONST_R) return gy / k;
+  else if constexpr (OP == B200_OP_DIV_CONST_L) return -y * gy / x;
+  else if constexpr (OP == B200_OP_POW_CONST_R) return k * gy * y / x;
+  else if constexpr (OP == B200_OP_POW_CONST_L) return logf(k) * gy * y;
+  else if constexpr (OP == B200_OP_PRELU) return x > 0.f ? gy : k * gy;
+  else if constexpr (OP == B200_OP_ELU) return x > 0.f ? gy : (y + k) * gy;
+  else if constexpr (OP == B200_OP_POWN) return static_cast<float>(ik) * gy * y / x;
+  return 0.f;
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(kBlock) unary_fw_kernel(const T *__restrict__ x, T *__restrict__ y,
+                                                          u64 n, float k, int ik, int vec) {
+  const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
+  constexpr int N = Vec<T>::N;
+  const u64 nv = vec ? n / N : 0;
+  for (u64 i = tid; i < nv; i += stride) {
+    Vec<T> v;
+    v.load(x + i * N);
+#pragma unroll
+    for (int j = 0; j < N; ++j) v.set(j, unary_f<OP>(v.get(j), k, ik));
+    v.store(y + i * N);
+  }
+  for (u64 i = nv * N + tid; i < n; i += stride) st(y, i, unary_f<OP>(ld(x, i), k, ik));
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(kBlock) unary_bw_kernel(const T *__restrict__ x, const T *__restrict__ y,
+                                                          const T *__restrict__ gy, T *__restrict__ gx,
+                                                          u64 n, float k, int ik, int vec) {
+  const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
+  constexpr int N = Vec<T>::N;
+  const u64 nv = vec ? n / N : 0;
+  for (u64 i = tid; i < nv; i += stride) {
+    Vec<T> vx, vy, vg, vo;
+    vx.load(x + i * N);
+    vy.load(y + i * N);
+    vg.load(gy + i * N);
+    vo.load(gx + i * N);
+#pragma unroll
+    for (int j = 0; j < N; ++j) vo.set(j, vo.get(j) + unary_d<OP>(vx.get(j), vy.get(j), vg.get(j), k, ik));
+    vo.store(gx + i * N);
+  }
+  for (u64 i = nv * N + tid; i < n; i += stride)
+    st(gx, i, ld(gx, i) + unary_d<OP>(ld(x, i), ld(y, i), ld(gy, i), k, ik));
+}
+
+// ------------------------------- binary --------------------------------------
+
+template <int OP>
+__device__ __forceinline__ float binary_f(float a, float b) {
+  if constexpr (OP == B200_OP_ADD) return a + b;
+  else if constexpr (OP == B200_OP_SUBTRACT) return a - b;
+  else if constexpr (OP == B200_OP_MULTIPLY) return a * b;
+  else if constexpr (OP == B200_OP_DIVIDE) return a / b;
+  else if constexpr (OP == B200_OP_POW) return powf(a, b);
+  else if constexpr (OP == B200_OP_SUBTRACT_L) return b - a;
+  else if constexpr (OP == B200_OP_DIVIDE_L) return b / a;
+  else if constexpr (OP == B200_OP_POW_L) return powf(b, a);
+  return 0.f;
+}
+
+template <int OP>
+__device__ __forceinline__ void binary_d(float a, float b, float y, float gy, float &da, float &db) {
+  if constexpr (OP == B200_OP_ADD) { da = gy; db = gy; }
+  else if constexpr (OP == B200_OP_SUBTRACT) { da = gy; db = -gy; }
+  else if constexpr (OP == B200_OP_MULTIPLY) { da = gy * b; db = gy * a; }
+  else if constexpr (OP == B200_OP_DIVIDE) { const float t = gy / b; da = t; db = -t * y; }
+  else if constexpr (OP == B200_OP_POW) { const float t = gy * y; da = t * b / a; db = t * logf(a); }
+  else { da = 0.f; db = 0.f; }
+}
+
+// y[n][i] = f(a[n or 0][i], b[n or 0][i]); flat over volume * batch
+template <typename T, int OP>
+__global__ void __launch_bounds__(kBlock) binary_fw_kernel(const T *__restrict__ a, const T *__restrict__ b,
+                                                           T *__restrict__ y, u64 volume, u64 total,
+                                                           int a_batched, int b_batched, int vec) {
+  const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
+  constexpr int N = Vec<T>::N;
+  const u64 nv = vec ? total / N : 0;  // vec implies volume % N == 0: a vector never straddles a batch
+  for (u64 i = tid; i < nv; i += stride) {
+    const u64 e = i * N;
+    const u64 in_vol = e % volume;
+    Vec<T> va, vb, vo;
+    va.load(a + (a_batched ? e : in_vol));
+    vb.load(b + (b_batched ? e : in_vol));
+#pragma unroll
+    for (int j = 0; j < N; ++j) vo.set(j, binary_f<OP>(va.get(j), vb.get(j)));
+    vo.store(y + e);
+  }
+  for (u64 e = nv * N + tid; e < total; e += stride) {
+    const u64 in_vol = e % volume;
+    st(y, e, binary_f<OP>(ld(a, a_batched ? e : in_vol), ld(b, b_batched ? e : in_vol)));
+  }
+}
+
+// one thread per element of the volume, walking the batch in order
+template <typename T, int OP>
+__global__ void __launch_bounds__(kBlock) binary_bw_kernel(const T *__restrict__ a, const T *__restrict__ b,
+                                                           const T *__restrict__ y, const T *__restrict__ gy,
+                                                           T *__restrict__ ga, T *__restrict__ gb, u64 volume,
+                                                           uint32_t batch, int a_batched, int b_batched) {
+  const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
+  for (u64 i = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; i < volume; i += stride) {
+    float sum_a = 0.f, sum_b = 0.f;
+    for (uint32_t n = 0; n < batch; ++n) {
+      const u64 e = static_cast<u64>(n) * volume + i;
+      const u64 ea = a_batched ? e : i, eb = b_batched ? e : i;
+      float da, db;
+      binary_d<OP>(ld(a, ea), ld(b, eb), ld(y, e), ld(gy, e), da, db);
+      if (a_batched) st(ga, e, ld(ga, e) + da); else sum_a += da;
+      if (b_batched) st(gb, e, ld(gb, e) + db); else sum_b += db;
+    }
+    if (!a_batched) st(ga, i, ld(ga, i) + sum_a);
+    if (!b_batched) st(gb, i, ld(gb, i) + sum_b);
+  }
+}
+
+// y[n][i] = x[n or 0][i] op k[n or 0]
+template <typename T, int OP>
+__global__ void __launch_bounds__(kBlock) scalar_fw_kernel(const T *__restrict__ x, const T *__restrict__ k,
+                                                           T *__restrict__ y, u64 volume, u64 total,
+                                                           int x_batched, int k_batched) {
+  const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
+  for (u64 e = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const u64 n = e / volume, i = e - n * volume;
+    st(y, e, binary_f<OP>(ld(x, x_batched ? e : i), ld(k, k_batched ? n : 0)));
+  }
+}
+
+// y[n or 0] += sign * x[n or 0]
+template <typename T>
+__global__ void __launch_bounds__(kBlock) inplace_add_kernel(const T *__restrict__ x, T *__restrict__ y,
+                                                             u64 volume, uint32_t bx, uint32_t by, float sign,
+                                                             int vec) {
+  const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
+  constexpr int N = Vec<T>::N;
+  if (by >= bx && by > 1 || bx == by) {
+    // every destination element gets exactly one source element: flat and vectorised
+    const u64 total = volume * by;
+    const u64 nv = vec ? total / N : 0;
+    for (u64 i = tid; i < nv; i += stride) {
+      const u64 e = i * N;
+      Vec<T> vx, vy;
+      vx.load(x + (bx > 1 ? e : e % volume));
+      vy.load(y + e);
+#pragma unroll
+      for (int j = 0; j < N; ++j) vy.set(j, vy.get(j) + sign * vx.get(j));
+      vy.store(y + e);
+    }
+    for (u64 e = nv * N + tid; e < total; e += stride)
+      st(y, e, ld(y, e) + sign * ld(x, bx > 1 ? e : e % volume));
+  } else {
+    // by == 1 < bx: the destination receives the sum over the batch, in batch order
+    for (u64 i = tid; i < volume; i += stride) {
+      float acc = ld(y, i);
+      for (uint32_t n = 0; n < bx; ++n) acc += sign * ld(x, static_cast<u64>(n) * volume + i);
+      st(y, i, acc);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kBlock) fill_kernel(T *__restrict__ y, u64 n, float value, int vec) {
+  const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
+  constexpr int N = Vec<T>::N;
+  const u64 nv = vec ? n / N : 0;
+  Vec<T> v;
+#pragma unroll
+  for (int j = 0; j < N; ++j) v.set(j, value);
+  for (u64 i = tid; i < nv; i += stride) v.store(y + i * N);
+  for (u64 i = nv * N + tid; i < n; i += stride) st(y, i, value);
+}
+
+// in place, so no __restrict__ / read-only loads here
+template <typename T>
+__global__ void __launch_bounds__(kBlock) scale_kernel(T *x, u64 n, float k) {
+  const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
+  for (u64 i = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    st(x, i, ld(x, i) * k);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kBlock) identity_kernel(T *__restrict__ y, uint32_t size) {
+  const u64 total = static_cast<u64>(size) * size;
+  const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
+  for (u64 e = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride)
+    st(y, e, (e % (static_cast<u64>(size) + 1)) == 0 ? 1.f : 0.f);
+}
+
+template <typename S, typename D>
+__global__ void __launch_bounds__(kBlock) convert_kernel(const S *__restrict__ x, D *__restrict__ y, u64 n) {
+  const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
+  for (u64 i = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) st(y, i, ld(x, i));
+}
+
+#define B200_UNARY_OPS(X) \
+  X(0) X(1) X(2) X(3) X(4) X(5) X(6) X(7) X(8) X(9) X(10) X(11) X(12) X(13) X(14) X(15) X(16) X(17) \
+  X(18) X(19) X(20) X(21)
+#define B200_BINARY_OPS(X) X(0) X(1) X(2) X(3) X(4)
+#define B200_SCALAR_OPS(X) X(0) X(1) X(2) X(3) X(4) X(5) X(6) X(7)
+
+template <typename T>
+void launch_unary_fw(b200_ctx *ctx, cudaStream_t s, int op, const void *x, void *y, u64 n, float k,
+                     int ik, int vec) {
+  const unsigned grid = grid_for(ctx, n / (vec ? Vec<T>::N : 1) + 1, kBlock);
+  switch (op) {
+#define X(OP) case OP: unary_fw_kernel<T, OP><<<grid, kBlock, 0, s>>>(static_cast<const T *>(x), static_cast<T *>(y), n, k, ik, vec); break;
+    B200_UNARY_OPS(X)
+#undef X
+  }
+}
+
+template <typename T>
+void launch_unary_bw(b200_ctx *ctx, cudaStream_t s, int op, const void *x, const void *y, const void *gy,
+                     void *gx, u64 n, float k, int ik, int vec) {
+  const unsigned grid = grid_for(ctx, n / (vec ? Vec<T>::N : 1) + 1, kBlock);
+  switch (op) {
+#define X(OP) case OP: unary_bw_kernel<T, OP><<<grid, kBlock, 0, s>>>(static_cast<const T *>(x), static_cast<const T *>(y), static_cast<const T *>(gy), static_cast<T *>(gx), n, k, ik, vec); break;
+    B200_UNARY_OPS(X)
+#undef X
+  }
+}
+
+template <typename T>
+void launch_scalar_fw(b200_ctx *ctx, cudaStream_t s, int op, const void *x, const void *k, void *y,
+                      u64 volume, u64 total, int x_batched, int k_batched) {
+  const unsigned grid = grid_for(ctx, total, kBlock);
+  switch (op) {
+#define X(OP) case OP: scalar_fw_kernel<T, OP><<<grid, kBlock, 0, s>>>(static_cast<const T *>(x), static_cast<const T *>(k), static_cast<T *>(y), volume, total, x_batched, k_batched); break;
+    B200_SCALAR_OPS(X)
+#undef X
+  }
+}
+
+template <typename T>
+void launch_binary_fw(b200_ctx *ctx, cudaStream_t s, int op, const void *a, const void *b, void *y,
+                      u64 volume, u64 total, int a_batched, int b_batched) {
+  const int vec = aligned16(a) && aligned16(b) && aligned16(y) && volume % Vec<T>::N == 0;
+  const unsigned grid = grid_for(ctx, total / (vec ? Vec<T>::N : 1) + 1, kBlock);
+  switch (op) {
+#define X(OP) case OP: binary_fw_kernel<T, OP><<<grid, kBlock, 0, s>>>(static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(y), volume, total, a_batched, b_batched, vec); break;
+    B200_BINARY_OPS(X)
+#undef X
+  }
+}
+
+template <typename T>
+void launch_binary_bw(b200_ctx *ctx, cudaStream_t s, int op, const void *a, const void *b, const void *y,
+                      const void *gy, void *ga, void *gb, u64 volume, uint32_t batch, int a_batched,
+                      int b_batched) {
+  const unsigned grid = grid_for(ctx, volume, kBlock);
+  switch (op) {
+#define X(OP) case OP: binary_bw_kernel<T, OP><<<grid, kBlock, 0, s>>>(static_cast<const T *>(a), static_cast<const T *>(b), static_cast<const T *>(y), static_cast<const T *>(gy), static_cast<T *>(ga), static_cast<T *>(gb), volume, batch, a_batched, b_batched); break;
+    B200_BINARY_OPS(X)
+#undef X
+  }
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_unary_fw(b200_ctx *ctx, int mode, int op, const void *x, void *y, uint64_t n, float k,
+                  int32_t ik, void *stream) {
+  B200_OPS_PROLOGUE(ctx);
+  if (n == 0) return B200_OK;
+  if (!x || !y || op < 0 || op >= B200_OP_UNARY_COUNT) return B200_ERR_INVALID_ARG;
+  const int vec = aligned16(x) && aligned16(y);
+  ProfScope prof(ctx, kProfElementwise, s);
+  B200_DISPATCH_MODE(mode, { launch_unary_fw<T>(ctx, s, op, x, y, n, k, ik, vec); });
+  B200_OPS_EPILOGUE(ctx);
+}
+
+int b200_unary_bw(b200_ctx *ctx, int mode, int op, const void *x, const void *y, const void *gy,
+                  void *gx, uint64_t n, float k, int32_t ik, void *stream) {
+  B200_OPS_PROLOGUE(ctx);
+  if (n == 0) return B200_OK;
+  if (!x || !y || !gy || !gx || op < 0 || op >= B200_OP_UNARY_COUNT) return B200_ERR_INVALID_ARG;
+  const int vec = aligned16(x) && aligned16(y) && aligned16(gy) && aligned16(gx);
+  ProfScope prof(ctx, kProfElementwise, s);
+  B200_DISPATCH_MODE(mode, { launch_unary_bw<T>(ctx, s, op, x, y, gy, gx, n, k, ik, vec); });
+  B200_OPS_EPILOGUE(ctx);
+}
+
+int b200_scalar_fw(b200_ctx *ctx, int mode, int op, const void *x, const void *k, void *y,
+                   uint64_t volume, uint32_t batch, int x_batched, int k_batched, void *stream) {
+  B200_OPS_PROLOGUE(ctx);
+  const u64 total = volume * batch;
+  if (total == 0) return B200_OK;
+  if (!x || !k || !y || op < 0 || op >= B200_OP_BINARY_COUNT) return B200_ERR_INVALID_ARG;
+  ProfScope prof(ctx, kProfElementwise, s);
+  B200_DISPATCH_MODE(mode, { launch_scalar_fw<T>(ctx, s, op, x, k, y, volume, total, x_batched, k_batched); });
+  B200_OPS_EPILOGUE(ctx);
+}
+
+int b200_binary_fw(b200_ctx *ctx, int mode, int op, const void *a, const void *b, void *y,
+                   uint64_t volume, uint32_t batch, int a_batched, int b_batched, void *stream) {
+  B200_OPS_PROLOGUE(ctx);
+  const u64 total = volume * batch;
+  if (total == 0) return B200_OK;
+  if (!a || !b || !y || op < 0 || op > B200_OP_POW) return B200_ERR_INVALID_ARG;
+  ProfScope prof(ctx, kProfElementwise, s);
+  B200_DISPATCH_MODE(mode, { launch_binary_fw<T>(ctx, s, op, a, b, y, volume, total, a_batched, b_batched); });
+  B200_OPS_EPILOGUE(ctx);
+}
+
+int b200_binary_bw(b200_ctx *ctx, int mode, int op, const void *a, const void *b, const void *y,
+                   const void *gy, void *ga, void *gb, uint64_t volume, uint32_t batch, int a_batched,
+                   int b_batched, void *stream) {
+  B200_OPS_PROLOGUE(ctx);
+  if (volume == 0 || batch == 0) return B200_OK;
+  if (!a || !b || !y || !gy || !ga || !gb || op < 0 || op > B200_OP_POW) return B200_ERR_INVALID_ARG;
+  ProfScope prof(ctx, kProfElementwise, s);
+  B200_DISPATCH_MODE(mode, { launch_binary_bw<T>(ctx, s, op, a, b, y, gy, ga, gb, volume, batch, a_batched, b_batched); });
+  B200_OPS_EPILOGUE(ctx);
+}
+
+int b200_inplace_add(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t volume, uint32_t bx,
+                     uint32_t by, float sign, void *stream) {
+  B200_OPS_PROLOGUE(ctx);
+  if (volume == 0 || bx == 0 || by == 0) return B200_OK;
+  if (!x || !y || (bx != by && bx != 1 && by != 1)) return B200_ERR_INVALID_ARG;
+  ProfScope prof(ctx, kProfElementwise, s);
+  B200_DISPATCH_MODE(mode, {
+    const int vec = aligned16(x) && aligned16(y) && volume % Vec<T>::N == 0;
+    const u64 work = (by == 1 && bx > 1) ? volume : volume * by / (vec ? Vec<T>::N : 1) + 1;
+    inplace_add_kernel<T><<<grid_for(ctx, work, kBlock), kBlock, 0, s>>>(
+        static_cast<const T *>(x), static_cast<T *>(y), volume, bx, by, sign, vec);
+  });
+  B200_OPS_EPILOGUE(ctx);
+}
+
+int b200_inplace_multiply_const(b200_ctx *ctx, int mode, void *x, uint64_t n, float k, void *stream) {
+  B200_OPS_PROLOGUE(ctx);
+  if (n == 0) return B200_OK;
+  if (!x) return B200_ERR_INVALID_ARG;
+  ProfScope prof(ctx, kProfElementwise, s);
+  B200_DISPATCH_MODE(mode, {
+    scale_kernel<T><<<grid_for(ctx, n, kBlock), kBlock, 0, s>>>(static_cast<T *>(x), n, k);
+  });
+  B200_OPS_EPILOGUE(ctx);
+}
+
+int b200_fill(b200_ctx *ctx, int mode, void *y, uint64_t n, float value, void *stream) {
+  B200_OPS_PROLOGUE(ctx);
+  if (n == 0) return B200_OK;
+  if (!y) return B200_ERR_INVALID_ARG;
+  const int vec = aligned16(y);
+  ProfScope prof(ctx, kProfElementwise, s);
+  B200_DISPATCH_MODE(mode, {
+    fill_kernel<T><<<grid_for(ctx, n / (vec ? Vec<T>::N : 1) + 1, kBlock), kBlock, 0, s>>>(
+        static_cast<T *>(y), n, value, vec);
+  });
+  B200_OPS_EPILOGUE(ctx);
+}
+
+int b200_identity(b200_ctx *ctx, int mode, void *y, uint32_t size, void *stream) {
+  B200_OPS_PROLOGUE(ctx);
+  if (size == 0) return B200_OK;
+  if (!y) return B200_ERR_INVALID_ARG;
+  ProfScope prof(ctx, kProfElementwise, s);
+  B200_DISPATCH_MODE(mode, {
+    identity_kernel<T><<<grid_for(ctx, static_cast<u64>(size) * size, kBlock), kBlock, 0, s>>>(
+        static_cast<T *>(y), size);
+  });
+  B200_OPS_EPILOGUE(ctx);
+}
+
+int b200_upload(b200_ctx *ctx, int mode, const float *values_host, void *y, uint64_t n, void *stream) {
+  B200_OPS_PROLOGUE(ctx);
+  if (n == 0) return B200_OK;
+  if (!values_host || !y) return B200_ERR_INVALID_ARG;
+  if (mode != B200_MODE_FP16) {
+    B200_CUDA_TRY(cudaMemcpyAsync(y, values_host, n * sizeof(float), cudaMemcpyHostToDevice, s));
+    B200_CUDA_TRY(cudaStreamSynchronize(s));
+    return B200_OK;
+  }
+  void *tmp = nullptr;
+  int rc = ctx->pool.alloc(n * sizeof(float), &tmp, nullptr);
+  if (rc) return rc;
+  cudaError_t e = cudaMemcpyAsync(tmp, values_host, n * sizeof(float), cudaMemcpyHostToDevice, s);
+  if (e == cudaSuccess) {
+    convert_kernel<float, __half><<<grid_for(ctx, n, kBlock), kBlock, 0, s>>>(
+        static_cast<const float *>(tmp), static_cast<__half *>(y), n);
+    ++ctx->launches;
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  ctx->pool.free(tmp);
+  return static_cast<int>(e);
+}
+
+int b200_download(b200_ctx *ctx, int mode, const void *x, float *values_host, uint64_t n, void *stream) {
+  B200_OPS_PROLOGUE(ctx);
+  if (n == 0) return B200_OK;
+  if (!values_host || !x) return B200_ERR_INVALID_ARG;
+  if (mode != B200_MODE_FP16) {
+    B200_CUDA_TRY(cudaMemcpyAsync(values_host, x, n * sizeof(float), cudaMemcpyDeviceToHost, s));
+    B200_CUDA_TRY(cudaStreamSynchronize(s));
+    return B200_OK;
+  }
+  void *tmp = nullptr;
+  int rc = ctx->pool.alloc(n * sizeof(float), &tmp, nullptr);
+  if (rc) return rc;
+  convert_kernel<__half, float><<<grid_for(ctx, n, kBlock), kBlock, 0, s>>>(
+      static_cast<const __half *>(x), static_cast<float *>(tmp), n);
+  ++ctx->launches;
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaMemcpyAsync(values_host, tmp, n * sizeof(float), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  ctx->pool.free(tmp);
+  return static_cast<int>(e);
+}
+
+int b200_copy(b200_ctx *ctx, int src_mode, const void *x, int dst_mode, void *y, uint64_t n, void *stream) {
+  B200_OPS_PROLOGUE(ctx);
+  if (n == 0) return B200_OK;
+  if (!x || !y) return B200_ERR_INVALID_ARG;
+  const bool sh = src_mode == B200_MODE_FP16, dh = dst_mode == B200_MODE_FP16;
+  if (sh == dh) {
+    // cudaMemcpyDefault: also right when x lives on another GPU of this process (unified addressing)
+    B200_CUDA_TRY(cudaMemcpyAsync(y, x, n * (sh ? 2 : 4), cudaMemcpyDefault, s));
+    return B200_OK;
+  }
+  const unsigned grid = grid_for(ctx, n, kBlock);
+  if (sh)
+    convert_kernel<__half, float><<<grid, kBlock, 0, s>>>(static_cast<const __half *>(x), static_cast<float *>(y), n);
+  else
+    convert_kernel<float, __half><<<grid, kBlock, 0, s>>>(static_cast<const float *>(x), static_cast<__half *>(y), n);
+  B200_OPS_EPILOGUE(ctx);
+}
+
+}  // extern "C"

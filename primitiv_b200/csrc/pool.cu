@@ -89,10 +89,12 @@ void Pool::stats(std::uint64_t out[4]) const {
 }
 
 Pool::~Pool() {
-  // Blocks still in use belong to tensors that outlive the device; they are
-  // released with the CUDA context.  Cached blocks are returned now.
+  // Everything goes back to the driver, blocks still handed out included: a tensor may
+  // outlive its device (garbage-collected bindings), and its handle then only needs to be
+  // safe to drop, not to use (primitiv/core/memory_pool.cc:18-33 does the same).
   for (auto &kv : cached_)
     for (void *p : kv.second) cudaFree(p);
+  for (auto &kv : in_use_) cudaFree(kv.first);
 }
 
 }  // namespace b200

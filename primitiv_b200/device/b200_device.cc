@@ -1,0 +1,493 @@
+// primitiv::devices::B200: every Device virtual expressed as a call into the C ABI.
+//
+// What the base class has already done before any *_impl runs (primitiv/core/device.cc):
+// checked that all tensors live on this device, validated and inferred shapes, allocated
+// the output.  So nothing here validates shapes; it only derives the flat extents
+// (base / repeat / skip, volumes, batch flags) that the kernels take, with the same
+// definitions as the reference's Naive device (primitiv/devices/naive/ops/<op>.cc).
+#include "b200_device.h"
+
+#include <cstdlib>
+#include <cstring>
+#include <iostream>
+#include <string>
+
+#include <primitiv/core/error.h>
+
+#include "../../include/primitiv_b200_ops.h"
+
+// A non-zero return code of the C ABI becomes primitiv::Error, the way CUDA_CALL and
+// CUBLAS_CALL do for the reference device (primitiv/internal/cuda/utils.h:20-48).
+#define B200_CALL(expr)                                                       \
+  do {                                                                        \
+    const int rc__ = (expr);                                                  \
+    if (rc__ != 0) {                                                          \
+      PRIMITIV_THROW_ERROR("B200 call `" #expr "` failed: "                   \
+                           << ::b200_error_string(rc__) << " [" << rc__ << "]"); \
+    }                                                                         \
+  } while (0)
+
+#define CDATA(x) (get_handle(x))
+#define MDATA(x) (get_mutable_handle(x))
+
+namespace primitiv {
+namespace devices {
+
+// Owns the context.  Handles keep a weak reference: a Tensor may outlive its device
+// (primitiv/test/cuda_device_test.cc:66-78 requires that destroying it then is safe); once
+// the state is gone the block has already been released together with the pool.
+struct B200::State {
+  ::b200_ctx *ctx = nullptr;
+  ~State() {
+    if (ctx) ::b200_ctx_destroy(ctx);
+  }
+};
+
+namespace {
+
+B200::Mode mode_from_environment() {
+  const char *e = std::getenv("PRIMITIV_B200_MODE");
+  if (!e) return B200::Mode::FP32_3XTF32;
+  const std::string v(e);
+  if (v == "tf32" || v == "TF32" || v == "tf32_fast") return B200::Mode::TF32_FAST;
+  if (v == "fp16" || v == "FP16" || v == "half") return B200::Mode::FP16;
+  if (v == "3xtf32" || v == "3XTF32" || v == "fp32") return B200::Mode::FP32_3XTF32;
+  PRIMITIV_THROW_ERROR("Unknown PRIMITIV_B200_MODE: '" << v << "' (3xtf32 | tf32 | fp16)");
+}
+
+}  // namespace
+
+std::uint32_t B200::num_devices() {
+  // Probe ordinals until context creation reports that the ordinal does not exist.
+  std::uint32_t n = 0;
+  for (; n < 64; ++n) {
+    ::b200_ctx *c = nullptr;
+    const int rc = ::b200_ctx_create(static_cast<int>(n), &c);
+    if (rc != 0) break;
+    ::b200_ctx_destroy(c);
+  }
+  return n;
+}
+
+B200::B200(std::uint32_t device_id) : device_id_(device_id), mode_(mode_from_environment()) {
+  initialize(0);
+}
+
+B200::B200(std::uint32_t device_id, std::uint32_t rng_seed)
+    : device_id_(device_id), mode_(mode_from_environment()) {
+  initialize(rng_seed);
+}
+
+B200::B200(std::uint32_t device_id, std::uint32_t rng_seed, Mode mode) : device_id_(device_id), mode_(mode) {
+  initialize(rng_seed);
+}
+
+void B200::initialize(std::uint32_t rng_seed) {
+  state_ = std::make_shared<State>();
+  const int rc = ::b200_ctx_create(static_cast<int>(device_id_), &state_->ctx);
+  if (rc != 0) {
+    state_.reset();
+    PRIMITIV_THROW_ERROR("Could not create a B200 device on GPU " << device_id_ << ": "
+                         << ::b200_error_string(rc) << " [" << rc << "]");
+  }
+  B200_CALL(::b200_seed(state_->ctx, rng_seed));
+}
+
+B200::~B200() {
+  // Outstanding handles only hold weak references, so this releases the context now.
+  state_.reset();
+}
+
+::b200_ctx *B200::context() const { return state_->ctx; }
+
+void B200::set_matmul_path_policy(int policy) { B200_CALL(::b200_set_path_policy(state_->ctx, policy)); }
+
+void B200::dump_description() const {
+  int dev = 0, sms = 0;
+  ::b200_ctx_device(state_->ctx, &dev, &sms);
+  std::uint64_t st[4] = {0, 0, 0, 0};
+  ::b200_pool_stats(state_->ctx, st);
+  static const char *names[] = {"FP32 (3xTF32)", "TF32 (single pass)", "FP16"};
+  std::cerr << "Device " << this << std::endl;
+  std::cerr << "  Type: B200 (sm_100a, libprimitiv_b200)" << std::endl;
+  std::cerr << "  GPU ordinal ........ " << dev << std::endl;
+  std::cerr << "  SMs ................ " << sms << std::endl;
+  std::cerr << "  Numeric mode ....... " << names[imode()] << std::endl;
+  std::cerr << "  Pool in use ........ " << st[0] << " bytes" << std::endl;
+  std::cerr << "  Pool cached ........ " << st[1] << " bytes" << std::endl;
+}
+
+// ---------------------------------------------------------------- memory and host I/O
+
+std::shared_ptr<void> B200::new_handle(const Shape &shape, std::size_t *const allocated_size) {
+  void *ptr = nullptr;
+  std::size_t got = 0;
+  B200_CALL(::b200_pool_alloc(state_->ctx, elem_size() * shape.size(), &ptr, &got));
+  if (allocated_size) *allocated_size = got;
+  std::weak_ptr<State> weak = state_;
+  return std::shared_ptr<void>(ptr, [weak](void *p) {
+    if (std::shared_ptr<State> st = weak.lock()) ::b200_pool_free(st->ctx, p);
+  });
+}
+
+std::vector<float> B200::tensor_to_vector_impl(const Tensor &x) {
+  std::vector<float> ret(x.shape().size());
+  B200_CALL(::b200_download(state_->ctx, imode(), CDATA(x), ret.data(), ret.size(), nullptr));
+  return ret;
+}
+
+std::vector<std::uint32_t> B200::argmax_impl(const Tensor &x, std::uint32_t dim) {
+  const Shape &s = x.shape();
+  const std::uint32_t n = s[dim];
+  std::vector<std::uint32_t> ret(s.size() / n);
+  B200_CALL(::b200_argminmax(state_->ctx, imode(), 1, CDATA(x), ret.data(), n, s.lower_volume(dim), ret.size(),
+                             nullptr));
+  return ret;
+}
+
+std::vector<std::uint32_t> B200::argmin_impl(const Tensor &x, std::uint32_t dim) {
+  const Shape &s = x.shape();
+  const std::uint32_t n = s[dim];
+  std::vector<std::uint32_t> ret(s.size() / n);
+  B200_CALL(::b200_argminmax(state_->ctx, imode(), 0, CDATA(x), ret.data(), n, s.lower_volume(dim), ret.size(),
+                             nullptr));
+  return ret;
+}
+
+void B200::reset_tensor_impl(float k, Tensor &x) {
+  B200_CALL(::b200_fill(state_->ctx, imode(), MDATA(x), x.shape().size(), k, nullptr));
+}
+
+void B200::reset_tensor_by_array_impl(const float values[], Tensor &x) {
+  B200_CALL(::b200_upload(state_->ctx, imode(), values, MDATA(x), x.shape().size(), nullptr));
+}
+
+void B200::copy_tensor_impl(const Tensor &x, Tensor &y) {
+  // This device reports CUDA / CUDA16 as its type, so the source is identified by its class,
+  // not by type(): another B200 (any GPU, any mode) is copied on the device, a Naive tensor is
+  // read straight from its host buffer (primitiv/devices/cuda/ops/copy_tensor.cu:12-14), anything
+  // else goes through to_vector().
+  const std::uint64_t n = x.shape().size();
+  if (const B200 *src = dynamic_cast<const B200 *>(&x.device())) {
+    if (src->device_id_ == device_id_ || src->mode_ == mode_) {
+      if (src->device_id_ != device_id_) {
+        // The two GPUs' default streams do not order against each other: let the source
+        // device finish whatever still writes x before this device reads it.
+        int code = 0;
+        B200_CALL(::b200_status_poll(src->state_->ctx, nullptr, &code));
+      }
+      B200_CALL(::b200_copy(state_->ctx, src->imode(), CDATA(x), imode(), MDATA(y), n, nullptr));
+      return;
+    }
+  } else if (x.device().type() == DeviceType::NAIVE) {
+    reset_tensor_by_array(static_cast<const float *>(CDATA(x)), y);
+    return;
+  }
+  reset_tensor_by_vector(x.to_vector(), y);
+}
+
+void B200::identity_impl(Tensor &y) {
+  B200_CALL(::b200_identity(state_->ctx, imode(), MDATA(y), y.shape()[0], nullptr));
+}
+
+// ---------------------------------------------------------------- random fills
+
+void B200::random_bernoulli_impl(float p, Tensor &y) {
+  B200_CALL(::b200_random(state_->ctx, imode(), B200_RAND_BERNOULLI, p, 0.f, MDATA(y), y.shape().size(), nullptr));
+}
+void B200::random_uniform_impl(float lower, float upper, Tensor &y) {
+  B200_CALL(::b200_random(state_->ctx, imode(), B200_RAND_UNIFORM, lower, upper, MDATA(y), y.shape().size(), nullptr));
+}
+void B200::random_normal_impl(float mean, float sd, Tensor &y) {
+  B200_CALL(::b200_random(state_->ctx, imode(), B200_RAND_NORMAL, mean, sd, MDATA(y), y.shape().size(), nullptr));
+}
+void B200::random_log_normal_impl(float mean, float sd, Tensor &y) {
+  B200_CALL(::b200_random(state_->ctx, imode(), B200_RAND_LOG_NORMAL, mean, sd, MDATA(y), y.shape().size(), nullptr));
+}
+
+// ---------------------------------------------------------------- pick / slice / concat
+
+void B200::pick_fw_impl(const Tensor &x, const std::vector<std::uint32_t> &ids, std::uint32_t dim, Tensor &y) {
+  const std::uint64_t base = y.shape().lower_volume(dim);
+  B200_CALL(::b200_pick_fw(state_->ctx, imode(), CDATA(x), ids.data(), static_cast<std::uint32_t>(ids.size()),
+                           MDATA(y), base, x.shape()[dim], y.shape().volume() / base, y.shape().batch(),
+                           x.shape().has_batch(), nullptr));
+}
+
+void B200::pick_bw_impl(const Tensor &gy, const std::vector<std::uint32_t> &ids, std::uint32_t dim, Tensor &gx) {
+  const std::uint64_t base = gy.shape().lower_volume(dim);
+  B200_CALL(::b200_pick_bw(state_->ctx, imode(), CDATA(gy), ids.data(), static_cast<std::uint32_t>(ids.size()),
+                           MDATA(gx), base, gx.shape()[dim], gy.shape().volume() / base, gy.shape().batch(),
+                           gx.shape().has_batch(), nullptr));
+}
+
+void B200::slice_fw_impl(const Tensor &x, std::uint32_t dim, std::uint32_t offset, Tensor &y) {
+  const std::uint64_t base = y.shape().lower_volume(dim);
+  const std::uint32_t y_dim = y.shape()[dim];
+  B200_CALL(::b200_slice_fw(state_->ctx, imode(), CDATA(x), MDATA(y), base, x.shape()[dim], y_dim, offset,
+                            y.shape().size() / (base * y_dim), nullptr));
+}
+
+void B200::slice_bw_impl(const Tensor &gy, std::uint32_t dim, std::uint32_t offset, Tensor &gx) {
+  const Shape &sx = gx.shape();
+  const std::uint64_t base = sx.lower_volume(dim);
+  const std::uint32_t x_dim = sx[dim];
+  B200_CALL(::b200_slice_bw(state_->ctx, imode(), CDATA(gy), MDATA(gx), base, x_dim, gy.shape()[dim], offset,
+                            sx.volume() / (base * x_dim), sx.batch(), gy.shape().batch(), nullptr));
+}
+
+void B200::concat_fw_impl(const std::vector<const Tensor *> &xs, std::uint32_t dim, Tensor &y) {
+  const Shape &sy = y.shape();
+  const std::uint64_t base = sy.lower_volume(dim);
+  const std::uint32_t y_dim = sy[dim];
+  const std::uint64_t repeat = sy.volume() / (base * y_dim);
+  void *dest = MDATA(y);
+  std::uint32_t offset = 0;
+  for (const Tensor *x : xs) {
+    const std::uint32_t x_dim = x->shape()[dim];
+    B200_CALL(::b200_concat_part(state_->ctx, imode(), CDATA(*x), dest, base, x_dim, y_dim, offset, repeat,
+                                 sy.batch(), x->shape().has_batch(), nullptr));
+    offset += x_dim;
+  }
+}
+
+// ---------------------------------------------------------------- elementwise, one tensor
+
+#define B200_IMPL_X_FW(name, op)                                                                   \
+  void B200::name##_fw_impl(const Tensor &x, Tensor &y) {                                          \
+    B200_CALL(::b200_unary_fw(state_->ctx, imode(), op, CDATA(x), MDATA(y), x.shape().size(), 0.f, 0, nullptr)); \
+  }
+#define B200_IMPL_X_BW(name, op)                                                                   \
+  void B200::name##_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, Tensor &gx) {      \
+    B200_CALL(::b200_unary_bw(state_->ctx, imode(), op, CDATA(x), CDATA(y), CDATA(gy), MDATA(gx),  \
+                              x.shape().size(), 0.f, 0, nullptr));                                 \
+  }
+#define B200_IMPL_X(name, op) B200_IMPL_X_FW(name, op) B200_IMPL_X_BW(name, op)
+
+B200_IMPL_X_FW(negate, B200_OP_NEGATE)
+B200_IMPL_X(abs, B200_OP_ABS)
+B200_IMPL_X(sqrt, B200_OP_SQRT)
+B200_IMPL_X(exp, B200_OP_EXP)
+B200_IMPL_X(log, B200_OP_LOG)
+B200_IMPL_X(tanh, B200_OP_TANH)
+B200_IMPL_X(sigmoid, B200_OP_SIGMOID)
+B200_IMPL_X(softplus, B200_OP_SOFTPLUS)
+B200_IMPL_X(sin, B200_OP_SIN)
+B200_IMPL_X(cos, B200_OP_COS)
+B200_IMPL_X(tan, B200_OP_TAN)
+
+#define B200_IMPL_X_CONST(name, op)                                                                \
+  void B200::name##_fw_impl(const Tensor &x, float k, Tensor &y) {                                 \
+    B200_CALL(::b200_unary_fw(state_->ctx, imode(), op, CDATA(x), MDATA(y), x.shape().size(), k, 0, nullptr)); \
+  }                                                                                                \
+  void B200::name##_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, float k, Tensor &gx) { \
+    B200_CALL(::b200_unary_bw(state_->ctx, imode(), op, CDATA(x), CDATA(y), CDATA(gy), MDATA(gx),  \
+                              x.shape().size(), k, 0, nullptr));                                   \
+  }
+
+B200_IMPL_X_CONST(add_const, B200_OP_ADD_CONST)
+B200_IMPL_X_CONST(subtract_const_r, B200_OP_SUB_CONST_R)
+B200_IMPL_X_CONST(subtract_const_l, B200_OP_SUB_CONST_L)
+B200_IMPL_X_CONST(multiply_const, B200_OP_MUL_CONST)
+B200_IMPL_X_CONST(divide_const_r, B200_OP_DIV_CONST_R)
+B200_IMPL_X_CONST(divide_const_l, B200_OP_DIV_CONST_L)
+B200_IMPL_X_CONST(pow_const_r, B200_OP_POW_CONST_R)
+B200_IMPL_X_CONST(pow_const_l, B200_OP_POW_CONST_L)
+B200_IMPL_X_CONST(prelu, B200_OP_PRELU)
+B200_IMPL_X_CONST(elu, B200_OP_ELU)
+
+void B200::pown_fw_impl(const Tensor &x, std::int32_t k, Tensor &y) {
+  B200_CALL(::b200_unary_fw(state_->ctx, imode(), B200_OP_POWN, CDATA(x), MDATA(y), x.shape().size(), 0.f, k, nullptr));
+}
+void B200::pown_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, std::int32_t k, Tensor &gx) {
+  B200_CALL(::b200_unary_bw(state_->ctx, imode(), B200_OP_POWN, CDATA(x), CDATA(y), CDATA(gy), MDATA(gx),
+                            x.shape().size(), 0.f, k, nullptr));
+}
+
+// ---------------------------------------------------------------- transpose / permute / flip
+
+void B200::transpose_fw_impl(const Tensor &x, Tensor &y) {
+  B200_CALL(::b200_transpose(state_->ctx, imode(), CDATA(x), MDATA(y), x.shape()[0], x.shape()[1],
+                             x.shape().batch(), 0, nullptr));
+}
+void B200::transpose_bw_impl(const Tensor &, const Tensor &, const Tensor &gy, Tensor &gx) {
+  B200_CALL(::b200_transpose(state_->ctx, imode(), CDATA(gy), MDATA(gx), gy.shape()[0], gy.shape()[1],
+                             gy.shape().batch(), 1, nullptr));
+}
+
+void B200::permute_dims_fw_impl(const Tensor &x, const std::vector<std::uint32_t> &perm, Tensor &y) {
+  std::uint32_t dims[8];
+  const std::uint32_t nd = static_cast<std::uint32_t>(perm.size());
+  for (std::uint32_t i = 0; i < nd && i < 8; ++i) dims[i] = x.shape()[i];
+  B200_CALL(::b200_permute_dims(state_->ctx, imode(), CDATA(x), MDATA(y), nd, dims, perm.data(),
+                                x.shape().batch(), 0, nullptr));
+}
+void B200::permute_dims_bw_impl(const Tensor &, const Tensor &, const Tensor &gy,
+                                const std::vector<std::uint32_t> &perm, Tensor &gx) {
+  std::uint32_t dims[8];
+  const std::uint32_t nd = static_cast<std::uint32_t>(perm.size());
+  for (std::uint32_t i = 0; i < nd && i < 8; ++i) dims[i] = gx.shape()[i];
+  B200_CALL(::b200_permute_dims(state_->ctx, imode(), CDATA(gy), MDATA(gx), nd, dims, perm.data(),
+                                gx.shape().batch(), 1, nullptr));
+}
+
+void B200::flip_fw_impl(const Tensor &x, std::uint32_t dim, Tensor &y) {
+  const Shape &s = x.shape();
+  B200_CALL(::b200_flip(state_->ctx, imode(), CDATA(x), MDATA(y), s.lower_volume(dim), s[dim], s.size(), 0, nullptr));
+}
+void B200::flip_bw_impl(const Tensor &gy, std::uint32_t dim, Tensor &gx) {
+  const Shape &s = gx.shape();
+  B200_CALL(::b200_flip(state_->ctx, imode(), CDATA(gy), MDATA(gx), s.lower_volume(dim), s[dim], s.size(), 1, nullptr));
+}
+
+// ---------------------------------------------------------------- elementwise, tensor and scalar tensor
+
+#define B200_IMPL_X_SCALAR(name, op)                                                               \
+  void B200::name##_fw_impl(const Tensor &x, const Tensor &k, Tensor &y) {                         \
+    B200_CALL(::b200_scalar_fw(state_->ctx, imode(), op, CDATA(x), CDATA(k), MDATA(y), y.shape().volume(), \
+                               y.shape().batch(), x.shape().has_batch(), k.shape().has_batch(), nullptr)); \
+  }
+
+B200_IMPL_X_SCALAR(add_scalar, B200_OP_ADD)
+B200_IMPL_X_SCALAR(subtract_scalar_r, B200_OP_SUBTRACT)
+B200_IMPL_X_SCALAR(subtract_scalar_l, B200_OP_SUBTRACT_L)
+B200_IMPL_X_SCALAR(multiply_scalar, B200_OP_MULTIPLY)
+B200_IMPL_X_SCALAR(divide_scalar_r, B200_OP_DIVIDE)
+B200_IMPL_X_SCALAR(divide_scalar_l, B200_OP_DIVIDE_L)
+B200_IMPL_X_SCALAR(pow_scalar_r, B200_OP_POW)
+B200_IMPL_X_SCALAR(pow_scalar_l, B200_OP_POW_L)
+
+// ---------------------------------------------------------------- elementwise, two tensors
+
+#define B200_IMPL_AB(name, op)                                                                     \
+  void B200::name##_fw_impl(const Tensor &a, const Tensor &b, Tensor &y) {                         \
+    B200_CALL(::b200_binary_fw(state_->ctx, imode(), op, CDATA(a), CDATA(b), MDATA(y), y.shape().volume(), \
+                               y.shape().batch(), a.shape().has_batch(), b.shape().has_batch(), nullptr)); \
+  }                                                                                                \
+  void B200::name##_bw_impl(const Tensor &a, const Tensor &b, const Tensor &y, const Tensor &gy,   \
+                            Tensor &ga, Tensor &gb) {                                              \
+    B200_CALL(::b200_binary_bw(state_->ctx, imode(), op, CDATA(a), CDATA(b), CDATA(y), CDATA(gy), MDATA(ga), \
+                               MDATA(gb), gy.shape().volume(), gy.shape().batch(), a.shape().has_batch(), \
+                               b.shape().has_batch(), nullptr));                                   \
+  }
+
+B200_IMPL_AB(add, B200_OP_ADD)
+B200_IMPL_AB(subtract, B200_OP_SUBTRACT)
+B200_IMPL_AB(multiply, B200_OP_MULTIPLY)
+B200_IMPL_AB(divide, B200_OP_DIVIDE)
+B200_IMPL_AB(pow, B200_OP_POW)
+
+// ---------------------------------------------------------------- the hot path
+
+void B200::matmul_fw_impl(const Tensor &a, const Tensor &b, Tensor &y) {
+  B200_CALL(::b200_matmul_fw(state_->ctx, imode(), CDATA(a), CDATA(b), MDATA(y), a.shape()[0], a.shape()[1],
+                             b.shape()[1], a.shape().batch(), b.shape().batch(), nullptr));
+}
+
+void B200::matmul_bw_impl(const Tensor &a, const Tensor &b, const Tensor &, const Tensor &gy, Tensor &ga,
+                          Tensor &gb) {
+  B200_CALL(::b200_matmul_bw(state_->ctx, imode(), CDATA(a), CDATA(b), CDATA(gy), MDATA(ga), MDATA(gb),
+                             a.shape()[0], a.shape()[1], b.shape()[1], a.shape().batch(), b.shape().batch(),
+                             nullptr));
+}
+
+// ---------------------------------------------------------------- reductions and broadcast
+
+#define B200_IMPL_REDUCE(name, red)                                                                \
+  void B200::name##_fw_impl(const Tensor &x, std::uint32_t dim, Tensor &y) {                       \
+    B200_CALL(::b200_reduce_fw(state_->ctx, imode(), red, CDATA(x), MDATA(y), x.shape()[dim],      \
+                               y.shape().lower_volume(dim), y.shape().size(), nullptr));           \
+  }
+
+B200_IMPL_REDUCE(max, B200_RED_MAX)
+B200_IMPL_REDUCE(min, B200_RED_MIN)
+B200_IMPL_REDUCE(sum, B200_RED_SUM)
+B200_IMPL_REDUCE(logsumexp, B200_RED_LOGSUMEXP)
+
+void B200::max_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, std::uint32_t dim, Tensor &gx) {
+  B200_CALL(::b200_minmax_bw(state_->ctx, imode(), CDATA(x), CDATA(y), CDATA(gy), MDATA(gx), x.shape()[dim],
+                             y.shape().lower_volume(dim), y.shape().size(), nullptr));
+}
+void B200::min_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, std::uint32_t dim, Tensor &gx) {
+  B200_CALL(::b200_minmax_bw(state_->ctx, imode(), CDATA(x), CDATA(y), CDATA(gy), MDATA(gx), x.shape()[dim],
+                             y.shape().lower_volume(dim), y.shape().size(), nullptr));
+}
+
+void B200::broadcast_fw_impl(const Tensor &x, std::uint32_t dim, std::uint32_t size, Tensor &y) {
+  B200_CALL(::b200_broadcast_fw(state_->ctx, imode(), CDATA(x), MDATA(y), x.shape().size(),
+                                y.shape().lower_volume(dim), size, nullptr));
+}
+
+// ---------------------------------------------------------------- batch operations
+
+void B200::batch_pick_fw_impl(const Tensor &x, const std::vector<std::uint32_t> &ids, Tensor &y) {
+  B200_CALL(::b200_batch_pick_fw(state_->ctx, imode(), CDATA(x), ids.data(), static_cast<std::uint32_t>(ids.size()),
+                                 MDATA(y), x.shape().volume(), nullptr));
+}
+void B200::batch_pick_bw_impl(const Tensor &gy, const std::vector<std::uint32_t> &ids, Tensor &gx) {
+  B200_CALL(::b200_batch_pick_bw(state_->ctx, imode(), CDATA(gy), ids.data(), static_cast<std::uint32_t>(ids.size()),
+                                 MDATA(gx), gx.shape().volume(), nullptr));
+}
+
+void B200::batch_slice_fw_impl(const Tensor &x, std::uint32_t offset, Tensor &y) {
+  const std::uint64_t volume = y.shape().volume();
+  const char *src = static_cast<const char *>(CDATA(x)) + elem_size() * volume * offset;
+  B200_CALL(::b200_copy(state_->ctx, imode(), src, imode(), MDATA(y), volume * y.shape().batch(), nullptr));
+}
+void B200::batch_slice_bw_impl(const Tensor &gy, std::uint32_t offset, Tensor &gx) {
+  const std::uint64_t volume = gy.shape().volume();
+  char *dest = static_cast<char *>(MDATA(gx)) + elem_size() * volume * offset;
+  B200_CALL(::b200_inplace_add(state_->ctx, imode(), CDATA(gy), dest, volume * gy.shape().batch(), 1, 1, 1.f, nullptr));
+}
+
+void B200::batch_concat_fw_impl(const std::vector<const Tensor *> &xs, Tensor &y) {
+  char *dest = static_cast<char *>(MDATA(y));
+  for (const Tensor *x : xs) {
+    const std::uint64_t span = x->shape().size();
+    B200_CALL(::b200_copy(state_->ctx, imode(), CDATA(*x), imode(), dest, span, nullptr));
+    dest += elem_size() * span;
+  }
+}
+
+void B200::batch_sum_fw_impl(const Tensor &x, Tensor &y) {
+  B200_CALL(::b200_batch_sum_fw(state_->ctx, imode(), CDATA(x), MDATA(y), y.shape().size(), x.shape().batch(), nullptr));
+}
+
+// ---------------------------------------------------------------- not provided
+
+// Convolution and pooling are off the matmul path; like devices::CUDA built without cuDNN
+// (primitiv/devices/cuda/ops/conv2d.cu:77-88) they report NotImplementedError.
+void B200::conv2d_fw_impl(const Tensor &, const Tensor &, std::uint32_t, std::uint32_t, std::uint32_t,
+                          std::uint32_t, std::uint32_t, std::uint32_t, Tensor &) {
+  PRIMITIV_THROW_NOT_IMPLEMENTED;
+}
+void B200::conv2d_bw_impl(const Tensor &, const Tensor &, const Tensor &, const Tensor &, std::uint32_t,
+                          std::uint32_t, std::uint32_t, std::uint32_t, std::uint32_t, std::uint32_t, Tensor &,
+                          Tensor &) {
+  PRIMITIV_THROW_NOT_IMPLEMENTED;
+}
+void B200::max_pool2d_fw_impl(const Tensor &, std::uint32_t, std::uint32_t, std::uint32_t, std::uint32_t,
+                              std::uint32_t, std::uint32_t, Tensor &) {
+  PRIMITIV_THROW_NOT_IMPLEMENTED;
+}
+void B200::max_pool2d_bw_impl(const Tensor &, const Tensor &, const Tensor &, std::uint32_t, std::uint32_t,
+                              std::uint32_t, std::uint32_t, std::uint32_t, std::uint32_t, Tensor &) {
+  PRIMITIV_THROW_NOT_IMPLEMENTED;
+}
+
+// ---------------------------------------------------------------- in place
+
+void B200::inplace_multiply_const_impl(float k, Tensor &x) {
+  B200_CALL(::b200_inplace_multiply_const(state_->ctx, imode(), MDATA(x), x.shape().size(), k, nullptr));
+}
+void B200::inplace_add_impl(const Tensor &x, Tensor &y) {
+  B200_CALL(::b200_inplace_add(state_->ctx, imode(), CDATA(x), MDATA(y), y.shape().volume(), x.shape().batch(),
+                               y.shape().batch(), 1.f, nullptr));
+}
+void B200::inplace_subtract_impl(const Tensor &x, Tensor &y) {
+  B200_CALL(::b200_inplace_add(state_->ctx, imode(), CDATA(x), MDATA(y), y.shape().volume(), x.shape().batch(),
+                               y.shape().batch(), -1.f, nullptr));
+}
+
+}  // namespace devices
+}  // namespace primitiv
