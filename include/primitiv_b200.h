@@ -177,6 +177,11 @@ B200_API int b200_gemm_3xtf32_noalloc(b200_ctx *ctx, int trans_a, int trans_b,
  * kernel whenever the operands are eligible, however small the problem. */
 B200_API int b200_set_path_policy(b200_ctx *ctx, int policy);
 
+/* Tile shape of the tensor-core kernel: 0 (default) = a pair of CTAs per 256-row tile
+ * (tcgen05 cta_group::2) whenever the problem has more than 128 rows and at least 128
+ * columns, 1 = always one CTA per 128-row tile. */
+B200_API int b200_set_pair_policy(b200_ctx *ctx, int policy);
+
 /* Optional per-launch timing.  While enabled, every kernel launch of this context is
  * bracketed by a pair of CUDA events on its stream.  b200_profile_read synchronises the
  * device, sums elapsed milliseconds and launch counts per kernel kind since the last

@@ -40,6 +40,7 @@ SIGNATURES = {
                          _u64, _u64, _u64, _u64, _u64, _int, _int, _vp]),
     "b200_gemm_3xtf32_noalloc": (_int, [_vp, _int, _int, _vp, _vp, _vp, _u32, _u32, _u32, _int, _vp]),
     "b200_set_path_policy": (_int, [_vp, _int]),
+    "b200_set_pair_policy": (_int, [_vp, _int]),
     "b200_profile_enable": (_int, [_vp, _int]),
     "b200_profile_read": (_int, [_vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_u64)]),
     "b200_launch_count": (_int, [_vp, ctypes.POINTER(_u64)]),
@@ -147,6 +148,9 @@ class Context:
 
     def set_path_policy(self, policy):
         _check(lib().b200_set_path_policy(self._h, policy), "set_path_policy")
+
+    def set_pair_policy(self, policy):
+        _check(lib().b200_set_pair_policy(self._h, policy), "set_pair_policy")
 
     def profile_enable(self, on=True):
         _check(lib().b200_profile_enable(self._h, int(on)))

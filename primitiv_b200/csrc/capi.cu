@@ -132,6 +132,12 @@ int b200_set_path_policy(b200_ctx *ctx, int policy) {
   return B200_OK;
 }
 
+int b200_set_pair_policy(b200_ctx *ctx, int policy) {
+  if (!ctx || policy < 0 || policy > 1) return B200_ERR_INVALID_ARG;
+  ctx->pair_policy = policy;
+  return B200_OK;
+}
+
 int b200_profile_enable(b200_ctx *ctx, int on) {
   if (!ctx) return B200_ERR_INVALID_ARG;
   ctx->profiling = on != 0;

@@ -46,12 +46,13 @@
 // chunk per tile, and the two TMEM buffers overlap a tile's epilogue with the next
 // tile's main loop.
 //
-// Every device-side wait is bounded (wall-clock, %globaltimer).  A wait that runs
+// Every device-side wait is bounded (a few seconds, counted in SM clock cycles).  A wait that runs
 // out raises a CTA-wide abort flag, writes B200_ERR_KERNEL_TIMEOUT into the
 // context's status word, drains the CTA's own TMA copies and MMAs with bounded
 // waits, frees TMEM and returns.
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "ctx.h"
@@ -61,10 +62,11 @@ namespace {
 
 constexpr uint32_t kBM = 128;
 constexpr uint32_t kMaxStages = 8;
+constexpr uint32_t kKSteps = 4;  // MMAs per 128-byte k-block: 32 bytes of k each (8 tf32 / 16 fp16)
 constexpr uint32_t kThreads = 320;
 constexpr uint32_t kEpilogueWarps = 8;
 constexpr uint32_t kChunkKBlocks = 8;  // 3xTF32: promote to registers every 8 k-blocks (256 k)
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s at boost clock, 4 s at the lowest
 
 struct alignas(64) TcParams {
   CUtensorMap mapA[2];  // [0] = values (or hi plane), [1] = lo plane
@@ -87,8 +89,9 @@ struct alignas(64) TcParams {
   uint32_t passes;
   uint32_t chunk_kblocks;  // k-blocks per accumulation chunk
   uint32_t accumulate, out_half, kind_f16;
-  uint32_t a_stage_bytes, stage_bytes;
+  uint32_t a_stage_bytes, b_stage_bytes, stage_bytes;  // per plane, per CTA; stage = planes * (a + b)
   uint32_t tmem_cols;
+  uint32_t debug;  // development switches: 1 = no global stores, 2 = no MMA, 4 = no TMA loads
   int *status;
 };
 
@@ -130,16 +133,22 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 
 // Bounded wait.  Returns false if the CTA is aborting or the limit ran out (in
-// which case it raises the abort flag itself).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *s_abort) {
+// which case it raises the abort flag itself).  The limit is counted in SM clock
+// cycles (%clock64 is a few cycles to read; %globaltimer costs hundreds of nanoseconds
+// per read and, on the path every pipeline stage takes, was itself the bottleneck),
+// and the clock is only consulted after a run of failed polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *s_abort,
+                                          uint32_t sleep_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
   uint32_t spins = 0;
+  long long t0 = 0;
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 31u) == 0u) {
+    if (sleep_ns) __nanosleep(sleep_ns);  // leave the issue slots to the warps that are not waiting
+    if (++spins == 256u) t0 = clock64();
+    if (spins > 256u && (spins & 255u) == 0u) {
       if (*s_abort) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (clock64() - t0 > kWaitLimitCycles) {
         *s_abort = 1;
         return false;
       }
@@ -147,11 +156,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// A whole warp waits, but only lane 0 polls the barrier (32 pollers per warp on one
+// shared-memory word slow everyone else's barrier traffic down).
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int *s_abort, uint32_t lane) {
+  uint32_t ok = 1u;
+  if (lane == 0) {
+    // The epilogue waits for a whole chunk of main loop: sleep between polls so that the
+    // MMA issuer, which shares a scheduler with two epilogue warps, keeps its issue slots.
+    ok = mbar_wait(bar, parity, s_abort, 256u) ? 1u : 0u;
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0u;
+}
+
 // Wait used only on the abort path: never raises anything, just gives up.
 __device__ __forceinline__ void mbar_wait_quiet(uint32_t bar, uint32_t parity) {
-  const unsigned long long t0 = globaltimer_ns();
+  const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (globaltimer_ns() - t0 > kWaitLimitNs / 4) return;
+    if (clock64() - t0 > kWaitLimitCycles / 4) return;
   }
 }
 
@@ -164,37 +185,55 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
       : "memory");
 }
 
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo,
-                                                   uint32_t layout) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16;
-  d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
-  d |= static_cast<uint64_t>(1) << 46;  // descriptor version for sm_100
-  d |= static_cast<uint64_t>(layout & 7u) << 61;
-  return d;
+// One tcgen05.mma.  The 64-bit shared-memory descriptors are passed as 32-bit halves and
+// assembled inside the asm block: the high half (stride offset, version, swizzle) never
+// changes during a launch and the low half only advances by a constant per k-step, so the
+// issuing thread spends a handful of instructions per MMA.  (With the descriptors rebuilt
+// from scratch for every MMA the single issuing thread, sharing its scheduler with polling
+// warps, could not feed the tensor core: ~190 ns per MMA whatever the tile width.)
+#define B200_MMA_ASM(GROUP, KIND)                                                      \
+  asm volatile(                                                                        \
+      "{\n\t"                                                                          \
+      ".reg .pred p;\n\t"                                                              \
+      ".reg .b64 da, db;\n\t"                                                          \
+      "setp.ne.b32 p, %6, 0;\n\t"                                                      \
+      "mov.b64 da, {%1, %2};\n\t"                                                      \
+      "mov.b64 db, {%3, %4};\n\t"                                                      \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %5, p;\n\t"       \
+      "}\n" ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) \
+      : "memory")
+
+template <int kCtas, bool kF16>
+__device__ __forceinline__ void mma_issue(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                          uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (kCtas == 2) {
+    if constexpr (kF16) B200_MMA_ASM("2", "f16"); else B200_MMA_ASM("2", "tf32");
+  } else {
+    if constexpr (kF16) B200_MMA_ASM("1", "f16"); else B200_MMA_ASM("1", "tf32");
+  }
 }
 
-__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc,
-                                         uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
-      "}\n" ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc,
-                                        uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "}\n" ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-      : "memory");
+// Runs the k-steps (and, for 3xTF32, the three hi/lo pass combinations) of one pipeline stage.
+template <int kCtas, bool kF16>
+__device__ __forceinline__ void mma_stage(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t a_plane, uint32_t b_plane,
+                                          uint32_t a_hi, uint32_t b_hi, uint32_t a_lo_fixed, uint32_t b_lo_fixed,
+                                          uint32_t kstep_a, uint32_t kstep_b, uint32_t idesc, uint32_t passes,
+                                          bool first) {
+  uint32_t acc = first ? 0u : 1u;
+  for (uint32_t ps = 0; ps < passes; ++ps) {
+    // 3xTF32: (lo, hi), (hi, lo), (hi, hi) -- small terms first
+    const uint32_t ia = (passes == 3u && ps == 0u) ? a_plane : 0u;
+    const uint32_t ib = (passes == 3u && ps == 1u) ? b_plane : 0u;
+    uint32_t a_lo = a_lo_fixed | (((sa + ia) & 0x3FFFFu) >> 4);
+    uint32_t b_lo = b_lo_fixed | (((sb + ib) & 0x3FFFFu) >> 4);
+#pragma unroll
+    for (uint32_t ks = 0; ks < kKSteps; ++ks) {
+      mma_issue<kCtas, kF16>(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, acc);
+      acc = 1u;
+      a_lo += kstep_a;  // in 16-byte units; never carries out of the 14-bit address field within a stage
+      b_lo += kstep_b;
+    }
+  }
 }
 
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
@@ -224,6 +263,53 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- CTA-pair (cta_group::2) forms.  Two CTAs of a cluster share one MMA: the leader
+// (cluster rank 0) issues it for both, each CTA stages its own 128 rows of A and its own
+// half of B's rows, and holds the 128 accumulator rows of its half of M in its own TMEM. ----
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// shared::cluster address of the same shared-memory location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// TMA load whose completion is signalled on a barrier that may live in the peer CTA.
+// The data itself lands only in the issuing CTA's shared memory: every CTA fetches its own tiles.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster_addr,
+                                                 int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<unsigned long long>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1),
+        "r"(c2)
+      : "memory");
+}
+
+// arrives (once) on the barrier at this shared-memory offset in BOTH CTAs of the pair when
+// the MMAs issued so far have retired
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(static_cast<uint16_t>(3))
+      : "memory");
+}
+
 // Writes 32 consecutive output columns of one row (this lane's) to column-major C.
 template <typename T>
 __device__ __forceinline__ void store_cols(T *C, unsigned long long base, uint32_t m, uint32_t n,
@@ -245,7 +331,13 @@ __device__ __forceinline__ void store_cols(T *C, unsigned long long base, uint32
   }
 }
 
-template <bool kChunked>
+// kCtas == 1: one CTA per 128 x bn tile.  kCtas == 2: a cluster of two CTAs per 256 x bn
+// tile (tcgen05 cta_group::2): CTA r of the pair stages rows [128 r, 128 r + 128) of A and
+// rows [bn/2 r, bn/2 r + bn/2) of B, the leader (r = 0) issues every MMA for both, and each
+// CTA's TMEM receives the 128 accumulator rows of its half of M for all bn columns.  Per
+// CTA that is a third less shared-memory fill and operand traffic per FLOP than the
+// single-CTA tile, which is what bounds this kernel.
+template <bool kChunked, int kCtas>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
@@ -260,6 +352,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   volatile int *abort_flag = &s_abort;
+  const uint32_t cta_rank = kCtas == 2 ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0u;
+  const uint32_t first_tile = blockIdx.x / kCtas;   // tiles are dealt to CTAs (kCtas == 1) or to pairs
+  const uint32_t tile_step = gridDim.x / kCtas;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -269,20 +365,29 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     }
     for (uint32_t b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&tmem_full_bar[b]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[b]), kEpilogueWarps);
+      mbar_init(smem_u32(&tmem_empty_bar[b]), kEpilogueWarps * kCtas);  // only the leader's copy is waited on
     }
     mbar_init(smem_u32(&drain_bar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(&tmem_slot)),
-                 "r"(p.tmem_cols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (kCtas == 2) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(&tmem_slot)),
+                   "r"(p.tmem_cols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(&tmem_slot)),
+                   "r"(p.tmem_cols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (kCtas == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
 
@@ -290,6 +395,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
   const uint32_t total_tiles = tiles_per_group * p.groups;
   const uint32_t kb_per_tile = p.red * p.kblocks;  // k-blocks of one tile, over both contraction axes
   const uint32_t chunks_per_tile = (kb_per_tile + p.chunk_kblocks - 1) / p.chunk_kblocks;
+  const uint32_t planes = p.passes == 3u ? 2u : 1u;  // hi and lo planes share a stage
+  const uint32_t b_rows = p.bn / kCtas;               // rows of B this CTA stages
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -297,53 +404,68 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       uint32_t stage = 0, phase = 0;
       uint32_t armed_mask = 0, armed_parity = 0;
       bool ok = true;
-      for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         const uint32_t g = tile / tiles_per_group;
         const uint32_t rem = tile - g * tiles_per_group;
-        const int m0 = static_cast<int>((rem % p.tiles_m) * kBM);
-        const int n0 = static_cast<int>((rem / p.tiles_m) * p.bn);
+        const int m0 = static_cast<int>((rem % p.tiles_m) * (kBM * kCtas) + cta_rank * kBM);
+        const int n0 = static_cast<int>((rem / p.tiles_m) * p.bn + cta_rank * b_rows);
         for (uint32_t r = 0; ok && r < p.red; ++r) {
           const int za = static_cast<int>(g * p.a_gmul + r * p.a_rmul);
           const int zb = static_cast<int>(g * p.b_gmul + r * p.b_rmul);
-          for (uint32_t kb = 0; ok && kb < p.kblocks; ++kb) {
+          for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
             const int k0 = static_cast<int>(kb * p.bk);
-            for (uint32_t ps = 0; ps < p.passes; ++ps) {
-              if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
-                ok = false;
-                break;
-              }
-              const uint32_t ia = (p.passes == 3u && ps == 0u) ? 1u : 0u;
-              const uint32_t ib = (p.passes == 3u && ps == 1u) ? 1u : 0u;
-              const uint32_t bar = smem_u32(&full_bar[stage]);
-              const uint32_t sa = smem_base + stage * p.stage_bytes;
-              const uint32_t sb = sa + p.a_stage_bytes;
-              mbar_arrive_expect_tx(bar, p.stage_bytes);
+            if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, 32u)) {
+              ok = false;
+              break;
+            }
+            const uint32_t own_bar = smem_u32(&full_bar[stage]);
+            // both CTAs of a pair report their bytes to the leader's barrier
+            const uint32_t bar = kCtas == 2 ? map_to_cta(own_bar, 0u) : own_bar;
+            if (p.debug & 4u) {
+              if (leader) mbar_arrive(own_bar);
+              if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+              continue;
+            }
+            if (leader) {
+              mbar_arrive_expect_tx(own_bar, p.stage_bytes * kCtas);
               armed_mask |= 1u << stage;
               armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+            }
+            const uint32_t sa = smem_base + stage * p.stage_bytes;
+            const uint32_t sb = sa + planes * p.a_stage_bytes;
+            for (uint32_t pl = 0; pl < planes; ++pl) {
+              const uint32_t da = sa + pl * p.a_stage_bytes, db = sb + pl * p.b_stage_bytes;
               if (p.a_mn_major) {
-                for (uint32_t c = 0; c < p.a_chunks; ++c)
-                  tma_load_3d(sa + c * p.a_chunk_bytes, &p.mapA[ia], bar,
-                              m0 + static_cast<int>(c * p.a_chunk_elems), k0, za);
+                for (uint32_t c = 0; c < p.a_chunks; ++c) {
+                  const int mc = m0 + static_cast<int>(c * p.a_chunk_elems);
+                  if constexpr (kCtas == 2) tma_load_3d_pair(da + c * p.a_chunk_bytes, &p.mapA[pl], bar, mc, k0, za);
+                  else tma_load_3d(da + c * p.a_chunk_bytes, &p.mapA[pl], bar, mc, k0, za);
+                }
               } else {
-                tma_load_3d(sa, &p.mapA[ia], bar, k0, m0, za);
+                if constexpr (kCtas == 2) tma_load_3d_pair(da, &p.mapA[pl], bar, k0, m0, za);
+                else tma_load_3d(da, &p.mapA[pl], bar, k0, m0, za);
               }
               if (p.b_mn_major) {
-                for (uint32_t c = 0; c < p.b_chunks; ++c)
-                  tma_load_3d(sb + c * p.b_chunk_bytes, &p.mapB[ib], bar,
-                              n0 + static_cast<int>(c * p.b_chunk_elems), k0, zb);
+                for (uint32_t c = 0; c < p.b_chunks; ++c) {
+                  const int nc = n0 + static_cast<int>(c * p.b_chunk_elems);
+                  if constexpr (kCtas == 2) tma_load_3d_pair(db + c * p.b_chunk_bytes, &p.mapB[pl], bar, nc, k0, zb);
+                  else tma_load_3d(db + c * p.b_chunk_bytes, &p.mapB[pl], bar, nc, k0, zb);
+                }
               } else {
-                tma_load_3d(sb, &p.mapB[ib], bar, k0, n0, zb);
+                if constexpr (kCtas == 2) tma_load_3d_pair(db, &p.mapB[pl], bar, k0, n0, zb);
+                else tma_load_3d(db, &p.mapB[pl], bar, k0, n0, zb);
               }
-              if (++stage == p.stages) {
-                stage = 0;
-                phase ^= 1u;
-              }
+            }
+            if (++stage == p.stages) {
+              stage = 0;
+              phase ^= 1u;
             }
           }
         }
       }
-      if (*abort_flag) {
-        // let this CTA's own copies land before its shared memory is given up
+      if (*abort_flag && leader) {
+        // let the copies in flight (this CTA's and, for a pair, the peer's, which report to
+        // the same barriers) land before shared memory is given up
         for (uint32_t s = 0; s < p.stages; ++s)
           if (armed_mask & (1u << s))
             mbar_wait_quiet(smem_u32(&full_bar[s]), (armed_parity >> s) & 1u);
@@ -352,11 +474,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       uint32_t stage = 0, phase = 0;
       uint32_t chunk_no = 0;  // chunks this CTA has started, over all its tiles
       bool ok = true;
-      for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      // descriptor halves that do not change during the launch
+      const uint32_t a_hi = ((p.sbo_a >> 4) & 0x3FFFu) | (1u << 14) | ((p.layout_a & 7u) << 29);
+      const uint32_t b_hi = ((p.sbo_b >> 4) & 0x3FFFu) | (1u << 14) | ((p.layout_b & 7u) << 29);
+      const uint32_t a_lo_fixed = ((p.lbo_a >> 4) & 0x3FFFu) << 16;
+      const uint32_t b_lo_fixed = ((p.lbo_b >> 4) & 0x3FFFu) << 16;
+      const uint32_t kstep_a = p.kstep_a_bytes >> 4, kstep_b = p.kstep_b_bytes >> 4;
+      for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         uint32_t kb_left = kb_per_tile;
         for (uint32_t c = 0; ok && c < chunks_per_tile; ++c, ++chunk_no) {
           const uint32_t buf = chunk_no & 1u;
@@ -369,36 +497,40 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
           const uint32_t d_tmem = tmem_base + buf * p.bn;
           const uint32_t kbs = kb_left < p.chunk_kblocks ? kb_left : p.chunk_kblocks;
           kb_left -= kbs;
-          const uint32_t iters = kbs * p.passes;
-          for (uint32_t it = 0; it < iters; ++it) {
-            if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag)) {
+          for (uint32_t it = 0; it < kbs; ++it) {
+            if (!(p.debug & 8u) && !mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag)) {
               ok = false;
               break;
             }
             tc_fence_after();
             const uint32_t sa = smem_base + stage * p.stage_bytes;
-            const uint32_t sb = sa + p.a_stage_bytes;
-            for (uint32_t ks = 0; ks < p.ksteps; ++ks) {
-              const uint64_t da = make_smem_desc(sa + ks * p.kstep_a_bytes, p.lbo_a, p.sbo_a, p.layout_a);
-              const uint64_t db = make_smem_desc(sb + ks * p.kstep_b_bytes, p.lbo_b, p.sbo_b, p.layout_b);
-              const uint32_t acc = (it | ks) != 0u ? 1u : 0u;
+            const uint32_t sb = sa + planes * p.a_stage_bytes;
+            if (!(p.debug & 2u)) {
               if (p.kind_f16)
-                mma_f16(d_tmem, da, db, p.idesc, acc);
+                mma_stage<kCtas, true>(d_tmem, sa, sb, p.a_stage_bytes, p.b_stage_bytes, a_hi, b_hi, a_lo_fixed,
+                                       b_lo_fixed, kstep_a, kstep_b, p.idesc, p.passes, it == 0u);
               else
-                mma_tf32(d_tmem, da, db, p.idesc, acc);
+                mma_stage<kCtas, false>(d_tmem, sa, sb, p.a_stage_bytes, p.b_stage_bytes, a_hi, b_hi, a_lo_fixed,
+                                        b_lo_fixed, kstep_a, kstep_b, p.idesc, p.passes, it == 0u);
             }
-            mma_commit(smem_u32(&empty_bar[stage]));  // frees the stage when these MMAs retire
+            // frees the stage (in both CTAs of a pair) when these MMAs retire
+            if constexpr (kCtas == 2) mma_commit_pair(smem_u32(&empty_bar[stage]));
+            else mma_commit(smem_u32(&empty_bar[stage]));
             if (++stage == p.stages) {
               stage = 0;
               phase ^= 1u;
             }
           }
-          if (ok) mma_commit(smem_u32(&tmem_full_bar[buf]));
+          if (ok) {
+            if constexpr (kCtas == 2) mma_commit_pair(smem_u32(&tmem_full_bar[buf]));
+            else mma_commit(smem_u32(&tmem_full_bar[buf]));
+          }
         }
       }
       if (*abort_flag) {
         // retire whatever was issued before TMEM is freed
-        mma_commit(smem_u32(&drain_bar));
+        if constexpr (kCtas == 2) mma_commit_pair(smem_u32(&drain_bar));
+        else mma_commit(smem_u32(&drain_bar));
         mbar_wait_quiet(smem_u32(&drain_bar), 0);
       }
     }
@@ -409,24 +541,27 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     const uint32_t half = (warp - 2u) >> 2;     // which half of the tile's columns
     const uint32_t cols_per = p.bn >> 1;        // 32, 64 or 128 columns per thread
     const uint32_t col_base = half * cols_per;
-    const uint32_t row_in_tile = quarter * 32u + lane;
+    const uint32_t row_in_tile = cta_rank * kBM + quarter * 32u + lane;
     const uint32_t lane_addr = (quarter * 32u) << 16;
     uint32_t chunk_no = 0;
     bool ok = true;
-    for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+    // the accumulator buffers are handed back to the leader's MMA thread
+    const uint32_t empty0 = kCtas == 2 ? map_to_cta(smem_u32(&tmem_empty_bar[0]), 0u) : smem_u32(&tmem_empty_bar[0]);
+    const uint32_t empty1 = kCtas == 2 ? map_to_cta(smem_u32(&tmem_empty_bar[1]), 0u) : smem_u32(&tmem_empty_bar[1]);
+    for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
       const uint32_t g = tile / tiles_per_group;
       const uint32_t rem = tile - g * tiles_per_group;
-      const uint32_t m0 = (rem % p.tiles_m) * kBM;
+      const uint32_t m0 = (rem % p.tiles_m) * (kBM * kCtas);
       const uint32_t n0 = (rem / p.tiles_m) * p.bn;
       const uint32_t row = m0 + row_in_tile;
-      const bool row_ok = row < p.m;
+      const bool row_ok = row < p.m && !(p.debug & 1u);
       const unsigned long long base =
           static_cast<unsigned long long>(g) * p.c_gs + static_cast<unsigned long long>(row);
       if constexpr (kChunked) {
         float acc[4][32];
         for (uint32_t c = 0; ok && c < chunks_per_tile; ++c, ++chunk_no) {
           const uint32_t buf = chunk_no & 1u;
-          if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), (chunk_no >> 1) & 1u, abort_flag)) {
+          if (!warp_wait(smem_u32(&tmem_full_bar[buf]), (chunk_no >> 1) & 1u, abort_flag, lane)) {
             ok = false;
             break;
           }
@@ -447,7 +582,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
           }
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+          if (lane == 0) {
+            if constexpr (kCtas == 2) mbar_arrive_cluster(buf ? empty1 : empty0);
+            else mbar_arrive(buf ? empty1 : empty0);
+          }
         }
         if (ok && row_ok) {
 #pragma unroll
@@ -463,7 +601,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         }
       } else {
         const uint32_t buf = chunk_no & 1u;
-        if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), (chunk_no >> 1) & 1u, abort_flag)) {
+        if (!warp_wait(smem_u32(&tmem_full_bar[buf]), (chunk_no >> 1) & 1u, abort_flag, lane)) {
           ok = false;
           break;
         }
@@ -486,19 +624,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+        if (lane == 0) {
+          if constexpr (kCtas == 2) mbar_arrive_cluster(buf ? empty1 : empty0);
+          else mbar_arrive(buf ? empty1 : empty0);
+        }
       }
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  // neither CTA of a pair may leave (or free TMEM) while the other can still signal its
+  // barriers or read accumulators the shared MMA wrote
+  if constexpr (kCtas == 2) cluster_sync_all();
   if (threadIdx.x == 0 && s_abort) atomicCAS(p.status, 0, B200_ERR_KERNEL_TIMEOUT);
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(p.tmem_cols)
-                 : "memory");
+    if constexpr (kCtas == 2)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols)
+                   : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols)
+                   : "memory");
   }
 }
 
@@ -659,7 +806,11 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   p.kblocks = (g.k + p.bk - 1) / p.bk;
   p.red = g.red;
   p.groups = g.groups;
-  p.tiles_m = (g.m + kBM - 1) / kBM;
+  // A pair of CTAs per 256-row tile when the problem has the rows and columns for it
+  // (each CTA then stages bn/2 >= 64 rows of B) and the context allows it.
+  const uint32_t ctas = (ctx->pair_policy != 1 && g.m > kBM && p.bn >= 128u && ctx->sm_count >= 2) ? 2u : 1u;
+  const uint32_t tile_m = kBM * ctas;
+  p.tiles_m = (g.m + tile_m - 1) / tile_m;
   p.tiles_n = (g.n + p.bn - 1) / p.bn;
   const uint64_t total_tiles = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * g.groups;
   if (total_tiles > 0x7fffffffull) return B200_ERR_TOO_LARGE;
@@ -729,8 +880,11 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   p.a_mn_major = va.mn_major ? 1u : 0u;
   p.b_mn_major = vb.mn_major ? 1u : 0u;
   p.ksteps = p.bk / umma_k;
+  const uint32_t planes = passes == 3 ? 2u : 1u;
+  const uint32_t b_rows = p.bn / ctas;  // rows of B each CTA stages
   p.a_stage_bytes = kBM * 128u;
-  p.stage_bytes = (kBM + p.bn) * 128u;
+  p.b_stage_bytes = b_rows * 128u;
+  p.stage_bytes = planes * (p.a_stage_bytes + p.b_stage_bytes);
   p.layout_a = p.layout_b = 2u;  // 128-byte swizzle
   CUtensorMapSwizzle swz_a = CU_TENSOR_MAP_SWIZZLE_128B, swz_b = CU_TENSOR_MAP_SWIZZLE_128B;
   if (p.a_mn_major) {
@@ -752,7 +906,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     p.kstep_a_bytes = umma_k * eb;
   }
   if (p.b_mn_major) {
-    p.b_chunks = p.bn / chunk;
+    p.b_chunks = b_rows / chunk;
     p.b_chunk_elems = chunk;
     p.b_chunk_bytes = p.bk * 128u;
     p.lbo_b = p.b_chunk_bytes;
@@ -771,7 +925,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   }
   const uint32_t fmt = f16 ? 0u : 2u;  // F16 = 0 (kind::f16), TF32 = 2 (kind::tf32)
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (p.a_mn_major << 15) | (p.b_mn_major << 16) |
-            ((p.bn >> 3) << 17) | ((kBM >> 4) << 24);
+            ((p.bn >> 3) << 17) | ((tile_m >> 4) << 24);
   p.passes = passes;
   const bool chunked = passes == 3 && static_cast<uint64_t>(g.red) * p.kblocks > kChunkKBlocks;
   p.chunk_kblocks = chunked ? kChunkKBlocks : g.red * p.kblocks;
@@ -782,10 +936,17 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   p.c_gs = g.c_gs;
   p.status = ctx->d_status;
   p.tmem_cols = p.bn * 2u;  // 128, 256 or 512: powers of two
+  {
+    static const char *dbg = std::getenv("PRIMITIV_B200_TC_DEBUG");
+    p.debug = dbg ? static_cast<uint32_t>(std::atoi(dbg)) : 0u;
+    static const char *st = std::getenv("PRIMITIV_B200_TC_STAGES");
+    if (st) ctx->debug_stage_cap = std::atoi(st);
+  }
 
   const size_t budget = ctx->smem_optin > 8192 ? ctx->smem_optin - 4096 : 0;
   uint32_t stages = budget > 1024 ? static_cast<uint32_t>((budget - 1024) / p.stage_bytes) : 0;
   if (stages > kMaxStages) stages = kMaxStages;
+  if (ctx->debug_stage_cap > 0 && stages > (uint32_t)ctx->debug_stage_cap) stages = ctx->debug_stage_cap;
   int rc = stages >= 2 ? B200_OK : B200_ERR_INVALID_ARG;
   p.stages = stages;
   const size_t smem_bytes = static_cast<size_t>(stages) * p.stage_bytes + 1024;
@@ -793,26 +954,49 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   for (int i = 0; i < (passes == 3 ? 2 : 1) && rc == B200_OK; ++i) {
     rc = encode_map(ctx, &p.mapA[i], a_src[i], va, eb, p.a_mn_major ? chunk : kBM, p.bk, swz_a);
     if (rc == B200_OK)
-      rc = encode_map(ctx, &p.mapB[i], b_src[i], vb, eb, p.b_mn_major ? chunk : p.bn, p.bk, swz_b);
+      rc = encode_map(ctx, &p.mapB[i], b_src[i], vb, eb, p.b_mn_major ? chunk : b_rows, p.bk, swz_b);
   }
   if (rc == B200_OK && !ctx->tc_smem_configured) {
     const int max_dyn = static_cast<int>(ctx->smem_optin - 2048);
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
+      e = cudaFuncSetAttribute(gemm_tc_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_tc_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_tc_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
     if (e != cudaSuccess) rc = static_cast<int>(e);
     ctx->tc_smem_configured = (e == cudaSuccess);
   }
   if (rc == B200_OK) {
-    const unsigned grid =
-        static_cast<unsigned>(total_tiles < (uint64_t)ctx->sm_count ? total_tiles : ctx->sm_count);
+    // persistent: one CTA (or one pair) per tile up to one CTA per SM
+    const uint64_t units = static_cast<uint64_t>(ctx->sm_count) / ctas;
+    const unsigned grid = static_cast<unsigned>((total_tiles < units ? total_tiles : units) * ctas);
     ProfScope prof(ctx, kProfGemmTc, stream);
-    if (chunked)
-      gemm_tc_kernel<true><<<grid, kThreads, smem_bytes, stream>>>(p);
-    else
-      gemm_tc_kernel<false><<<grid, kThreads, smem_bytes, stream>>>(p);
+    if (ctas == 2) {
+      cudaLaunchConfig_t cfg;
+      memset(&cfg, 0, sizeof(cfg));
+      cfg.gridDim = dim3(grid);
+      cfg.blockDim = dim3(kThreads);
+      cfg.dynamicSmemBytes = smem_bytes;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      const cudaError_t e = chunked ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, 2>, p)
+                                    : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2>, p);
+      rc = static_cast<int>(e);
+    } else if (chunked) {
+      gemm_tc_kernel<true, 1><<<grid, kThreads, smem_bytes, stream>>>(p);
+    } else {
+      gemm_tc_kernel<false, 1><<<grid, kThreads, smem_bytes, stream>>>(p);
+    }
     ++ctx->launches;
-    rc = static_cast<int>(cudaGetLastError());
+    if (rc == B200_OK) rc = static_cast<int>(cudaGetLastError());
   }
   if (scratch) ctx->pool.free(scratch);  // stream-ordered reuse: later work queues behind this GEMM
   return rc;
