@@ -68,6 +68,8 @@ class ClockSampler(threading.Thread):
         self.index, self.samples, self.stop_flag = index, [], False
 
     def run(self):
+        if self._run_nvml():
+            return
         while not self.stop_flag:
             try:
                 out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
@@ -78,6 +80,29 @@ class ClockSampler(threading.Thread):
             except Exception:
                 pass
             time.sleep(0.05)
+
+    def _run_nvml(self):
+        """Reads the same counters through NVML (read-only calls), every 20 ms."""
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            bits = [(pynvml.nvmlClocksEventReasonHwSlowdown, 2), (pynvml.nvmlClocksEventReasonHwThermalSlowdown, 3),
+                    (pynvml.nvmlClocksEventReasonSwThermalSlowdown, 4), (pynvml.nvmlClocksEventReasonSwPowerCap, 5)]
+        except Exception:
+            return False
+        while not self.stop_flag:
+            try:
+                row = [str(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)), str(mx), "", "", "", ""]
+                r = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                for bit, col in bits:
+                    row[col] = "Active" if (r & bit) else "Not Active"
+                self.samples.append(row)
+            except Exception:
+                pass
+            time.sleep(0.02)
+        return True
 
     def summary(self):
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -263,17 +288,24 @@ def emit(args, world, ms, prof, launches, sampler, e2e):
     tc_avg_ms = tc_ms / max(tc_n, 1)
     achieved = issued_flops_per_launch / (tc_avg_ms * 1e-3) / 1e12 if tc_n else 0.0
     tf32_peak = peaks["bf16_sustained"] / 2.0
+    tf32_burst = peaks["bf16_burst"] / 2.0
+    # DRAM bytes of one gemm_tc_kernel launch: ncu capture of the batch-2 case (1.64 GB, see profiles/),
+    # scaled by the batch (independent products, traffic grows in proportion)
+    traffic = 1.64e9 * BATCH / 2.0
     line = {
         "metric": METRIC, "value": value, "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "tf32x3 (fp32 storage, fp32 accumulate)", "data": "synthetic",
         "config": workload_config(world),
         "roofline": {
-            "bound": "tensor", "kernel": "gemm_tc_kernel<chunked>", "achieved": achieved, "peak": tf32_peak,
-            "unit": "TFLOP/s", "frac": achieved / tf32_peak, "traffic": None,
+            "bound": "tensor", "kernel": "gemm_tc_kernel<chunked, cta pair>", "achieved": achieved,
+            "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak, "traffic": traffic,
+            "frac_of_burst_peak": achieved / tf32_burst,
             "note": ("achieved = tensor-issued FLOP/s (3 TF32 passes x algorithmic 2mnk) / mean CUDA-event "
-                     "duration of %d launches; peak = %s bf16 sustained / 2 (TF32 runs at half the 16-bit rate)"
-                     % (tc_n, peaks["source"])),
+                     "duration of %d launches; peak = %s bf16 sustained / 2 (TF32 runs at half the 16-bit rate; "
+                     "the timed region is a fraction of a second, so the burst figure / 2 = %.0f is given beside it); "
+                     "traffic = ncu dram bytes of the batch-2 capture scaled to this batch"
+                     % (tc_n, peaks["source"], tf32_burst)),
             "algorithmic_tflops_in_kernel": achieved / 3.0,
             "kernel_ms_per_step": tc_ms / args.steps, "pack_ms_per_step": prof["pack"][0] / args.steps,
         },

@@ -311,21 +311,31 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
 }
 
 // Writes 32 consecutive output columns of one row (this lane's) to column-major C.
+// For += all 32 old values are fetched before the first store: written as one
+// load-add-store per column the stores would order the loads behind them (the compiler
+// must assume they alias) and the epilogue would pay one memory latency per column.
 template <typename T>
 __device__ __forceinline__ void store_cols(T *C, unsigned long long base, uint32_t m, uint32_t n,
                                            uint32_t col0, const float (&x)[32], bool accumulate) {
+  T *q = C + base + static_cast<unsigned long long>(col0) * m;
+  const uint32_t left = n - col0;  // caller guarantees col0 < n
 #pragma unroll
-  for (uint32_t j = 0; j < 32u; ++j) {
-    const uint32_t col = col0 + j;
-    if (col < n) {
-      T *q = C + base + static_cast<unsigned long long>(col) * m;
-      float v = x[j];
-      if constexpr (sizeof(T) == 2) {
-        if (accumulate) v += __half2float(*q);
-        *q = __float2half_rn(v);
-      } else {
-        if (accumulate) v += *q;
-        *q = v;
+  for (uint32_t h = 0; h < 32u; h += 8u) {  // 8 loads in flight per thread, then 8 stores
+    float old[8];
+#pragma unroll
+    for (uint32_t j = 0; j < 8u; ++j) {
+      old[j] = 0.f;
+      if (accumulate && h + j < left) {
+        if constexpr (sizeof(T) == 2) old[j] = __half2float(q[static_cast<unsigned long long>(h + j) * m]);
+        else old[j] = q[static_cast<unsigned long long>(h + j) * m];
+      }
+    }
+#pragma unroll
+    for (uint32_t j = 0; j < 8u; ++j) {
+      if (h + j < left) {
+        const float v = x[h + j] + old[j];
+        if constexpr (sizeof(T) == 2) q[static_cast<unsigned long long>(h + j) * m] = __float2half_rn(v);
+        else q[static_cast<unsigned long long>(h + j) * m] = v;
       }
     }
   }
@@ -717,6 +727,74 @@ __global__ void __launch_bounds__(256) pack_tf32_kernel(
   }
 }
 
+// Fast paths of the packing pre-pass (both move 128 bits per thread per access).
+//
+// pack_flat_kernel: a K-major source whose rows need no padding (k % 4 == 0) and whose
+// matrices are back to back is one flat array; the planes have the same layout, so the
+// split is purely elementwise.
+__global__ void __launch_bounds__(256) pack_flat_kernel(const float4 *__restrict__ src, float4 *__restrict__ hi,
+                                                        float4 *__restrict__ lo, unsigned long long n4) {
+  const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
+  for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+       i += stride) {
+    const float4 v = src[i];
+    float4 h, l;
+    h.x = rn_tf32(v.x); l.x = rn_tf32(v.x - h.x);
+    h.y = rn_tf32(v.y); l.y = rn_tf32(v.y - h.y);
+    h.z = rn_tf32(v.z); l.z = rn_tf32(v.z - h.z);
+    h.w = rn_tf32(v.w); l.w = rn_tf32(v.w - h.w);
+    hi[i] = h;
+    if (lo) lo[i] = l;
+  }
+}
+
+// pack_transpose64_kernel: an MN-major source with mn % 4 == 0 and k % 4 == 0.  64 x 64
+// tiles through shared memory: float4 reads along mn, float4 writes along k.
+__global__ void __launch_bounds__(256) pack_transpose64_kernel(const float *__restrict__ src, float *__restrict__ hi,
+                                                               float *__restrict__ lo, uint32_t mn, uint32_t k,
+                                                               unsigned long long src_bs, uint32_t tiles_mn,
+                                                               uint32_t tiles_k, unsigned long long total_tiles) {
+  __shared__ float tile[64][65];  // [k][mn]
+  const uint32_t t = threadIdx.x;
+  for (unsigned long long tl = blockIdx.x; tl < total_tiles; tl += gridDim.x) {
+    const unsigned long long per_b = static_cast<unsigned long long>(tiles_mn) * tiles_k;
+    const unsigned long long b = tl / per_b;
+    const uint32_t rem = static_cast<uint32_t>(tl - b * per_b);
+    const uint32_t i0 = (rem % tiles_mn) * 64u, p0 = (rem / tiles_mn) * 64u;
+    const float *s = src + b * src_bs;
+    const unsigned long long dst_b = b * static_cast<unsigned long long>(mn) * k;
+    // 64 k-rows x 16 float4 along mn = 1024 float4, 4 per thread
+#pragma unroll
+    for (uint32_t r = 0; r < 4u; ++r) {
+      const uint32_t e = t + r * 256u;
+      const uint32_t pk = e >> 4, im = (e & 15u) * 4u;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p0 + pk < k && i0 + im < mn)
+        v = *reinterpret_cast<const float4 *>(s + static_cast<unsigned long long>(p0 + pk) * mn + i0 + im);
+      tile[pk][im] = v.x; tile[pk][im + 1] = v.y; tile[pk][im + 2] = v.z; tile[pk][im + 3] = v.w;
+    }
+    __syncthreads();
+    // 64 mn-rows x 16 float4 along k
+#pragma unroll
+    for (uint32_t r = 0; r < 4u; ++r) {
+      const uint32_t e = t + r * 256u;
+      const uint32_t im = e >> 4, pk = (e & 15u) * 4u;
+      if (i0 + im < mn && p0 + pk < k) {
+        const float x0 = tile[pk][im], x1 = tile[pk + 1][im], x2 = tile[pk + 2][im], x3 = tile[pk + 3][im];
+        float4 h, l;
+        h.x = rn_tf32(x0); l.x = rn_tf32(x0 - h.x);
+        h.y = rn_tf32(x1); l.y = rn_tf32(x1 - h.y);
+        h.z = rn_tf32(x2); l.z = rn_tf32(x2 - h.z);
+        h.w = rn_tf32(x3); l.w = rn_tf32(x3 - h.w);
+        const unsigned long long o = dst_b + static_cast<unsigned long long>(i0 + im) * k + p0 + pk;
+        *reinterpret_cast<float4 *>(hi + o) = h;
+        if (lo) *reinterpret_cast<float4 *>(lo + o) = l;
+      }
+    }
+    __syncthreads();
+  }
+}
+
 struct OperandView {
   const void *ptr;
   uint32_t mn, k;         // extents
@@ -856,17 +934,34 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
       float *hi = cursor;
       float *lo = passes == 3 ? cursor + plane_elems[o] : nullptr;
       cursor += planes * plane_elems[o];
-      const uint32_t tiles_mn = (v.mn + 31u) / 32u, tiles_k = (v.k + 31u) / 32u;
-      const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
-      const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
-      const unsigned blocks = static_cast<unsigned>(tt < cap ? tt : cap);
+      const bool src_ok = (reinterpret_cast<uintptr_t>(v.ptr) & 15u) == 0 && v.k % 4u == 0 &&
+                          (v.nbatch <= 1 || v.batch_stride % 4u == 0);
+      const bool dense = v.nbatch <= 1 || v.batch_stride == static_cast<uint64_t>(v.mn) * v.k;
       ProfScope prof(ctx, kProfPack, stream);
-      if (v.mn_major)
-        pack_tf32_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const float *>(v.ptr), hi, lo, v.mn, v.k,
-                                                          kpad[o], v.batch_stride, tiles_mn, tiles_k, tt);
-      else
-        pack_tf32_kernel<false><<<blocks, 256, 0, stream>>>(static_cast<const float *>(v.ptr), hi, lo, v.mn, v.k,
-                                                           kpad[o], v.batch_stride, tiles_mn, tiles_k, tt);
+      if (!v.mn_major && src_ok && dense) {
+        const unsigned long long n4 = static_cast<unsigned long long>(v.nbatch) * v.mn * v.k / 4ull;
+        const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
+        const unsigned long long need = (n4 + 255ull) / 256ull;
+        pack_flat_kernel<<<static_cast<unsigned>(need < cap ? need : cap), 256, 0, stream>>>(
+            static_cast<const float4 *>(v.ptr), reinterpret_cast<float4 *>(hi), reinterpret_cast<float4 *>(lo), n4);
+      } else if (v.mn_major && src_ok && v.mn % 4u == 0) {
+        const uint32_t tiles_mn = (v.mn + 63u) / 64u, tiles_k = (v.k + 63u) / 64u;
+        const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
+        const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 8ull;
+        pack_transpose64_kernel<<<static_cast<unsigned>(tt < cap ? tt : cap), 256, 0, stream>>>(
+            static_cast<const float *>(v.ptr), hi, lo, v.mn, v.k, v.batch_stride, tiles_mn, tiles_k, tt);
+      } else {
+        const uint32_t tiles_mn = (v.mn + 31u) / 32u, tiles_k = (v.k + 31u) / 32u;
+        const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
+        const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
+        const unsigned blocks = static_cast<unsigned>(tt < cap ? tt : cap);
+        if (v.mn_major)
+          pack_tf32_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const float *>(v.ptr), hi, lo, v.mn, v.k,
+                                                            kpad[o], v.batch_stride, tiles_mn, tiles_k, tt);
+        else
+          pack_tf32_kernel<false><<<blocks, 256, 0, stream>>>(static_cast<const float *>(v.ptr), hi, lo, v.mn, v.k,
+                                                             kpad[o], v.batch_stride, tiles_mn, tiles_k, tt);
+      }
       ++ctx->launches;
       srcs[o][0] = hi;
       srcs[o][1] = lo;
