@@ -4,24 +4,26 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload (one "step" = one forward plus both backward products over the batch):
+Default workload (one "step" = one forward plus both backward products over the batch):
 non-broadcast batched square GEMM, fp32 in 3xTF32 mode: A and B each
-Shape({4096,4096}, batch 8) ~ N(0, 0.02), upstream gradient N(0,1), seeded
-synthetic data.  With N GPUs every rank holds a full batch-8 shard of its own
-(weak scaling; the products of different batch elements are independent, so the
-data path has no collective).
+Shape({4096,4096}, batch 8) ~ N(0, 0.02), upstream gradient N(0,1), seeded synthetic
+data.  With N GPUs every rank holds a full batch-8 shard of its own (weak scaling; the
+products of different batch elements are independent, so the data path has no collective).
 
-Prints ONE JSON line on rank 0.  `value` is algorithmic GFLOP/s (2*m*n*k per product,
-three products per batch element) over all ranks with operands resident in HBM;
-`e2e` is the same metric through the host-buffer entry points of the C ABI with the
-host<->device copies inside the timed region.
+`--workload fp16_broadcast` runs the half-precision workload instead: A {8192,8192}
+broadcast, B {8192,2048} x 32, fp32 accumulation, gA summed over the batch (and, with
+N GPUs, all-reduced over NCCL: B, gy, y, gB are batch-sharded 32 per GPU, A is replicated).
 
---impl reference times the reference's own CPU implementation of the path (its
-Naive device compiled from its sources into oracle/_ref, else the C restatement
-under oracle/) on a bounded sample of the same workload.
+Prints ONE JSON line on rank 0.  `value` is algorithmic GFLOP/s (2*m*n*k per product, three
+products per step) over all ranks with operands resident in HBM; `e2e` is the same metric
+through the host-buffer entry points of the C ABI with the host<->device copies inside the
+timed region.
+
+--impl reference times the reference's own CPU implementation of the path (its Naive
+device compiled from its sources into oracle/_ref, else the C restatement under oracle/)
+on a bounded sample of the same workload.
 """
 import argparse
-import ctypes
 import json
 import os
 import subprocess
@@ -32,19 +34,53 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-N_DIM = 4096
-BATCH = 8
 METRIC = "matmul_fw_bw_gflops"
-FLOPS_PER_STEP = 3 * 2 * N_DIM ** 3 * BATCH        # 3,298,534,883,328
-# CPU sample: one batch element, restricted to the first 64 columns of b / gy
-SAMPLE_DK = 64
-SAMPLE_FLOPS = 3 * 2 * N_DIM * N_DIM * SAMPLE_DK
 
 
-def set_batch(batch):
-    global BATCH, FLOPS_PER_STEP
-    BATCH = batch
-    FLOPS_PER_STEP = 3 * 2 * N_DIM ** 3 * BATCH
+class Workload:
+    """Shapes in primitiv terms: a {di,dj} x ba, b {dj,dk} x bb; per-GPU batch sizes."""
+
+    def __init__(self, name, batch):
+        self.name = name
+        if name == "batched_square":
+            self.di = self.dj = self.dk = 4096
+            self.ba = self.bb = batch if batch else 8
+            self.mode_name, self.passes, self.half = "3xTF32", 3, False
+            self.sa, self.sb, self.sgy = 0.02, 0.02, 1.0
+            self.dtype = "tf32x3 (fp32 storage, fp32 accumulate)"
+            self.sample_dk = 64
+        elif name == "fp16_broadcast":
+            self.di = self.dj = 8192
+            self.dk = 2048
+            self.ba, self.bb = 1, (batch if batch else 32)
+            self.mode_name, self.passes, self.half = "FP16", 1, True
+            self.sa, self.sb, self.sgy = 0.05, 0.05, 1.0
+            self.dtype = "f16 (half storage, fp32 accumulate)"
+            self.sample_dk = 16
+        else:
+            raise ValueError(name)
+        self.bs = max(self.ba, self.bb)
+        self.flops = 3 * 2 * self.di * self.dj * self.dk * self.bs
+        self.sample_flops = 3 * 2 * self.di * self.dj * self.sample_dk
+        self.elem = 2 if self.half else 4
+
+    def label(self):
+        if self.name == "batched_square":
+            return "batched_square_gemm_4096x4096x4096_batch%d_fp32_3xtf32_fw_bw" % self.bs
+        return "fp16_a8192x8192_broadcast_b8192x2048_batch%d_fw_bw" % self.bs
+
+    def sample_text(self):
+        return ("one batch element, first %d columns of b and gy: fw {%d,%d}.{%d,%d} plus both backward "
+                "products, %d FLOP" % (self.sample_dk, self.di, self.dj, self.dj, self.sample_dk, self.sample_flops))
+
+    def config(self, n_gpus):
+        collective = ("none: no broadcast operand" if self.ba == self.bb else
+                      "all-reduce (sum) of the broadcast operand's gradient partial, NCCL")
+        return {"workload": self.label(), "a": [self.di, self.dj, self.ba], "b": [self.dj, self.dk, self.bb],
+                "batch_per_gpu": self.bs, "global_batch": self.bs * n_gpus, "mode": self.mode_name,
+                "flops_per_step_per_gpu": self.flops,
+                "l2": "every batched operand (>= 512 MiB) is larger than L2 (126 MB); no flush needed",
+                "parallelism": "batch-sharded x%d" % n_gpus, "collective": collective}
 
 
 def measured_peaks():
@@ -59,7 +95,7 @@ def measured_peaks():
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons of one GPU while the timed region runs."""
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs (read-only)."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -67,22 +103,7 @@ class ClockSampler(threading.Thread):
         super().__init__(daemon=True)
         self.index, self.samples, self.stop_flag = index, [], False
 
-    def run(self):
-        if self._run_nvml():
-            return
-        while not self.stop_flag:
-            try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
-                                     timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([c.strip() for c in out.split(",")])
-            except Exception:
-                pass
-            time.sleep(0.05)
-
     def _run_nvml(self):
-        """Reads the same counters through NVML (read-only calls), every 20 ms."""
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -104,6 +125,20 @@ class ClockSampler(threading.Thread):
             time.sleep(0.02)
         return True
 
+    def run(self):
+        if self._run_nvml():
+            return
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
+                                     timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            time.sleep(0.05)
+
     def summary(self):
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         mhz, reasons, mx = [], set(), None
@@ -121,16 +156,18 @@ class ClockSampler(threading.Thread):
                     reasons=sorted(reasons), samples=len(mhz))
 
 
-def cpu_sample():
+def cpu_sample(wl):
     """Times fw + bw of the reference CPU path on the bounded sample.  Returns (seconds, kind, cores)."""
     import numpy as np
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as ol
-    di, dj, dk = N_DIM, N_DIM, SAMPLE_DK
+    di, dj, dk = wl.di, wl.dj, wl.sample_dk
     rng = np.random.default_rng(0)
-    a = (rng.standard_normal(di * dj) * 0.02).astype(np.float32)
-    b = (rng.standard_normal(dj * dk) * 0.02).astype(np.float32)
-    gy = rng.standard_normal(di * dk).astype(np.float32)
+    a = (rng.standard_normal(di * dj) * wl.sa).astype(np.float32)
+    b = (rng.standard_normal(dj * dk) * wl.sb).astype(np.float32)
+    gy = (rng.standard_normal(di * dk) * wl.sgy).astype(np.float32)
+    if wl.half:   # the CPU reference computes in fp32 on the half-rounded values
+        a, b, gy = ol.round_to_half(a), ol.round_to_half(b), ol.round_to_half(gy)
     ga0, gb0 = np.zeros(di * dj, np.float32), np.zeros(dj * dk, np.float32)
     if ol.have_ref():
         _, t_fw = ol.ref_fw(a, b, di, dj, dk, 1, 1)
@@ -143,43 +180,33 @@ def cpu_sample():
     return time.perf_counter() - t0, "port", 1
 
 
-SAMPLE_TEXT = ("one batch element, first %d columns of b and gy: fw {4096,4096}.{4096,%d} plus both "
-               "backward products, %d FLOP" % (SAMPLE_DK, SAMPLE_DK, SAMPLE_FLOPS))
-
-
-def run_reference(args, rank):
+def run_reference(args, wl, rank):
     if rank != 0:
         return
     for _ in range(args.warmup):
-        cpu_sample()
+        cpu_sample(wl)
     total, kind, cores = 0.0, "port", 1
     for _ in range(args.steps):
-        t, kind, cores = cpu_sample()
+        t, kind, cores = cpu_sample(wl)
         total += t
-    gflops = SAMPLE_FLOPS * args.steps / total / 1e9
+    gflops = wl.sample_flops * args.steps / total / 1e9
     line = {
         "impl": "reference", "metric": METRIC, "value": gflops, "unit": "GFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": gflops, "unit": "GFLOP/s", "cores": cores, "kind": kind, "sample": SAMPLE_TEXT},
+        "config": wl.config(args.gpus),
+        "cpu_baseline": {"value": gflops, "unit": "GFLOP/s", "cores": cores, "kind": kind,
+                         "sample": wl.sample_text()},
         "e2e": {"value": gflops, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus):
-    return {"workload": "batched_square_gemm_4096x4096x4096_batch%d_fp32_3xtf32_fw_bw" % BATCH,
-            "shape": [N_DIM, N_DIM, N_DIM], "batch_per_gpu": BATCH, "global_batch": BATCH * n_gpus,
-            "mode": "3xTF32", "flops_per_step_per_gpu": FLOPS_PER_STEP,
-            "l2": "every operand (512 MiB) is larger than L2 (126 MB); no flush needed",
-            "parallelism": "batch-sharded x%d, no collective on the data path" % n_gpus}
-
-
-def run_ours(args, rank, local_rank, world):
+def run_ours(args, wl, rank, local_rank, world):
     import torch
     import primitiv_b200 as pb
+    from primitiv_b200.sharding import GpuBackend, ShardedMatmul, nccl_all_reduce
 
     torch.cuda.set_device(local_rank)
     dist = None
@@ -187,21 +214,27 @@ def run_ours(args, rank, local_rank, world):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = pb.Context(local_rank)
-    mode = pb.MODE_FP32_3XTF32
-    n, bs = N_DIM, BATCH
+    mode = pb.MODE_FP16 if wl.half else pb.MODE_FP32_3XTF32
+    dt = torch.float16 if wl.half else torch.float32
     g = torch.Generator(device="cuda")
     g.manual_seed(1234 + rank)
-    a = torch.randn(n * n * bs, generator=g, device="cuda") * 0.02
-    b = torch.randn(n * n * bs, generator=g, device="cuda") * 0.02
-    gy = torch.randn(n * n * bs, generator=g, device="cuda")
-    y = torch.empty(n * n * bs, device="cuda")
-    ga = torch.zeros(n * n * bs, device="cuda")
-    gb = torch.zeros(n * n * bs, device="cuda")
-    P = lambda t: t.data_ptr()
+    shared = torch.Generator(device="cuda")
+    shared.manual_seed(99)            # a replicated operand is the same on every rank
+    na, nb, ny = wl.di * wl.dj * wl.ba, wl.dj * wl.dk * wl.bb, wl.di * wl.dk * wl.bs
+    a = (torch.randn(na, generator=(shared if wl.ba == 1 else g), device="cuda") * wl.sa).to(dt)
+    b = (torch.randn(nb, generator=g, device="cuda") * wl.sb).to(dt)
+    gy = (torch.randn(ny, generator=g, device="cuda") * wl.sgy).to(dt)
+    y = torch.empty(ny, device="cuda", dtype=dt)
+    ga = torch.zeros(na, device="cuda", dtype=dt)
+    gb = torch.zeros(nb, device="cuda", dtype=dt)
+    # global batch sizes as the sharded orchestration sees them (1 = replicated operand)
+    gba = 1 if wl.ba == 1 else wl.ba * world
+    gbb = 1 if wl.bb == 1 else wl.bb * world
+    sm = ShardedMatmul(GpuBackend(ctx, mode), world, rank, nccl_all_reduce)
 
     def step():
-        ctx.matmul_fw(mode, P(a), P(b), P(y), n, n, n, bs, bs)
-        ctx.matmul_bw(mode, P(a), P(b), P(gy), P(ga), P(gb), n, n, n, bs, bs)
+        sm.forward(a, b, y, wl.di, wl.dj, wl.dk, gba, gbb)
+        sm.backward(a, b, gy, ga, gb, wl.di, wl.dj, wl.dk, gba, gbb)
 
     def barrier():
         if dist is not None:
@@ -216,6 +249,7 @@ def run_ours(args, rank, local_rank, world):
     ctx.profile_read()
     ctx.profile_enable(True)
     launches0 = ctx.launch_count()
+    coll0 = sm.collectives
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
@@ -227,6 +261,7 @@ def run_ours(args, rank, local_rank, world):
     ctx.profile_enable(False)
     prof = ctx.profile_read()
     launches = ctx.launch_count() - launches0
+    collectives = sm.collectives - coll0
     sampler.stop_flag = True
     sampler.join(timeout=3)
     assert ctx.status_poll() == 0, "a kernel reported a bounded-wait timeout"
@@ -234,35 +269,33 @@ def run_ours(args, rank, local_rank, world):
     # ---- end to end through the host-buffer entry points (pinned host memory) ----
     e2e = None
     if not args.skip_e2e:
-        e2e = run_e2e(args, ctx, mode, a, b, gy, barrier, dist, torch)
+        e2e = run_e2e(args, wl, ctx, mode, a, b, gy, barrier, torch)
     if dist is not None:
         t = torch.tensor([ms, e2e["ms"] if e2e else 0.0], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t[0])
         if e2e:
             e2e["ms"] = float(t[1])
-    if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
-        return
-    emit(args, world, ms, prof, launches, sampler, e2e)
+    if rank == 0:
+        emit(args, wl, world, ms, prof, launches, sampler, e2e, collectives)
     if dist is not None:
         dist.destroy_process_group()
 
 
-def run_e2e(args, ctx, mode, a, b, gy, barrier, dist, torch):
-    n, bs = N_DIM, BATCH
+def run_e2e(args, wl, ctx, mode, a, b, gy, barrier, torch):
+    """Each rank pushes its own shard through b200_matmul_{fw,bw}_host (no collective on this leg)."""
     P = lambda t: t.data_ptr()
     e2e_steps = max(1, min(args.steps, 3))
     hb = lambda src: src.cpu().pin_memory()
     ha, hbm, hgy = hb(a), hb(b), hb(gy)
-    hy = torch.empty(n * n * bs).pin_memory()
-    hga = torch.zeros(n * n * bs).pin_memory()
-    hgb = torch.zeros(n * n * bs).pin_memory()
+    hy = torch.empty(gy.numel(), dtype=gy.dtype).pin_memory()
+    hga = torch.zeros(a.numel(), dtype=a.dtype).pin_memory()
+    hgb = torch.zeros(b.numel(), dtype=b.dtype).pin_memory()
+    dims = (wl.di, wl.dj, wl.dk, wl.ba, wl.bb)
 
     def e2e_step():
-        ctx.matmul_fw_host(mode, P(ha), P(hbm), P(hy), n, n, n, bs, bs)
-        ctx.matmul_bw_host(mode, P(ha), P(hbm), P(hgy), P(hga), P(hgb), n, n, n, bs, bs)
+        ctx.matmul_fw_host(mode, P(ha), P(hbm), P(hy), *dims)
+        ctx.matmul_bw_host(mode, P(ha), P(hbm), P(hgy), P(hga), P(hgb), *dims)
         return float(hga[0])  # the step's result is read on the host
 
     e2e_step()
@@ -273,54 +306,55 @@ def run_e2e(args, ctx, mode, a, b, gy, barrier, dist, torch):
         e2e_step()
     f1.record()
     barrier()
-    tensor_bytes = n * n * bs * 4
+    ba, bb_, by = a.numel() * wl.elem, b.numel() * wl.elem, gy.numel() * wl.elem
     return {"ms": f0.elapsed_time(f1), "steps": e2e_steps,
-            "h2d": (2 + 5) * tensor_bytes,   # fw: a, b;  bw: a, b, gy, ga, gb (gradients hold the values added to)
-            "d2h": (1 + 2) * tensor_bytes}   # y; ga, gb
+            "h2d": (ba + bb_) + (ba + bb_ + by + ba + bb_),   # fw: a, b;  bw: a, b, gy and the gradients added to
+            "d2h": by + ba + bb_}                              # y; ga, gb
 
 
-def emit(args, world, ms, prof, launches, sampler, e2e):
+def emit(args, wl, world, ms, prof, launches, sampler, e2e, collectives):
     peaks = measured_peaks()
     ms_per_step = ms / args.steps
-    value = FLOPS_PER_STEP * world / (ms_per_step * 1e-3) / 1e9
+    value = wl.flops * world / (ms_per_step * 1e-3) / 1e9
     tc_ms, tc_n = prof["gemm_tc"]
-    issued_flops_per_launch = 3.0 * FLOPS_PER_STEP * args.steps / max(tc_n, 1)  # 3 TF32 passes per product
+    issued_flops_per_launch = float(wl.passes) * wl.flops * args.steps / max(tc_n, 1)
     tc_avg_ms = tc_ms / max(tc_n, 1)
     achieved = issued_flops_per_launch / (tc_avg_ms * 1e-3) / 1e12 if tc_n else 0.0
-    tf32_peak = peaks["bf16_sustained"] / 2.0
-    tf32_burst = peaks["bf16_burst"] / 2.0
-    # DRAM bytes of one gemm_tc_kernel launch: ncu capture of the batch-2 case (1.64 GB, see profiles/),
-    # scaled by the batch (independent products, traffic grows in proportion)
-    traffic = 1.64e9 * BATCH / 2.0
+    div = 1.0 if wl.half else 2.0     # TF32 runs at half the 16-bit rate
+    peak, burst = peaks["bf16_sustained"] / div, peaks["bf16_burst"] / div
+    # DRAM bytes of one gemm_tc_kernel launch: ncu capture of the batch-2 square case (1.64 GB, see
+    # profiles/), scaled by the batch (independent products, traffic grows in proportion)
+    traffic = 1.64e9 * wl.bs / 2.0 if wl.name == "batched_square" else None
     line = {
         "metric": METRIC, "value": value, "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "tf32x3 (fp32 storage, fp32 accumulate)", "data": "synthetic",
-        "config": workload_config(world),
+        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config(world),
         "roofline": {
-            "bound": "tensor", "kernel": "gemm_tc_kernel<chunked, cta pair>", "achieved": achieved,
-            "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak, "traffic": traffic,
-            "frac_of_burst_peak": achieved / tf32_burst,
-            "note": ("achieved = tensor-issued FLOP/s (3 TF32 passes x algorithmic 2mnk) / mean CUDA-event "
-                     "duration of %d launches; peak = %s bf16 sustained / 2 (TF32 runs at half the 16-bit rate; "
-                     "the timed region is a fraction of a second, so the burst figure / 2 = %.0f is given beside it); "
-                     "traffic = ncu dram bytes of the batch-2 capture scaled to this batch"
-                     % (tc_n, peaks["source"], tf32_burst)),
-            "algorithmic_tflops_in_kernel": achieved / 3.0,
+            "bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05, cta pair)", "achieved": achieved,
+            "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
+            "frac_of_burst_peak": achieved / burst,
+            "note": ("achieved = tensor-issued FLOP/s (%d tensor-core pass(es) x algorithmic 2mnk) / mean "
+                     "CUDA-event duration of %d launches; peak = %s bf16 sustained%s; the timed region is a "
+                     "fraction of a second, so the burst figure %.0f is given beside it; traffic = ncu dram "
+                     "bytes of the batch-2 capture scaled to this batch"
+                     % (wl.passes, tc_n, peaks["source"],
+                        "" if wl.half else " / 2 (TF32 runs at half the 16-bit rate)", burst)),
+            "algorithmic_tflops_in_kernel": achieved / wl.passes,
             "kernel_ms_per_step": tc_ms / args.steps, "pack_ms_per_step": prof["pack"][0] / args.steps,
         },
         "gpu_launches": int(launches),
+        "collectives_per_step": collectives / max(args.steps, 1),
         "clocks": sampler.summary(),
     }
     if e2e:
         per = e2e["ms"] / e2e["steps"]
-        line["e2e"] = {"value": FLOPS_PER_STEP * world / (per * 1e-3) / 1e9, "unit": "GFLOP/s",
+        line["e2e"] = {"value": wl.flops * world / (per * 1e-3) / 1e9, "unit": "GFLOP/s",
                        "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                        "steps": e2e["steps"], "ms_per_step": per}
     if world == 1 and not args.skip_cpu:
-        t, kind, cores = cpu_sample()
-        line["cpu_baseline"] = {"value": SAMPLE_FLOPS / t / 1e9, "unit": "GFLOP/s", "cores": cores,
-                                "kind": kind, "sample": SAMPLE_TEXT}
+        t, kind, cores = cpu_sample(wl)
+        line["cpu_baseline"] = {"value": wl.sample_flops / t / 1e9, "unit": "GFLOP/s", "cores": cores,
+                                "kind": kind, "sample": wl.sample_text()}
     print(json.dumps(line), flush=True)
 
 
@@ -330,20 +364,21 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=BATCH,
-                    help="batch elements per GPU (default 8 = the benchmark workload; smaller values are for "
-                         "profiler captures and are marked in config.workload)")
+    ap.add_argument("--workload", default="batched_square", choices=["batched_square", "fp16_broadcast"])
+    ap.add_argument("--batch", type=int, default=0,
+                    help="batch elements per GPU (default: the workload's own, 8 / 32; smaller values are for "
+                         "profiler captures and show in config.workload)")
     ap.add_argument("--skip-e2e", action="store_true", help="leave out the host-buffer leg (profiler captures)")
     ap.add_argument("--skip-cpu", action="store_true", help="leave out the CPU baseline leg (profiler captures)")
     args = ap.parse_args()
-    set_batch(args.batch)
+    wl = Workload(args.workload, args.batch)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, wl, rank)
     else:
-        run_ours(args, rank, local_rank, world)
+        run_ours(args, wl, rank, local_rank, world)
 
 
 if __name__ == "__main__":

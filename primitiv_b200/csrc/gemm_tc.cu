@@ -89,7 +89,8 @@ struct alignas(64) TcParams {
   uint32_t passes;
   uint32_t chunk_kblocks;  // k-blocks per accumulation chunk
   uint32_t accumulate, out_half, kind_f16;
-  uint32_t a_stage_bytes, b_stage_bytes, stage_bytes;  // per plane, per CTA; stage = planes * (a + b)
+  uint32_t a_stage_bytes, b_stage_bytes, stage_bytes;  // per plane, per CTA; stage = subs * planes * (a + b)
+  uint32_t subs, sub_bytes;  // k-blocks per pipeline stage and the bytes of one (planes * (a + b))
   uint32_t tmem_cols;
   uint32_t debug;  // development switches: 1 = no global stores, 2 = no MMA, 4 = no TMA loads
   int *status;
@@ -341,6 +342,28 @@ __device__ __forceinline__ void store_cols(T *C, unsigned long long base, uint32
   }
 }
 
+// Tile order.  Tiles of one group (one output matrix) are walked in bands of kBandTilesM
+// row-tiles: inside a band the row-tile index runs fastest, then the column-tile index.
+// The CTAs of one wave therefore work on a roughly square patch of the output (8 row-tiles
+// by sm_count/8 column-tiles) and share both operand panels through L2, instead of
+// sweeping all of A for a couple of B panels (which for an A larger than L2, e.g.
+// 8192 x 8192 halves, re-reads A from HBM for every column-tile).
+constexpr uint32_t kBandTilesM = 8;
+
+__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t &g,
+                                            uint32_t &mt, uint32_t &nt) {
+  const uint32_t per_group = tiles_m * tiles_n;
+  g = tile / per_group;
+  const uint32_t rem = tile - g * per_group;
+  const uint32_t band_tiles = kBandTilesM * tiles_n;
+  const uint32_t band = rem / band_tiles;
+  const uint32_t in_band = rem - band * band_tiles;
+  const uint32_t first_m = band * kBandTilesM;
+  const uint32_t rows = tiles_m - first_m < kBandTilesM ? tiles_m - first_m : kBandTilesM;
+  mt = first_m + in_band % rows;
+  nt = in_band / rows;
+}
+
 // kCtas == 1: one CTA per 128 x bn tile.  kCtas == 2: a cluster of two CTAs per 256 x bn
 // tile (tcgen05 cta_group::2): CTA r of the pair stages rows [128 r, 128 r + 128) of A and
 // rows [bn/2 r, bn/2 r + bn/2) of B, the leader (r = 0) issues every MMA for both, and each
@@ -415,16 +438,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       uint32_t armed_mask = 0, armed_parity = 0;
       bool ok = true;
       for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
-        const uint32_t g = tile / tiles_per_group;
-        const uint32_t rem = tile - g * tiles_per_group;
-        const int m0 = static_cast<int>((rem % p.tiles_m) * (kBM * kCtas) + cta_rank * kBM);
-        const int n0 = static_cast<int>((rem / p.tiles_m) * p.bn + cta_rank * b_rows);
+        uint32_t g, mt, nt;
+        tile_coords(tile, p.tiles_m, p.tiles_n, g, mt, nt);
+        const int m0 = static_cast<int>(mt * (kBM * kCtas) + cta_rank * kBM);
+        const int n0 = static_cast<int>(nt * p.bn + cta_rank * b_rows);
         for (uint32_t r = 0; ok && r < p.red; ++r) {
           const int za = static_cast<int>(g * p.a_gmul + r * p.a_rmul);
           const int zb = static_cast<int>(g * p.b_gmul + r * p.b_rmul);
           for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
-            const int k0 = static_cast<int>(kb * p.bk);
-            if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag, 32u)) {
+            if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
               ok = false;
               break;
             }
@@ -441,7 +463,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
               armed_mask |= 1u << stage;
               armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
             }
-            const uint32_t sa = smem_base + stage * p.stage_bytes;
+            for (uint32_t sub = 0; sub < p.subs; ++sub) {
+            const int k0 = static_cast<int>((kb * p.subs + sub) * p.bk);
+            const uint32_t sa = smem_base + stage * p.stage_bytes + sub * p.sub_bytes;
             const uint32_t sb = sa + planes * p.a_stage_bytes;
             for (uint32_t pl = 0; pl < planes; ++pl) {
               const uint32_t da = sa + pl * p.a_stage_bytes, db = sb + pl * p.b_stage_bytes;
@@ -465,6 +489,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 if constexpr (kCtas == 2) tma_load_3d_pair(db, &p.mapB[pl], bar, k0, n0, zb);
                 else tma_load_3d(db, &p.mapB[pl], bar, k0, n0, zb);
               }
+            }
             }
             if (++stage == p.stages) {
               stage = 0;
@@ -513,15 +538,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
               break;
             }
             tc_fence_after();
-            const uint32_t sa = smem_base + stage * p.stage_bytes;
-            const uint32_t sb = sa + planes * p.a_stage_bytes;
-            if (!(p.debug & 2u)) {
+            for (uint32_t sub = 0; sub < p.subs && !(p.debug & 2u); ++sub) {
+              const uint32_t sa = smem_base + stage * p.stage_bytes + sub * p.sub_bytes;
+              const uint32_t sb = sa + planes * p.a_stage_bytes;
+              const bool first = (it | sub) == 0u;
               if (p.kind_f16)
                 mma_stage<kCtas, true>(d_tmem, sa, sb, p.a_stage_bytes, p.b_stage_bytes, a_hi, b_hi, a_lo_fixed,
-                                       b_lo_fixed, kstep_a, kstep_b, p.idesc, p.passes, it == 0u);
+                                       b_lo_fixed, kstep_a, kstep_b, p.idesc, p.passes, first);
               else
                 mma_stage<kCtas, false>(d_tmem, sa, sb, p.a_stage_bytes, p.b_stage_bytes, a_hi, b_hi, a_lo_fixed,
-                                        b_lo_fixed, kstep_a, kstep_b, p.idesc, p.passes, it == 0u);
+                                        b_lo_fixed, kstep_a, kstep_b, p.idesc, p.passes, first);
             }
             // frees the stage (in both CTAs of a pair) when these MMAs retire
             if constexpr (kCtas == 2) mma_commit_pair(smem_u32(&empty_bar[stage]));
@@ -559,10 +585,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     const uint32_t empty0 = kCtas == 2 ? map_to_cta(smem_u32(&tmem_empty_bar[0]), 0u) : smem_u32(&tmem_empty_bar[0]);
     const uint32_t empty1 = kCtas == 2 ? map_to_cta(smem_u32(&tmem_empty_bar[1]), 0u) : smem_u32(&tmem_empty_bar[1]);
     for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
-      const uint32_t g = tile / tiles_per_group;
-      const uint32_t rem = tile - g * tiles_per_group;
-      const uint32_t m0 = (rem % p.tiles_m) * (kBM * kCtas);
-      const uint32_t n0 = (rem / p.tiles_m) * p.bn;
+      uint32_t g, mt, nt;
+      tile_coords(tile, p.tiles_m, p.tiles_n, g, mt, nt);
+      const uint32_t m0 = mt * (kBM * kCtas);
+      const uint32_t n0 = nt * p.bn;
       const uint32_t row = m0 + row_in_tile;
       const bool row_ok = row < p.m && !(p.debug & 1u);
       const unsigned long long base =
@@ -979,7 +1005,13 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   const uint32_t b_rows = p.bn / ctas;  // rows of B each CTA stages
   p.a_stage_bytes = kBM * 128u;
   p.b_stage_bytes = b_rows * 128u;
-  p.stage_bytes = planes * (p.a_stage_bytes + p.b_stage_bytes);
+  p.sub_bytes = planes * (p.a_stage_bytes + p.b_stage_bytes);
+  // Single-pass modes issue only four MMAs per k-block; two k-blocks per pipeline stage halve
+  // the per-stage hand-off cost as long as three such stages still fit.
+  const size_t smem_budget = ctx->smem_optin > 8192 ? ctx->smem_optin - 1024 : 0;
+  p.subs = (passes == 1 && g.k > p.bk && smem_budget >= 1024 + 3ull * 2 * p.sub_bytes) ? 2u : 1u;
+  p.stage_bytes = p.subs * p.sub_bytes;
+  p.kblocks = (g.k + p.bk * p.subs - 1) / (p.bk * p.subs);  // pipeline-stage iterations along k
   p.layout_a = p.layout_b = 2u;  // 128-byte swizzle
   CUtensorMapSwizzle swz_a = CU_TENSOR_MAP_SWIZZLE_128B, swz_b = CU_TENSOR_MAP_SWIZZLE_128B;
   if (p.a_mn_major) {
@@ -1038,7 +1070,8 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     if (st) ctx->debug_stage_cap = std::atoi(st);
   }
 
-  const size_t budget = ctx->smem_optin > 8192 ? ctx->smem_optin - 4096 : 0;
+  // everything the SM offers minus the kernel's static shared memory (barriers, ~200 B) and some slack
+  const size_t budget = ctx->smem_optin > 8192 ? ctx->smem_optin - 1024 : 0;
   uint32_t stages = budget > 1024 ? static_cast<uint32_t>((budget - 1024) / p.stage_bytes) : 0;
   if (stages > kMaxStages) stages = kMaxStages;
   if (ctx->debug_stage_cap > 0 && stages > (uint32_t)ctx->debug_stage_cap) stages = ctx->debug_stage_cap;
@@ -1052,7 +1085,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
       rc = encode_map(ctx, &p.mapB[i], b_src[i], vb, eb, p.b_mn_major ? chunk : b_rows, p.bk, swz_b);
   }
   if (rc == B200_OK && !ctx->tc_smem_configured) {
-    const int max_dyn = static_cast<int>(ctx->smem_optin - 2048);
+    const int max_dyn = static_cast<int>(ctx->smem_optin - 512);
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(gemm_tc_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
