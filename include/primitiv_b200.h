@@ -65,6 +65,12 @@ B200_API int b200_ctx_device(const b200_ctx *ctx, int *device_id, int *sm_count)
  * ran out.  Synchronises `stream`.  *code is 0 when no kernel reported anything. */
 B200_API int b200_status_poll(b200_ctx *ctx, void *stream, int *code);
 
+/* Exercises the failure-reporting path without any failure: launches a one-warp kernel that
+ * waits about a millisecond on a barrier nothing arrives at, gives up, and writes
+ * B200_ERR_KERNEL_TIMEOUT to the status word.  The kernel returns normally and the context stays
+ * usable; b200_status_poll then returns 1004 once. */
+B200_API int b200_selftest_wait_timeout(b200_ctx *ctx, void *stream);
+
 /* ---- caching memory pool --------------------------------------------------------
  * Replaces primitiv::MemoryPool (primitiv/core/memory_pool.cc:35-94) as configured
  * by the CUDA device (primitiv/internal/cuda/utils.h:327-342).  Blocks are 256-byte

@@ -26,6 +26,7 @@ SIGNATURES = {
     "b200_ctx_destroy": (_int, [_vp]),
     "b200_ctx_device": (_int, [_vp, ctypes.POINTER(_int), ctypes.POINTER(_int)]),
     "b200_status_poll": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
+    "b200_selftest_wait_timeout": (_int, [_vp, _vp]),
     "b200_pool_alloc": (_int, [_vp, ctypes.c_size_t, ctypes.POINTER(_vp), ctypes.POINTER(ctypes.c_size_t)]),
     "b200_pool_free": (_int, [_vp, _vp]),
     "b200_pool_release_cached": (_int, [_vp]),

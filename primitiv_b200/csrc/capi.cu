@@ -94,6 +94,12 @@ int b200_status_poll(b200_ctx *ctx, void *stream, int *code) {
   return B200_OK;
 }
 
+int b200_selftest_wait_timeout(b200_ctx *ctx, void *stream) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  DeviceGuard guard(ctx->device);
+  return b200::selftest_wait_timeout(ctx, static_cast<cudaStream_t>(stream));
+}
+
 int b200_pool_alloc(b200_ctx *ctx, size_t bytes, void **ptr, size_t *allocated) {
   if (!ctx) return B200_ERR_INVALID_ARG;
   DeviceGuard guard(ctx->device);

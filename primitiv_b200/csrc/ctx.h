@@ -120,6 +120,8 @@ int gemm_simt(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
 // tcgen05 path.  tc_eligible() says whether the operands meet TMA's alignment rules.
 bool gemm_tc_eligible(const b200_ctx *ctx, const GemmArgs &g);
 int gemm_tc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
+// Launches a kernel whose only wait runs out (see b200_selftest_wait_timeout).
+int selftest_wait_timeout(b200_ctx *ctx, cudaStream_t stream);
 // 3xTF32 product whose packing planes live in a fixed device array: allocates nothing.
 int gemm_3xtf32_noalloc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
 

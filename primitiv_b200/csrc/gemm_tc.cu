@@ -1136,6 +1136,37 @@ int gemm_tc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream) {
   return gemm_tc_run(ctx, g, stream, nullptr, 0);
 }
 
+// ---------------- self-test of the bounded-wait machinery ----------------
+namespace {
+
+// Waits on a barrier that nothing ever arrives at, with a limit of `limit_cycles`, then
+// reports through the status word exactly as gemm_tc_kernel does when one of its waits
+// runs out.  Nothing faults or traps: the kernel returns normally.
+__global__ void wait_timeout_selftest_kernel(int *status, long long limit_cycles) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const long long t0 = clock64();
+    bool timed_out = false;
+    while (!mbar_try_wait(smem_u32(&bar), 0)) {
+      if (clock64() - t0 > limit_cycles) {
+        timed_out = true;
+        break;
+      }
+    }
+    if (timed_out) atomicCAS(status, 0, B200_ERR_KERNEL_TIMEOUT);
+  }
+}
+
+}  // namespace
+
+int selftest_wait_timeout(b200_ctx *ctx, cudaStream_t stream) {
+  wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>(ctx->d_status, 2000000ll);  // about a millisecond
+  ++ctx->launches;
+  return static_cast<int>(cudaGetLastError());
+}
+
 // ---------------- allocation-free 3xTF32 product (b200_gemm_3xtf32_noalloc) ----------------
 //
 // The packing planes of this variant live in a file-scope device array instead of

@@ -68,3 +68,21 @@ def test_free_of_unknown_pointer_is_an_error(own_ctx):
 def test_invalid_device_id_is_rejected():
     with pytest.raises(pb.B200Error):
         pb.Context(9999)
+
+
+def test_bounded_wait_reports_and_context_survives(own_ctx):
+    """A device-side wait that runs out is reported through the status word, not by a fault."""
+    import numpy as np
+    import torch
+    c = own_ctx
+    assert c.status_poll() == 0
+    c.op("b200_selftest_wait_timeout", None)
+    assert c.status_poll() == 1004          # B200_ERR_KERNEL_TIMEOUT, read once ...
+    assert c.status_poll() == 0             # ... and cleared
+    # the same context still computes
+    a = torch.eye(64, device="cuda").flatten()
+    b = torch.arange(64 * 64, device="cuda", dtype=torch.float32)
+    y = torch.empty(64 * 64, device="cuda")
+    c.matmul_fw(pb.MODE_TF32, a.data_ptr(), b.data_ptr(), y.data_ptr(), 64, 64, 64, 1, 1)
+    torch.cuda.synchronize()
+    assert np.array_equal(y.cpu().numpy(), b.cpu().numpy())
