@@ -167,8 +167,8 @@ B200_API int b200_gemm(b200_ctx *ctx, int mode, int trans_a, int trans_b,
  * fit the array, i.e. roughly (m + n) * k <= 4 Mi elements (1024 x 1024 x 2048, 2048 x 2048 x
  * 1024, ...).  Larger products return B200_ERR_TOO_LARGE and launch nothing.
  *
- * The first call on each device looks up the array's device address (cudaGetSymbolAddress);
- * make that first call outside any stream capture.  All calls share the one array: it keeps
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress)
+ * and keeps it.  All calls share the one array: it keeps
  * whatever the previous call packed, nothing in it needs clearing because the packing pass
  * rewrites every element the product reads, and two calls whose kernels can overlap on the
  * GPU (different streams, or different contexts on the same device) race on it. */
