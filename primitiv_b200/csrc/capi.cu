@@ -70,6 +70,8 @@ int b200_ctx_destroy(b200_ctx *ctx) {
   if (!ctx) return B200_OK;
   DeviceGuard guard(ctx->device);
   cudaDeviceSynchronize();
+  for (cudaStream_t st : ctx->pipe_streams) if (st) cudaStreamDestroy(st);
+  for (cudaEvent_t ev : ctx->pipe_events) cudaEventDestroy(ev);
   cudaFree(ctx->d_status);
   delete ctx;  // the pool's destructor returns cached blocks
   return B200_OK;
@@ -279,6 +281,52 @@ struct Scratch {
 
 }  // namespace
 
+// The host-buffer entry points run as a three-stream pipeline over chunks of the batch:
+// while chunk c is multiplied, chunk c+1 is on its way up and chunk c-1 on its way down,
+// so the call costs about max(upload, download, compute) instead of their sum.  Tensors
+// with batch 1 (and their gradients) travel once, before the first / after the last chunk.
+// The streams are ordinary blocking streams: their first work waits for whatever the caller
+// queued on the legacy default stream, and the call returns only when all three are idle.
+namespace {
+
+constexpr int kPipeUp = 0, kPipeRun = 1, kPipeDown = 2;
+// In fp16 mode every chunk rounds a batch-summed gradient to half once more, hence fewer chunks.
+constexpr uint32_t kPipeMaxChunks = 16, kPipeMaxChunksHalf = 8;
+constexpr size_t kPipeMinChunkBytes = 4u << 20;
+
+int pipe_prepare(b200_ctx *ctx, uint32_t events) {
+  for (cudaStream_t &st : ctx->pipe_streams)
+    if (!st) B200_CUDA_TRY(cudaStreamCreate(&st));
+  while (ctx->pipe_events.size() < events) {
+    cudaEvent_t ev;
+    B200_CUDA_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    ctx->pipe_events.push_back(ev);
+  }
+  return B200_OK;
+}
+
+// Number of batch chunks: enough for overlap, each still a worthwhile transfer.
+uint32_t pipe_chunks(int mode, uint32_t bs, size_t batched_bytes) {
+  const uint32_t cap = mode == B200_MODE_FP16 ? kPipeMaxChunksHalf : kPipeMaxChunks;
+  uint32_t c = bs < cap ? bs : cap;
+  while (c > 1 && batched_bytes / c < kPipeMinChunkBytes) --c;
+  return c;
+}
+
+int pipe_finish(b200_ctx *ctx, int rc) {
+  // drain all three streams whatever happened, so that the scratch blocks can go back to the pool
+  for (cudaStream_t st : ctx->pipe_streams) {
+    const cudaError_t e = cudaStreamSynchronize(st);
+    if (!rc && e != cudaSuccess) rc = static_cast<int>(e);
+  }
+  return rc;
+}
+
+inline const char *cbytes(const void *p, size_t off) { return static_cast<const char *>(p) + off; }
+inline char *mbytes(void *p, size_t off) { return static_cast<char *>(p) + off; }
+
+}  // namespace
+
 int b200_matmul_fw_host(b200_ctx *ctx, int mode, const void *a_host, const void *b_host,
                         void *y_host, uint32_t di, uint32_t dj, uint32_t dk, uint32_t ba,
                         uint32_t bb) {
@@ -288,16 +336,37 @@ int b200_matmul_fw_host(b200_ctx *ctx, int mode, const void *a_host, const void 
   DeviceGuard guard(ctx->device);
   const size_t eb = b200::elem_bytes(mode);
   const uint32_t bs = ba > bb ? ba : bb;
-  const size_t sa = (size_t)di * dj * ba * eb, sb = (size_t)dj * dk * bb * eb, sy = (size_t)di * dk * bs * eb;
+  const size_t ia = (size_t)di * dj * eb, ib = (size_t)dj * dk * eb, iy = (size_t)di * dk * eb;  // one item
+  const size_t sa = ia * ba, sb = ib * bb, sy = iy * bs;
+  if (sa == 0 || sb == 0 || sy == 0) return sy == 0 ? B200_OK : B200_ERR_INVALID_ARG;
   Scratch da(ctx), db(ctx), dy(ctx);
   if ((rc = da.get(sa)) || (rc = db.get(sb)) || (rc = dy.get(sy))) return rc;
-  B200_CUDA_TRY(cudaMemcpyAsync(da.p, a_host, sa, cudaMemcpyHostToDevice, 0));
-  B200_CUDA_TRY(cudaMemcpyAsync(db.p, b_host, sb, cudaMemcpyHostToDevice, 0));
-  rc = b200_matmul_fw(ctx, mode, da.p, db.p, dy.p, di, dj, dk, ba, bb, nullptr);
-  if (rc) return rc;
-  B200_CUDA_TRY(cudaMemcpyAsync(y_host, dy.p, sy, cudaMemcpyDeviceToHost, 0));
-  B200_CUDA_TRY(cudaStreamSynchronize(0));
-  return B200_OK;
+  const uint32_t chunks = pipe_chunks(mode, bs, (ba > 1 ? sa : 0) + (bb > 1 ? sb : 0) + sy);
+  if ((rc = pipe_prepare(ctx, 2 * chunks))) return rc;
+  cudaStream_t up = ctx->pipe_streams[kPipeUp], run = ctx->pipe_streams[kPipeRun],
+               down = ctx->pipe_streams[kPipeDown];
+  auto body = [&]() -> int {
+    if (ba == 1) B200_CUDA_TRY(cudaMemcpyAsync(da.p, a_host, sa, cudaMemcpyHostToDevice, up));
+    if (bb == 1) B200_CUDA_TRY(cudaMemcpyAsync(db.p, b_host, sb, cudaMemcpyHostToDevice, up));
+    for (uint32_t c = 0; c < chunks; ++c) {
+      const uint32_t n0 = (uint32_t)((uint64_t)bs * c / chunks), n1 = (uint32_t)((uint64_t)bs * (c + 1) / chunks);
+      const uint32_t cnt = n1 - n0;
+      const size_t oa = ba > 1 ? ia * n0 : 0, ob = bb > 1 ? ib * n0 : 0, oy = iy * n0;
+      if (ba > 1) B200_CUDA_TRY(cudaMemcpyAsync(mbytes(da.p, oa), cbytes(a_host, oa), ia * cnt, cudaMemcpyHostToDevice, up));
+      if (bb > 1) B200_CUDA_TRY(cudaMemcpyAsync(mbytes(db.p, ob), cbytes(b_host, ob), ib * cnt, cudaMemcpyHostToDevice, up));
+      cudaEvent_t uploaded = ctx->pipe_events[2 * c], computed = ctx->pipe_events[2 * c + 1];
+      B200_CUDA_TRY(cudaEventRecord(uploaded, up));
+      B200_CUDA_TRY(cudaStreamWaitEvent(run, uploaded, 0));
+      const int r = b200_matmul_fw(ctx, mode, cbytes(da.p, oa), cbytes(db.p, ob), mbytes(dy.p, oy), di, dj, dk,
+                                   ba > 1 ? cnt : 1, bb > 1 ? cnt : 1, run);
+      if (r) return r;
+      B200_CUDA_TRY(cudaEventRecord(computed, run));
+      B200_CUDA_TRY(cudaStreamWaitEvent(down, computed, 0));
+      B200_CUDA_TRY(cudaMemcpyAsync(mbytes(y_host, oy), cbytes(dy.p, oy), iy * cnt, cudaMemcpyDeviceToHost, down));
+    }
+    return B200_OK;
+  };
+  return pipe_finish(ctx, body());
 }
 
 int b200_matmul_bw_host(b200_ctx *ctx, int mode, const void *a_host, const void *b_host,
@@ -309,22 +378,58 @@ int b200_matmul_bw_host(b200_ctx *ctx, int mode, const void *a_host, const void 
   DeviceGuard guard(ctx->device);
   const size_t eb = b200::elem_bytes(mode);
   const uint32_t bs = ba > bb ? ba : bb;
-  const size_t sa = (size_t)di * dj * ba * eb, sb = (size_t)dj * dk * bb * eb, sy = (size_t)di * dk * bs * eb;
+  const size_t ia = (size_t)di * dj * eb, ib = (size_t)dj * dk * eb, iy = (size_t)di * dk * eb;
+  const size_t sa = ia * ba, sb = ib * bb, sy = iy * bs;
+  if (sa == 0 || sb == 0 || sy == 0) return B200_OK;  // an empty extent: nothing to add
   Scratch da(ctx), db(ctx), dgy(ctx), dga(ctx), dgb(ctx);
   if ((rc = da.get(sa)) || (rc = db.get(sb)) || (rc = dgy.get(sy)) || (rc = dga.get(sa)) ||
       (rc = dgb.get(sb)))
     return rc;
-  B200_CUDA_TRY(cudaMemcpyAsync(da.p, a_host, sa, cudaMemcpyHostToDevice, 0));
-  B200_CUDA_TRY(cudaMemcpyAsync(db.p, b_host, sb, cudaMemcpyHostToDevice, 0));
-  B200_CUDA_TRY(cudaMemcpyAsync(dgy.p, gy_host, sy, cudaMemcpyHostToDevice, 0));
-  B200_CUDA_TRY(cudaMemcpyAsync(dga.p, ga_host, sa, cudaMemcpyHostToDevice, 0));
-  B200_CUDA_TRY(cudaMemcpyAsync(dgb.p, gb_host, sb, cudaMemcpyHostToDevice, 0));
-  rc = b200_matmul_bw(ctx, mode, da.p, db.p, dgy.p, dga.p, dgb.p, di, dj, dk, ba, bb, nullptr);
-  if (rc) return rc;
-  B200_CUDA_TRY(cudaMemcpyAsync(ga_host, dga.p, sa, cudaMemcpyDeviceToHost, 0));
-  B200_CUDA_TRY(cudaMemcpyAsync(gb_host, dgb.p, sb, cudaMemcpyDeviceToHost, 0));
-  B200_CUDA_TRY(cudaStreamSynchronize(0));
-  return B200_OK;
+  const uint32_t chunks = pipe_chunks(mode, bs, (ba > 1 ? 2 * sa : 0) + (bb > 1 ? 2 * sb : 0) + sy);
+  if ((rc = pipe_prepare(ctx, 2 * chunks))) return rc;
+  cudaStream_t up = ctx->pipe_streams[kPipeUp], run = ctx->pipe_streams[kPipeRun],
+               down = ctx->pipe_streams[kPipeDown];
+  auto body = [&]() -> int {
+    // batch-1 operands and the gradients that every chunk adds into go up first
+    if (ba == 1) {
+      B200_CUDA_TRY(cudaMemcpyAsync(da.p, a_host, sa, cudaMemcpyHostToDevice, up));
+      B200_CUDA_TRY(cudaMemcpyAsync(dga.p, ga_host, sa, cudaMemcpyHostToDevice, up));
+    }
+    if (bb == 1) {
+      B200_CUDA_TRY(cudaMemcpyAsync(db.p, b_host, sb, cudaMemcpyHostToDevice, up));
+      B200_CUDA_TRY(cudaMemcpyAsync(dgb.p, gb_host, sb, cudaMemcpyHostToDevice, up));
+    }
+    for (uint32_t c = 0; c < chunks; ++c) {
+      const uint32_t n0 = (uint32_t)((uint64_t)bs * c / chunks), n1 = (uint32_t)((uint64_t)bs * (c + 1) / chunks);
+      const uint32_t cnt = n1 - n0;
+      const size_t oa = ba > 1 ? ia * n0 : 0, ob = bb > 1 ? ib * n0 : 0, oy = iy * n0;
+      if (ba > 1) {
+        B200_CUDA_TRY(cudaMemcpyAsync(mbytes(da.p, oa), cbytes(a_host, oa), ia * cnt, cudaMemcpyHostToDevice, up));
+        B200_CUDA_TRY(cudaMemcpyAsync(mbytes(dga.p, oa), cbytes(ga_host, oa), ia * cnt, cudaMemcpyHostToDevice, up));
+      }
+      if (bb > 1) {
+        B200_CUDA_TRY(cudaMemcpyAsync(mbytes(db.p, ob), cbytes(b_host, ob), ib * cnt, cudaMemcpyHostToDevice, up));
+        B200_CUDA_TRY(cudaMemcpyAsync(mbytes(dgb.p, ob), cbytes(gb_host, ob), ib * cnt, cudaMemcpyHostToDevice, up));
+      }
+      B200_CUDA_TRY(cudaMemcpyAsync(mbytes(dgy.p, oy), cbytes(gy_host, oy), iy * cnt, cudaMemcpyHostToDevice, up));
+      cudaEvent_t uploaded = ctx->pipe_events[2 * c], computed = ctx->pipe_events[2 * c + 1];
+      B200_CUDA_TRY(cudaEventRecord(uploaded, up));
+      B200_CUDA_TRY(cudaStreamWaitEvent(run, uploaded, 0));
+      const int r = b200_matmul_bw(ctx, mode, cbytes(da.p, oa), cbytes(db.p, ob), cbytes(dgy.p, oy),
+                                   mbytes(dga.p, oa), mbytes(dgb.p, ob), di, dj, dk,
+                                   ba > 1 ? cnt : 1, bb > 1 ? cnt : 1, run);
+      if (r) return r;
+      B200_CUDA_TRY(cudaEventRecord(computed, run));
+      B200_CUDA_TRY(cudaStreamWaitEvent(down, computed, 0));
+      if (ba > 1) B200_CUDA_TRY(cudaMemcpyAsync(mbytes(ga_host, oa), cbytes(dga.p, oa), ia * cnt, cudaMemcpyDeviceToHost, down));
+      if (bb > 1) B200_CUDA_TRY(cudaMemcpyAsync(mbytes(gb_host, ob), cbytes(dgb.p, ob), ib * cnt, cudaMemcpyDeviceToHost, down));
+    }
+    // `down` already waits for the last chunk's products: the batch-summed gradients are complete
+    if (ba == 1) B200_CUDA_TRY(cudaMemcpyAsync(ga_host, dga.p, sa, cudaMemcpyDeviceToHost, down));
+    if (bb == 1) B200_CUDA_TRY(cudaMemcpyAsync(gb_host, dgb.p, sb, cudaMemcpyDeviceToHost, down));
+    return B200_OK;
+  };
+  return pipe_finish(ctx, body());
 }
 
 }  // extern "C"

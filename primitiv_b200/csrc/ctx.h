@@ -66,6 +66,10 @@ struct b200_ctx {
   bool profiling = false;
   struct ProfRec { cudaEvent_t start, stop; int kind; };
   std::vector<ProfRec> prof;
+  // host-buffer entry points (b200_matmul_*_host): upload, compute and download streams
+  // and the events that chain them, created on first use
+  cudaStream_t pipe_streams[3] = {nullptr, nullptr, nullptr};
+  std::vector<cudaEvent_t> pipe_events;
 };
 
 namespace b200 {

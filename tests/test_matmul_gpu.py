@@ -191,3 +191,31 @@ def test_host_buffer_entry_points(ctx):
                        ga.ctypes.data, gb.ctypes.data, *args)
     ga64, gb64 = ol.bw_f64(c["a"], c["b"], c["gy"], c["ga0"], c["gb0"], *args)
     assert ol.rel_err(ga, ga64) < 1e-5 and ol.rel_err(gb, gb64) < 1e-5
+
+
+@pytest.mark.parametrize("batches", [(6, 6), (1, 6), (6, 1)], ids=lambda b: "ba%d_bb%d" % b)
+@pytest.mark.parametrize("mode", ["3xtf32", "fp16"])
+def test_host_buffer_entry_points_pipeline_over_batch_chunks(ctx, mode, batches):
+    """Large enough that the host-buffer calls split the batch into several ragged chunks
+    (6 items in 4 chunks) and overlap upload, products and download; gradients pre-filled 0.5,
+    so a chunk added twice, skipped, or downloaded before its product finished would show."""
+    di = dj = dk = 512
+    ba, bb = batches
+    bs = max(ba, bb)
+    rng = np.random.default_rng(100 + 10 * ba + bb)
+    half = mode == "fp16"
+    dt = np.float16 if half else np.float32
+    a = rng.uniform(-1, 1, di * dj * ba).astype(np.float32).astype(dt)
+    b = rng.uniform(-1, 1, dj * dk * bb).astype(np.float32).astype(dt)
+    gy = rng.standard_normal(di * dk * bs).astype(np.float32).astype(dt)
+    a32, b32, gy32 = (x.astype(np.float32) for x in (a, b, gy))
+    args = (di, dj, dk, ba, bb)
+    tol = 2e-3 if half else 1e-5
+    y = np.full(di * dk * bs, 7.0, dt)
+    ctx.matmul_fw_host(MODES[mode], a.ctypes.data, b.ctypes.data, y.ctypes.data, *args)
+    assert ol.rel_err(y.astype(np.float32), ol.fw_f64(a32, b32, *args)) < tol
+    ga, gb = np.full(di * dj * ba, 0.5, dt), np.full(dj * dk * bb, 0.5, dt)
+    ctx.matmul_bw_host(MODES[mode], a.ctypes.data, b.ctypes.data, gy.ctypes.data, ga.ctypes.data, gb.ctypes.data, *args)
+    ga64, gb64 = ol.bw_f64(a32, b32, gy32, np.full(di * dj * ba, 0.5, np.float32),
+                           np.full(dj * dk * bb, 0.5, np.float32), *args)
+    assert ol.rel_err(ga.astype(np.float32), ga64) < tol and ol.rel_err(gb.astype(np.float32), gb64) < tol
