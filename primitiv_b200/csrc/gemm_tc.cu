@@ -195,15 +195,19 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
 #define B200_MMA_ASM(GROUP, KIND)                                                      \
   asm volatile(                                                                        \
       "{\n\t"                                                                          \
-      ".reg .pred p;\n\t"                                                              \
+      ".reg .pred p, e;\n\t"                                                           \
       ".reg .b64 da, db;\n\t"                                                          \
+      "elect.sync _|e, 0xffffffff;\n\t"                                                \
       "setp.ne.b32 p, %6, 0;\n\t"                                                      \
       "mov.b64 da, {%1, %2};\n\t"                                                      \
       "mov.b64 db, {%3, %4};\n\t"                                                      \
-      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %5, p;\n\t"       \
+      "@e tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %5, p;\n\t"    \
       "}\n" ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) \
       : "memory")
 
+// Called by ALL 32 lanes of the converged MMA warp with warp-uniform arguments; the
+// instruction itself is issued by the one lane elect.sync picks (the same lane every
+// time for a full mask, so tcgen05.commit from that lane tracks these MMAs).
 template <int kCtas, bool kF16>
 __device__ __forceinline__ void mma_issue(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
                                           uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
@@ -215,16 +219,20 @@ __device__ __forceinline__ void mma_issue(uint32_t d_tmem, uint32_t a_lo, uint32
 }
 
 // Runs the k-steps (and, for 3xTF32, the three hi/lo pass combinations) of one pipeline stage.
-template <int kCtas, bool kF16>
+// Runs the k-steps (and, for 3xTF32, the three hi/lo pass combinations) of one k-block as
+// straight-line code: every transfer of control between two MMAs showed up as a gap in the
+// tensor pipe, so a pipeline stage is one basic block of 8 (single-pass, two k-blocks) or 12
+// (3xTF32) MMAs.
+template <int kCtas, bool kF16, int kPasses>
 __device__ __forceinline__ void mma_stage(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t a_plane, uint32_t b_plane,
                                           uint32_t a_hi, uint32_t b_hi, uint32_t a_lo_fixed, uint32_t b_lo_fixed,
-                                          uint32_t kstep_a, uint32_t kstep_b, uint32_t idesc, uint32_t passes,
-                                          bool first) {
+                                          uint32_t kstep_a, uint32_t kstep_b, uint32_t idesc, bool first) {
   uint32_t acc = first ? 0u : 1u;
-  for (uint32_t ps = 0; ps < passes; ++ps) {
+#pragma unroll
+  for (int ps = 0; ps < kPasses; ++ps) {
     // 3xTF32: (lo, hi), (hi, lo), (hi, hi) -- small terms first
-    const uint32_t ia = (passes == 3u && ps == 0u) ? a_plane : 0u;
-    const uint32_t ib = (passes == 3u && ps == 1u) ? b_plane : 0u;
+    const uint32_t ia = (kPasses == 3 && ps == 0) ? a_plane : 0u;
+    const uint32_t ib = (kPasses == 3 && ps == 1) ? b_plane : 0u;
     uint32_t a_lo = a_lo_fixed | (((sa + ia) & 0x3FFFFu) >> 4);
     uint32_t b_lo = b_lo_fixed | (((sb + ib) & 0x3FFFFu) >> 4);
 #pragma unroll
@@ -238,8 +246,13 @@ __device__ __forceinline__ void mma_stage(uint32_t d_tmem, uint32_t sa, uint32_t
 }
 
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
+  asm volatile(
+      "{\n\t"
+      ".reg .pred e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}\n" ::"r"(bar)
+      : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() {
@@ -306,7 +319,11 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
 // the MMAs issued so far have retired
 __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
   asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "{\n\t"
+      ".reg .pred e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t"
+      "}\n" ::"r"(bar),
       "h"(static_cast<uint16_t>(3))
       : "memory");
 }
@@ -370,8 +387,12 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uin
 // CTA's TMEM receives the 128 accumulator rows of its half of M for all bn columns.  Per
 // CTA that is a third less shared-memory fill and operand traffic per FLOP than the
 // single-CTA tile, which is what bounds this kernel.
-template <bool kChunked, int kCtas>
+template <bool kChunked, int kCtas, int kKind>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ TcParams p) {
+  constexpr int kPasses = kKind == 0 ? 3 : 1;   // kind 0 = 3xTF32, 1 = TF32, 2 = FP16
+  constexpr uint32_t kSubs = kPasses == 1 ? 2u : 1u;  // k-blocks per pipeline stage
+  constexpr bool kF16 = kKind == 2;
+  static_assert(!kChunked || kKind == 0, "only the 3xTF32 product is chunked");
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
   __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
@@ -428,77 +449,79 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
   const uint32_t total_tiles = tiles_per_group * p.groups;
   const uint32_t kb_per_tile = p.red * p.kblocks;  // k-blocks of one tile, over both contraction axes
   const uint32_t chunks_per_tile = (kb_per_tile + p.chunk_kblocks - 1) / p.chunk_kblocks;
-  const uint32_t planes = p.passes == 3u ? 2u : 1u;  // hi and lo planes share a stage
+  constexpr uint32_t planes = kPasses == 3 ? 2u : 1u;  // hi and lo planes share a stage
   const uint32_t b_rows = p.bn / kCtas;               // rows of B this CTA stages
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+    // The whole warp walks the loop; the boxes of one pipeline stage are issued side by side,
+    // one per lane (each lane keeps its box's shared-memory offset, tensor map and coordinate
+    // offsets in registers), so a stage costs one wait and one issue slot, not a serial chain.
+    {
       uint32_t stage = 0, phase = 0;
       uint32_t armed_mask = 0, armed_parity = 0;
       bool ok = true;
+      const uint32_t stage_bytes = p.stage_bytes, nstages = p.stages, dbg = p.debug, kblocks = p.kblocks,
+                     red = p.red, kstage = kSubs * p.bk;
+      const uint32_t tx_bytes = p.stage_bytes * kCtas;
+      // this lane's box: [sub][plane][A boxes..., B boxes...]
+      const uint32_t a_boxes = p.a_mn_major ? p.a_chunks : 1u, b_boxes = p.b_mn_major ? p.b_chunks : 1u;
+      const uint32_t per_plane = a_boxes + b_boxes;
+      const uint32_t nboxes = kSubs * planes * per_plane;  // <= 32, checked on the host
+      const bool has_box = lane < nboxes;
+      const uint32_t bsub = lane / (planes * per_plane), brem = lane % (planes * per_plane);
+      const uint32_t bpl = (brem / per_plane) & 1u, bidx = brem % per_plane;
+      const bool is_b = bidx >= a_boxes;
+      const uint32_t bchunk = is_b ? bidx - a_boxes : bidx;
+      const bool box_mn = is_b ? p.b_mn_major != 0u : p.a_mn_major != 0u;
+      const uint32_t box_dst = bsub * p.sub_bytes +
+                               (is_b ? planes * p.a_stage_bytes + bpl * p.b_stage_bytes + bchunk * p.b_chunk_bytes
+                                     : bpl * p.a_stage_bytes + bchunk * p.a_chunk_bytes);
+      const int box_k = static_cast<int>(bsub * p.bk);
+      const int box_mn_off = static_cast<int>(box_mn ? bchunk * (is_b ? p.b_chunk_elems : p.a_chunk_elems) : 0u);
+      const CUtensorMap *box_map = is_b ? &p.mapB[bpl] : &p.mapA[bpl];
       for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         uint32_t g, mt, nt;
         tile_coords(tile, p.tiles_m, p.tiles_n, g, mt, nt);
         const int m0 = static_cast<int>(mt * (kBM * kCtas) + cta_rank * kBM);
         const int n0 = static_cast<int>(nt * p.bn + cta_rank * b_rows);
-        for (uint32_t r = 0; ok && r < p.red; ++r) {
-          const int za = static_cast<int>(g * p.a_gmul + r * p.a_rmul);
-          const int zb = static_cast<int>(g * p.b_gmul + r * p.b_rmul);
-          for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
-            if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
+        const int mn = (is_b ? n0 : m0) + box_mn_off;
+        for (uint32_t r = 0; ok && r < red; ++r) {
+          const int z = static_cast<int>(is_b ? g * p.b_gmul + r * p.b_rmul : g * p.a_gmul + r * p.a_rmul);
+          int k0 = box_k;
+          for (uint32_t kb = 0; kb < kblocks; ++kb, k0 += static_cast<int>(kstage)) {
+            if (dbg & 16u) continue;  // development: the MMA thread runs without stage hand-offs
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag))) {
               ok = false;
               break;
             }
             const uint32_t own_bar = smem_u32(&full_bar[stage]);
             // both CTAs of a pair report their bytes to the leader's barrier
             const uint32_t bar = kCtas == 2 ? map_to_cta(own_bar, 0u) : own_bar;
-            if (p.debug & 4u) {
-              if (leader) mbar_arrive(own_bar);
-              if (++stage == p.stages) { stage = 0; phase ^= 1u; }
-              continue;
-            }
-            if (leader) {
-              mbar_arrive_expect_tx(own_bar, p.stage_bytes * kCtas);
-              armed_mask |= 1u << stage;
-              armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
-            }
-            for (uint32_t sub = 0; sub < p.subs; ++sub) {
-            const int k0 = static_cast<int>((kb * p.subs + sub) * p.bk);
-            const uint32_t sa = smem_base + stage * p.stage_bytes + sub * p.sub_bytes;
-            const uint32_t sb = sa + planes * p.a_stage_bytes;
-            for (uint32_t pl = 0; pl < planes; ++pl) {
-              const uint32_t da = sa + pl * p.a_stage_bytes, db = sb + pl * p.b_stage_bytes;
-              if (p.a_mn_major) {
-                for (uint32_t c = 0; c < p.a_chunks; ++c) {
-                  const int mc = m0 + static_cast<int>(c * p.a_chunk_elems);
-                  if constexpr (kCtas == 2) tma_load_3d_pair(da + c * p.a_chunk_bytes, &p.mapA[pl], bar, mc, k0, za);
-                  else tma_load_3d(da + c * p.a_chunk_bytes, &p.mapA[pl], bar, mc, k0, za);
-                }
-              } else {
-                if constexpr (kCtas == 2) tma_load_3d_pair(da, &p.mapA[pl], bar, k0, m0, za);
-                else tma_load_3d(da, &p.mapA[pl], bar, k0, m0, za);
+            if (dbg & 4u) {
+              if (leader && lane == 0) mbar_arrive(own_bar);
+            } else {
+              if (leader) {
+                if (lane == 0) mbar_arrive_expect_tx(own_bar, tx_bytes);
+                armed_mask |= 1u << stage;
+                armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
               }
-              if (p.b_mn_major) {
-                for (uint32_t c = 0; c < p.b_chunks; ++c) {
-                  const int nc = n0 + static_cast<int>(c * p.b_chunk_elems);
-                  if constexpr (kCtas == 2) tma_load_3d_pair(db + c * p.b_chunk_bytes, &p.mapB[pl], bar, nc, k0, zb);
-                  else tma_load_3d(db + c * p.b_chunk_bytes, &p.mapB[pl], bar, nc, k0, zb);
-                }
-              } else {
-                if constexpr (kCtas == 2) tma_load_3d_pair(db, &p.mapB[pl], bar, k0, n0, zb);
-                else tma_load_3d(db, &p.mapB[pl], bar, k0, n0, zb);
+              if (has_box) {
+                const uint32_t dst = smem_base + stage * stage_bytes + box_dst;
+                const int c0 = box_mn ? mn : k0, c1 = box_mn ? k0 : mn;
+                if constexpr (kCtas == 2) tma_load_3d_pair(dst, box_map, bar, c0, c1, z);
+                else tma_load_3d(dst, box_map, bar, c0, c1, z);
               }
             }
-            }
-            if (++stage == p.stages) {
+            __syncwarp();
+            if (++stage == nstages) {
               stage = 0;
               phase ^= 1u;
             }
           }
         }
       }
-      if (*abort_flag && leader) {
+      if (*abort_flag && leader && lane == 0) {
         // let the copies in flight (this CTA's and, for a pair, the peer's, which report to
         // the same barriers) land before shared memory is given up
         for (uint32_t s = 0; s < p.stages; ++s)
@@ -509,7 +532,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0 && leader) {
+    // The whole warp walks the loop and waits on the barriers together; one lane issues.
+    // (A lone lane looping inside a diverged warp pays a scheduling penalty at every loop
+    // back-edge, which showed as ~200 ns per pipeline stage.)
+    if (leader) {
       uint32_t stage = 0, phase = 0;
       uint32_t chunk_no = 0;  // chunks this CTA has started, over all its tiles
       bool ok = true;
@@ -519,42 +545,52 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       const uint32_t a_lo_fixed = ((p.lbo_a >> 4) & 0x3FFFu) << 16;
       const uint32_t b_lo_fixed = ((p.lbo_b >> 4) & 0x3FFFu) << 16;
       const uint32_t kstep_a = p.kstep_a_bytes >> 4, kstep_b = p.kstep_b_bytes >> 4;
+      // Everything the loop needs sits in registers: the asm statements below clobber memory,
+      // and a parameter re-read after each of them is latency the tensor core waits out
+      // (the issue queue is shallow, so a gap between two MMAs is a gap in the pipe).
+      const uint32_t stage_bytes = p.stage_bytes, sub_bytes = p.sub_bytes;
+      const uint32_t a_plane = p.a_stage_bytes, b_plane = p.b_stage_bytes, b_off = planes * p.a_stage_bytes;
+      const uint32_t idesc = p.idesc, nstages = p.stages, dbg = p.debug;
+      const uint32_t chunk_kblocks = p.chunk_kblocks, bn = p.bn;
       for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         uint32_t kb_left = kb_per_tile;
         for (uint32_t c = 0; ok && c < chunks_per_tile; ++c, ++chunk_no) {
           const uint32_t buf = chunk_no & 1u;
           const uint32_t buf_phase = (chunk_no >> 1) & 1u;
-          if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abort_flag)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abort_flag))) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + buf * p.bn;
-          const uint32_t kbs = kb_left < p.chunk_kblocks ? kb_left : p.chunk_kblocks;
+          const uint32_t d_tmem = tmem_base + buf * bn;
+          const uint32_t kbs = kb_left < chunk_kblocks ? kb_left : chunk_kblocks;
           kb_left -= kbs;
+          uint32_t sa = smem_base + stage * stage_bytes;
           for (uint32_t it = 0; it < kbs; ++it) {
-            if (!(p.debug & 8u) && !mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag)) {
+            // No tcgen05 fence after this wait: the barrier orders the TMA writes (async proxy)
+            // before the MMA's reads (async proxy); the fence is for tcgen05.ld/st of other threads.
+            if (!(dbg & 24u) && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag))) {
               ok = false;
               break;
             }
-            tc_fence_after();
-            for (uint32_t sub = 0; sub < p.subs && !(p.debug & 2u); ++sub) {
-              const uint32_t sa = smem_base + stage * p.stage_bytes + sub * p.sub_bytes;
-              const uint32_t sb = sa + planes * p.a_stage_bytes;
-              const bool first = (it | sub) == 0u;
-              if (p.kind_f16)
-                mma_stage<kCtas, true>(d_tmem, sa, sb, p.a_stage_bytes, p.b_stage_bytes, a_hi, b_hi, a_lo_fixed,
-                                       b_lo_fixed, kstep_a, kstep_b, p.idesc, p.passes, first);
-              else
-                mma_stage<kCtas, false>(d_tmem, sa, sb, p.a_stage_bytes, p.b_stage_bytes, a_hi, b_hi, a_lo_fixed,
-                                        b_lo_fixed, kstep_a, kstep_b, p.idesc, p.passes, first);
+            if (!(dbg & 2u)) {
+#pragma unroll
+              for (uint32_t sub = 0; sub < kSubs; ++sub) {
+                const uint32_t ssa = sa + sub * sub_bytes;
+                mma_stage<kCtas, kF16, kPasses>(d_tmem, ssa, ssa + b_off, a_plane, b_plane, a_hi, b_hi, a_lo_fixed,
+                                                b_lo_fixed, kstep_a, kstep_b, idesc, (it | sub) == 0u);
+              }
             }
             // frees the stage (in both CTAs of a pair) when these MMAs retire
-            if constexpr (kCtas == 2) mma_commit_pair(smem_u32(&empty_bar[stage]));
-            else mma_commit(smem_u32(&empty_bar[stage]));
-            if (++stage == p.stages) {
+            if (!(dbg & 16u)) {
+              if constexpr (kCtas == 2) mma_commit_pair(smem_u32(&empty_bar[stage]));
+              else mma_commit(smem_u32(&empty_bar[stage]));
+            }
+            sa += stage_bytes;
+            if (++stage == nstages) {
               stage = 0;
               phase ^= 1u;
+              sa = smem_base;
             }
           }
           if (ok) {
@@ -565,6 +601,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       }
       if (*abort_flag) {
         // retire whatever was issued before TMEM is freed
+        __syncwarp();
         if constexpr (kCtas == 2) mma_commit_pair(smem_u32(&drain_bar));
         else mma_commit(smem_u32(&drain_bar));
         mbar_wait_quiet(smem_u32(&drain_bar), 0);
@@ -1006,10 +1043,14 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   p.a_stage_bytes = kBM * 128u;
   p.b_stage_bytes = b_rows * 128u;
   p.sub_bytes = planes * (p.a_stage_bytes + p.b_stage_bytes);
-  // Single-pass modes issue only four MMAs per k-block; two k-blocks per pipeline stage halve
-  // the per-stage hand-off cost as long as three such stages still fit.
-  const size_t smem_budget = ctx->smem_optin > 8192 ? ctx->smem_optin - 1024 : 0;
-  p.subs = (passes == 1 && g.k > p.bk && smem_budget >= 1024 + 3ull * 2 * p.sub_bytes) ? 2u : 1u;
+  // Single-pass modes issue only four MMAs per k-block: their pipeline stage holds two k-blocks
+  // (a k-block past the end of k is zero-filled by TMA and adds nothing), 3xTF32 stages hold one.
+  p.subs = passes == 1 ? 2u : 1u;
+  {
+    // the producer warp issues one TMA box per lane and stage
+    const uint32_t boxes = planes * ((p.a_mn_major ? kBM / chunk : 1u) + (p.b_mn_major ? b_rows / chunk : 1u));
+    if (p.subs * boxes > 32u) return B200_ERR_INVALID_ARG;
+  }
   p.stage_bytes = p.subs * p.sub_bytes;
   p.kblocks = (g.k + p.bk * p.subs - 1) / (p.bk * p.subs);  // pipeline-stage iterations along k
   p.layout_a = p.layout_b = 2u;  // 128-byte swizzle
@@ -1086,13 +1127,18 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   }
   if (rc == B200_OK && !ctx->tc_smem_configured) {
     const int max_dyn = static_cast<int>(ctx->smem_optin - 512);
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_tc_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_tc_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_tc_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
+    cudaError_t e = cudaSuccess;
+    auto allow = [&](auto kernel) {
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn);
+    };
+    allow(gemm_tc_kernel<true, 1, 0>);
+    allow(gemm_tc_kernel<false, 1, 0>);
+    allow(gemm_tc_kernel<false, 1, 1>);
+    allow(gemm_tc_kernel<false, 1, 2>);
+    allow(gemm_tc_kernel<true, 2, 0>);
+    allow(gemm_tc_kernel<false, 2, 0>);
+    allow(gemm_tc_kernel<false, 2, 1>);
+    allow(gemm_tc_kernel<false, 2, 2>);
     if (e != cudaSuccess) rc = static_cast<int>(e);
     ctx->tc_smem_configured = (e == cudaSuccess);
   }
@@ -1115,13 +1161,20 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
       attr.val.clusterDim.z = 1;
       cfg.attrs = &attr;
       cfg.numAttrs = 1;
-      const cudaError_t e = chunked ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, 2>, p)
-                                    : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2>, p);
+      cudaError_t e;
+      if (chunked) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, 2, 0>, p);
+      else if (passes == 3) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 0>, p);
+      else if (!f16) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 1>, p);
+      else e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 2>, p);
       rc = static_cast<int>(e);
     } else if (chunked) {
-      gemm_tc_kernel<true, 1><<<grid, kThreads, smem_bytes, stream>>>(p);
+      gemm_tc_kernel<true, 1, 0><<<grid, kThreads, smem_bytes, stream>>>(p);
+    } else if (passes == 3) {
+      gemm_tc_kernel<false, 1, 0><<<grid, kThreads, smem_bytes, stream>>>(p);
+    } else if (!f16) {
+      gemm_tc_kernel<false, 1, 1><<<grid, kThreads, smem_bytes, stream>>>(p);
     } else {
-      gemm_tc_kernel<false, 1><<<grid, kThreads, smem_bytes, stream>>>(p);
+      gemm_tc_kernel<false, 1, 2><<<grid, kThreads, smem_bytes, stream>>>(p);
     }
     ++ctx->launches;
     if (rc == B200_OK) rc = static_cast<int>(cudaGetLastError());
