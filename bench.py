@@ -322,9 +322,10 @@ def emit(args, wl, world, ms, prof, launches, sampler, e2e, collectives):
     achieved = issued_flops_per_launch / (tc_avg_ms * 1e-3) / 1e12 if tc_n else 0.0
     div = 1.0 if wl.half else 2.0     # TF32 runs at half the 16-bit rate
     peak, burst = peaks["bf16_sustained"] / div, peaks["bf16_burst"] / div
-    # DRAM bytes of one gemm_tc_kernel launch: ncu capture of the batch-2 square case (1.64 GB, see
-    # profiles/), scaled by the batch (independent products, traffic grows in proportion)
-    traffic = 1.64e9 * wl.bs / 2.0 if wl.name == "batched_square" else None
+    # DRAM bytes of one gemm_tc_kernel launch: ncu capture of the batch-2 square case (1.48 GB, mean of
+    # an overwriting and an accumulating launch, see profiles/), scaled by the batch (independent
+    # products, traffic grows in proportion)
+    traffic = 1.48e9 * wl.bs / 2.0 if wl.name == "batched_square" else None
     line = {
         "metric": METRIC, "value": value, "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",

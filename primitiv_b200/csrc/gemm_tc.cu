@@ -31,7 +31,16 @@
 // i.e. a stride-byte-offset of 512; under the plain pattern it returns zeros.
 //
 // Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
-// owner, warps 2-9 = epilogue.  Output row i of the tile lives in TMEM lane i, so
+// owner, warps 2-9 = epilogue.  Both pipeline warps walk their loops converged:
+// all 32 lanes wait on the barriers, the boxes of a stage are issued side by side
+// (one per lane), and the MMAs of a stage are one straight-line block issued under
+// elect.sync with everything they need in registers.  (A lone lane looping in a
+// diverged warp, parameter re-reads after each asm statement, and branches between
+// MMAs each left the tensor pipe idle for 100-200 ns per stage; with them gone the
+// issue path alone sustains the tensor peak, and MN-major operands, which need more
+// and smaller boxes, load as fast as K-major ones.)  A pipeline stage is one k-block
+// with hi and lo planes (3xTF32: 12 MMAs) or two k-blocks (single pass: 8 MMAs).
+// Output row i of the tile lives in TMEM lane i, so
 // for a fixed output column the 32 lanes of a warp hold 32 consecutive rows:
 // column-major C is written (and, for +=, read) with coalesced 128-byte accesses
 // straight from registers.
@@ -73,7 +82,7 @@ struct alignas(64) TcParams {
   CUtensorMap mapB[2];
   void *C;
   unsigned long long c_gs;
-  uint32_t m, n;
+  uint32_t m, n, k;
   uint32_t kblocks, red, groups;
   uint32_t tiles_m, tiles_n;
   uint32_t bn, bk, stages;
@@ -89,6 +98,7 @@ struct alignas(64) TcParams {
   uint32_t passes;
   uint32_t chunk_kblocks;  // k-blocks per accumulation chunk
   uint32_t accumulate, out_half, kind_f16;
+  uint32_t band_m;  // tile-rows per band of the tile order
   uint32_t a_stage_bytes, b_stage_bytes, stage_bytes;  // per plane, per CTA; stage = subs * planes * (a + b)
   uint32_t subs, sub_bytes;  // k-blocks per pipeline stage and the bytes of one (planes * (a + b))
   uint32_t tmem_cols;
@@ -367,16 +377,16 @@ __device__ __forceinline__ void store_cols(T *C, unsigned long long base, uint32
 // 8192 x 8192 halves, re-reads A from HBM for every column-tile).
 constexpr uint32_t kBandTilesM = 8;
 
-__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t &g,
-                                            uint32_t &mt, uint32_t &nt) {
+__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t band_m,
+                                            uint32_t &g, uint32_t &mt, uint32_t &nt) {
   const uint32_t per_group = tiles_m * tiles_n;
   g = tile / per_group;
   const uint32_t rem = tile - g * per_group;
-  const uint32_t band_tiles = kBandTilesM * tiles_n;
+  const uint32_t band_tiles = band_m * tiles_n;
   const uint32_t band = rem / band_tiles;
   const uint32_t in_band = rem - band * band_tiles;
-  const uint32_t first_m = band * kBandTilesM;
-  const uint32_t rows = tiles_m - first_m < kBandTilesM ? tiles_m - first_m : kBandTilesM;
+  const uint32_t first_m = band * band_m;
+  const uint32_t rows = tiles_m - first_m < band_m ? tiles_m - first_m : band_m;
   mt = first_m + in_band % rows;
   nt = in_band / rows;
 }
@@ -482,7 +492,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       const CUtensorMap *box_map = is_b ? &p.mapB[bpl] : &p.mapA[bpl];
       for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         uint32_t g, mt, nt;
-        tile_coords(tile, p.tiles_m, p.tiles_n, g, mt, nt);
+        tile_coords(tile, p.tiles_m, p.tiles_n, p.band_m, g, mt, nt);
         const int m0 = static_cast<int>(mt * (kBM * kCtas) + cta_rank * kBM);
         const int n0 = static_cast<int>(nt * p.bn + cta_rank * b_rows);
         const int mn = (is_b ? n0 : m0) + box_mn_off;
@@ -623,7 +633,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     const uint32_t empty1 = kCtas == 2 ? map_to_cta(smem_u32(&tmem_empty_bar[1]), 0u) : smem_u32(&tmem_empty_bar[1]);
     for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
       uint32_t g, mt, nt;
-      tile_coords(tile, p.tiles_m, p.tiles_n, g, mt, nt);
+      tile_coords(tile, p.tiles_m, p.tiles_n, p.band_m, g, mt, nt);
       const uint32_t m0 = mt * (kBM * kCtas);
       const uint32_t n0 = nt * p.bn;
       const uint32_t row = m0 + row_in_tile;
@@ -944,6 +954,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   p.bn = g.n > 128 ? 256u : (g.n > 64 ? 128u : 64u);
   p.m = g.m;
   p.n = g.n;
+  p.k = g.k;
   p.kblocks = (g.k + p.bk - 1) / p.bk;
   p.red = g.red;
   p.groups = g.groups;
@@ -1107,6 +1118,8 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   {
     static const char *dbg = std::getenv("PRIMITIV_B200_TC_DEBUG");
     p.debug = dbg ? static_cast<uint32_t>(std::atoi(dbg)) : 0u;
+    static const char *bd = std::getenv("PRIMITIV_B200_TC_BAND");
+    p.band_m = bd && std::atoi(bd) > 0 ? static_cast<uint32_t>(std::atoi(bd)) : kBandTilesM;
     static const char *st = std::getenv("PRIMITIV_B200_TC_STAGES");
     if (st) ctx->debug_stage_cap = std::atoi(st);
   }
