@@ -196,7 +196,9 @@ int b200_gemm(b200_ctx *ctx, int mode, int trans_a, int trans_b, const void *A, 
   // A 128-row MMA tile on a problem this small is mostly padding; the CUDA-core
   // kernel wins below roughly a tile's worth of work.
   const double macs = static_cast<double>(m) * n * k * groups * red;
-  if (eligible && m >= 32 && n >= 16 && macs >= 2097152.0) return b200::gemm_tc(ctx, g, s);
+  // (a few rows against a long contraction are still worth it: the tensor-core path splits k
+  // over all SMs and streams the big operand once, the CUDA-core kernel would run on a few CTAs)
+  if (eligible && n >= 16 && macs >= 2097152.0 && (m >= 32 || macs >= 67108864.0)) return b200::gemm_tc(ctx, g, s);
   return b200::gemm_simt(ctx, g, s);
 }
 

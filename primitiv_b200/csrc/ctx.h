@@ -61,6 +61,7 @@ struct b200_ctx {
   int path_policy = 0;           // 0 = choose per problem, 1 = CUDA-core kernel, 2 = tensor-core kernel when eligible
   int debug_stage_cap = 0;       // development: cap on pipeline stages (0 = none)
   int pair_policy = 0;           // 0 = CTA pairs (cta_group::2) when the problem allows, 1 = single CTAs only
+  int split_policy = 0;          // 0 = split k over idle CTAs when there are few output tiles, 1 = never
   std::uint64_t rng_seed = 0, rng_calls = 0;  // Philox key and fill counter (b200_seed / b200_random)
   // optional per-launch timing (b200_profile_*): event pairs, summed when read
   bool profiling = false;

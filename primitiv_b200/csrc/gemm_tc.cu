@@ -99,6 +99,8 @@ struct alignas(64) TcParams {
   uint32_t chunk_kblocks;  // k-blocks per accumulation chunk
   uint32_t accumulate, out_half, kind_f16;
   uint32_t band_m;  // tile-rows per band of the tile order
+  uint32_t splits;  // k-splits per output tile (split-K): `groups` then counts groups x splits,
+                    // kblocks is per split and C is the fp32 partial buffer [group][split][m x n]
   uint32_t a_stage_bytes, b_stage_bytes, stage_bytes;  // per plane, per CTA; stage = subs * planes * (a + b)
   uint32_t subs, sub_bytes;  // k-blocks per pipeline stage and the bytes of one (planes * (a + b))
   uint32_t tmem_cols;
@@ -474,6 +476,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       const uint32_t stage_bytes = p.stage_bytes, nstages = p.stages, dbg = p.debug, kblocks = p.kblocks,
                      red = p.red, kstage = kSubs * p.bk;
       const uint32_t tx_bytes = p.stage_bytes * kCtas;
+      const uint32_t splits = p.splits;
       // this lane's box: [sub][plane][A boxes..., B boxes...]
       const uint32_t a_boxes = p.a_mn_major ? p.a_chunks : 1u, b_boxes = p.b_mn_major ? p.b_chunks : 1u;
       const uint32_t per_plane = a_boxes + b_boxes;
@@ -491,14 +494,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       const int box_mn_off = static_cast<int>(box_mn ? bchunk * (is_b ? p.b_chunk_elems : p.a_chunk_elems) : 0u);
       const CUtensorMap *box_map = is_b ? &p.mapB[bpl] : &p.mapA[bpl];
       for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
-        uint32_t g, mt, nt;
-        tile_coords(tile, p.tiles_m, p.tiles_n, p.band_m, g, mt, nt);
+        uint32_t vg, mt, nt;
+        tile_coords(tile, p.tiles_m, p.tiles_n, p.band_m, vg, mt, nt);
+        const uint32_t g = vg / splits, split = vg - g * splits;  // split-K: this tile's slice of k
         const int m0 = static_cast<int>(mt * (kBM * kCtas) + cta_rank * kBM);
         const int n0 = static_cast<int>(nt * p.bn + cta_rank * b_rows);
         const int mn = (is_b ? n0 : m0) + box_mn_off;
         for (uint32_t r = 0; ok && r < red; ++r) {
           const int z = static_cast<int>(is_b ? g * p.b_gmul + r * p.b_rmul : g * p.a_gmul + r * p.a_rmul);
-          int k0 = box_k;
+          int k0 = box_k + static_cast<int>(split * kblocks * kstage);
           for (uint32_t kb = 0; kb < kblocks; ++kb, k0 += static_cast<int>(kstage)) {
             if (dbg & 16u) continue;  // development: the MMA thread runs without stage hand-offs
             if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag))) {
@@ -729,6 +733,30 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     else
       asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols)
                    : "memory");
+  }
+}
+
+// ------------------------------ split-K reduction ------------------------------
+//
+// A product with few output tiles and a long contraction (the gradient of a broadcast weight:
+// m x n small, k = everything in the minibatch) would leave most SMs idle.  Its k range is cut
+// into `splits` slices, every (tile, slice) is a work item of the main kernel writing an fp32
+// partial tile, and this kernel adds the slices in a fixed order (no atomics: results are the
+// same bits every run) into C.
+template <typename T>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ partial, T *__restrict__ C,
+                                                            unsigned long long mn, uint32_t groups, uint32_t splits,
+                                                            unsigned long long c_gs, int accumulate) {
+  const unsigned long long total = mn * groups;
+  for (unsigned long long idx = blockIdx.x * 256ull + threadIdx.x; idx < total;
+       idx += static_cast<unsigned long long>(gridDim.x) * 256ull) {
+    const unsigned long long g = idx / mn, i = idx - g * mn;
+    const float *src = partial + g * splits * mn + i;
+    float sum = src[0];
+    for (uint32_t sidx = 1; sidx < splits; ++sidx) sum += src[sidx * mn];
+    T *dst = C + g * c_gs + i;
+    if (accumulate) sum += static_cast<float>(*dst);
+    *dst = static_cast<T>(sum);
   }
 }
 
@@ -1064,6 +1092,28 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   }
   p.stage_bytes = p.subs * p.sub_bytes;
   p.kblocks = (g.k + p.bk * p.subs - 1) / (p.bk * p.subs);  // pipeline-stage iterations along k
+  // Split-K: with fewer tiles than half the CTAs (or pairs) and a long contraction, slices of k go
+  // to the idle ones (at least four pipeline stages each) and splitk_reduce_kernel adds them up.
+  uint32_t splits = 1;
+  void *partial = nullptr;
+  {
+    const uint64_t units = static_cast<uint64_t>(ctx->sm_count) / ctas;
+    static const char *sp = std::getenv("PRIMITIV_B200_TC_SPLIT");  // development: 0 = never split
+    const bool allow = !(sp && std::atoi(sp) == 0) && ctx->split_policy != 1;
+    if (!fixed_scratch && allow && total_tiles * 2 <= units && p.kblocks >= 16u) {
+      uint64_t want = units / total_tiles;
+      if (want > p.kblocks / 4u) want = p.kblocks / 4u;
+      if (want > 64u) want = 64u;
+      if (want >= 2u) {
+        const uint32_t per = (p.kblocks + static_cast<uint32_t>(want) - 1u) / static_cast<uint32_t>(want);
+        splits = (p.kblocks + per - 1u) / per;  // no empty slices
+        p.kblocks = per;
+      }
+    }
+  }
+  p.splits = splits;
+  p.groups = g.groups * splits;
+  const uint64_t launch_tiles = total_tiles * splits;
   p.layout_a = p.layout_b = 2u;  // 128-byte swizzle
   CUtensorMapSwizzle swz_a = CU_TENSOR_MAP_SWIZZLE_128B, swz_b = CU_TENSOR_MAP_SWIZZLE_128B;
   if (p.a_mn_major) {
@@ -1113,6 +1163,18 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   p.kind_f16 = f16 ? 1u : 0u;
   p.C = g.C;
   p.c_gs = g.c_gs;
+  if (splits > 1) {
+    const uint64_t mn = static_cast<uint64_t>(g.m) * g.n;
+    const int arc = ctx->pool.alloc(mn * g.groups * splits * sizeof(float), &partial, nullptr);
+    if (arc != B200_OK) {
+      if (scratch) ctx->pool.free(scratch);
+      return arc;
+    }
+    p.C = partial;
+    p.c_gs = mn;
+    p.accumulate = 0u;
+    p.out_half = 0u;
+  }
   p.status = ctx->d_status;
   p.tmem_cols = p.bn * 2u;  // 128, 256 or 512: powers of two
   {
@@ -1158,7 +1220,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   if (rc == B200_OK) {
     // persistent: one CTA (or one pair) per tile up to one CTA per SM
     const uint64_t units = static_cast<uint64_t>(ctx->sm_count) / ctas;
-    const unsigned grid = static_cast<unsigned>((total_tiles < units ? total_tiles : units) * ctas);
+    const unsigned grid = static_cast<unsigned>((launch_tiles < units ? launch_tiles : units) * ctas);
     ProfScope prof(ctx, kProfGemmTc, stream);
     if (ctas == 2) {
       cudaLaunchConfig_t cfg;
@@ -1191,7 +1253,24 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     }
     ++ctx->launches;
     if (rc == B200_OK) rc = static_cast<int>(cudaGetLastError());
+    if (rc == B200_OK && splits > 1) {
+      const unsigned long long mn = static_cast<unsigned long long>(g.m) * g.n;
+      const unsigned long long need = (mn * g.groups + 255ull) / 256ull;
+      const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 8ull;
+      const unsigned blocks = static_cast<unsigned>(need < cap ? need : cap);
+      if (f16)
+        splitk_reduce_kernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const float *>(partial),
+                                                                   static_cast<__half *>(g.C), mn, g.groups, splits,
+                                                                   g.c_gs, g.accumulate);
+      else
+        splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float *>(partial),
+                                                                  static_cast<float *>(g.C), mn, g.groups, splits,
+                                                                  g.c_gs, g.accumulate);
+      ++ctx->launches;
+      rc = static_cast<int>(cudaGetLastError());
+    }
   }
+  if (partial) ctx->pool.free(partial);
   if (scratch) ctx->pool.free(scratch);  // stream-ordered reuse: later work queues behind this GEMM
   return rc;
 }

@@ -219,3 +219,34 @@ def test_host_buffer_entry_points_pipeline_over_batch_chunks(ctx, mode, batches)
     ga64, gb64 = ol.bw_f64(a32, b32, gy32, np.full(di * dj * ba, 0.5, np.float32),
                            np.full(dj * dk * bb, 0.5, np.float32), *args)
     assert ol.rel_err(ga.astype(np.float32), ga64) < tol and ol.rel_err(gb.astype(np.float32), gb64) < tol
+
+
+# Few output tiles against a long contraction: the tensor-core path cuts k into slices for the
+# idle SMs and adds the slices in a fixed order.  (di, dj, dk, ba, bb)
+SPLIT_K_SHAPES = [
+    (384, 320, 1, 1, 4096),    # gradient of a broadcast weight: 384 x 320 output, k = 4096 batch items
+    (10, 1024, 1, 1, 8192),    # a 10-row weight (classifier layer): a few rows, long k
+    (4096, 512, 1, 1, 64),     # recurrent step: gb is 512 x 64 with k = 4096
+    (200, 136, 8, 1, 700),     # ragged extents, slices that do not divide k
+]
+
+
+@pytest.mark.parametrize("mode", list(MODES))
+@pytest.mark.parametrize("shape", SPLIT_K_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_split_k_products(ctx, shape, mode):
+    di, dj, dk, ba, bb = shape
+    rng = np.random.default_rng(hash(shape) % (2 ** 32))
+    a = rng.uniform(-1, 1, di * dj * ba).astype(np.float32)
+    b = rng.uniform(-1, 1, dj * dk * bb).astype(np.float32)
+    gy = rng.standard_normal(di * dk * max(ba, bb)).astype(np.float32)
+    if mode == "fp16":   # keep the batch-summed gradients inside half's range
+        gy *= 0.05
+    for policy in (0, 2):
+        ctx.set_path_policy(policy)
+        try:
+            first = _check_all(ctx, mode, a, b, gy, di, dj, dk, ba, bb)
+            again = _check_all(ctx, mode, a, b, gy, di, dj, dk, ba, bb)
+        finally:
+            ctx.set_path_policy(0)
+        for x, y in zip(first, again):   # slices are added in a fixed order: same bits every run
+            assert np.array_equal(x, y)
