@@ -169,25 +169,49 @@ __global__ void __launch_bounds__(kBlock) binary_fw_kernel(const T *__restrict__
   }
 }
 
-// one thread per element of the volume, walking the batch in order
+// Both operands batched (or no batch at all): every gradient element receives exactly one term.
 template <typename T, int OP>
-__global__ void __launch_bounds__(kBlock) binary_bw_kernel(const T *__restrict__ a, const T *__restrict__ b,
-                                                           const T *__restrict__ y, const T *__restrict__ gy,
-                                                           T *__restrict__ ga, T *__restrict__ gb, u64 volume,
-                                                           uint32_t batch, int a_batched, int b_batched) {
+__global__ void __launch_bounds__(kBlock) binary_bw_flat_kernel(const T *__restrict__ a, const T *__restrict__ b,
+                                                                const T *__restrict__ y, const T *__restrict__ gy,
+                                                                T *__restrict__ ga, T *__restrict__ gb, u64 total) {
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
-  for (u64 i = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; i < volume; i += stride) {
-    float sum_a = 0.f, sum_b = 0.f;
-    for (uint32_t n = 0; n < batch; ++n) {
-      const u64 e = static_cast<u64>(n) * volume + i;
-      const u64 ea = a_batched ? e : i, eb = b_batched ? e : i;
-      float da, db;
-      binary_d<OP>(ld(a, ea), ld(b, eb), ld(y, e), ld(gy, e), da, db);
-      if (a_batched) st(ga, e, ld(ga, e) + da); else sum_a += da;
-      if (b_batched) st(gb, e, ld(gb, e) + db); else sum_b += db;
+  for (u64 e = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
+    float da, db;
+    binary_d<OP>(ld(a, e), ld(b, e), ld(y, e), ld(gy, e), da, db);
+    st(ga, e, ld(ga, e) + da);
+    st(gb, e, ld(gb, e) + db);
+  }
+}
+
+// One operand is broadcast over the batch: its gradient is the sum over the batch of the
+// per-item terms (32 x 8 CTAs over volume x batch slices, see batch_sum_tile_kernel); the
+// batched operand's gradient is updated in place on the way.
+template <typename T, int OP>
+__global__ void __launch_bounds__(256) binary_bw_mixed_kernel(const T *__restrict__ a, const T *__restrict__ b,
+                                                              const T *__restrict__ y, const T *__restrict__ gy,
+                                                              T *ga, T *gb, float *partial, u64 volume,
+                                                              uint32_t batch, uint32_t slice_len, int a_batched) {
+  __shared__ float buf[kSumLanes][32];
+  T *g_batched = a_batched ? ga : gb, *g_summed = a_batched ? gb : ga;
+  for (u64 tile = blockIdx.x; tile * 32ull < volume; tile += gridDim.x) {
+    const u64 i = tile * 32ull + threadIdx.x;
+    const uint32_t lo = blockIdx.y * slice_len;
+    const uint32_t hi = lo + slice_len < batch ? lo + slice_len : batch;
+    float v = 0.f;
+    if (i < volume) {
+      for (uint32_t n = lo + threadIdx.y; n < hi; n += kSumLanes) {
+        const u64 e = static_cast<u64>(n) * volume + i;
+        float da, db;
+        binary_d<OP>(ld(a, a_batched ? e : i), ld(b, a_batched ? i : e), ld(y, e), ld(gy, e), da, db);
+        st(g_batched, e, ld(g_batched, e) + (a_batched ? da : db));
+        v += a_batched ? db : da;
+      }
     }
-    if (!a_batched) st(ga, i, ld(ga, i) + sum_a);
-    if (!b_batched) st(gb, i, ld(gb, i) + sum_b);
+    const float t = combine_batch_lanes(v, buf);
+    if (threadIdx.y == 0 && i < volume) {
+      if (gridDim.y == 1) st(g_summed, i, ld(g_summed, i) + t);
+      else partial[static_cast<u64>(blockIdx.y) * volume + i] = t;
+    }
   }
 }
 
@@ -211,8 +235,9 @@ __global__ void __launch_bounds__(kBlock) inplace_add_kernel(const T *__restrict
   const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   constexpr int N = Vec<T>::N;
-  if (by >= bx && by > 1 || bx == by) {
+  {
     // every destination element gets exactly one source element: flat and vectorised
+    // (a batch-1 destination of a batched source is a batch sum: launch_batch_sum)
     const u64 total = volume * by;
     const u64 nv = vec ? total / N : 0;
     for (u64 i = tid; i < nv; i += stride) {
@@ -226,13 +251,6 @@ __global__ void __launch_bounds__(kBlock) inplace_add_kernel(const T *__restrict
     }
     for (u64 e = nv * N + tid; e < total; e += stride)
       st(y, e, ld(y, e) + sign * ld(x, bx > 1 ? e : e % volume));
-  } else {
-    // by == 1 < bx: the destination receives the sum over the batch, in batch order
-    for (u64 i = tid; i < volume; i += stride) {
-      float acc = ld(y, i);
-      for (uint32_t n = 0; n < bx; ++n) acc += sign * ld(x, static_cast<u64>(n) * volume + i);
-      st(y, i, acc);
-    }
   }
 }
 
@@ -323,15 +341,41 @@ void launch_binary_fw(b200_ctx *ctx, cudaStream_t s, int op, const void *a, cons
 }
 
 template <typename T>
-void launch_binary_bw(b200_ctx *ctx, cudaStream_t s, int op, const void *a, const void *b, const void *y,
-                      const void *gy, void *ga, void *gb, u64 volume, uint32_t batch, int a_batched,
-                      int b_batched) {
-  const unsigned grid = grid_for(ctx, volume, kBlock);
+int launch_binary_bw(b200_ctx *ctx, cudaStream_t s, int op, const void *a, const void *b, const void *y,
+                     const void *gy, void *ga, void *gb, u64 volume, uint32_t batch, int a_batched,
+                     int b_batched) {
+  const T *pa = static_cast<const T *>(a), *pb = static_cast<const T *>(b), *py = static_cast<const T *>(y),
+          *pgy = static_cast<const T *>(gy);
+  T *pga = static_cast<T *>(ga), *pgb = static_cast<T *>(gb);
+  if (batch == 1 || (a_batched && b_batched)) {
+    const u64 total = volume * batch;
+    const unsigned grid = grid_for(ctx, total, kBlock);
+    switch (op) {
+#define X(OP) case OP: binary_bw_flat_kernel<T, OP><<<grid, kBlock, 0, s>>>(pa, pb, py, pgy, pga, pgb, total); break;
+      B200_BINARY_OPS(X)
+#undef X
+    }
+    return B200_OK;
+  }
+  const BatchSlices bs = batch_slices(ctx, volume, batch);
+  void *partial = nullptr;
+  if (bs.slices > 1) {
+    const int rc = ctx->pool.alloc(static_cast<size_t>(bs.slices) * volume * sizeof(float), &partial, nullptr);
+    if (rc != B200_OK) return rc;
+  }
+  const dim3 grid(bs.tiles, bs.slices), block(32, kSumLanes);
   switch (op) {
-#define X(OP) case OP: binary_bw_kernel<T, OP><<<grid, kBlock, 0, s>>>(static_cast<const T *>(a), static_cast<const T *>(b), static_cast<const T *>(y), static_cast<const T *>(gy), static_cast<T *>(ga), static_cast<T *>(gb), volume, batch, a_batched, b_batched); break;
+#define X(OP) case OP: binary_bw_mixed_kernel<T, OP><<<grid, block, 0, s>>>(pa, pb, py, pgy, pga, pgb, static_cast<float *>(partial), volume, batch, bs.slice_len, a_batched); break;
     B200_BINARY_OPS(X)
 #undef X
   }
+  if (bs.slices > 1) {
+    batch_final_kernel<T><<<grid_for(ctx, volume, 256), 256, 0, s>>>(static_cast<const float *>(partial),
+                                                                     a_batched ? pgb : pga, volume, bs.slices, 1.f, 1);
+    ++ctx->launches;
+    ctx->pool.free(partial);  // stream-ordered reuse
+  }
+  return B200_OK;
 }
 
 }  // namespace
@@ -392,7 +436,10 @@ int b200_binary_bw(b200_ctx *ctx, int mode, int op, const void *a, const void *b
   if (volume == 0 || batch == 0) return B200_OK;
   if (!a || !b || !y || !gy || !ga || !gb || op < 0 || op > B200_OP_POW) return B200_ERR_INVALID_ARG;
   ProfScope prof(ctx, kProfElementwise, s);
-  B200_DISPATCH_MODE(mode, { launch_binary_bw<T>(ctx, s, op, a, b, y, gy, ga, gb, volume, batch, a_batched, b_batched); });
+  B200_DISPATCH_MODE(mode, {
+    const int rc = launch_binary_bw<T>(ctx, s, op, a, b, y, gy, ga, gb, volume, batch, a_batched, b_batched);
+    if (rc != B200_OK) return rc;
+  });
   B200_OPS_EPILOGUE(ctx);
 }
 
@@ -403,10 +450,16 @@ int b200_inplace_add(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t v
   if (!x || !y || (bx != by && bx != 1 && by != 1)) return B200_ERR_INVALID_ARG;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    const int vec = aligned16(x) && aligned16(y) && volume % Vec<T>::N == 0;
-    const u64 work = (by == 1 && bx > 1) ? volume : volume * by / (vec ? Vec<T>::N : 1) + 1;
-    inplace_add_kernel<T><<<grid_for(ctx, work, kBlock), kBlock, 0, s>>>(
-        static_cast<const T *>(x), static_cast<T *>(y), volume, bx, by, sign, vec);
+    if (by == 1 && bx > 1) {
+      // the destination receives the sum over the batch
+      const int rc = launch_batch_sum<T>(ctx, s, x, y, volume, bx, sign, 1);
+      if (rc != B200_OK) return rc;
+    } else {
+      const int vec = aligned16(x) && aligned16(y) && volume % Vec<T>::N == 0;
+      const u64 work = volume * by / (vec ? Vec<T>::N : 1) + 1;
+      inplace_add_kernel<T><<<grid_for(ctx, work, kBlock), kBlock, 0, s>>>(
+          static_cast<const T *>(x), static_cast<T *>(y), volume, bx, by, sign, vec);
+    }
   });
   B200_OPS_EPILOGUE(ctx);
 }

@@ -24,25 +24,37 @@ __global__ void __launch_bounds__(kBlock) slice_fw_kernel(const T *__restrict__ 
   }
 }
 
-// gx[n or 0][r][offset + j][i] += gy[n or 0][r][j][i]
+// gx[n][r][offset + j][i] += gy[n or 0][r][j][i]: gx has the full batch, every destination
+// element receives exactly one term
 template <typename T>
-__global__ void __launch_bounds__(kBlock) slice_bw_kernel(const T *__restrict__ gy, T *gx, u64 span, u64 skip,
-                                                          u64 off, u64 per_batch, u64 x_volume, uint32_t bx,
-                                                          uint32_t by) {
-  const uint32_t bs = bx > by ? bx : by;
+__global__ void __launch_bounds__(kBlock) slice_bw_flat_kernel(const T *__restrict__ gy, T *gx, u64 span, u64 skip,
+                                                               u64 off, u64 per_batch, u64 x_volume, u64 total,
+                                                               int gy_batched) {
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
-  for (u64 e = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; e < per_batch; e += stride) {
+  for (u64 t = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const u64 n = t / per_batch, e = t - n * per_batch;
     const u64 r = e / span, j = e - r * span;
-    const u64 d = off + r * skip + j;
-    if (bx > 1) {
-      for (uint32_t n = 0; n < bs; ++n) {
-        const u64 dn = static_cast<u64>(n) * x_volume + d;
-        st(gx, dn, ld(gx, dn) + ld(gy, (by > 1 ? static_cast<u64>(n) * per_batch : 0) + e));
-      }
-    } else {
-      float acc = ld(gx, d);
-      for (uint32_t n = 0; n < bs; ++n) acc += ld(gy, (by > 1 ? static_cast<u64>(n) * per_batch : 0) + e);
-      st(gx, d, acc);
+    const u64 d = n * x_volume + off + r * skip + j;
+    st(gx, d, ld(gx, d) + ld(gy, gy_batched ? t : e));
+  }
+}
+
+// gx[0][r][offset + j][i] += sum_n gy[n][r][j][i]: a batch-1 destination of a batched gradient
+// (32 x 8 CTAs over elements x batch lanes, lanes combined in order: deterministic)
+template <typename T>
+__global__ void __launch_bounds__(256) slice_bw_sum_kernel(const T *__restrict__ gy, T *gx, u64 span, u64 skip,
+                                                           u64 off, u64 per_batch, uint32_t batch) {
+  __shared__ float buf[kSumLanes][32];
+  for (u64 tile = blockIdx.x; tile * 32ull < per_batch; tile += gridDim.x) {
+    const u64 e = tile * 32ull + threadIdx.x;
+    float v = 0.f;
+    if (e < per_batch)
+      for (uint32_t n = threadIdx.y; n < batch; n += kSumLanes) v += ld(gy, static_cast<u64>(n) * per_batch + e);
+    const float t = combine_batch_lanes(v, buf);
+    if (threadIdx.y == 0 && e < per_batch) {
+      const u64 r = e / span, j = e - r * span;
+      const u64 d = off + r * skip + j;
+      st(gx, d, ld(gx, d) + t);
     }
   }
 }
@@ -87,6 +99,21 @@ __global__ void __launch_bounds__(kBlock) pick_bw_kernel(const T *__restrict__ g
       const u64 d = (gx_batched ? static_cast<u64>(n) * x_volume : 0) + base * id + r * skip + i;
       st(gx, d, ld(gx, d) + ld(gy, static_cast<u64>(n) * per_batch + e));
     }
+  }
+}
+
+// the same with a batched gx: item n only touches gx[n], so (n, r, i) decides the destination
+template <typename T>
+__global__ void __launch_bounds__(kBlock) pick_bw_flat_kernel(const T *__restrict__ gy,
+                                                              const uint32_t *__restrict__ ids, T *gx, u64 base,
+                                                              u64 skip, u64 per_batch, u64 x_volume, u64 total,
+                                                              int ids_batched) {
+  const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
+  for (u64 t = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const u64 n = t / per_batch, e = t - n * per_batch;
+    const u64 r = e / base, i = e - r * base;
+    const u64 d = n * x_volume + base * ids[ids_batched ? n : 0] + r * skip + i;
+    st(gx, d, ld(gx, d) + ld(gy, t));
   }
 }
 
@@ -244,9 +271,17 @@ int b200_slice_bw(b200_ctx *ctx, int mode, const void *gy, void *gx, uint64_t ba
   if (!gx || !gy || offset + y_dim > x_dim) return B200_ERR_INVALID_ARG;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    slice_bw_kernel<T><<<grid_for(ctx, per_batch, kBlock), kBlock, 0, s>>>(
-        static_cast<const T *>(gy), static_cast<T *>(gx), span, skip, base * offset, per_batch, skip * repeat,
-        bx, by);
+    if (bx > 1 || by == 1) {
+      const u64 total = per_batch * bx;
+      slice_bw_flat_kernel<T><<<grid_for(ctx, total, kBlock), kBlock, 0, s>>>(
+          static_cast<const T *>(gy), static_cast<T *>(gx), span, skip, base * offset, per_batch, skip * repeat,
+          total, by > 1);
+    } else {
+      const u64 tiles = (per_batch + 31ull) / 32ull;
+      const u64 cap = static_cast<u64>(ctx->sm_count) * 16ull;
+      slice_bw_sum_kernel<T><<<static_cast<unsigned>(tiles < cap ? tiles : cap), dim3(32, kSumLanes), 0, s>>>(
+          static_cast<const T *>(gy), static_cast<T *>(gx), span, skip, base * offset, per_batch, by);
+    }
   });
   B200_OPS_EPILOGUE(ctx);
 }
@@ -300,9 +335,17 @@ int b200_pick_bw(b200_ctx *ctx, int mode, const void *gy, const uint32_t *ids_ho
   if (rc) return rc;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    pick_bw_kernel<T><<<grid_for(ctx, per_batch, kBlock), kBlock, 0, s>>>(
-        static_cast<const T *>(gy), ids.get(), static_cast<T *>(gx), base, skip, per_batch, skip * repeat, batch,
-        gx_batched, n_ids > 1);
+    if (gx_batched) {
+      const u64 total = per_batch * batch;
+      pick_bw_flat_kernel<T><<<grid_for(ctx, total, kBlock), kBlock, 0, s>>>(
+          static_cast<const T *>(gy), ids.get(), static_cast<T *>(gx), base, skip, per_batch, skip * repeat, total,
+          n_ids > 1);
+    } else {
+      // a batch-1 gx can receive several items at the same place: one thread per (r, i), items in order
+      pick_bw_kernel<T><<<grid_for(ctx, per_batch, kBlock), kBlock, 0, s>>>(
+          static_cast<const T *>(gy), ids.get(), static_cast<T *>(gx), base, skip, per_batch, skip * repeat, batch,
+          gx_batched, n_ids > 1);
+    }
   });
   B200_OPS_EPILOGUE(ctx);
 }

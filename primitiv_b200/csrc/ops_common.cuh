@@ -50,6 +50,106 @@ inline unsigned grid_for(const b200_ctx *ctx, u64 work, unsigned block) {
   return static_cast<unsigned>(g ? g : 1);
 }
 
+// ---- sums over the batch axis, deterministic and parallel in both directions ----
+//
+// A CTA is 32 x 8 threads: 32 consecutive elements i of the volume (coalesced) by 8 batch
+// lanes.  grid.x walks the volume, grid.y cuts the batch into slices so that a small volume
+// with a large batch (a bias gradient over 65536 samples) still fills the machine.  Inside a
+// slice, batch lane t adds items t, t + 8, ... in order and the 8 lanes are combined in lane
+// order; slices are combined in slice order by batch_final_kernel.  No atomics: the result is
+// the same bits on every run.
+constexpr unsigned kSumLanes = 8;
+
+struct BatchSlices {
+  unsigned tiles;      // grid.x: volume / 32, rounded up
+  unsigned slices;     // grid.y
+  uint32_t slice_len;  // batch items per slice
+};
+
+inline BatchSlices batch_slices(const b200_ctx *ctx, u64 volume, uint32_t batch) {
+  BatchSlices r;
+  const u64 tiles = (volume + 31ull) / 32ull;
+  r.tiles = static_cast<unsigned>(tiles < 0x7fffffffull ? tiles : 0x7fffffffull);
+  u64 want = (2ull * static_cast<u64>(ctx->sm_count) + tiles - 1) / tiles;  // about two CTAs per SM
+  const u64 most = batch / (4u * kSumLanes) ? batch / (4u * kSumLanes) : 1;  // >= 32 items per slice
+  if (want > most) want = most;
+  if (want > 65535ull) want = 65535ull;
+  if (want < 1) want = 1;
+  r.slice_len = static_cast<uint32_t>((batch + want - 1) / want);
+  r.slices = static_cast<unsigned>((batch + r.slice_len - 1) / r.slice_len);
+  return r;
+}
+
+// Combines the 8 batch lanes of a CTA (lane order) and returns the total in batch lane 0.
+__device__ __forceinline__ float combine_batch_lanes(float v, float (*buf)[32]) {
+  buf[threadIdx.y][threadIdx.x] = v;
+  __syncthreads();
+  float t = 0.f;
+  if (threadIdx.y == 0) {
+#pragma unroll
+    for (unsigned l = 0; l < kSumLanes; ++l) t += buf[l][threadIdx.x];
+  }
+  __syncthreads();
+  return t;
+}
+
+// y[i] = (accumulate ? y[i] : 0) + scale * sum over slices of partial[slice][i]
+template <typename T>
+__global__ void __launch_bounds__(256) batch_final_kernel(const float *__restrict__ partial, T *y, u64 volume,
+                                                          unsigned slices, float scale, int accumulate) {
+  const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
+  for (u64 i = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; i < volume; i += stride) {
+    float t = 0.f;
+    for (unsigned sl = 0; sl < slices; ++sl) t += partial[static_cast<u64>(sl) * volume + i];
+    st(y, i, (accumulate ? ld(y, i) : 0.f) + scale * t);
+  }
+}
+
+// y[i] = (accumulate ? y[i] : 0) + scale * sum_n x[n][i]; with more than one slice the CTA's
+// sum goes to partial[slice][i] instead.
+template <typename T>
+__global__ void __launch_bounds__(256) batch_sum_tile_kernel(const T *__restrict__ x, T *y, float *partial,
+                                                             u64 volume, uint32_t batch, uint32_t slice_len,
+                                                             float scale, int accumulate) {
+  __shared__ float buf[kSumLanes][32];
+  for (u64 tile = blockIdx.x; tile * 32ull < volume; tile += gridDim.x) {
+    const u64 i = tile * 32ull + threadIdx.x;
+    const uint32_t lo = blockIdx.y * slice_len;
+    const uint32_t hi = lo + slice_len < batch ? lo + slice_len : batch;
+    float v = 0.f;
+    if (i < volume)
+      for (uint32_t n = lo + threadIdx.y; n < hi; n += kSumLanes) v += ld(x, static_cast<u64>(n) * volume + i);
+    const float t = combine_batch_lanes(v, buf);
+    if (threadIdx.y == 0 && i < volume) {
+      if (gridDim.y == 1) st(y, i, (accumulate ? ld(y, i) : 0.f) + scale * t);
+      else partial[static_cast<u64>(blockIdx.y) * volume + i] = t;
+    }
+  }
+}
+
+// Host side of the two kernels above.  Returns a CUDA / library status.
+template <typename T>
+int launch_batch_sum(b200_ctx *ctx, cudaStream_t s, const void *x, void *y, u64 volume, uint32_t batch,
+                     float scale, int accumulate) {
+  const BatchSlices bs = batch_slices(ctx, volume, batch);
+  void *partial = nullptr;
+  if (bs.slices > 1) {
+    const int rc = ctx->pool.alloc(static_cast<size_t>(bs.slices) * volume * sizeof(float), &partial, nullptr);
+    if (rc != B200_OK) return rc;
+  }
+  batch_sum_tile_kernel<T><<<dim3(bs.tiles, bs.slices), dim3(32, kSumLanes), 0, s>>>(
+      static_cast<const T *>(x), static_cast<T *>(y), static_cast<float *>(partial), volume, batch, bs.slice_len,
+      scale, accumulate);
+  if (bs.slices > 1) {
+    batch_final_kernel<T><<<grid_for(ctx, volume, 256), 256, 0, s>>>(static_cast<const float *>(partial),
+                                                                     static_cast<T *>(y), volume, bs.slices, scale,
+                                                                     accumulate);
+    ++ctx->launches;
+    ctx->pool.free(partial);  // stream-ordered reuse
+  }
+  return B200_OK;
+}
+
 #define B200_OPS_PROLOGUE(ctx)                         \
   if (!(ctx)) return B200_ERR_INVALID_ARG;             \
   b200::DeviceGuard guard__((ctx)->device);            \

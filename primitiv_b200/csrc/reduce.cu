@@ -153,17 +153,6 @@ __global__ void __launch_bounds__(kBlock) minmax_bw_kernel(const T *__restrict__
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kBlock) batch_sum_kernel(const T *__restrict__ x, T *__restrict__ y, u64 volume,
-                                                           uint32_t batch) {
-  const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
-  for (u64 i = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; i < volume; i += stride) {
-    float a = 0.f;
-    for (uint32_t n = 0; n < batch; ++n) a += ld(x, static_cast<u64>(n) * volume + i);
-    st(y, i, a);
-  }
-}
-
 template <typename T, int RED>
 void launch_reduce(b200_ctx *ctx, cudaStream_t s, const void *x, void *y, uint32_t n, u64 skip1, u64 outputs) {
   if (skip1 == 1 && n >= 64) {
@@ -246,8 +235,8 @@ int b200_batch_sum_fw(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t 
   if (!x || !y) return B200_ERR_INVALID_ARG;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    batch_sum_kernel<T><<<grid_for(ctx, volume, kBlock), kBlock, 0, s>>>(static_cast<const T *>(x),
-                                                                         static_cast<T *>(y), volume, batch);
+    const int rc = launch_batch_sum<T>(ctx, s, x, y, volume, batch, 1.f, 0);
+    if (rc != B200_OK) return rc;
   });
   B200_OPS_EPILOGUE(ctx);
 }
