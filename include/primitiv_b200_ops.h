@@ -94,7 +94,10 @@ B200_API int b200_identity(b200_ctx *ctx, int mode, void *y, uint32_t size, void
 
 /* Host I/O (reset_tensor_by_array.cc, tensor_to_vector.cc) and device copies (copy_tensor.cc).
  * Host arrays are always float; in fp16 mode the conversion runs on the device.
- * Both calls synchronise the stream before returning, like the reference's blocking cudaMemcpy. */
+ * b200_upload copies the array into pinned staging memory of the context and returns: the
+ * array may be reused at once, the device copy is ordered on the stream like a kernel, and
+ * the stream is not waited for.  b200_download returns when the values are in the host array
+ * (it synchronises the stream, like the reference's blocking cudaMemcpy). */
 B200_API int b200_upload(b200_ctx *ctx, int mode, const float *values_host, void *y, uint64_t n, void *stream);
 B200_API int b200_download(b200_ctx *ctx, int mode, const void *x, float *values_host, uint64_t n, void *stream);
 /* y = x, converting between storage types when the modes differ (a copy between two B200 devices). */

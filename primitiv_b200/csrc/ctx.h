@@ -48,6 +48,33 @@ typedef CUresult (*EncodeTiledFn)(
 
 }  // namespace b200
 
+namespace b200 {
+
+// Pinned staging ring for host-to-device copies of caller memory that may be pageable.
+// A copy from pageable memory makes the CUDA runtime wait for the stream first; staging
+// through pinned slots keeps uploads asynchronous: the host copies into a slot, queues the
+// DMA and an event, and only waits when it comes round to a slot whose DMA is still pending.
+class StagingRing {
+ public:
+  static constexpr std::size_t kSlotBytes = 1u << 20;
+  static constexpr int kSlots = 16;
+  ~StagingRing();
+  // dst (device) <- src (host, any kind), bytes; ordered on `stream`.  The source may be
+  // reused as soon as this returns.
+  int upload(void *dst, const void *src, std::size_t bytes, cudaStream_t stream);
+  // waits for every pending DMA out of the ring
+  void drain();
+
+ private:
+  char *base_ = nullptr;
+  cudaEvent_t events_[kSlots] = {};
+  bool pending_[kSlots] = {};
+  int next_ = 0;
+  int prepare();
+};
+
+}  // namespace b200
+
 struct b200_ctx {
   int device = 0;
   int sm_count = 0;
@@ -69,6 +96,7 @@ struct b200_ctx {
   std::vector<ProfRec> prof;
   // host-buffer entry points (b200_matmul_*_host): upload, compute and download streams
   // and the events that chain them, created on first use
+  b200::StagingRing staging;     // uploads of host arrays (tensor contents, index lists)
   cudaStream_t pipe_streams[3] = {nullptr, nullptr, nullptr};
   std::vector<cudaEvent_t> pipe_events;
 };

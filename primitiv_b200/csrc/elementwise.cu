@@ -504,24 +504,22 @@ int b200_upload(b200_ctx *ctx, int mode, const float *values_host, void *y, uint
   B200_OPS_PROLOGUE(ctx);
   if (n == 0) return B200_OK;
   if (!values_host || !y) return B200_ERR_INVALID_ARG;
-  if (mode != B200_MODE_FP16) {
-    B200_CUDA_TRY(cudaMemcpyAsync(y, values_host, n * sizeof(float), cudaMemcpyHostToDevice, s));
-    B200_CUDA_TRY(cudaStreamSynchronize(s));
-    return B200_OK;
-  }
+  // Through the context's pinned staging ring: the caller's array may be reused when this
+  // returns, and the stream is not waited for (a copy straight from pageable memory would
+  // make the runtime drain the stream first, once per input of every step).
+  if (mode != B200_MODE_FP16) return ctx->staging.upload(y, values_host, n * sizeof(float), s);
   void *tmp = nullptr;
   int rc = ctx->pool.alloc(n * sizeof(float), &tmp, nullptr);
   if (rc) return rc;
-  cudaError_t e = cudaMemcpyAsync(tmp, values_host, n * sizeof(float), cudaMemcpyHostToDevice, s);
-  if (e == cudaSuccess) {
+  rc = ctx->staging.upload(tmp, values_host, n * sizeof(float), s);
+  if (rc == B200_OK) {
     convert_kernel<float, __half><<<grid_for(ctx, n, kBlock), kBlock, 0, s>>>(
         static_cast<const float *>(tmp), static_cast<__half *>(y), n);
     ++ctx->launches;
-    e = cudaGetLastError();
+    rc = static_cast<int>(cudaGetLastError());
   }
-  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
-  ctx->pool.free(tmp);
-  return static_cast<int>(e);
+  ctx->pool.free(tmp);  // stream-ordered reuse
+  return rc;
 }
 
 int b200_download(b200_ctx *ctx, int mode, const void *x, float *values_host, uint64_t n, void *stream) {

@@ -236,8 +236,7 @@ struct DeviceIds {
   int put(const uint32_t *host, uint32_t n, cudaStream_t s) {
     int rc = ctx->pool.alloc(static_cast<size_t>(n) * sizeof(uint32_t), &p, nullptr);
     if (rc) return rc;
-    return static_cast<int>(cudaMemcpyAsync(p, host, static_cast<size_t>(n) * sizeof(uint32_t),
-                                            cudaMemcpyHostToDevice, s));
+    return ctx->staging.upload(p, host, static_cast<size_t>(n) * sizeof(uint32_t), s);
   }
   const uint32_t *get() const { return static_cast<const uint32_t *>(p); }
 };

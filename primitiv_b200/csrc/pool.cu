@@ -8,6 +8,8 @@
 // handed back for the next request of the same class (same pointer), and when the
 // device allocator fails every cached block is released and the request retried
 // once before giving up.
+#include <cstring>
+
 #include "ctx.h"
 
 namespace b200 {
@@ -95,6 +97,72 @@ Pool::~Pool() {
   for (auto &kv : cached_)
     for (void *p : kv.second) cudaFree(p);
   for (auto &kv : in_use_) cudaFree(kv.first);
+}
+
+}  // namespace b200
+
+// ---------------------------------------------------------------------------------
+// StagingRing
+
+namespace b200 {
+
+int StagingRing::prepare() {
+  if (base_) return B200_OK;
+  void *p = nullptr;
+  cudaError_t e = cudaHostAlloc(&p, kSlotBytes * kSlots, cudaHostAllocDefault);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  for (int i = 0; i < kSlots; ++i) {
+    e = cudaEventCreateWithFlags(&events_[i], cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+      for (int j = 0; j < i; ++j) cudaEventDestroy(events_[j]);
+      cudaFreeHost(p);
+      return static_cast<int>(e);
+    }
+  }
+  base_ = static_cast<char *>(p);
+  return B200_OK;
+}
+
+int StagingRing::upload(void *dst, const void *src, std::size_t bytes, cudaStream_t stream) {
+  int rc = prepare();
+  if (rc != B200_OK) return rc;
+  const char *from = static_cast<const char *>(src);
+  char *to = static_cast<char *>(dst);
+  while (bytes > 0) {
+    const std::size_t n = bytes < kSlotBytes ? bytes : kSlotBytes;
+    const int slot = next_;
+    next_ = (next_ + 1) % kSlots;
+    if (pending_[slot]) {
+      const cudaError_t e = cudaEventSynchronize(events_[slot]);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      pending_[slot] = false;
+    }
+    char *stage = base_ + static_cast<std::size_t>(slot) * kSlotBytes;
+    std::memcpy(stage, from, n);
+    cudaError_t e = cudaMemcpyAsync(to, stage, n, cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess) e = cudaEventRecord(events_[slot], stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    pending_[slot] = true;
+    from += n;
+    to += n;
+    bytes -= n;
+  }
+  return B200_OK;
+}
+
+void StagingRing::drain() {
+  if (!base_) return;
+  for (int i = 0; i < kSlots; ++i) {
+    if (pending_[i]) cudaEventSynchronize(events_[i]);
+    pending_[i] = false;
+  }
+}
+
+StagingRing::~StagingRing() {
+  if (!base_) return;
+  drain();
+  for (int i = 0; i < kSlots; ++i) cudaEventDestroy(events_[i]);
+  cudaFreeHost(base_);
 }
 
 }  // namespace b200

@@ -91,3 +91,34 @@ def test_primitiv_c_api_runs_matmul_on_b200():
     for t in (a, b, y):
         capi.primitivDeleteTensor(t)
     capi.primitivDeleteDevice(dev)
+
+
+def _run_json(binary, *args):
+    import json
+    path = os.path.join(ROOT, "primitiv_b200", "device", "_build", binary)
+    assert os.path.exists(path), "%s is not built" % path
+    r = subprocess.run([path] + [str(a) for a in args], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    return json.loads(r.stdout.strip().splitlines()[-1])
+
+
+@pytest.mark.gpu
+@needs_plugin
+@pytest.mark.parametrize("mode,tol", [("3xtf32", 2e-5), ("tf32", 4e-3)])
+def test_recurrent_step_loop_matches_reference_naive(mode, tol):
+    """An LSTM step loop through primitiv's Graph (forward and backward through time): the loss
+    and the weight gradients of a 3-step prefix agree with the reference's Naive device."""
+    out = _run_json("lstm_steps", mode, 6, 1, 3)
+    assert out["loss_rel_diff"] < tol and out["grad_wx_rel_diff"] < tol and out["grad_wh_rel_diff"] < tol, out
+    assert out["launches_per_loop"]["gemm_tc"] > 0     # the products ran on the tensor-core kernel
+
+
+@pytest.mark.gpu
+@needs_plugin
+@pytest.mark.parametrize("mode,tol", [("3xtf32", 1e-5), ("tf32", 2e-3)])
+def test_perceptron_training_step_matches_reference_naive(mode, tol):
+    """Two SGD steps of the 784-1024-1024-10 perceptron (softmax cross entropy) at batch 256 on
+    both devices: loss and updated weights agree; then one step at a batch above 65535."""
+    out = _run_json("mlp_step", mode, 65600, 1, 256)
+    assert out["loss_rel_diff"] < tol and out["w1_rel_diff"] < tol and out["w3_rel_diff"] < tol, out
+    assert 2.0 < out["loss"] < 2.6                      # ln(10) = 2.30 for an untrained 10-way classifier
