@@ -1013,6 +1013,11 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     for (int o = 0; o < 2; ++o) {
       const OperandView &v = *views[o];
       const bool direct = direct_ok(v.ptr, v.ld, v.batch_stride, v.nbatch, 4);
+      // 3xTF32 always repacks, even operands the tensor core could read where they lie (it
+      // truncates fp32 words to TF32, so the caller's array could serve as the hi plane and only
+      // lo = rn(x - trunc(x)) be written).  That was tried: the pre-pass got a third cheaper, but
+      // the main loop, which runs against the power cap, slowed by as much with un-rounded
+      // operand words (and by more with MN-major 4 KB boxes).
       pack[o] = passes == 3 || !direct;
       if (pack[o]) {
         kpad[o] = (v.k + 3u) & ~3u;
@@ -1330,6 +1335,14 @@ static float *g_static_scratch_addr[kMaxDevices] = {};
 
 int gemm_3xtf32_noalloc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream) {
   if (ctx->device < 0 || ctx->device >= kMaxDevices) return B200_ERR_INVALID_ARG;
+  {
+    // The documented limit, checked here so that it does not depend on how the operands end up
+    // being packed: hi and lo planes of both operands, k padded to 4, each plane rounded to 64.
+    const uint64_t kpad = (static_cast<uint64_t>(g.k) + 3ull) & ~3ull;
+    const uint64_t pa = (static_cast<uint64_t>(g.m) * kpad + 63ull) & ~63ull;
+    const uint64_t pb = (static_cast<uint64_t>(g.n) * kpad + 63ull) & ~63ull;
+    if (2ull * (pa + pb) > kStaticScratchFloats) return B200_ERR_TOO_LARGE;
+  }
   float *&addr = g_static_scratch_addr[ctx->device];
   if (!addr) {
     void *sym = nullptr;
