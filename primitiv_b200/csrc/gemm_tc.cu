@@ -338,16 +338,18 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
 // For += all 32 old values are fetched before the first store: written as one
 // load-add-store per column the stores would order the loads behind them (the compiler
 // must assume they alias) and the epilogue would pay one memory latency per column.
-template <typename T>
+// kWide = old values in flight per thread: 8 where registers are tight (the chunked kernel holds
+// a whole tile row in registers), 32 elsewhere.
+template <uint32_t kWide, typename T>
 __device__ __forceinline__ void store_cols(T *C, unsigned long long base, uint32_t m, uint32_t n,
                                            uint32_t col0, const float (&x)[32], bool accumulate) {
   T *q = C + base + static_cast<unsigned long long>(col0) * m;
   const uint32_t left = n - col0;  // caller guarantees col0 < n
 #pragma unroll
-  for (uint32_t h = 0; h < 32u; h += 8u) {  // 8 loads in flight per thread, then 8 stores
-    float old[8];
+  for (uint32_t h = 0; h < 32u; h += kWide) {  // kWide loads in flight per thread, then kWide stores
+    float old[kWide];
 #pragma unroll
-    for (uint32_t j = 0; j < 8u; ++j) {
+    for (uint32_t j = 0; j < kWide; ++j) {
       old[j] = 0.f;
       if (accumulate && h + j < left) {
         if constexpr (sizeof(T) == 2) old[j] = __half2float(q[static_cast<unsigned long long>(h + j) * m]);
@@ -355,7 +357,7 @@ __device__ __forceinline__ void store_cols(T *C, unsigned long long base, uint32
       }
     }
 #pragma unroll
-    for (uint32_t j = 0; j < 8u; ++j) {
+    for (uint32_t j = 0; j < kWide; ++j) {
       if (h + j < left) {
         const float v = x[h + j] + old[j];
         if constexpr (sizeof(T) == 2) q[static_cast<unsigned long long>(h + j) * m] = __float2half_rn(v);
@@ -674,9 +676,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             const uint32_t col0 = n0 + col_base + j * 32u;
             if (j * 32u < cols_per && col0 < p.n) {
               if (p.out_half)
-                store_cols(static_cast<__half *>(p.C), base, p.m, p.n, col0, acc[j], p.accumulate != 0u);
+                store_cols<8>(static_cast<__half *>(p.C), base, p.m, p.n, col0, acc[j], p.accumulate != 0u);
               else
-                store_cols(static_cast<float *>(p.C), base, p.m, p.n, col0, acc[j], p.accumulate != 0u);
+                store_cols<8>(static_cast<float *>(p.C), base, p.m, p.n, col0, acc[j], p.accumulate != 0u);
             }
           }
         }
@@ -698,9 +700,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 #pragma unroll
             for (uint32_t i = 0; i < 32u; ++i) x[i] = __uint_as_float(v[i]);
             if (p.out_half)
-              store_cols(static_cast<__half *>(p.C), base, p.m, p.n, col0, x, p.accumulate != 0u);
+              store_cols<32>(static_cast<__half *>(p.C), base, p.m, p.n, col0, x, p.accumulate != 0u);
             else
-              store_cols(static_cast<float *>(p.C), base, p.m, p.n, col0, x, p.accumulate != 0u);
+              store_cols<32>(static_cast<float *>(p.C), base, p.m, p.n, col0, x, p.accumulate != 0u);
           }
         }
         tc_fence_before();
