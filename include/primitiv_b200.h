@@ -119,6 +119,15 @@ B200_API int b200_matmul_bw(b200_ctx *ctx, int mode,
                             uint32_t di, uint32_t dj, uint32_t dk,
                             uint32_t ba, uint32_t bb, void *stream);
 
+/* b200_matmul_bw with a choice per gradient between `+=` (1, the reference's semantics) and
+ * `=` (0, for a gradient known to hold zeros: saves reading it and the fill that zeroed it). */
+B200_API int b200_matmul_bw_ex(b200_ctx *ctx, int mode,
+                               const void *a, const void *b, const void *gy,
+                               void *ga, void *gb,
+                               uint32_t di, uint32_t dj, uint32_t dk,
+                               uint32_t ba, uint32_t bb,
+                               int accumulate_a, int accumulate_b, void *stream);
+
 /* Same two operations with HOST buffers: copies the operands to the device
  * (pool memory), runs the kernels, copies the result back and synchronises.
  * This is what a caller holding host data pays end to end

@@ -66,11 +66,16 @@ enum {
   B200_OP_BINARY_COUNT
 };
 
-/* Device::<op>_fw_impl(x, [k], y) and <op>_bw_impl(x, y, gy, [k], gx) for the unary list above. */
+/* Device::<op>_fw_impl(x, [k], y) and <op>_bw_impl(x, y, gy, [k], gx) for the unary list above.
+ * The reference's backward kernels add into gx; `accumulate` = 0 writes gx instead, which is what
+ * a caller wants when gx is known to hold zeros (primitiv zero-fills every gradient before its
+ * first use, primitiv/core/graph.cc:191-212: the device class defers that fill and turns the
+ * first `+=` into a store). */
 B200_API int b200_unary_fw(b200_ctx *ctx, int mode, int op, const void *x, void *y, uint64_t n,
                            float k, int32_t ik, void *stream);
 B200_API int b200_unary_bw(b200_ctx *ctx, int mode, int op, const void *x, const void *y,
-                           const void *gy, void *gx, uint64_t n, float k, int32_t ik, void *stream);
+                           const void *gy, void *gx, uint64_t n, float k, int32_t ik, int accumulate,
+                           void *stream);
 
 /* Device::<op>_scalar_*_fw_impl: y[b][i] = x[b or 0][i] op k[b or 0]   (CPUDEV_FW_X_SCALAR,
  * primitiv/devices/naive/ops/common.h:50-66). */
@@ -80,9 +85,12 @@ B200_API int b200_scalar_fw(b200_ctx *ctx, int mode, int op, const void *x, cons
 /* Device::<op>_fw_impl(a, b, y) and <op>_bw_impl(a, b, y, gy, ga, gb) for ADD .. POW. */
 B200_API int b200_binary_fw(b200_ctx *ctx, int mode, int op, const void *a, const void *b, void *y,
                             uint64_t volume, uint32_t batch, int a_batched, int b_batched, void *stream);
+/* ga and gb may be the same array (x + x); accumulate_a / accumulate_b as for b200_unary_bw,
+ * applied in that order. */
 B200_API int b200_binary_bw(b200_ctx *ctx, int mode, int op, const void *a, const void *b,
                             const void *y, const void *gy, void *ga, void *gb,
-                            uint64_t volume, uint32_t batch, int a_batched, int b_batched, void *stream);
+                            uint64_t volume, uint32_t batch, int a_batched, int b_batched,
+                            int accumulate_a, int accumulate_b, void *stream);
 
 /* inplace_add.cc / inplace_subtract.cc: y[b or 0] += sign * x[b or 0] over max(bx, by) batches. */
 B200_API int b200_inplace_add(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t volume,

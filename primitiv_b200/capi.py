@@ -35,6 +35,7 @@ SIGNATURES = {
     "b200_pool_size_class": (ctypes.c_size_t, [ctypes.c_size_t]),
     "b200_matmul_fw": (_int, [_vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp]),
     "b200_matmul_bw": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp]),
+    "b200_matmul_bw_ex": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _int, _int, _vp]),
     "b200_matmul_fw_host": (_int, [_vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32]),
     "b200_matmul_bw_host": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32]),
     "b200_gemm": (_int, [_vp, _int, _int, _int, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32,
@@ -47,10 +48,10 @@ SIGNATURES = {
     "b200_launch_count": (_int, [_vp, ctypes.POINTER(_u64)]),
     # ---- include/primitiv_b200_ops.h ----
     "b200_unary_fw": (_int, [_vp, _int, _int, _vp, _vp, _u64, ctypes.c_float, ctypes.c_int32, _vp]),
-    "b200_unary_bw": (_int, [_vp, _int, _int, _vp, _vp, _vp, _vp, _u64, ctypes.c_float, ctypes.c_int32, _vp]),
+    "b200_unary_bw": (_int, [_vp, _int, _int, _vp, _vp, _vp, _vp, _u64, ctypes.c_float, ctypes.c_int32, _int, _vp]),
     "b200_scalar_fw": (_int, [_vp, _int, _int, _vp, _vp, _vp, _u64, _u32, _int, _int, _vp]),
     "b200_binary_fw": (_int, [_vp, _int, _int, _vp, _vp, _vp, _u64, _u32, _int, _int, _vp]),
-    "b200_binary_bw": (_int, [_vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _u32, _int, _int, _vp]),
+    "b200_binary_bw": (_int, [_vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _u32, _int, _int, _int, _int, _vp]),
     "b200_inplace_add": (_int, [_vp, _int, _vp, _vp, _u64, _u32, _u32, ctypes.c_float, _vp]),
     "b200_inplace_multiply_const": (_int, [_vp, _int, _vp, _u64, ctypes.c_float, _vp]),
     "b200_fill": (_int, [_vp, _int, _vp, _u64, ctypes.c_float, _vp]),

@@ -238,6 +238,13 @@ int b200_matmul_fw(b200_ctx *ctx, int mode, const void *a, const void *b, void *
 int b200_matmul_bw(b200_ctx *ctx, int mode, const void *a, const void *b, const void *gy, void *ga,
                    void *gb, uint32_t di, uint32_t dj, uint32_t dk, uint32_t ba, uint32_t bb,
                    void *stream) {
+  return b200_matmul_bw_ex(ctx, mode, a, b, gy, ga, gb, di, dj, dk, ba, bb, 1, 1, stream);
+}
+
+int b200_matmul_bw_ex(b200_ctx *ctx, int mode, const void *a, const void *b, const void *gy, void *ga,
+                      void *gb, uint32_t di, uint32_t dj, uint32_t dk, uint32_t ba, uint32_t bb,
+                      int accumulate_a, int accumulate_b, void *stream) {
+  const int acc_a = accumulate_a ? 1 : 0, acc_b = accumulate_b ? 1 : 0;
   int rc = check_matmul(ctx, mode, ba, bb);
   if (rc) return rc;
   if (!a || !b || !gy) return B200_ERR_INVALID_ARG;
@@ -246,26 +253,26 @@ int b200_matmul_bw(b200_ctx *ctx, int mode, const void *a, const void *b, const 
     const uint32_t dkb = dk * bb;
     // ga += gy_all . b_all^T : the batch sum is the tail of one long contraction
     if (ga) {
-      rc = b200_gemm(ctx, mode, 0, 1, gy, b, ga, di, dj, dkb, 1, 1, 0, 0, 0, 0, 0, 1, 0, stream);
+      rc = b200_gemm(ctx, mode, 0, 1, gy, b, ga, di, dj, dkb, 1, 1, 0, 0, 0, 0, 0, acc_a, 0, stream);
       if (rc) return rc;
     }
     // gb_all += a^T . gy_all
-    if (gb) rc = b200_gemm(ctx, mode, 1, 0, a, gy, gb, dj, dkb, di, 1, 1, 0, 0, 0, 0, 0, 1, 0, stream);
+    if (gb) rc = b200_gemm(ctx, mode, 1, 0, a, gy, gb, dj, dkb, di, 1, 1, 0, 0, 0, 0, 0, acc_b, 0, stream);
     return rc;
   }
   // ga[n] += gy[n] . b[n or 0]^T
   if (ga) {
-    rc = b200_gemm(ctx, mode, 0, 1, gy, b, ga, di, dj, dk, ba, 1, ny, 0, bb > 1 ? nb : 0, 0, na, 1, 0,
+    rc = b200_gemm(ctx, mode, 0, 1, gy, b, ga, di, dj, dk, ba, 1, ny, 0, bb > 1 ? nb : 0, 0, na, acc_a, 0,
                    stream);
     if (rc) return rc;
   }
   if (gb) {
     if (bb > 1) {
       // gb[n] += a[n]^T . gy[n]
-      rc = b200_gemm(ctx, mode, 1, 0, a, gy, gb, dj, dk, di, ba, 1, na, 0, ny, 0, nb, 1, 0, stream);
+      rc = b200_gemm(ctx, mode, 1, 0, a, gy, gb, dj, dk, di, ba, 1, na, 0, ny, 0, nb, acc_b, 0, stream);
     } else {
       // gb += sum_n a[n]^T . gy[n] : one launch, the batch is a second contraction axis
-      rc = b200_gemm(ctx, mode, 1, 0, a, gy, gb, dj, dk, di, 1, ba, 0, na, 0, ny, 0, 1, 0, stream);
+      rc = b200_gemm(ctx, mode, 1, 0, a, gy, gb, dj, dk, di, 1, ba, 0, na, 0, ny, 0, acc_b, 0, stream);
     }
   }
   return rc;

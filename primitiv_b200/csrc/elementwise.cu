@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(kBlock) unary_fw_kernel(const T *__restrict__ 
 template <typename T, int OP>
 __global__ void __launch_bounds__(kBlock) unary_bw_kernel(const T *__restrict__ x, const T *__restrict__ y,
                                                           const T *__restrict__ gy, T *__restrict__ gx,
-                                                          u64 n, float k, int ik, int vec) {
+                                                          u64 n, float k, int ik, int vec, int accumulate) {
   const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   constexpr int N = Vec<T>::N;
@@ -110,13 +110,14 @@ __global__ void __launch_bounds__(kBlock) unary_bw_kernel(const T *__restrict__ 
     vx.load(x + i * N);
     vy.load(y + i * N);
     vg.load(gy + i * N);
-    vo.load(gx + i * N);
+    if (accumulate) vo.load(gx + i * N);
 #pragma unroll
-    for (int j = 0; j < N; ++j) vo.set(j, vo.get(j) + unary_d<OP>(vx.get(j), vy.get(j), vg.get(j), k, ik));
+    for (int j = 0; j < N; ++j)
+      vo.set(j, (accumulate ? vo.get(j) : 0.f) + unary_d<OP>(vx.get(j), vy.get(j), vg.get(j), k, ik));
     vo.store(gx + i * N);
   }
   for (u64 i = nv * N + tid; i < n; i += stride)
-    st(gx, i, ld(gx, i) + unary_d<OP>(ld(x, i), ld(y, i), ld(gy, i), k, ik));
+    st(gx, i, (accumulate ? ld(gx, i) : 0.f) + unary_d<OP>(ld(x, i), ld(y, i), ld(gy, i), k, ik));
 }
 
 // ------------------------------- binary --------------------------------------
@@ -173,13 +174,15 @@ __global__ void __launch_bounds__(kBlock) binary_fw_kernel(const T *__restrict__
 template <typename T, int OP>
 __global__ void __launch_bounds__(kBlock) binary_bw_flat_kernel(const T *__restrict__ a, const T *__restrict__ b,
                                                                 const T *__restrict__ y, const T *__restrict__ gy,
-                                                                T *__restrict__ ga, T *__restrict__ gb, u64 total) {
+                                                                T *ga, T *gb, u64 total, int acc_a, int acc_b) {
+  // ga and gb are deliberately not __restrict__: for x + x (or x * x) they are the same array,
+  // and the two updates of an element must then happen one after the other.
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 e = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
     float da, db;
     binary_d<OP>(ld(a, e), ld(b, e), ld(y, e), ld(gy, e), da, db);
-    st(ga, e, ld(ga, e) + da);
-    st(gb, e, ld(gb, e) + db);
+    st(ga, e, (acc_a ? ld(ga, e) : 0.f) + da);
+    st(gb, e, (acc_b ? ld(gb, e) : 0.f) + db);
   }
 }
 
@@ -190,7 +193,8 @@ template <typename T, int OP>
 __global__ void __launch_bounds__(256) binary_bw_mixed_kernel(const T *__restrict__ a, const T *__restrict__ b,
                                                               const T *__restrict__ y, const T *__restrict__ gy,
                                                               T *ga, T *gb, float *partial, u64 volume,
-                                                              uint32_t batch, uint32_t slice_len, int a_batched) {
+                                                              uint32_t batch, uint32_t slice_len, int a_batched,
+                                                              int acc_batched, int acc_summed) {
   __shared__ float buf[kSumLanes][32];
   T *g_batched = a_batched ? ga : gb, *g_summed = a_batched ? gb : ga;
   for (u64 tile = blockIdx.x; tile * 32ull < volume; tile += gridDim.x) {
@@ -203,13 +207,13 @@ __global__ void __launch_bounds__(256) binary_bw_mixed_kernel(const T *__restric
         const u64 e = static_cast<u64>(n) * volume + i;
         float da, db;
         binary_d<OP>(ld(a, a_batched ? e : i), ld(b, a_batched ? i : e), ld(y, e), ld(gy, e), da, db);
-        st(g_batched, e, ld(g_batched, e) + (a_batched ? da : db));
+        st(g_batched, e, (acc_batched ? ld(g_batched, e) : 0.f) + (a_batched ? da : db));
         v += a_batched ? db : da;
       }
     }
     const float t = combine_batch_lanes(v, buf);
     if (threadIdx.y == 0 && i < volume) {
-      if (gridDim.y == 1) st(g_summed, i, ld(g_summed, i) + t);
+      if (gridDim.y == 1) st(g_summed, i, (acc_summed ? ld(g_summed, i) : 0.f) + t);
       else partial[static_cast<u64>(blockIdx.y) * volume + i] = t;
     }
   }
@@ -308,10 +312,10 @@ void launch_unary_fw(b200_ctx *ctx, cudaStream_t s, int op, const void *x, void 
 
 template <typename T>
 void launch_unary_bw(b200_ctx *ctx, cudaStream_t s, int op, const void *x, const void *y, const void *gy,
-                     void *gx, u64 n, float k, int ik, int vec) {
+                     void *gx, u64 n, float k, int ik, int vec, int accumulate) {
   const unsigned grid = grid_for(ctx, n / (vec ? Vec<T>::N : 1) + 1, kBlock);
   switch (op) {
-#define X(OP) case OP: unary_bw_kernel<T, OP><<<grid, kBlock, 0, s>>>(static_cast<const T *>(x), static_cast<const T *>(y), static_cast<const T *>(gy), static_cast<T *>(gx), n, k, ik, vec); break;
+#define X(OP) case OP: unary_bw_kernel<T, OP><<<grid, kBlock, 0, s>>>(static_cast<const T *>(x), static_cast<const T *>(y), static_cast<const T *>(gy), static_cast<T *>(gx), n, k, ik, vec, accumulate); break;
     B200_UNARY_OPS(X)
 #undef X
   }
@@ -343,7 +347,7 @@ void launch_binary_fw(b200_ctx *ctx, cudaStream_t s, int op, const void *a, cons
 template <typename T>
 int launch_binary_bw(b200_ctx *ctx, cudaStream_t s, int op, const void *a, const void *b, const void *y,
                      const void *gy, void *ga, void *gb, u64 volume, uint32_t batch, int a_batched,
-                     int b_batched) {
+                     int b_batched, int acc_a, int acc_b) {
   const T *pa = static_cast<const T *>(a), *pb = static_cast<const T *>(b), *py = static_cast<const T *>(y),
           *pgy = static_cast<const T *>(gy);
   T *pga = static_cast<T *>(ga), *pgb = static_cast<T *>(gb);
@@ -351,7 +355,7 @@ int launch_binary_bw(b200_ctx *ctx, cudaStream_t s, int op, const void *a, const
     const u64 total = volume * batch;
     const unsigned grid = grid_for(ctx, total, kBlock);
     switch (op) {
-#define X(OP) case OP: binary_bw_flat_kernel<T, OP><<<grid, kBlock, 0, s>>>(pa, pb, py, pgy, pga, pgb, total); break;
+#define X(OP) case OP: binary_bw_flat_kernel<T, OP><<<grid, kBlock, 0, s>>>(pa, pb, py, pgy, pga, pgb, total, acc_a, acc_b); break;
       B200_BINARY_OPS(X)
 #undef X
     }
@@ -365,13 +369,14 @@ int launch_binary_bw(b200_ctx *ctx, cudaStream_t s, int op, const void *a, const
   }
   const dim3 grid(bs.tiles, bs.slices), block(32, kSumLanes);
   switch (op) {
-#define X(OP) case OP: binary_bw_mixed_kernel<T, OP><<<grid, block, 0, s>>>(pa, pb, py, pgy, pga, pgb, static_cast<float *>(partial), volume, batch, bs.slice_len, a_batched); break;
+#define X(OP) case OP: binary_bw_mixed_kernel<T, OP><<<grid, block, 0, s>>>(pa, pb, py, pgy, pga, pgb, static_cast<float *>(partial), volume, batch, bs.slice_len, a_batched, a_batched ? acc_a : acc_b, a_batched ? acc_b : acc_a); break;
     B200_BINARY_OPS(X)
 #undef X
   }
   if (bs.slices > 1) {
     batch_final_kernel<T><<<grid_for(ctx, volume, 256), 256, 0, s>>>(static_cast<const float *>(partial),
-                                                                     a_batched ? pgb : pga, volume, bs.slices, 1.f, 1);
+                                                                     a_batched ? pgb : pga, volume, bs.slices, 1.f,
+                                                                     a_batched ? acc_b : acc_a);
     ++ctx->launches;
     ctx->pool.free(partial);  // stream-ordered reuse
   }
@@ -397,13 +402,13 @@ int b200_unary_fw(b200_ctx *ctx, int mode, int op, const void *x, void *y, uint6
 }
 
 int b200_unary_bw(b200_ctx *ctx, int mode, int op, const void *x, const void *y, const void *gy,
-                  void *gx, uint64_t n, float k, int32_t ik, void *stream) {
+                  void *gx, uint64_t n, float k, int32_t ik, int accumulate, void *stream) {
   B200_OPS_PROLOGUE(ctx);
   if (n == 0) return B200_OK;
   if (!x || !y || !gy || !gx || op < 0 || op >= B200_OP_UNARY_COUNT) return B200_ERR_INVALID_ARG;
   const int vec = aligned16(x) && aligned16(y) && aligned16(gy) && aligned16(gx);
   ProfScope prof(ctx, kProfElementwise, s);
-  B200_DISPATCH_MODE(mode, { launch_unary_bw<T>(ctx, s, op, x, y, gy, gx, n, k, ik, vec); });
+  B200_DISPATCH_MODE(mode, { launch_unary_bw<T>(ctx, s, op, x, y, gy, gx, n, k, ik, vec, accumulate ? 1 : 0); });
   B200_OPS_EPILOGUE(ctx);
 }
 
@@ -431,13 +436,14 @@ int b200_binary_fw(b200_ctx *ctx, int mode, int op, const void *a, const void *b
 
 int b200_binary_bw(b200_ctx *ctx, int mode, int op, const void *a, const void *b, const void *y,
                    const void *gy, void *ga, void *gb, uint64_t volume, uint32_t batch, int a_batched,
-                   int b_batched, void *stream) {
+                   int b_batched, int accumulate_a, int accumulate_b, void *stream) {
   B200_OPS_PROLOGUE(ctx);
   if (volume == 0 || batch == 0) return B200_OK;
   if (!a || !b || !y || !gy || !ga || !gb || op < 0 || op > B200_OP_POW) return B200_ERR_INVALID_ARG;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    const int rc = launch_binary_bw<T>(ctx, s, op, a, b, y, gy, ga, gb, volume, batch, a_batched, b_batched);
+    const int rc = launch_binary_bw<T>(ctx, s, op, a, b, y, gy, ga, gb, volume, batch, a_batched, b_batched,
+                                       accumulate_a ? 1 : 0, accumulate_b ? 1 : 0);
     if (rc != B200_OK) return rc;
   });
   B200_OPS_EPILOGUE(ctx);

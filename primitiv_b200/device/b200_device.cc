@@ -11,6 +11,7 @@
 #include <cstring>
 #include <iostream>
 #include <string>
+#include <unordered_map>
 
 #include <primitiv/core/error.h>
 
@@ -27,8 +28,8 @@
     }                                                                         \
   } while (0)
 
-#define CDATA(x) (get_handle(x))
-#define MDATA(x) (get_mutable_handle(x))
+#define CDATA(x) (in(x))
+#define MDATA(x) (out(x))
 
 namespace primitiv {
 namespace devices {
@@ -38,6 +39,9 @@ namespace devices {
 // the state is gone the block has already been released together with the pool.
 struct B200::State {
   ::b200_ctx *ctx = nullptr;
+  int mode = 0;
+  // tensors whose zero-fill has been deferred: device pointer -> element count
+  std::unordered_map<const void *, std::uint64_t> zero_pending;
   ~State() {
     if (ctx) ::b200_ctx_destroy(ctx);
   }
@@ -90,7 +94,44 @@ void B200::initialize(std::uint32_t rng_seed) {
     PRIMITIV_THROW_ERROR("Could not create a B200 device on GPU " << device_id_ << ": "
                          << ::b200_error_string(rc) << " [" << rc << "]");
   }
+  state_->mode = imode();
   B200_CALL(::b200_seed(state_->ctx, rng_seed));
+}
+
+void B200::materialize(const void *ptr) {
+  auto &pending = state_->zero_pending;
+  if (pending.empty()) return;
+  const auto it = pending.find(ptr);
+  if (it == pending.end()) return;
+  const std::uint64_t n = it->second;
+  pending.erase(it);
+  B200_CALL(::b200_fill(state_->ctx, imode(), const_cast<void *>(ptr), n, 0.f, nullptr));
+}
+
+const void *B200::in(const Tensor &x) {
+  const void *p = get_handle(x);
+  materialize(p);
+  return p;
+}
+
+void *B200::out(Tensor &x) {
+  void *p = get_mutable_handle(x);  // may clone a shared tensor (copy-on-write) through copy_tensor_impl
+  materialize(p);
+  return p;
+}
+
+void *B200::out_acc(Tensor &x, int *accumulate) {
+  void *p = get_mutable_handle(x);
+  auto &pending = state_->zero_pending;
+  *accumulate = 1;
+  if (!pending.empty()) {
+    const auto it = pending.find(p);
+    if (it != pending.end()) {
+      pending.erase(it);
+      *accumulate = 0;  // the kernel stores where it would have added to zeros
+    }
+  }
+  return p;
 }
 
 B200::~B200() {
@@ -126,7 +167,10 @@ std::shared_ptr<void> B200::new_handle(const Shape &shape, std::size_t *const al
   if (allocated_size) *allocated_size = got;
   std::weak_ptr<State> weak = state_;
   return std::shared_ptr<void>(ptr, [weak](void *p) {
-    if (std::shared_ptr<State> st = weak.lock()) ::b200_pool_free(st->ctx, p);
+    if (std::shared_ptr<State> st = weak.lock()) {
+      st->zero_pending.erase(p);  // a fill that nobody needed
+      ::b200_pool_free(st->ctx, p);
+    }
   });
 }
 
@@ -155,7 +199,13 @@ std::vector<std::uint32_t> B200::argmin_impl(const Tensor &x, std::uint32_t dim)
 }
 
 void B200::reset_tensor_impl(float k, Tensor &x) {
-  B200_CALL(::b200_fill(state_->ctx, imode(), MDATA(x), x.shape().size(), k, nullptr));
+  void *p = get_mutable_handle(x);
+  if (k == 0.f) {
+    state_->zero_pending[p] = x.shape().size();  // deferred: see in() / out_acc()
+    return;
+  }
+  state_->zero_pending.erase(p);  // overwritten as a whole
+  B200_CALL(::b200_fill(state_->ctx, imode(), p, x.shape().size(), k, nullptr));
 }
 
 void B200::reset_tensor_by_array_impl(const float values[], Tensor &x) {
@@ -170,13 +220,15 @@ void B200::copy_tensor_impl(const Tensor &x, Tensor &y) {
   const std::uint64_t n = x.shape().size();
   if (const B200 *src = dynamic_cast<const B200 *>(&x.device())) {
     if (src->device_id_ == device_id_ || src->mode_ == mode_) {
+      // a zero-fill still pending on x is the source device's to launch
+      const void *px = const_cast<B200 *>(src)->in(x);
       if (src->device_id_ != device_id_) {
         // The two GPUs' default streams do not order against each other: let the source
         // device finish whatever still writes x before this device reads it.
         int code = 0;
         B200_CALL(::b200_status_poll(src->state_->ctx, nullptr, &code));
       }
-      B200_CALL(::b200_copy(state_->ctx, src->imode(), CDATA(x), imode(), MDATA(y), n, nullptr));
+      B200_CALL(::b200_copy(state_->ctx, src->imode(), px, imode(), MDATA(y), n, nullptr));
       return;
     }
   } else if (x.device().type() == DeviceType::NAIVE) {
@@ -253,14 +305,23 @@ void B200::concat_fw_impl(const std::vector<const Tensor *> &xs, std::uint32_t d
 
 // ---------------------------------------------------------------- elementwise, one tensor
 
+// gx (+)= d op(x, y) * gy: the operands are resolved first, then gx, which stores instead of
+// adding when its zero-fill is still pending.
+void B200::unary_bw(int op, const Tensor &x, const Tensor &y, const Tensor &gy, float k, std::int32_t ik,
+                    Tensor &gx) {
+  const void *px = in(x), *py = in(y), *pgy = in(gy);
+  int acc = 1;
+  void *pgx = out_acc(gx, &acc);
+  B200_CALL(::b200_unary_bw(state_->ctx, imode(), op, px, py, pgy, pgx, x.shape().size(), k, ik, acc, nullptr));
+}
+
 #define B200_IMPL_X_FW(name, op)                                                                   \
   void B200::name##_fw_impl(const Tensor &x, Tensor &y) {                                          \
     B200_CALL(::b200_unary_fw(state_->ctx, imode(), op, CDATA(x), MDATA(y), x.shape().size(), 0.f, 0, nullptr)); \
   }
 #define B200_IMPL_X_BW(name, op)                                                                   \
   void B200::name##_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, Tensor &gx) {      \
-    B200_CALL(::b200_unary_bw(state_->ctx, imode(), op, CDATA(x), CDATA(y), CDATA(gy), MDATA(gx),  \
-                              x.shape().size(), 0.f, 0, nullptr));                                 \
+    unary_bw(op, x, y, gy, 0.f, 0, gx);                                                            \
   }
 #define B200_IMPL_X(name, op) B200_IMPL_X_FW(name, op) B200_IMPL_X_BW(name, op)
 
@@ -281,8 +342,7 @@ B200_IMPL_X(tan, B200_OP_TAN)
     B200_CALL(::b200_unary_fw(state_->ctx, imode(), op, CDATA(x), MDATA(y), x.shape().size(), k, 0, nullptr)); \
   }                                                                                                \
   void B200::name##_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, float k, Tensor &gx) { \
-    B200_CALL(::b200_unary_bw(state_->ctx, imode(), op, CDATA(x), CDATA(y), CDATA(gy), MDATA(gx),  \
-                              x.shape().size(), k, 0, nullptr));                                   \
+    unary_bw(op, x, y, gy, k, 0, gx);                                                              \
   }
 
 B200_IMPL_X_CONST(add_const, B200_OP_ADD_CONST)
@@ -300,8 +360,7 @@ void B200::pown_fw_impl(const Tensor &x, std::int32_t k, Tensor &y) {
   B200_CALL(::b200_unary_fw(state_->ctx, imode(), B200_OP_POWN, CDATA(x), MDATA(y), x.shape().size(), 0.f, k, nullptr));
 }
 void B200::pown_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, std::int32_t k, Tensor &gx) {
-  B200_CALL(::b200_unary_bw(state_->ctx, imode(), B200_OP_POWN, CDATA(x), CDATA(y), CDATA(gy), MDATA(gx),
-                            x.shape().size(), 0.f, k, nullptr));
+  unary_bw(B200_OP_POWN, x, y, gy, 0.f, k, gx);
 }
 
 // ---------------------------------------------------------------- transpose / permute / flip
@@ -366,9 +425,13 @@ B200_IMPL_X_SCALAR(pow_scalar_l, B200_OP_POW_L)
   }                                                                                                \
   void B200::name##_bw_impl(const Tensor &a, const Tensor &b, const Tensor &y, const Tensor &gy,   \
                             Tensor &ga, Tensor &gb) {                                              \
-    B200_CALL(::b200_binary_bw(state_->ctx, imode(), op, CDATA(a), CDATA(b), CDATA(y), CDATA(gy), MDATA(ga), \
-                               MDATA(gb), gy.shape().volume(), gy.shape().batch(), a.shape().has_batch(), \
-                               b.shape().has_batch(), nullptr));                                   \
+    const void *pa = in(a), *pb = in(b), *py = in(y), *pgy = in(gy);                               \
+    int acc_a = 1, acc_b = 1;                                                                      \
+    void *pga = out_acc(ga, &acc_a);                                                               \
+    void *pgb = out_acc(gb, &acc_b); /* the same tensor as ga for x op x: then it accumulates */   \
+    B200_CALL(::b200_binary_bw(state_->ctx, imode(), op, pa, pb, py, pgy, pga, pgb, gy.shape().volume(), \
+                               gy.shape().batch(), a.shape().has_batch(), b.shape().has_batch(), acc_a, \
+                               acc_b, nullptr));                                                   \
   }
 
 B200_IMPL_AB(add, B200_OP_ADD)
@@ -386,9 +449,12 @@ void B200::matmul_fw_impl(const Tensor &a, const Tensor &b, Tensor &y) {
 
 void B200::matmul_bw_impl(const Tensor &a, const Tensor &b, const Tensor &, const Tensor &gy, Tensor &ga,
                           Tensor &gb) {
-  B200_CALL(::b200_matmul_bw(state_->ctx, imode(), CDATA(a), CDATA(b), CDATA(gy), MDATA(ga), MDATA(gb),
-                             a.shape()[0], a.shape()[1], b.shape()[1], a.shape().batch(), b.shape().batch(),
-                             nullptr));
+  const void *pa = in(a), *pb = in(b), *pgy = in(gy);
+  int acc_a = 1, acc_b = 1;
+  void *pga = out_acc(ga, &acc_a);
+  void *pgb = out_acc(gb, &acc_b);
+  B200_CALL(::b200_matmul_bw_ex(state_->ctx, imode(), pa, pb, pgy, pga, pgb, a.shape()[0], a.shape()[1],
+                                b.shape()[1], a.shape().batch(), b.shape().batch(), acc_a, acc_b, nullptr));
 }
 
 // ---------------------------------------------------------------- reductions and broadcast
@@ -481,8 +547,20 @@ void B200::inplace_multiply_const_impl(float k, Tensor &x) {
   B200_CALL(::b200_inplace_multiply_const(state_->ctx, imode(), MDATA(x), x.shape().size(), k, nullptr));
 }
 void B200::inplace_add_impl(const Tensor &x, Tensor &y) {
-  B200_CALL(::b200_inplace_add(state_->ctx, imode(), CDATA(x), MDATA(y), y.shape().volume(), x.shape().batch(),
-                               y.shape().batch(), 1.f, nullptr));
+  const void *px = in(x);
+  int acc = 1;
+  void *py = out_acc(y, &acc);
+  const std::uint32_t bx = x.shape().batch(), by = y.shape().batch();
+  if (!acc && bx == by) {
+    // y held (deferred) zeros: y = x
+    B200_CALL(::b200_copy(state_->ctx, imode(), px, imode(), py, y.shape().size(), nullptr));
+  } else if (!acc && by == 1) {
+    // y = sum over the batch of x
+    B200_CALL(::b200_batch_sum_fw(state_->ctx, imode(), px, py, y.shape().volume(), bx, nullptr));
+  } else {
+    if (!acc) B200_CALL(::b200_fill(state_->ctx, imode(), py, y.shape().size(), 0.f, nullptr));
+    B200_CALL(::b200_inplace_add(state_->ctx, imode(), px, py, y.shape().volume(), bx, by, 1.f, nullptr));
+  }
 }
 void B200::inplace_subtract_impl(const Tensor &x, Tensor &y) {
   B200_CALL(::b200_inplace_add(state_->ctx, imode(), CDATA(x), MDATA(y), y.shape().volume(), x.shape().batch(),

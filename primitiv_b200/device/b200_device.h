@@ -72,6 +72,17 @@ private:
   Mode mode_;
 
   void initialize(std::uint32_t rng_seed);
+
+  // Tensor -> device pointer.  primitiv zero-fills every gradient right before the first `+=`
+  // into it (primitiv/core/graph.cc:191-212).  reset_tensor(0) therefore only notes the
+  // tensor as "zero pending"; the fill is launched when something reads it or writes part of
+  // it (in / out), and never if the first writer is an accumulating kernel that can store
+  // instead of add (out_acc).
+  const void *in(const Tensor &x);
+  void *out(Tensor &x);
+  void *out_acc(Tensor &x, int *accumulate);
+  void materialize(const void *ptr);
+  void unary_bw(int op, const Tensor &x, const Tensor &y, const Tensor &gy, float k, std::int32_t ik, Tensor &gx);
   int imode() const { return static_cast<int>(mode_); }
   std::size_t elem_size() const { return mode_ == Mode::FP16 ? 2 : 4; }
 

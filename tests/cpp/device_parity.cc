@@ -543,6 +543,105 @@ void test_not_implemented(Pair &p) {
   expect(threw, "conv2d reports NotImplementedError");
 }
 
+// Gradients that start as zeros.  primitiv zero-fills a gradient right before the first `+=`
+// into it; the B200 device defers that fill and lets the first accumulating kernel store
+// instead.  Everything that can meet such a tensor first is run here from
+// new_tensor_by_constant(shape, 0) on both devices: accumulating kernels (store path), a reader,
+// a partial writer (the fill must then really happen), x op x (both gradients are one tensor),
+// a second accumulation (must add), reset(0) of a live tensor, and a tensor dropped while its
+// fill was still pending.
+void test_zero_gradients(Pair &p) {
+  Device *devs[2] = {&p.naive, &p.dev};
+  const float tol = g_tol * 4;
+  for (const auto &bb : kBatches) {
+    const std::uint32_t bs = std::max(bb[0], bb[1]);
+    const Shape sa({6, 5}, bb[0]), sb({6, 5}, bb[1]), sy({6, 5}, bs);
+    const vector<float> av = on_grid(rnd(sa.size(), .5f, 2.f)), bv = on_grid(rnd(sb.size(), .5f, 2.f));
+    const vector<float> gv = on_grid(rnd(sy.size()));
+    vector<float> r[2][6];
+    for (int d = 0; d < 2; ++d) {
+      Device &dev = *devs[d];
+      Tensor a = p.on(dev, sa, av), b = p.on(dev, sb, bv), gy = p.on(dev, sy, gv);
+      Tensor y = dev.multiply_fw(a, b);
+      Tensor ga = dev.new_tensor_by_constant(sa, 0), gb = dev.new_tensor_by_constant(sb, 0);
+      dev.multiply_bw(a, b, y, gy, ga, gb);              // first writer stores
+      r[d][0] = ga.to_vector(); r[d][1] = gb.to_vector();
+      dev.add_bw(a, b, y, gy, ga, gb);                   // second writer adds
+      r[d][2] = ga.to_vector(); r[d][3] = gb.to_vector();
+      Tensor acc = dev.new_tensor_by_constant(sa, 0);
+      dev.inplace_add(gy, acc);                          // same batch: copy; batch 1 <- 3: batch sum
+      dev.inplace_add(gy, acc);
+      r[d][4] = acc.to_vector();
+      Tensor wide = dev.new_tensor_by_constant(sy, 0);
+      dev.inplace_add(a, wide);                          // batch 3 <- 1 when a is broadcast
+      r[d][5] = wide.to_vector();
+    }
+    const std::string tag = " batches " + std::to_string(bb[0]) + "," + std::to_string(bb[1]);
+    expect_close(r[0][0], r[1][0], "multiply_bw into zeros: ga" + tag, tol);
+    expect_close(r[0][1], r[1][1], "multiply_bw into zeros: gb" + tag, tol);
+    expect_close(r[0][2], r[1][2], "add_bw after it: ga" + tag, tol);
+    expect_close(r[0][3], r[1][3], "add_bw after it: gb" + tag, tol);
+    expect_close(r[0][4], r[1][4], "inplace_add twice into zeros" + tag, tol);
+    expect_close(r[0][5], r[1][5], "inplace_add of a (possibly broadcast) tensor into zeros" + tag, tol);
+  }
+  {
+    const Shape s({7, 3}, 2), ss({3, 3}, 2);
+    const vector<float> xv = on_grid(rnd(s.size())), gv = on_grid(rnd(s.size())), sv = on_grid(rnd(ss.size()));
+    vector<float> r[2][7];
+    for (int d = 0; d < 2; ++d) {
+      Device &dev = *devs[d];
+      Tensor x = p.on(dev, s, xv), gy = p.on(dev, s, gv), gs = p.on(dev, ss, sv);
+      Tensor y = dev.tanh_fw(x);
+      Tensor gx = dev.new_tensor_by_constant(s, 0);
+      dev.tanh_bw(x, y, gy, gx);
+      r[d][0] = gx.to_vector();
+      dev.prelu_bw(x, y, gy, 0.1f, gx);
+      r[d][1] = gx.to_vector();
+      Tensor z = dev.new_tensor_by_constant(s, 0);
+      r[d][2] = z.to_vector();                           // a reader sees zeros
+      Tensor part = dev.new_tensor_by_constant(s, 0);
+      dev.slice_bw(gs, 0, 2, part);                      // writes rows 2..4 only
+      r[d][3] = part.to_vector();
+      Tensor twice = dev.new_tensor_by_constant(s, 0);   // x * x: both gradients are this tensor
+      Tensor sq = dev.multiply_fw(x, x);
+      dev.multiply_bw(x, x, sq, gy, twice, twice);
+      r[d][4] = twice.to_vector();
+      Tensor live = p.on(dev, s, xv);
+      live.reset(0);
+      dev.inplace_add(gy, live);
+      r[d][5] = live.to_vector();
+      { Tensor dropped = dev.new_tensor_by_constant(s, 0); }   // never used
+      Tensor next = p.on(dev, s, gv);                    // may reuse the dropped block
+      r[d][6] = next.to_vector();
+    }
+    expect_close(r[0][0], r[1][0], "tanh_bw into zeros", tol);
+    expect_close(r[0][1], r[1][1], "prelu_bw after it", tol);
+    expect_close(r[0][2], r[1][2], "zeros read back", 0.f);
+    expect_close(r[0][3], r[1][3], "slice_bw into zeros", tol);
+    expect_close(r[0][4], r[1][4], "multiply_bw with ga == gb into zeros", tol);
+    expect_close(r[0][5], r[1][5], "reset(0) of a live tensor, then inplace_add", tol);
+    expect_close(r[0][6], r[1][6], "a block reused after a dropped pending fill", 0.f);
+  }
+  for (const auto &bb : kBatches) {
+    const std::uint32_t bs = std::max(bb[0], bb[1]);
+    const Shape sa({64, 48}, bb[0]), sb({48, 40}, bb[1]), sy({64, 40}, bs);
+    const vector<float> av = on_grid(rnd(sa.size())), bv = on_grid(rnd(sb.size())), gv = on_grid(rnd(sy.size()));
+    vector<float> gas[2], gbs[2];
+    for (int d = 0; d < 2; ++d) {
+      Device &dev = *devs[d];
+      Tensor a = p.on(dev, sa, av), b = p.on(dev, sb, bv), gy = p.on(dev, sy, gv);
+      Tensor y = dev.matmul_fw(a, b);
+      Tensor ga = dev.new_tensor_by_constant(sa, 0), gb = dev.new_tensor_by_constant(sb, 0);
+      dev.matmul_bw(a, b, y, gy, ga, gb);   // stores
+      dev.matmul_bw(a, b, y, gy, ga, gb);   // adds
+      gas[d] = ga.to_vector(); gbs[d] = gb.to_vector();
+    }
+    const std::string tag = " " + sa.to_string() + " . " + sb.to_string();
+    expect_normwise(gas[0], gas[1], "matmul_bw twice into zeros: ga" + tag, g_mm_tol);
+    expect_normwise(gbs[0], gbs[1], "matmul_bw twice into zeros: gb" + tag, g_mm_tol);
+  }
+}
+
 // A small MLP trained through primitiv's Graph, Parameter and SGD on both devices from the
 // same initial weights: the loss trajectories must coincide (test/graph_test.cc:362-435 pins
 // such a run for the Naive device).
@@ -603,6 +702,7 @@ int main(int argc, char **argv) {
     test_batch_ops_and_inplace(p);
     test_random(p);
     test_not_implemented(p);
+    test_zero_gradients(p);
     test_graph_training(p);
   } catch (const std::exception &e) {
     std::cerr << "EXCEPTION: " << e.what() << std::endl;
