@@ -227,6 +227,13 @@ int b200_matmul_fw(b200_ctx *ctx, int mode, const void *a, const void *b, void *
   if (rc) return rc;
   if (!a || !b || !y) return B200_ERR_INVALID_ARG;
   const uint64_t na = (uint64_t)di * dj, nb = (uint64_t)dj * dk, ny = (uint64_t)di * dk;
+  if (ny == 0) return B200_OK;  // an empty result (primitiv's Shape never has a zero extent)
+  if (dj == 0) {                // an empty contraction: y = 0
+    DeviceGuard guard(ctx->device);
+    B200_CUDA_TRY(cudaMemsetAsync(y, 0, ny * (ba > bb ? ba : bb) * b200::elem_bytes(mode),
+                                  static_cast<cudaStream_t>(stream)));
+    return B200_OK;
+  }
   if (ba == 1) {
     // one product over the combined {dj, dk*bb} matrix: b's batches are adjacent columns
     return b200_gemm(ctx, mode, 0, 0, a, b, y, di, dk * bb, dj, 1, 1, 0, 0, 0, 0, 0, 0, 0, stream);
@@ -249,6 +256,14 @@ int b200_matmul_bw_ex(b200_ctx *ctx, int mode, const void *a, const void *b, con
   if (rc) return rc;
   if (!a || !b || !gy) return B200_ERR_INVALID_ARG;
   const uint64_t na = (uint64_t)di * dj, nb = (uint64_t)dj * dk, ny = (uint64_t)di * dk;
+  if (di == 0 || dj == 0 || dk == 0) {
+    // some extent is empty: nothing to add; a gradient that was to be written becomes zeros
+    DeviceGuard guard(ctx->device);
+    const size_t eb = b200::elem_bytes(mode);
+    if (ga && !acc_a && na) B200_CUDA_TRY(cudaMemsetAsync(ga, 0, na * ba * eb, static_cast<cudaStream_t>(stream)));
+    if (gb && !acc_b && nb) B200_CUDA_TRY(cudaMemsetAsync(gb, 0, nb * bb * eb, static_cast<cudaStream_t>(stream)));
+    return B200_OK;
+  }
   if (ba == 1) {
     const uint32_t dkb = dk * bb;
     // ga += gy_all . b_all^T : the batch sum is the tail of one long contraction

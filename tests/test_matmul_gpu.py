@@ -250,3 +250,39 @@ def test_split_k_products(ctx, shape, mode):
             ctx.set_path_policy(0)
         for x, y in zip(first, again):   # slices are added in a fixed order: same bits every run
             assert np.array_equal(x, y)
+
+
+# Extents of 1 in every position (scalars, dot products, outer products, matrix-vector), alone
+# and batched / broadcast: the shapes the reference's own small tests are made of.
+DEGENERATE = [
+    (1, 1, 1, 1, 1), (1, 1, 1, 4, 4), (1, 37, 1, 1, 3), (29, 1, 31, 3, 1), (1, 64, 40, 2, 2),
+    (48, 64, 1, 1, 5), (1, 4096, 1, 1, 1), (8, 8, 8, 1, 300),
+]
+
+
+@pytest.mark.parametrize("mode", list(MODES))
+@pytest.mark.parametrize("shape", DEGENERATE, ids=lambda s: "x".join(map(str, s)))
+def test_degenerate_extents(ctx, shape, mode):
+    di, dj, dk, ba, bb = shape
+    rng = np.random.default_rng(hash(shape) % (2 ** 32))
+    a = rng.uniform(-1, 1, di * dj * ba).astype(np.float32)
+    b = rng.uniform(-1, 1, dj * dk * bb).astype(np.float32)
+    gy = rng.standard_normal(di * dk * max(ba, bb)).astype(np.float32)
+    for policy in (0, 2):
+        ctx.set_path_policy(policy)
+        try:
+            _check_all(ctx, mode, a, b, gy, di, dj, dk, ba, bb)
+        finally:
+            ctx.set_path_policy(0)
+
+
+def test_zero_extent_is_a_no_op(ctx):
+    """An empty output launches nothing and touches nothing (the C ABI accepts what primitiv's
+    Shape can never produce, so that callers need not special-case it)."""
+    x = torch.full((16,), 3.0, device="cuda")
+    before = ctx.launch_count()
+    ctx.matmul_fw(pb.MODE_FP32_3XTF32, x.data_ptr(), x.data_ptr(), x.data_ptr(), 0, 4, 4, 1, 1)
+    ctx.matmul_bw(pb.MODE_FP32_3XTF32, x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(),
+                  4, 4, 0, 1, 1)
+    torch.cuda.synchronize()
+    assert ctx.launch_count() == before and float(x.sum()) == 48.0
