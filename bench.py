@@ -180,6 +180,38 @@ def cpu_sample(wl):
     return time.perf_counter() - t0, "port", 1
 
 
+def cpu_eigen_standin(wl):
+    """The reference's Eigen device cannot be built here (Eigen3 is not in the image): as a labelled
+    stand-in, the same three products of ONE batch element (forward, ga += gy.b^T, gb += a^T.gy) through
+    the host BLAS behind torch's CPU matmul, on all host threads.  Context beside the Naive figure,
+    never the baseline the speed-up is quoted against."""
+    import torch
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(0)
+    di, dj, dk = wl.di, wl.dj, wl.dk
+    a = torch.randn(di, dj, generator=g) * wl.sa
+    b = torch.randn(dj, dk, generator=g) * wl.sb
+    gy = torch.randn(di, dk, generator=g) * wl.sgy
+    if wl.half:
+        a, b, gy = a.half().float(), b.half().float(), gy.half().float()
+    ga, gb = torch.zeros(di, dj), torch.zeros(dj, dk)
+
+    def products():
+        y = a @ b
+        ga.add_(gy @ b.t())
+        gb.add_(a.t() @ gy)
+        return y
+
+    products()
+    t0 = time.perf_counter()
+    products()
+    t = time.perf_counter() - t0
+    return {"value": 3 * 2.0 * di * dj * dk / t / 1e9, "unit": "GFLOP/s", "cores": cores,
+            "kind": "stand-in for the reference's Eigen device: host BLAS sgemm via torch CPU, fp32",
+            "sample": "one batch element {%d,%d}.{%d,%d}, forward plus both backward products" % (di, dj, dj, dk)}
+
+
 def run_reference(args, wl, rank):
     if rank != 0:
         return
@@ -356,6 +388,7 @@ def emit(args, wl, world, ms, prof, launches, sampler, e2e, collectives):
         t, kind, cores = cpu_sample(wl)
         line["cpu_baseline"] = {"value": wl.sample_flops / t / 1e9, "unit": "GFLOP/s", "cores": cores,
                                 "kind": kind, "sample": wl.sample_text()}
+        line["cpu_eigen_standin"] = cpu_eigen_standin(wl)
     print(json.dumps(line), flush=True)
 
 
