@@ -42,9 +42,18 @@ def _stale(out, deps):
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(verbose=False, force=False):
+def build(verbose=False, force=False, dev_knobs=False):
+    """dev_knobs=True compiles the development switches of the tensor-core kernel in
+    (-DPRIMITIV_B200_DEV_KNOBS: environment variables that disable parts of it for
+    experiments).  The flag set is recorded beside the objects, so a product build after a
+    development build recompiles."""
     nvcc = _nvcc()
     os.makedirs(OBJ, exist_ok=True)
+    flags = NVCC_FLAGS + (["-DPRIMITIV_B200_DEV_KNOBS"] if dev_knobs else [])
+    stamp = os.path.join(OBJ, "flags.txt")
+    old_flags = open(stamp).read() if os.path.exists(stamp) else None
+    if old_flags != " ".join(flags):
+        force = True
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(os.path.dirname(PKG), "include", "primitiv_b200.h"))
     headers.append(os.path.join(os.path.dirname(PKG), "include", "primitiv_b200_ops.h"))
@@ -55,7 +64,7 @@ def build(verbose=False, force=False):
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
         if force or _stale(obj, [src] + headers):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+            cmd = [nvcc] + flags + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
             jobs.append(cmd)
 
     def run(cmd):
@@ -75,8 +84,10 @@ def build(verbose=False, force=False):
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
+    with open(stamp, "w") as f:
+        f.write(" ".join(flags))
     return LIB
 
 
 if __name__ == "__main__":
-    print(build(verbose="--verbose" in sys.argv, force="--force" in sys.argv))
+    print(build(verbose="--verbose" in sys.argv, force="--force" in sys.argv, dev_knobs="--dev-knobs" in sys.argv))

@@ -69,6 +69,16 @@
 namespace b200 {
 namespace {
 
+// Development knobs (environment variables that switch parts of the kernel off, cap the stage
+// count, change the tile band or forbid split-K) exist only in builds made with
+// -DPRIMITIV_B200_DEV_KNOBS; in the product build the flags below are constant zero and the
+// branches on them are compiled out.
+#ifdef PRIMITIV_B200_DEV_KNOBS
+constexpr bool kDevKnobs = true;
+#else
+constexpr bool kDevKnobs = false;
+#endif
+
 constexpr uint32_t kBM = 128;
 constexpr uint32_t kMaxStages = 8;
 constexpr uint32_t kKSteps = 4;  // MMAs per 128-byte k-block: 32 bytes of k each (8 tf32 / 16 fp16)
@@ -469,7 +479,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       uint32_t stage = 0, phase = 0;
       uint32_t armed_mask = 0, armed_parity = 0;
       bool ok = true;
-      const uint32_t stage_bytes = p.stage_bytes, nstages = p.stages, dbg = p.debug, kblocks = p.kblocks,
+      const uint32_t stage_bytes = p.stage_bytes, nstages = p.stages, dbg = kDevKnobs ? p.debug : 0u, kblocks = p.kblocks,
                      red = p.red, kstage = kSubs * p.bk;
       const uint32_t tx_bytes = p.stage_bytes * kCtas;
       const uint32_t splits = p.splits;
@@ -560,7 +570,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       // (the issue queue is shallow, so a gap between two MMAs is a gap in the pipe).
       const uint32_t stage_bytes = p.stage_bytes, sub_bytes = p.sub_bytes;
       const uint32_t a_plane = p.a_stage_bytes, b_plane = p.b_stage_bytes, b_off = planes * p.a_stage_bytes;
-      const uint32_t idesc = p.idesc, nstages = p.stages, dbg = p.debug;
+      const uint32_t idesc = p.idesc, nstages = p.stages, dbg = kDevKnobs ? p.debug : 0u;
       const uint32_t chunk_kblocks = p.chunk_kblocks, bn = p.bn;
       for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         uint32_t kb_left = kb_per_tile;
@@ -637,7 +647,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       const uint32_t m0 = mt * (kBM * kCtas);
       const uint32_t n0 = nt * p.bn;
       const uint32_t row = m0 + row_in_tile;
-      const bool row_ok = row < p.m && !(p.debug & 1u);
+      const bool row_ok = row < p.m && !(kDevKnobs && (p.debug & 1u));
       const unsigned long long base =
           static_cast<unsigned long long>(g) * p.c_gs + static_cast<unsigned long long>(row);
       if constexpr (kChunked) {
@@ -1099,7 +1109,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   void *partial = nullptr;
   {
     const uint64_t units = static_cast<uint64_t>(ctx->sm_count) / ctas;
-    static const char *sp = std::getenv("PRIMITIV_B200_TC_SPLIT");  // development: 0 = never split
+    static const char *sp = kDevKnobs ? std::getenv("PRIMITIV_B200_TC_SPLIT") : nullptr;  // 0 = never split
     const bool allow = !(sp && std::atoi(sp) == 0) && ctx->split_policy != 1;
     if (!fixed_scratch && allow && total_tiles * 2 <= units && p.kblocks >= 16u) {
       uint64_t want = units / total_tiles;
@@ -1178,11 +1188,13 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   }
   p.status = ctx->d_status;
   p.tmem_cols = p.bn * 2u;  // 128, 256 or 512: powers of two
-  {
+  p.debug = 0u;
+  p.band_m = kBandTilesM;
+  if (kDevKnobs) {
     static const char *dbg = std::getenv("PRIMITIV_B200_TC_DEBUG");
-    p.debug = dbg ? static_cast<uint32_t>(std::atoi(dbg)) : 0u;
+    if (dbg) p.debug = static_cast<uint32_t>(std::atoi(dbg));
     static const char *bd = std::getenv("PRIMITIV_B200_TC_BAND");
-    p.band_m = bd && std::atoi(bd) > 0 ? static_cast<uint32_t>(std::atoi(bd)) : kBandTilesM;
+    if (bd && std::atoi(bd) > 0) p.band_m = static_cast<uint32_t>(std::atoi(bd));
     static const char *st = std::getenv("PRIMITIV_B200_TC_STAGES");
     if (st) ctx->debug_stage_cap = std::atoi(st);
   }
