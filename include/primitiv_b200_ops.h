@@ -162,6 +162,34 @@ B200_API int b200_argminmax(b200_ctx *ctx, int mode, int want_max, const void *x
 B200_API int b200_batch_sum_fw(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t volume,
                                uint32_t batch, void *stream);
 
+/* conv2d.cc as a matrix product.  x {H, W, C} x batch, w {kh, kw, C, Cout} x batch, y {Ho, Wo, Cout},
+ * column-major, the kernel flipped as the reference does.  b200_im2col gathers
+ *     col[n][p + Ho*Wo * kk] = x[n or 0][yy*s0 - p0 + wy*d0, yx*s1 - p1 + wx*d1, c]   (0 outside the image)
+ * with p = yy + Ho*yx and kk = (c*kw + (kw-1-wx))*kh + (kh-1-wy), the order in which w is stored, so that
+ *     y = b200_matmul_fw(col {Ho*Wo, K}, w {K, Cout})      and
+ *     gcol, gw from b200_matmul_bw(col, w, gy)             with K = kh*kw*C,
+ * and b200_col2im adds gcol back: gx[n][xy, xx, c] += sum of the gcol entries that were read from
+ * there (a gather in a fixed order: deterministic).  `batch` counts the items of col / gcol. */
+B200_API int b200_im2col(b200_ctx *ctx, int mode, const void *x, void *col, uint32_t H, uint32_t W, uint32_t C,
+                         uint32_t kh, uint32_t kw, uint32_t Ho, uint32_t Wo, uint32_t pad0, uint32_t pad1,
+                         uint32_t stride0, uint32_t stride1, uint32_t dil0, uint32_t dil1, uint32_t batch,
+                         int x_batched, void *stream);
+B200_API int b200_col2im(b200_ctx *ctx, int mode, const void *gcol, void *gx, uint32_t H, uint32_t W, uint32_t C,
+                         uint32_t kh, uint32_t kw, uint32_t Ho, uint32_t Wo, uint32_t pad0, uint32_t pad1,
+                         uint32_t stride0, uint32_t stride1, uint32_t dil0, uint32_t dil1, uint32_t batch,
+                         void *stream);
+
+/* max_pool2d.cc: x {H, W} x repeat (channels x batch), y {Ho, Wo} x repeat; padding never wins the
+ * maximum; the backward adds gy to the first maximal element of each window (scan order: columns
+ * of the window outer, rows inner), overlapping windows in a fixed order. */
+B200_API int b200_max_pool2d_fw(b200_ctx *ctx, int mode, const void *x, void *y, uint32_t H, uint32_t W,
+                                uint32_t Ho, uint32_t Wo, uint32_t window0, uint32_t window1, uint32_t pad0,
+                                uint32_t pad1, uint32_t stride0, uint32_t stride1, uint64_t repeat, void *stream);
+B200_API int b200_max_pool2d_bw(b200_ctx *ctx, int mode, const void *x, const void *y, const void *gy, void *gx,
+                                uint32_t H, uint32_t W, uint32_t Ho, uint32_t Wo, uint32_t window0,
+                                uint32_t window1, uint32_t pad0, uint32_t pad1, uint32_t stride0, uint32_t stride1,
+                                uint64_t repeat, void *stream);
+
 /* Random fills (random_*.cc).  Counter-based Philox4x32-10 keyed by the context's seed and a
  * call counter: the stream of values depends only on (seed, call order, element index), not
  * on the launch geometry.  This is a generator of this library, not cuRAND's XORWOW. */

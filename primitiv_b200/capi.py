@@ -56,6 +56,10 @@ SIGNATURES = {
     "b200_inplace_multiply_const": (_int, [_vp, _int, _vp, _u64, ctypes.c_float, _vp]),
     "b200_fill": (_int, [_vp, _int, _vp, _u64, ctypes.c_float, _vp]),
     "b200_identity": (_int, [_vp, _int, _vp, _u32, _vp]),
+    "b200_im2col": (_int, [_vp, _int, _vp, _vp] + [_u32] * 14 + [_int, _vp]),
+    "b200_col2im": (_int, [_vp, _int, _vp, _vp] + [_u32] * 14 + [_vp]),
+    "b200_max_pool2d_fw": (_int, [_vp, _int, _vp, _vp] + [_u32] * 10 + [_u64, _vp]),
+    "b200_max_pool2d_bw": (_int, [_vp, _int, _vp, _vp, _vp, _vp] + [_u32] * 10 + [_u64, _vp]),
     "b200_upload": (_int, [_vp, _int, _vp, _vp, _u64, _vp]),
     "b200_download": (_int, [_vp, _int, _vp, _vp, _u64, _vp]),
     "b200_copy": (_int, [_vp, _int, _vp, _int, _vp, _u64, _vp]),

@@ -519,26 +519,82 @@ void B200::batch_sum_fw_impl(const Tensor &x, Tensor &y) {
   B200_CALL(::b200_batch_sum_fw(state_->ctx, imode(), CDATA(x), MDATA(y), y.shape().size(), x.shape().batch(), nullptr));
 }
 
-// ---------------------------------------------------------------- not provided
+// ---------------------------------------------------------------- convolution and pooling
 
-// Convolution and pooling are off the matmul path; like devices::CUDA built without cuDNN
-// (primitiv/devices/cuda/ops/conv2d.cu:77-88) they report NotImplementedError.
-void B200::conv2d_fw_impl(const Tensor &, const Tensor &, std::uint32_t, std::uint32_t, std::uint32_t,
-                          std::uint32_t, std::uint32_t, std::uint32_t, Tensor &) {
-  PRIMITIV_THROW_NOT_IMPLEMENTED;
+namespace {
+
+// Pool memory for the lifetime of one operation (the gathered input of a convolution).
+struct Scratch {
+  ::b200_ctx *ctx;
+  void *p = nullptr;
+  Scratch(::b200_ctx *c, std::size_t bytes) : ctx(c) {
+    std::size_t got = 0;
+    const int rc = ::b200_pool_alloc(ctx, bytes, &p, &got);
+    if (rc != 0) PRIMITIV_THROW_ERROR("B200: scratch allocation of " << bytes << " bytes failed: "
+                                      << ::b200_error_string(rc) << " [" << rc << "]");
+  }
+  ~Scratch() { if (p) ::b200_pool_free(ctx, p); }  // stream-ordered reuse: later work queues behind its readers
+  Scratch(const Scratch &) = delete;
+  Scratch &operator=(const Scratch &) = delete;
+};
+
+}  // namespace
+
+// conv2d = gather (im2col) + the matrix product of the hot path: y {P, Cout} = col {P, K} . w {K, Cout}
+// with P = Ho*Wo, K = kh*kw*C; the batch of x becomes the batch of col, a batch of w stays one
+// (the reference lets either operand broadcast, primitiv/devices/naive/ops/conv2d.cc:29-31).
+void B200::conv2d_fw_impl(const Tensor &x, const Tensor &w, std::uint32_t padding0, std::uint32_t padding1,
+                          std::uint32_t stride0, std::uint32_t stride1, std::uint32_t dilation0,
+                          std::uint32_t dilation1, Tensor &y) {
+  const Shape &xs = x.shape(), &ws = w.shape(), &ys = y.shape();
+  const std::uint32_t P = ys[0] * ys[1], K = ws[0] * ws[1] * xs[2], bx = xs.batch();
+  const void *px = in(x), *pw = in(w);
+  void *py = out(y);
+  Scratch col(state_->ctx, static_cast<std::size_t>(P) * K * bx * elem_size());
+  B200_CALL(::b200_im2col(state_->ctx, imode(), px, col.p, xs[0], xs[1], xs[2], ws[0], ws[1], ys[0], ys[1],
+                          padding0, padding1, stride0, stride1, dilation0, dilation1, bx, xs.has_batch(), nullptr));
+  B200_CALL(::b200_matmul_fw(state_->ctx, imode(), col.p, pw, py, P, K, ys[2], bx, ws.batch(), nullptr));
 }
-void B200::conv2d_bw_impl(const Tensor &, const Tensor &, const Tensor &, const Tensor &, std::uint32_t,
-                          std::uint32_t, std::uint32_t, std::uint32_t, std::uint32_t, std::uint32_t, Tensor &,
-                          Tensor &) {
-  PRIMITIV_THROW_NOT_IMPLEMENTED;
+
+void B200::conv2d_bw_impl(const Tensor &x, const Tensor &w, const Tensor &, const Tensor &gy,
+                          std::uint32_t padding0, std::uint32_t padding1, std::uint32_t stride0,
+                          std::uint32_t stride1, std::uint32_t dilation0, std::uint32_t dilation1, Tensor &gx,
+                          Tensor &gw) {
+  const Shape &xs = x.shape(), &ws = w.shape(), &ys = gy.shape();
+  const std::uint32_t P = ys[0] * ys[1], K = ws[0] * ws[1] * xs[2], bx = xs.batch();
+  const void *px = in(x), *pw = in(w), *pgy = in(gy);
+  int acc_w = 1;
+  void *pgw = out_acc(gw, &acc_w);
+  void *pgx = out(gx);
+  const std::size_t col_bytes = static_cast<std::size_t>(P) * K * bx * elem_size();
+  Scratch col(state_->ctx, col_bytes), gcol(state_->ctx, col_bytes);
+  B200_CALL(::b200_im2col(state_->ctx, imode(), px, col.p, xs[0], xs[1], xs[2], ws[0], ws[1], ys[0], ys[1],
+                          padding0, padding1, stride0, stride1, dilation0, dilation1, bx, xs.has_batch(), nullptr));
+  // gcol = gy . w^T (written, summed over the batch when x is broadcast); gw += col^T . gy
+  B200_CALL(::b200_matmul_bw_ex(state_->ctx, imode(), col.p, pw, pgy, gcol.p, pgw, P, K, ys[2], bx, ws.batch(),
+                                0, acc_w, nullptr));
+  B200_CALL(::b200_col2im(state_->ctx, imode(), gcol.p, pgx, xs[0], xs[1], xs[2], ws[0], ws[1], ys[0], ys[1],
+                          padding0, padding1, stride0, stride1, dilation0, dilation1, bx, nullptr));
 }
-void B200::max_pool2d_fw_impl(const Tensor &, std::uint32_t, std::uint32_t, std::uint32_t, std::uint32_t,
-                              std::uint32_t, std::uint32_t, Tensor &) {
-  PRIMITIV_THROW_NOT_IMPLEMENTED;
+
+void B200::max_pool2d_fw_impl(const Tensor &x, std::uint32_t window0, std::uint32_t window1,
+                              std::uint32_t padding0, std::uint32_t padding1, std::uint32_t stride0,
+                              std::uint32_t stride1, Tensor &y) {
+  const Shape &xs = x.shape(), &ys = y.shape();
+  const std::uint64_t repeat = xs.size() / (static_cast<std::uint64_t>(xs[0]) * xs[1]);
+  B200_CALL(::b200_max_pool2d_fw(state_->ctx, imode(), CDATA(x), MDATA(y), xs[0], xs[1], ys[0], ys[1], window0,
+                                 window1, padding0, padding1, stride0, stride1, repeat, nullptr));
 }
-void B200::max_pool2d_bw_impl(const Tensor &, const Tensor &, const Tensor &, std::uint32_t, std::uint32_t,
-                              std::uint32_t, std::uint32_t, std::uint32_t, std::uint32_t, Tensor &) {
-  PRIMITIV_THROW_NOT_IMPLEMENTED;
+
+void B200::max_pool2d_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, std::uint32_t window0,
+                              std::uint32_t window1, std::uint32_t padding0, std::uint32_t padding1,
+                              std::uint32_t stride0, std::uint32_t stride1, Tensor &gx) {
+  const Shape &xs = x.shape(), &ys = y.shape();
+  const std::uint64_t repeat = xs.size() / (static_cast<std::uint64_t>(xs[0]) * xs[1]);
+  const void *px = in(x), *py = in(y), *pgy = in(gy);
+  void *pgx = out(gx);
+  B200_CALL(::b200_max_pool2d_bw(state_->ctx, imode(), px, py, pgy, pgx, xs[0], xs[1], ys[0], ys[1], window0,
+                                 window1, padding0, padding1, stride0, stride1, repeat, nullptr));
 }
 
 // ---------------------------------------------------------------- in place

@@ -534,13 +534,91 @@ void test_random(Pair &p) {
   expect(a == b && b != c, "random fills are a function of (seed, call order)");
 }
 
-void test_not_implemented(Pair &p) {
-  bool threw = false;
-  try {
-    p.dev.conv2d_fw(p.dev.new_tensor_by_constant({4, 4, 1}, 1), p.dev.new_tensor_by_constant({2, 2, 1, 1}, 1),
-                    0, 0, 1, 1, 1, 1);
-  } catch (const primitiv::NotImplementedError &) { threw = true; }
-  expect(threw, "conv2d reports NotImplementedError");
+// conv2d and max_pool2d against Naive: paddings, strides, dilations, every batch broadcast
+// combination of x and w (primitiv/test/tensor_forward_test.cc:3103-3692, 3702-4068 run the
+// same sweeps against hard-coded answers), gradients accumulated into non-zero tensors, pooling
+// with ties and overlapping windows.
+void test_conv_and_pool(Pair &p) {
+  Device *devs[2] = {&p.naive, &p.dev};
+  struct Conv { std::uint32_t p0, p1, s0, s1, d0, d1; };
+  const Conv convs[] = {{0, 0, 1, 1, 1, 1}, {1, 2, 1, 1, 1, 1}, {0, 1, 2, 1, 1, 1}, {2, 0, 1, 2, 2, 1},
+                        {1, 1, 2, 2, 1, 2}, {3, 3, 3, 2, 2, 2}};
+  for (const Conv &c : convs) {
+    for (const auto &bb : kBatches) {
+      const Shape sx({7, 6, 3}, bb[0]), sw({3, 2, 3, 4}, bb[1]);
+      const vector<float> xv = on_grid(rnd(sx.size())), wv = on_grid(rnd(sw.size()));
+      vector<float> ys[2], gxs[2], gws[2];
+      Shape sy;
+      for (int d = 0; d < 2; ++d) {
+        Device &dev = *devs[d];
+        Tensor x = p.on(dev, sx, xv), w = p.on(dev, sw, wv);
+        Tensor y = dev.conv2d_fw(x, w, c.p0, c.p1, c.s0, c.s1, c.d0, c.d1);
+        sy = y.shape();
+        std::mt19937 local(99);
+        std::uniform_real_distribution<float> dist(-1.f, 1.f);
+        vector<float> gv(sy.size());
+        for (float &v : gv) v = to_half_grid(dist(local));
+        Tensor gy = p.on(dev, sy, gv);
+        Tensor gx = dev.new_tensor_by_constant(sx, 0.5f), gw = dev.new_tensor_by_constant(sw, 0.25f);
+        dev.conv2d_bw(x, w, y, gy, c.p0, c.p1, c.s0, c.s1, c.d0, c.d1, gx, gw);
+        ys[d] = y.to_vector(); gxs[d] = gx.to_vector(); gws[d] = gw.to_vector();
+      }
+      const std::string tag = " pad " + std::to_string(c.p0) + "," + std::to_string(c.p1) + " stride " +
+                              std::to_string(c.s0) + "," + std::to_string(c.s1) + " dilation " +
+                              std::to_string(c.d0) + "," + std::to_string(c.d1) + " batches " +
+                              std::to_string(bb[0]) + "," + std::to_string(bb[1]);
+      expect_normwise(ys[0], ys[1], "conv2d_fw" + tag, g_mm_tol);
+      expect_normwise(gxs[0], gxs[1], "conv2d_bw gx" + tag, g_mm_tol);
+      expect_normwise(gws[0], gws[1], "conv2d_bw gw" + tag, g_mm_tol);
+    }
+  }
+  {
+    // a convolution big enough for the tensor-core kernel: 32 x 32 x 16 image, 3 x 3 x 16 x 32 kernel, batch 4
+    const Shape sx({32, 32, 16}, 4), sw({3, 3, 16, 32});
+    const vector<float> xv = on_grid(rnd(sx.size())), wv = on_grid(rnd(sw.size(), -.2f, .2f));
+    vector<float> ys[2], gxs[2], gws[2];
+    for (int d = 0; d < 2; ++d) {
+      Device &dev = *devs[d];
+      Tensor x = p.on(dev, sx, xv), w = p.on(dev, sw, wv);
+      Tensor y = dev.conv2d_fw(x, w, 1, 1, 1, 1, 1, 1);
+      Tensor gy = dev.new_tensor_by_constant(y.shape(), 0.125f);
+      Tensor gx = dev.new_tensor_by_constant(sx, 0), gw = dev.new_tensor_by_constant(sw, 0);
+      dev.conv2d_bw(x, w, y, gy, 1, 1, 1, 1, 1, 1, gx, gw);
+      ys[d] = y.to_vector(); gxs[d] = gx.to_vector(); gws[d] = gw.to_vector();
+    }
+    expect_normwise(ys[0], ys[1], "conv2d_fw 32x32x16 * 3x3x16x32", g_mm_tol);
+    expect_normwise(gxs[0], gxs[1], "conv2d_bw gx 32x32x16 * 3x3x16x32", g_mm_tol);
+    expect_normwise(gws[0], gws[1], "conv2d_bw gw 32x32x16 * 3x3x16x32", g_mm_tol);
+  }
+  struct Pool { std::uint32_t w0, w1, p0, p1, s0, s1; };
+  const Pool pools[] = {{2, 2, 0, 0, 2, 2}, {3, 2, 1, 0, 1, 1}, {2, 3, 0, 1, 1, 2}, {3, 3, 1, 1, 2, 1},
+                        {7, 6, 0, 0, 1, 1}, {1, 1, 0, 0, 1, 1}, {2, 2, 1, 1, 3, 3}};
+  for (const Pool &c : pools) {
+    for (std::uint32_t batch : {1u, 3u}) {
+      const Shape sx({7, 6, 3}, batch);
+      vector<float> xv = rnd(sx.size(), -2.f, 2.f);
+      for (float &v : xv) v = std::round(v * 2.f) / 2.f;   // many ties: the first maximal element takes the gradient
+      vector<float> ys[2], gxs[2];
+      for (int d = 0; d < 2; ++d) {
+        Device &dev = *devs[d];
+        Tensor x = p.on(dev, sx, xv);
+        Tensor y = dev.max_pool2d_fw(x, c.w0, c.w1, c.p0, c.p1, c.s0, c.s1);
+        std::mt19937 local(7);
+        std::uniform_real_distribution<float> dist(-1.f, 1.f);
+        vector<float> gv(y.shape().size());
+        for (float &v : gv) v = to_half_grid(dist(local));
+        Tensor gy = p.on(dev, y.shape(), gv);
+        Tensor gx = dev.new_tensor_by_constant(sx, 0.5f);
+        dev.max_pool2d_bw(x, y, gy, c.w0, c.w1, c.p0, c.p1, c.s0, c.s1, gx);
+        ys[d] = y.to_vector(); gxs[d] = gx.to_vector();
+      }
+      const std::string tag = " window " + std::to_string(c.w0) + "," + std::to_string(c.w1) + " pad " +
+                              std::to_string(c.p0) + "," + std::to_string(c.p1) + " stride " +
+                              std::to_string(c.s0) + "," + std::to_string(c.s1) + " batch " + std::to_string(batch);
+      expect_close(ys[0], ys[1], "max_pool2d_fw" + tag, 0.f);
+      expect_close(gxs[0], gxs[1], "max_pool2d_bw" + tag, g_tol * 4);
+    }
+  }
 }
 
 // Gradients that start as zeros.  primitiv zero-fills a gradient right before the first `+=`
@@ -701,7 +779,7 @@ int main(int argc, char **argv) {
     test_movement(p);
     test_batch_ops_and_inplace(p);
     test_random(p);
-    test_not_implemented(p);
+    test_conv_and_pool(p);
     test_zero_gradients(p);
     test_graph_training(p);
   } catch (const std::exception &e) {
