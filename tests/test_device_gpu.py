@@ -122,3 +122,24 @@ def test_perceptron_training_step_matches_reference_naive(mode, tol):
     out = _run_json("mlp_step", mode, 65600, 1, 256)
     assert out["loss_rel_diff"] < tol and out["w1_rel_diff"] < tol and out["w3_rel_diff"] < tol, out
     assert 2.0 < out["loss"] < 2.6                      # ln(10) = 2.30 for an untrained 10-way classifier
+
+
+REF_SUITE = os.path.join(ROOT, "tests", "cpp", "_build", "ref_tensor_tests")
+
+
+@pytest.mark.gpu
+@needs_plugin
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32", "fp16"])
+def test_primitiv_own_tensor_tests_pass_on_b200(mode):
+    """The reference's own test/tensor_forward_test.cc, tensor_backward_test.cc and tensor_test.cc
+    (compiled from the reference tree, unmodified; 372 cases, each looping over every device in
+    the list) with two devices::B200 objects next to Naive in that list, at the reference's own
+    tolerances (4 ULPs for fp32 storage, the CUDA16 bound for half storage)."""
+    assert os.path.exists(REF_SUITE), "tests/cpp/_build/ref_tensor_tests is not built"
+    r = subprocess.run([REF_SUITE, mode], capture_output=True, text=True, timeout=900)
+    tail = (r.stdout + r.stderr)[-3000:]
+    assert r.returncode == 0, tail
+    summary = [l for l in r.stdout.splitlines() if l.startswith("[==========]")][-1]
+    ran, passed, failed = [int(w) for w in summary.replace(",", "").split() if w.isdigit()]
+    assert ran >= 370 and passed == ran and failed == 0, summary
+    assert r.stderr.count("Type: B200") >= 6   # two B200 objects in each of the three suites' lists
