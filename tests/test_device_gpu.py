@@ -143,3 +143,17 @@ def test_primitiv_own_tensor_tests_pass_on_b200(mode):
     ran, passed, failed = [int(w) for w in summary.replace(",", "").split() if w.isdigit()]
     assert ran >= 370 and passed == ran and failed == 0, summary
     assert r.stderr.count("Type: B200") >= 6   # two B200 objects in each of the three suites' lists
+
+
+@pytest.mark.gpu
+@needs_plugin
+def test_reference_xor_example_trains_on_b200():
+    """examples/xor/xor.cc of the reference, compiled from the reference tree with only its device
+    line swapped (a forced include turns `devices::Naive dev;` into a B200 on GPU 0): Graph,
+    Parameter, XavierUniform (device RNG), SGD and the matmul path, ten epochs, loss must fall."""
+    path = os.path.join(ROOT, "primitiv_b200", "device", "_build", "example_xor")
+    assert os.path.exists(path), "example_xor is not built"
+    r = subprocess.run([path], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-2000:]
+    losses = [float(l.split(":")[1]) for l in r.stdout.splitlines() if l.strip().startswith("loss:")]
+    assert len(losses) == 10 and losses[-1] < losses[0], losses
