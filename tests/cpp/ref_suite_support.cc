@@ -15,6 +15,7 @@
 #include <gtest/gtest.h>
 
 #include <cstdint>
+#include <cstdlib>
 #include <string>
 #include <vector>
 
@@ -39,9 +40,13 @@ void add_available_naive_devices(std::vector<primitiv::Device *> &devices) {
 void add_available_eigen_devices(std::vector<primitiv::Device *> &) {}
 void add_available_cuda_devices(std::vector<primitiv::Device *> &devices) {
   // devices::B200 stands where devices::CUDA / CUDA16 would
+  // PRIMITIV_B200_PATH_POLICY=2 sends even the tests' tiny products through the tensor-core kernel
+  const char *policy = std::getenv("PRIMITIV_B200_PATH_POLICY");
   for (std::uint32_t seed : {1u, 2u}) {
-    devices.emplace_back(new primitiv::devices::B200(0, seed, g_mode));
-    devices.back()->dump_description();
+    primitiv::devices::B200 *dev = new primitiv::devices::B200(0, seed, g_mode);
+    if (policy) dev->set_matmul_path_policy(std::atoi(policy));
+    devices.emplace_back(dev);
+    dev->dump_description();
   }
 }
 void add_available_cuda16_devices(std::vector<primitiv::Device *> &) {}

@@ -129,14 +129,17 @@ REF_SUITE = os.path.join(ROOT, "tests", "cpp", "_build", "ref_tensor_tests")
 
 @pytest.mark.gpu
 @needs_plugin
+@pytest.mark.parametrize("policy", ["0", "2"], ids=["auto", "tensorcore"])
 @pytest.mark.parametrize("mode", ["3xtf32", "tf32", "fp16"])
-def test_primitiv_own_tensor_tests_pass_on_b200(mode):
+def test_primitiv_own_tensor_tests_pass_on_b200(mode, policy):
     """The reference's own test/tensor_forward_test.cc, tensor_backward_test.cc and tensor_test.cc
     (compiled from the reference tree, unmodified; 372 cases, each looping over every device in
     the list) with two devices::B200 objects next to Naive in that list, at the reference's own
     tolerances (4 ULPs for fp32 storage, the CUDA16 bound for half storage)."""
     assert os.path.exists(REF_SUITE), "tests/cpp/_build/ref_tensor_tests is not built"
-    r = subprocess.run([REF_SUITE, mode], capture_output=True, text=True, timeout=900)
+    # policy 2: even the tests' tiny products go through the tensor-core kernel where eligible
+    env = dict(os.environ, PRIMITIV_B200_PATH_POLICY=policy)
+    r = subprocess.run([REF_SUITE, mode], capture_output=True, text=True, timeout=900, env=env)
     tail = (r.stdout + r.stderr)[-3000:]
     assert r.returncode == 0, tail
     summary = [l for l in r.stdout.splitlines() if l.startswith("[==========]")][-1]
