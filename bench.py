@@ -10,6 +10,7 @@ Shape({4096,4096}, batch 8) ~ N(0, 0.02), upstream gradient N(0,1), seeded synth
 data.  With N GPUs every rank holds a full batch-8 shard of its own (weak scaling; the
 products of different batch elements are independent, so the data path has no collective).
 
+`--workload batched_square_tf32` runs the same shapes in the single-pass TF32 fast mode, and
 `--workload fp16_broadcast` runs the half-precision workload instead: A {8192,8192}
 broadcast, B {8192,2048} x 32, fp32 accumulation, gA summed over the batch (and, with
 N GPUs, all-reduced over NCCL: B, gy, y, gB are batch-sharded 32 per GPU, A is replicated).
@@ -49,6 +50,14 @@ class Workload:
             self.sa, self.sb, self.sgy = 0.02, 0.02, 1.0
             self.dtype = "tf32x3 (fp32 storage, fp32 accumulate)"
             self.sample_dk = 64
+        elif name == "batched_square_tf32":
+            # the same shapes in the single-pass TF32 fast mode (tolerance 2e-3 instead of 1e-5)
+            self.di = self.dj = self.dk = 4096
+            self.ba = self.bb = batch if batch else 8
+            self.mode_name, self.passes, self.half = "TF32", 1, False
+            self.sa, self.sb, self.sgy = 0.02, 0.02, 1.0
+            self.dtype = "tf32 (fp32 storage, one tensor-core pass, fp32 accumulate)"
+            self.sample_dk = 64
         elif name == "fp16_broadcast":
             self.di = self.dj = 8192
             self.dk = 2048
@@ -67,6 +76,8 @@ class Workload:
     def label(self):
         if self.name == "batched_square":
             return "batched_square_gemm_4096x4096x4096_batch%d_fp32_3xtf32_fw_bw" % self.bs
+        if self.name == "batched_square_tf32":
+            return "batched_square_gemm_4096x4096x4096_batch%d_fp32_tf32_fast_fw_bw" % self.bs
         return "fp16_a8192x8192_broadcast_b8192x2048_batch%d_fw_bw" % self.bs
 
     def sample_text(self):
@@ -246,7 +257,7 @@ def run_ours(args, wl, rank, local_rank, world):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = pb.Context(local_rank)
-    mode = pb.MODE_FP16 if wl.half else pb.MODE_FP32_3XTF32
+    mode = pb.MODE_FP16 if wl.half else (pb.MODE_TF32 if wl.mode_name == "TF32" else pb.MODE_FP32_3XTF32)
     dt = torch.float16 if wl.half else torch.float32
     g = torch.Generator(device="cuda")
     g.manual_seed(1234 + rank)
@@ -398,7 +409,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="batched_square", choices=["batched_square", "fp16_broadcast"])
+    ap.add_argument("--workload", default="batched_square", choices=["batched_square", "batched_square_tf32", "fp16_broadcast"])
     ap.add_argument("--batch", type=int, default=0,
                     help="batch elements per GPU (default: the workload's own, 8 / 32; smaller values are for "
                          "profiler captures and show in config.workload)")
