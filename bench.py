@@ -10,7 +10,8 @@ Shape({4096,4096}, batch 8) ~ N(0, 0.02), upstream gradient N(0,1), seeded synth
 data.  With N GPUs every rank holds a full batch-8 shard of its own (weak scaling; the
 products of different batch elements are independent, so the data path has no collective).
 
-`--workload batched_square_tf32` runs the same shapes in the single-pass TF32 fast mode, and
+`--workload lstm_steps` / `--workload mlp_step` run the graph-level programs of the other named
+configurations (1 GPU).  `--workload batched_square_tf32` runs the same shapes in the single-pass TF32 fast mode, and
 `--workload fp16_broadcast` runs the half-precision workload instead: A {8192,8192}
 broadcast, B {8192,2048} x 32, fp32 accumulation, gA summed over the batch (and, with
 N GPUs, all-reduced over NCCL: B, gy, y, gB are batch-sharded 32 per GPU, A is replicated).
@@ -403,19 +404,78 @@ def emit(args, wl, world, ms, prof, launches, sampler, e2e, collectives):
     print(json.dumps(line), flush=True)
 
 
+GRAPH_PROGRAMS = {
+    # workload -> (binary under primitiv_b200/device/_build, arguments before the repeat count, what it is)
+    "lstm_steps": ("lstm_steps", ["tf32", "50"],
+                   "50 LSTM steps (E 512, H 1024, batch 64) forward + backward through primitiv's Graph, TF32 fast mode"),
+    "mlp_step": ("mlp_step", ["3xtf32", "65536"],
+                 "one SGD step of 784-1024-1024-10 at batch 65536 through primitiv's Graph, 3xTF32"),
+}
+
+
+def run_graph_program(args):
+    """The other named configurations are whole-graph programs on devices::B200 (C++, built where the
+    primitiv headers are available).  This leg runs one and reports it in the same line format; the
+    step is the program's own (one recurrent loop / one training step), timed by wall clock inside it
+    because host work is part of what it measures."""
+    import subprocess
+    binary, pre, what = GRAPH_PROGRAMS[args.workload]
+    path = os.path.join(ROOT, "primitiv_b200", "device", "_build", binary)
+    if not os.path.exists(path):
+        print(json.dumps({"workload": args.workload, "unavailable": "%s is not built (needs the primitiv headers)" % path}))
+        return
+    r = subprocess.run([path] + pre + [str(max(args.steps, 1)), "0"], capture_output=True, text=True, timeout=1800)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise SystemExit(r.returncode)
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    ms = out.get("ms_per_loop_mean", out.get("ms_per_step_mean"))
+    dev = out.get("device_ms_per_loop", out.get("device_ms_per_step"))
+    launches = out.get("launches_per_loop", out.get("launches_per_step"))
+    passes = 3.0 if pre[0] == "3xtf32" else 1.0
+    flops = out["matmul_gflops"] * 1e9 * ms * 1e-3   # algorithmic matmul FLOP of one step
+    peaks = measured_peaks()
+    peak = peaks["bf16_sustained"] / 2.0
+    achieved = passes * flops / (dev["gemm_tc"] * 1e-3) / 1e12 if dev["gemm_tc"] else 0.0
+    line = {
+        "metric": METRIC, "value": out["matmul_gflops"], "unit": "GFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": 2, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "tf32x3" if passes == 3.0 else "tf32", "data": "synthetic",
+        "config": {"workload": args.workload, "what": what, "timing": "wall clock inside the program, host work included"},
+        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel", "achieved": achieved, "peak": peak,
+                     "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                     "note": "the step is launch-bound: tensor-issued FLOP / device time of the product launches only "
+                             "(per-launch CUDA events of one extra, untimed step)",
+                     "device_ms_per_step": dev, "launches_per_step": launches},
+        "gpu_launches": int(sum(launches.values()) * args.steps),
+        "e2e": {"value": out["matmul_gflops"], "unit": "GFLOP/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
+                "note": "value is already end to end: inputs start in host vectors"},
+        "program_output": out,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="batched_square", choices=["batched_square", "batched_square_tf32", "fp16_broadcast"])
+    ap.add_argument("--workload", default="batched_square", choices=["batched_square", "batched_square_tf32", "fp16_broadcast", "lstm_steps", "mlp_step"])
     ap.add_argument("--batch", type=int, default=0,
                     help="batch elements per GPU (default: the workload's own, 8 / 32; smaller values are for "
                          "profiler captures and show in config.workload)")
     ap.add_argument("--skip-e2e", action="store_true", help="leave out the host-buffer leg (profiler captures)")
     ap.add_argument("--skip-cpu", action="store_true", help="leave out the CPU baseline leg (profiler captures)")
     args = ap.parse_args()
+    if args.workload in GRAPH_PROGRAMS:
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "workload": args.workload,
+                              "unavailable": "the program times the reference's Naive device itself "
+                                             "(naive_ms_per_step, on a prefix) when given a check size"}))
+        elif int(os.environ.get("RANK", "0")) == 0:
+            run_graph_program(args)
+        return
     wl = Workload(args.workload, args.batch)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
