@@ -59,6 +59,14 @@ class Workload:
             self.sa, self.sb, self.sgy = 0.02, 0.02, 1.0
             self.dtype = "tf32 (fp32 storage, one tensor-core pass, fp32 accumulate)"
             self.sample_dk = 64
+        elif name == "batched_square_3xfp16":
+            # the same shapes and fp32-grade results on the fp16 pipe (row-scaled half planes, 3 passes)
+            self.di = self.dj = self.dk = 4096
+            self.ba = self.bb = batch if batch else 8
+            self.mode_name, self.passes, self.half = "3xFP16", 3, False
+            self.sa, self.sb, self.sgy = 0.02, 0.02, 1.0
+            self.dtype = "f16x3 (fp32 storage, two scaled half planes per operand, fp32 accumulate)"
+            self.sample_dk = 64
         elif name == "fp16_broadcast":
             self.di = self.dj = 8192
             self.dk = 2048
@@ -77,6 +85,8 @@ class Workload:
     def label(self):
         if self.name == "batched_square":
             return "batched_square_gemm_4096x4096x4096_batch%d_fp32_3xtf32_fw_bw" % self.bs
+        if self.name == "batched_square_3xfp16":
+            return "batched_square_gemm_4096x4096x4096_batch%d_fp32_3xfp16_fw_bw" % self.bs
         if self.name == "batched_square_tf32":
             return "batched_square_gemm_4096x4096x4096_batch%d_fp32_tf32_fast_fw_bw" % self.bs
         return "fp16_a8192x8192_broadcast_b8192x2048_batch%d_fw_bw" % self.bs
@@ -258,7 +268,7 @@ def run_ours(args, wl, rank, local_rank, world):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = pb.Context(local_rank)
-    mode = pb.MODE_FP16 if wl.half else (pb.MODE_TF32 if wl.mode_name == "TF32" else pb.MODE_FP32_3XTF32)
+    mode = {"FP16": pb.MODE_FP16, "TF32": pb.MODE_TF32, "3xFP16": pb.MODE_FP32_3XFP16}.get(wl.mode_name, pb.MODE_FP32_3XTF32)
     dt = torch.float16 if wl.half else torch.float32
     g = torch.Generator(device="cuda")
     g.manual_seed(1234 + rank)
@@ -364,7 +374,7 @@ def emit(args, wl, world, ms, prof, launches, sampler, e2e, collectives):
     issued_flops_per_launch = float(wl.passes) * wl.flops * args.steps / max(tc_n, 1)
     tc_avg_ms = tc_ms / max(tc_n, 1)
     achieved = issued_flops_per_launch / (tc_avg_ms * 1e-3) / 1e12 if tc_n else 0.0
-    div = 1.0 if wl.half else 2.0     # TF32 runs at half the 16-bit rate
+    div = 1.0 if (wl.half or wl.mode_name == "3xFP16") else 2.0     # TF32 runs at half the 16-bit rate
     peak, burst = peaks["bf16_sustained"] / div, peaks["bf16_burst"] / div
     # DRAM bytes of one gemm_tc_kernel launch: ncu capture of the batch-2 square case (1.48 GB, mean of
     # an overwriting and an accumulating launch, see profiles/), scaled by the batch (independent
@@ -461,7 +471,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="batched_square", choices=["batched_square", "batched_square_tf32", "fp16_broadcast", "lstm_steps", "mlp_step"])
+    ap.add_argument("--workload", default="batched_square", choices=["batched_square", "batched_square_tf32", "batched_square_3xfp16", "fp16_broadcast", "lstm_steps",
+                             "mlp_step"])
     ap.add_argument("--batch", type=int, default=0,
                     help="batch elements per GPU (default: the workload's own, 8 / 32; smaller values are for "
                          "profiler captures and show in config.workload)")

@@ -37,7 +37,14 @@ typedef struct b200_ctx b200_ctx;
 enum {
   B200_MODE_FP32_3XTF32 = 0, /* fp32 storage; each product = 3 TF32 tensor-core passes on hi/lo splits; fp32 accuracy */
   B200_MODE_TF32        = 1, /* fp32 storage; one TF32 pass */
-  B200_MODE_FP16        = 2  /* half storage, fp32 accumulation, one rounding on store (mirrors primitiv::devices::CUDA16) */
+  B200_MODE_FP16        = 2, /* half storage, fp32 accumulation, one rounding on store (mirrors primitiv::devices::CUDA16) */
+  /* fp32 storage and fp32-grade results on the fp16 tensor pipe: every operand row is scaled by a
+   * power of two and split into two half planes, x*s = h0 + h1 (11 + 11 mantissa bits, as TF32 hi + lo),
+   * a product is three fp16 passes (h1,h0), (h0,h1), (h0,h0) at twice the TF32 rate, and the scales
+   * are undone in the epilogue.  Same normwise accuracy class as 3xTF32 (<= 1e-5); elements more than
+   * ~2^18 below the largest of their row lose relative (not absolute) precision, which 3xTF32, with
+   * TF32's 8-bit exponent, does not.  No counterpart in the reference. */
+  B200_MODE_FP32_3XFP16 = 3
 };
 
 /* Error codes (values >= 1000; smaller non-zero values are cudaError_t). */

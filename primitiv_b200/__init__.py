@@ -8,5 +8,5 @@ multi-GPU harness.  There is no Python or CPU implementation behind it: if the
 library is missing, or no sm_100 GPU is visible, the calls raise.
 """
 from .capi import (  # noqa: F401
-    MODE_FP32_3XTF32, MODE_TF32, MODE_FP16, B200Error, Context, lib, library_path,
+    MODE_FP32_3XTF32, MODE_TF32, MODE_FP16, MODE_FP32_3XFP16, B200Error, Context, lib, library_path,
 )

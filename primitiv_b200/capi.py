@@ -10,6 +10,7 @@ import os
 MODE_FP32_3XTF32 = 0
 MODE_TF32 = 1
 MODE_FP16 = 2
+MODE_FP32_3XFP16 = 3
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
 _LIB = None

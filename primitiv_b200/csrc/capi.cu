@@ -181,7 +181,7 @@ int b200_gemm(b200_ctx *ctx, int mode, int trans_a, int trans_b, const void *A, 
               uint64_t a_gs, uint64_t a_rs, uint64_t b_gs, uint64_t b_rs, uint64_t c_gs,
               int accumulate, int force_path, void *stream) {
   if (!ctx || !A || !B || !C) return B200_ERR_INVALID_ARG;
-  if (mode < B200_MODE_FP32_3XTF32 || mode > B200_MODE_FP16) return B200_ERR_INVALID_ARG;
+  if (mode < B200_MODE_FP32_3XTF32 || mode > B200_MODE_FP32_3XFP16) return B200_ERR_INVALID_ARG;
   if (m == 0 || n == 0 || groups == 0) return B200_OK;
   if (k == 0 || red == 0) return B200_ERR_INVALID_ARG;
   DeviceGuard guard(ctx->device);
@@ -215,7 +215,7 @@ int b200_gemm_3xtf32_noalloc(b200_ctx *ctx, int trans_a, int trans_b, const void
 
 static int check_matmul(const b200_ctx *ctx, int mode, uint32_t ba, uint32_t bb) {
   if (!ctx) return B200_ERR_INVALID_ARG;
-  if (mode < B200_MODE_FP32_3XTF32 || mode > B200_MODE_FP16) return B200_ERR_INVALID_ARG;
+  if (mode < B200_MODE_FP32_3XTF32 || mode > B200_MODE_FP32_3XFP16) return B200_ERR_INVALID_ARG;
   if (ba == 0 || bb == 0) return B200_ERR_INVALID_ARG;
   if (ba != bb && ba != 1 && bb != 1) return B200_ERR_INVALID_ARG;  // Shape::has_compatible_batch
   return B200_OK;

@@ -109,6 +109,10 @@ struct alignas(64) TcParams {
   uint32_t chunk_kblocks;  // k-blocks per accumulation chunk
   uint32_t accumulate, out_half, kind_f16;
   uint32_t band_m;  // tile-rows per band of the tile order
+  // 3xFP16 mode: the epilogue multiplies by 1/s of the output row (from A) and column (from B);
+  // per group when the operand has one matrix per group, else one set (stride 0)
+  const float *scale_a, *scale_b;
+  uint32_t scale_a_gs, scale_b_gs;
   uint32_t splits;  // k-splits per output tile (split-K): `groups` then counts groups x splits,
                     // kblocks is per split and C is the fp32 partial buffer [group][split][m x n]
   uint32_t a_stage_bytes, b_stage_bytes, stage_bytes;  // per plane, per CTA; stage = subs * planes * (a + b)
@@ -407,10 +411,10 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uin
 // single-CTA tile, which is what bounds this kernel.
 template <bool kChunked, int kCtas, int kKind>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ TcParams p) {
-  constexpr int kPasses = kKind == 0 ? 3 : 1;   // kind 0 = 3xTF32, 1 = TF32, 2 = FP16
+  constexpr int kPasses = (kKind == 0 || kKind == 3) ? 3 : 1;  // kind 0 = 3xTF32, 1 = TF32, 2 = FP16, 3 = 3xFP16
   constexpr uint32_t kSubs = kPasses == 1 ? 2u : 1u;  // k-blocks per pipeline stage
-  constexpr bool kF16 = kKind == 2;
-  static_assert(!kChunked || kKind == 0, "only the 3xTF32 product is chunked");
+  constexpr bool kF16 = kKind >= 2;
+  static_assert(!kChunked || kPasses == 3, "only the three-pass products are chunked");
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
   __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
@@ -650,6 +654,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       const bool row_ok = row < p.m && !(kDevKnobs && (p.debug & 1u));
       const unsigned long long base =
           static_cast<unsigned long long>(g) * p.c_gs + static_cast<unsigned long long>(row);
+      // 3xFP16: undo the power-of-two scales of this output row (from A) and of each column (from B)
+      float row_scale = 1.f;
+      const float *col_scale = nullptr;
+      if constexpr (kKind == 3) {
+        const uint32_t g_real = g / p.splits;
+        if (row < p.m) row_scale = p.scale_a[static_cast<unsigned long long>(g_real) * p.scale_a_gs + row];
+        col_scale = p.scale_b + static_cast<unsigned long long>(g_real) * p.scale_b_gs;
+      }
       if constexpr (kChunked) {
         float acc[4][32];
         for (uint32_t c = 0; ok && c < chunks_per_tile; ++c, ++chunk_no) {
@@ -685,6 +697,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
           for (uint32_t j = 0; j < 4u; ++j) {
             const uint32_t col0 = n0 + col_base + j * 32u;
             if (j * 32u < cols_per && col0 < p.n) {
+              if constexpr (kKind == 3) {
+#pragma unroll
+                for (uint32_t i = 0; i < 32u; ++i)
+                  if (col0 + i < p.n) acc[j][i] *= row_scale * col_scale[col0 + i];
+              }
               if (p.out_half)
                 store_cols<8>(static_cast<__half *>(p.C), base, p.m, p.n, col0, acc[j], p.accumulate != 0u);
               else
@@ -709,6 +726,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             float x[32];
 #pragma unroll
             for (uint32_t i = 0; i < 32u; ++i) x[i] = __uint_as_float(v[i]);
+            if constexpr (kKind == 3) {
+#pragma unroll
+              for (uint32_t i = 0; i < 32u; ++i)
+                if (col0 + i < p.n) x[i] *= row_scale * col_scale[col0 + i];
+            }
             if (p.out_half)
               store_cols<32>(static_cast<__half *>(p.C), base, p.m, p.n, col0, x, p.accumulate != 0u);
             else
@@ -834,6 +856,108 @@ __global__ void __launch_bounds__(256) pack_tf32_kernel(
   }
 }
 
+// ---- pre-pass of the 3xFP16 mode ----
+//
+// Every row of an operand (index mn, all of k) gets a power-of-two scale s that brings its
+// largest magnitude into [2^14, 2^15), half's top binades; then x*s = h0 + h1 with
+// h0 = rn_half(x*s), h1 = rn_half(x*s - h0): two half planes with 11 + 11 mantissa bits, the
+// same as TF32 hi + lo.  row_scale_kernel writes 1/s (what the epilogue multiplies by);
+// when the batch is itself a contraction axis (`shared`), one scale per row covers all batches.
+__device__ __forceinline__ float inv_scale_for(float amax) {
+  int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 127;  // floor(log2(amax)) for normal values
+  e = e < -100 ? -100 : (e > 127 ? 127 : e);
+  return __uint_as_float(static_cast<uint32_t>(e - 14 + 127) << 23);  // 2^(e-14), so that amax / it is in [2^14, 2^15)
+}
+
+// K-major source (k contiguous): one warp per row.
+__global__ void __launch_bounds__(256) row_scale_kmajor_kernel(const float *__restrict__ src, float *__restrict__ inv,
+                                                               uint32_t mn, uint32_t k, unsigned long long ld,
+                                                               unsigned long long src_bs, uint32_t nbatch, int shared) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const unsigned long long rows = static_cast<unsigned long long>(mn) * (shared ? 1u : nbatch);
+  for (unsigned long long r = blockIdx.x * 8ull + (threadIdx.x >> 5); r < rows; r += gridDim.x * 8ull) {
+    const unsigned long long b0 = shared ? 0 : r / mn, i = r - b0 * mn;
+    float amax = 0.f;
+    for (uint32_t b = 0; b < (shared ? nbatch : 1u); ++b) {
+      const float *row = src + (b0 + b) * src_bs + i * ld;
+      for (uint32_t p = lane; p < k; p += 32u) amax = fmaxf(amax, fabsf(row[p]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) inv[r] = inv_scale_for(amax);
+  }
+}
+
+// MN-major source (mn contiguous): 32 rows x 8 k-lanes per CTA, coalesced along mn.
+__global__ void __launch_bounds__(256) row_scale_mnmajor_kernel(const float *__restrict__ src, float *__restrict__ inv,
+                                                                uint32_t mn, uint32_t k, unsigned long long ld,
+                                                                unsigned long long src_bs, uint32_t nbatch, int shared) {
+  __shared__ float buf[8][32];
+  const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
+  const uint32_t tiles = (mn + 31u) / 32u;
+  const unsigned long long total = static_cast<unsigned long long>(tiles) * (shared ? 1u : nbatch);
+  for (unsigned long long t = blockIdx.x; t < total; t += gridDim.x) {
+    const unsigned long long b0 = shared ? 0 : t / tiles;
+    const uint32_t i = static_cast<uint32_t>(t - b0 * tiles) * 32u + tx;
+    float amax = 0.f;
+    if (i < mn)
+      for (uint32_t b = 0; b < (shared ? nbatch : 1u); ++b) {
+        const float *m0 = src + (b0 + b) * src_bs + i;
+        for (uint32_t p = ty; p < k; p += 8u) amax = fmaxf(amax, fabsf(m0[static_cast<unsigned long long>(p) * ld]));
+      }
+    buf[ty][tx] = amax;
+    __syncthreads();
+    if (ty == 0 && i < mn) {
+#pragma unroll
+      for (uint32_t l = 1; l < 8u; ++l) amax = fmaxf(amax, buf[l][tx]);
+      inv[b0 * mn + i] = inv_scale_for(amax);
+    }
+    __syncthreads();
+  }
+}
+
+// Writes the two half planes, K-major [b][i][k_pad] (k_pad a multiple of 8: 16-byte rows).
+// Same tiling as pack_tf32_kernel; inv holds 1/s per row ([b][i], or [i] when shared).
+template <bool kTranspose>
+__global__ void __launch_bounds__(256) pack_f16_kernel(const float *__restrict__ src, const float *__restrict__ inv,
+                                                       __half *__restrict__ h0, __half *__restrict__ h1, uint32_t mn,
+                                                       uint32_t k, uint32_t k_pad, unsigned long long ld,
+                                                       unsigned long long src_bs, uint32_t tiles_mn, uint32_t tiles_k,
+                                                       unsigned long long total_tiles, int shared) {
+  __shared__ float tile[32][33];
+  const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;  // 32 x 8
+  for (unsigned long long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    const unsigned long long per_b = static_cast<unsigned long long>(tiles_mn) * tiles_k;
+    const unsigned long long b = t / per_b;
+    const uint32_t rem = static_cast<uint32_t>(t - b * per_b);
+    const uint32_t i0 = (rem % tiles_mn) * 32u, p0 = (rem / tiles_mn) * 32u;
+    const float *s = src + b * src_bs;
+    const float *iv = inv + (shared ? 0ull : b * mn);
+    const unsigned long long dst_b = b * static_cast<unsigned long long>(mn) * k_pad;
+    if (kTranspose) {
+#pragma unroll
+      for (uint32_t j = 0; j < 32u; j += 8u) {
+        const uint32_t i = i0 + tx, pp = p0 + ty + j;
+        tile[ty + j][tx] = (i < mn && pp < k) ? s[static_cast<unsigned long long>(pp) * ld + i] : 0.f;
+      }
+      __syncthreads();
+    }
+#pragma unroll
+    for (uint32_t j = 0; j < 32u; j += 8u) {
+      const uint32_t i = i0 + ty + j, pp = p0 + tx;
+      if (i < mn && pp < k) {
+        const float x = kTranspose ? tile[tx][ty + j] : s[static_cast<unsigned long long>(i) * ld + pp];
+        const float xs = x * (1.f / iv[i]);  // 1/inv is the power-of-two scale: exact
+        const __half a = __float2half_rn(xs);
+        const unsigned long long o = dst_b + static_cast<unsigned long long>(i) * k_pad + pp;
+        h0[o] = a;
+        h1[o] = __float2half_rn(xs - __half2float(a));
+      }
+    }
+    if (kTranspose) __syncthreads();
+  }
+}
+
 // Fast paths of the packing pre-pass (both move 128 bits per thread per access).
 //
 // pack_flat_kernel: a K-major source whose rows need no padding (k % 4 == 0) and whose
@@ -896,6 +1020,107 @@ __global__ void __launch_bounds__(256) pack_transpose64_kernel(const float *__re
         const unsigned long long o = dst_b + static_cast<unsigned long long>(i0 + im) * k + p0 + pk;
         *reinterpret_cast<float4 *>(hi + o) = h;
         if (lo) *reinterpret_cast<float4 *>(lo + o) = l;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Fast paths of the 3xFP16 pre-pass.
+//
+// pack_f16_rows_kernel: a K-major source with 16-byte aligned rows and k % 8 == 0.  One CTA per
+// row at a time: the row's largest magnitude (float4 loads, block reduction), then the row once
+// more (it is still in L1 / L2) split into the two half planes with 16-byte stores.  Scale and
+// split in one kernel: 4 bytes read from HBM and 4 written per element.
+__global__ void __launch_bounds__(256) pack_f16_rows_kernel(const float *__restrict__ src, float *__restrict__ inv,
+                                                            __half *__restrict__ h0, __half *__restrict__ h1,
+                                                            uint32_t mn, uint32_t k, unsigned long long ld,
+                                                            unsigned long long src_bs, unsigned long long rows) {
+  __shared__ float red[8];
+  const uint32_t t = threadIdx.x, lane = t & 31u, warp = t >> 5;
+  const uint32_t k8 = k >> 3;
+  for (unsigned long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const unsigned long long b = r / mn, i = r - b * mn;
+    const float4 *row = reinterpret_cast<const float4 *>(src + b * src_bs + i * ld);
+    float amax = 0.f;
+    for (uint32_t c = t; c < 2u * k8; c += 256u) {
+      const float4 v = row[c];
+      amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) red[warp] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (uint32_t w = 1; w < 8u; ++w) amax = fmaxf(amax, red[w]);
+    const float iv = inv_scale_for(amax), sc = 1.f / iv;
+    if (t == 0) inv[r] = iv;
+    uint4 *d0 = reinterpret_cast<uint4 *>(h0 + r * static_cast<unsigned long long>(k));
+    uint4 *d1 = reinterpret_cast<uint4 *>(h1 + r * static_cast<unsigned long long>(k));
+    for (uint32_t c = t; c < k8; c += 256u) {
+      const float4 u = row[2u * c], v = row[2u * c + 1u];
+      const float x[8] = {u.x * sc, u.y * sc, u.z * sc, u.w * sc, v.x * sc, v.y * sc, v.z * sc, v.w * sc};
+      __align__(16) __half a[8], e[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        a[j] = __float2half_rn(x[j]);
+        e[j] = __float2half_rn(x[j] - __half2float(a[j]));
+      }
+      d0[c] = *reinterpret_cast<const uint4 *>(a);
+      d1[c] = *reinterpret_cast<const uint4 *>(e);
+    }
+    __syncthreads();  // red[] is reused by the next row
+  }
+}
+
+// pack_f16_transpose64_kernel: an MN-major source with mn % 4 == 0 and k % 8 == 0 whose row
+// scales are already known (row_scale_mnmajor_kernel).  64 x 64 tiles through shared memory:
+// float4 reads along mn, 16-byte half stores along k.
+__global__ void __launch_bounds__(256) pack_f16_transpose64_kernel(const float *__restrict__ src,
+                                                                   const float *__restrict__ inv,
+                                                                   __half *__restrict__ h0, __half *__restrict__ h1,
+                                                                   uint32_t mn, uint32_t k, unsigned long long ld,
+                                                                   unsigned long long src_bs, uint32_t tiles_mn,
+                                                                   uint32_t tiles_k, unsigned long long total_tiles,
+                                                                   int shared) {
+  __shared__ float tile[64][65];  // [k][mn]
+  const uint32_t t = threadIdx.x;
+  for (unsigned long long tl = blockIdx.x; tl < total_tiles; tl += gridDim.x) {
+    const unsigned long long per_b = static_cast<unsigned long long>(tiles_mn) * tiles_k;
+    const unsigned long long b = tl / per_b;
+    const uint32_t rem = static_cast<uint32_t>(tl - b * per_b);
+    const uint32_t i0 = (rem % tiles_mn) * 64u, p0 = (rem / tiles_mn) * 64u;
+    const float *s = src + b * src_bs;
+    const float *iv = inv + (shared ? 0ull : b * mn);
+    const unsigned long long dst_b = b * static_cast<unsigned long long>(mn) * k;
+#pragma unroll
+    for (uint32_t r = 0; r < 4u; ++r) {
+      const uint32_t e = t + r * 256u;
+      const uint32_t pk = e >> 4, im = (e & 15u) * 4u;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p0 + pk < k && i0 + im < mn)
+        v = *reinterpret_cast<const float4 *>(s + static_cast<unsigned long long>(p0 + pk) * ld + i0 + im);
+      tile[pk][im] = v.x; tile[pk][im + 1] = v.y; tile[pk][im + 2] = v.z; tile[pk][im + 3] = v.w;
+    }
+    __syncthreads();
+    // 64 mn-rows x 8 groups of 8 k = 512 groups, 2 per thread
+#pragma unroll
+    for (uint32_t r = 0; r < 2u; ++r) {
+      const uint32_t e = t + r * 256u;
+      const uint32_t im = e >> 3, pk = (e & 7u) * 8u;
+      if (i0 + im < mn && p0 + pk < k) {
+        const float sc = 1.f / iv[i0 + im];
+        __align__(16) __half a[8], d[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float x = tile[pk + j][im] * sc;
+          a[j] = __float2half_rn(x);
+          d[j] = __float2half_rn(x - __half2float(a[j]));
+        }
+        const unsigned long long o = dst_b + static_cast<unsigned long long>(i0 + im) * k + p0 + pk;
+        *reinterpret_cast<uint4 *>(h0 + o) = *reinterpret_cast<const uint4 *>(a);
+        *reinterpret_cast<uint4 *>(h1 + o) = *reinterpret_cast<const uint4 *>(d);
       }
     }
     __syncthreads();
@@ -976,9 +1201,11 @@ namespace {
 int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fixed_scratch,
                 uint64_t fixed_elems) {
   if (!gemm_tc_eligible(ctx, g)) return B200_ERR_INVALID_ARG;
-  const int eb = elem_bytes(g.mode);
-  const bool f16 = g.mode == B200_MODE_FP16;
-  const uint32_t passes = g.mode == B200_MODE_FP32_3XTF32 ? 3u : 1u;
+  const bool half_store = g.mode == B200_MODE_FP16;        // operands and C are half in memory
+  const bool split16 = g.mode == B200_MODE_FP32_3XFP16;    // fp32 in memory, two half planes per operand
+  const bool f16 = half_store || split16;                  // what the tensor core is fed: kind::f16
+  const int eb = f16 ? 2 : 4;                              // bytes of a tensor-core operand element
+  const uint32_t passes = (g.mode == B200_MODE_FP32_3XTF32 || split16) ? 3u : 1u;
 
   TcParams p;
   memset(&p, 0, sizeof(p));
@@ -1010,7 +1237,88 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
 
   const void *a_src[2] = {g.A, nullptr}, *b_src[2] = {g.B, nullptr};
   void *scratch = nullptr;
-  if (!f16) {
+  if (split16) {
+    // scales (1/s per row) and two half planes per operand, all in one scratch block
+    OperandView *views[2] = {&va, &vb};
+    const void **srcs[2] = {a_src, b_src};
+    const uint32_t rmul[2] = {p.a_rmul, p.b_rmul};
+    uint64_t plane_halves[2], scale_floats[2];
+    uint32_t kpad[2];
+    bool shared[2];
+    uint64_t bytes = 0;
+    for (int o = 0; o < 2; ++o) {
+      const OperandView &v = *views[o];
+      kpad[o] = (v.k + 7u) & ~7u;
+      plane_halves[o] = (static_cast<uint64_t>(v.nbatch) * v.mn * kpad[o] + 127ull) & ~127ull;
+      shared[o] = rmul[o] != 0u;  // the batch of this operand is summed over: one scale per row for all of it
+      scale_floats[o] = (static_cast<uint64_t>(v.mn) * (shared[o] ? 1u : v.nbatch) + 63ull) & ~63ull;
+      bytes += 2 * plane_halves[o] * sizeof(__half) + scale_floats[o] * sizeof(float);
+    }
+    if (fixed_scratch) return B200_ERR_INVALID_ARG;  // the allocation-free entry point is 3xTF32 only
+    int rc = ctx->pool.alloc(bytes, &scratch, nullptr);
+    if (rc != B200_OK) return rc;
+    char *cursor = static_cast<char *>(scratch);
+    for (int o = 0; o < 2; ++o) {
+      OperandView &v = *views[o];
+      float *inv = reinterpret_cast<float *>(cursor);
+      cursor += scale_floats[o] * sizeof(float);
+      __half *h0 = reinterpret_cast<__half *>(cursor);
+      __half *h1 = h0 + plane_halves[o];
+      cursor += 2 * plane_halves[o] * sizeof(__half);
+      const float *src = static_cast<const float *>(v.ptr);
+      const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
+      ProfScope prof(ctx, kProfPack, stream);
+      const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15u) == 0 && v.ld % 4u == 0 &&
+                           (v.nbatch <= 1 || v.batch_stride % 4u == 0) && v.k % 8u == 0;
+      if (!v.mn_major && aligned && !shared[o] && v.k >= 512u) {  // (a CTA per row pays only for long rows)
+        // scale and split in one kernel, a row per CTA
+        const unsigned long long rows = static_cast<unsigned long long>(v.mn) * v.nbatch;
+        pack_f16_rows_kernel<<<static_cast<unsigned>(rows < cap ? rows : cap), 256, 0, stream>>>(
+            src, inv, h0, h1, v.mn, v.k, v.ld, v.batch_stride, rows);
+        ctx->launches += 1;
+      } else {
+      if (v.mn_major) {
+        const unsigned long long t = static_cast<unsigned long long>((v.mn + 31u) / 32u) * (shared[o] ? 1u : v.nbatch);
+        row_scale_mnmajor_kernel<<<static_cast<unsigned>(t < cap ? t : cap), 256, 0, stream>>>(
+            src, inv, v.mn, v.k, v.ld, v.batch_stride, v.nbatch, shared[o]);
+      } else {
+        const unsigned long long t = (static_cast<unsigned long long>(v.mn) * (shared[o] ? 1u : v.nbatch) + 7ull) / 8ull;
+        row_scale_kmajor_kernel<<<static_cast<unsigned>(t < cap ? t : cap), 256, 0, stream>>>(
+            src, inv, v.mn, v.k, v.ld, v.batch_stride, v.nbatch, shared[o]);
+      }
+      if (v.mn_major && aligned && v.mn % 4u == 0) {
+        const uint32_t tiles_mn = (v.mn + 63u) / 64u, tiles_k = (v.k + 63u) / 64u;
+        const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
+        pack_f16_transpose64_kernel<<<static_cast<unsigned>(tt < cap ? tt : cap), 256, 0, stream>>>(
+            src, inv, h0, h1, v.mn, v.k, v.ld, v.batch_stride, tiles_mn, tiles_k, tt, shared[o]);
+      } else {
+        const uint32_t tiles_mn = (v.mn + 31u) / 32u, tiles_k = (v.k + 31u) / 32u;
+        const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
+        const unsigned blocks = static_cast<unsigned>(tt < cap ? tt : cap);
+        if (v.mn_major)
+          pack_f16_kernel<true><<<blocks, 256, 0, stream>>>(src, inv, h0, h1, v.mn, v.k, kpad[o], v.ld,
+                                                          v.batch_stride, tiles_mn, tiles_k, tt, shared[o]);
+        else
+          pack_f16_kernel<false><<<blocks, 256, 0, stream>>>(src, inv, h0, h1, v.mn, v.k, kpad[o], v.ld,
+                                                           v.batch_stride, tiles_mn, tiles_k, tt, shared[o]);
+      }
+      ctx->launches += 2;
+      }
+      srcs[o][0] = h0;
+      srcs[o][1] = h1;
+      if (o == 0) {
+        p.scale_a = inv;
+        p.scale_a_gs = (!shared[0] && p.a_gmul) ? v.mn : 0u;
+      } else {
+        p.scale_b = inv;
+        p.scale_b_gs = (!shared[1] && p.b_gmul) ? v.mn : 0u;
+      }
+      v.ptr = h0;
+      v.mn_major = false;
+      v.ld = kpad[o];
+      v.batch_stride = static_cast<uint64_t>(v.mn) * kpad[o];
+    }
+  } else if (!f16) {
     OperandView *views[2] = {&va, &vb};
     const void **srcs[2] = {a_src, b_src};
     bool pack[2];
@@ -1170,7 +1478,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   const bool chunked = passes == 3 && static_cast<uint64_t>(g.red) * p.kblocks > kChunkKBlocks;
   p.chunk_kblocks = chunked ? kChunkKBlocks : g.red * p.kblocks;
   p.accumulate = g.accumulate ? 1u : 0u;
-  p.out_half = f16 ? 1u : 0u;
+  p.out_half = half_store ? 1u : 0u;
   p.kind_f16 = f16 ? 1u : 0u;
   p.C = g.C;
   p.c_gs = g.c_gs;
@@ -1227,6 +1535,10 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     allow(gemm_tc_kernel<false, 2, 0>);
     allow(gemm_tc_kernel<false, 2, 1>);
     allow(gemm_tc_kernel<false, 2, 2>);
+    allow(gemm_tc_kernel<true, 1, 3>);
+    allow(gemm_tc_kernel<false, 1, 3>);
+    allow(gemm_tc_kernel<true, 2, 3>);
+    allow(gemm_tc_kernel<false, 2, 3>);
     if (e != cudaSuccess) rc = static_cast<int>(e);
     ctx->tc_smem_configured = (e == cudaSuccess);
   }
@@ -1250,11 +1562,17 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
       cfg.attrs = &attr;
       cfg.numAttrs = 1;
       cudaError_t e;
-      if (chunked) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, 2, 0>, p);
+      if (split16 && chunked) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, 2, 3>, p);
+      else if (split16) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 3>, p);
+      else if (chunked) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, 2, 0>, p);
       else if (passes == 3) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 0>, p);
       else if (!f16) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 1>, p);
       else e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 2>, p);
       rc = static_cast<int>(e);
+    } else if (split16 && chunked) {
+      gemm_tc_kernel<true, 1, 3><<<grid, kThreads, smem_bytes, stream>>>(p);
+    } else if (split16) {
+      gemm_tc_kernel<false, 1, 3><<<grid, kThreads, smem_bytes, stream>>>(p);
     } else if (chunked) {
       gemm_tc_kernel<true, 1, 0><<<grid, kThreads, smem_bytes, stream>>>(p);
     } else if (passes == 3) {
@@ -1271,7 +1589,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
       const unsigned long long need = (mn * g.groups + 255ull) / 256ull;
       const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 8ull;
       const unsigned blocks = static_cast<unsigned>(need < cap ? need : cap);
-      if (f16)
+      if (half_store)
         splitk_reduce_kernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const float *>(partial),
                                                                    static_cast<__half *>(g.C), mn, g.groups, splits,
                                                                    g.c_gs, g.accumulate);

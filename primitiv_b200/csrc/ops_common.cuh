@@ -166,7 +166,8 @@ int launch_batch_sum(b200_ctx *ctx, cudaStream_t s, const void *x, void *y, u64 
       typedef __half T;                                        \
       __VA_ARGS__                                              \
     } else if ((mode) == B200_MODE_FP32_3XTF32 ||              \
-               (mode) == B200_MODE_TF32) {                     \
+               (mode) == B200_MODE_TF32 ||                     \
+               (mode) == B200_MODE_FP32_3XFP16) {              \
       typedef float T;                                         \
       __VA_ARGS__                                              \
     } else {                                                   \

@@ -4,9 +4,10 @@ import torch
 
 import primitiv_b200 as pb
 
-MODES = {"3xtf32": pb.MODE_FP32_3XTF32, "tf32": pb.MODE_TF32, "fp16": pb.MODE_FP16}
+MODES = {"3xtf32": pb.MODE_FP32_3XTF32, "tf32": pb.MODE_TF32, "fp16": pb.MODE_FP16,
+         "3xfp16": pb.MODE_FP32_3XFP16}
 # normwise relative error bounds against the fp64 oracle
-TOL = {"3xtf32": 1e-5, "tf32": 2e-3, "fp16": 2e-3}
+TOL = {"3xtf32": 1e-5, "tf32": 2e-3, "fp16": 2e-3, "3xfp16": 1e-5}
 
 
 def dev(x, mode):

@@ -81,7 +81,7 @@ def test_against_reference_naive_fixtures(ctx, idx, mode, policy):
         y, ga, gb = _check_all(ctx, mode, a, b, gy, di, dj, dk, ba, bb)
     finally:
         ctx.set_path_policy(0)
-    if mode == "3xtf32":  # directly against what the reference's Naive device produced
+    if mode in ("3xtf32", "3xfp16"):  # directly against what the reference's Naive device produced
         for got, key in ((y, "y"), (ga, "ga"), (gb, "gb")):
             want = _REF["%s_%d" % (key, idx)]
             assert np.linalg.norm(got - want) <= 1e-5 * np.linalg.norm(want)
@@ -114,7 +114,7 @@ def test_plumbing_workload(ctx, mode):
     c = ol.config1_inputs()
     args = (c["di"], c["dj"], c["dk"], c["ba"], c["bb"])
     y, ga, gb = _check_all(ctx, mode, c["a"], c["b"], c["gy"], *args, prefill=0.5)
-    if mode == "3xtf32" and ol.have_ref():
+    if mode in ("3xtf32", "3xfp16") and ol.have_ref():
         y_ref, _ = ol.ref_fw(c["a"], c["b"], *args)
         ga_ref, gb_ref, _ = ol.ref_bw(c["a"], c["b"], c["gy"], c["ga0"], c["gb0"], *args)
         for got, want in ((y, y_ref), (ga, ga_ref), (gb, gb_ref)):
@@ -286,3 +286,24 @@ def test_zero_extent_is_a_no_op(ctx):
                   4, 4, 0, 1, 1)
     torch.cuda.synchronize()
     assert ctx.launch_count() == before and float(x.sum()) == 48.0
+
+
+def test_3xfp16_rows_of_very_different_magnitude(ctx):
+    """The fp16-pipe mode scales every operand row by its own power of two: rows (and columns)
+    whose magnitudes differ by 2^60 each keep fp32-grade accuracy, measured per output row and per
+    output column, not just over the whole matrix."""
+    di, dj, dk = 192, 640, 160
+    rng = np.random.default_rng(77)
+    a = rng.uniform(-1, 1, (di, dj)) * np.exp2(rng.integers(-30, 31, (di, 1)))
+    b = rng.uniform(-1, 1, (dj, dk)) * np.exp2(rng.integers(-30, 31, (1, dk)))
+    a32 = np.ascontiguousarray(a.T, np.float32).ravel()      # column-major {di, dj}
+    b32 = np.ascontiguousarray(b.T, np.float32).ravel()      # column-major {dj, dk}
+    ctx.set_path_policy(2)
+    try:
+        y = matmul_fw(ctx, pb.MODE_FP32_3XFP16, a32, b32, di, dj, dk, 1, 1).reshape(dk, di).T
+    finally:
+        ctx.set_path_policy(0)
+    want = a32.reshape(dj, di).T.astype(np.float64) @ b32.reshape(dk, dj).T.astype(np.float64)
+    row_err = np.linalg.norm(y - want, axis=1) / np.linalg.norm(want, axis=1)
+    col_err = np.linalg.norm(y - want, axis=0) / np.linalg.norm(want, axis=0)
+    assert row_err.max() < 1e-5 and col_err.max() < 1e-5, (row_err.max(), col_err.max())
