@@ -109,7 +109,7 @@ struct alignas(64) TcParams {
   uint32_t chunk_kblocks;  // k-blocks per accumulation chunk
   uint32_t accumulate, out_half, kind_f16;
   uint32_t band_m;  // tile-rows per band of the tile order
-  // 3xFP16 mode: the epilogue multiplies by 1/s of the output row (from A) and column (from B);
+  // 3xFP16 mode: row maxima of A and B; the epilogue multiplies by 1/s of the output row (from A) and column (from B);
   // per group when the operand has one matrix per group, else one set (stride 0)
   const float *scale_a, *scale_b;
   uint32_t scale_a_gs, scale_b_gs;
@@ -379,6 +379,13 @@ __device__ __forceinline__ void store_cols(T *C, unsigned long long base, uint32
       }
     }
   }
+}
+
+// 3xFP16 mode: 1/s for a row whose largest magnitude is amax (see the pre-pass further down).
+__device__ __forceinline__ float inv_scale_for(float amax) {
+  int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 127;  // floor(log2(amax)) for normal values
+  e = e < -100 ? -100 : (e > 127 ? 127 : e);
+  return __uint_as_float(static_cast<uint32_t>(e - 14 + 127) << 23);  // 2^(e-14), so that amax / it is in [2^14, 2^15)
 }
 
 // Tile order.  Tiles of one group (one output matrix) are walked in bands of kBandTilesM
@@ -659,7 +666,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       const float *col_scale = nullptr;
       if constexpr (kKind == 3) {
         const uint32_t g_real = g / p.splits;
-        if (row < p.m) row_scale = p.scale_a[static_cast<unsigned long long>(g_real) * p.scale_a_gs + row];
+        if (row < p.m) row_scale = inv_scale_for(p.scale_a[static_cast<unsigned long long>(g_real) * p.scale_a_gs + row]);
         col_scale = p.scale_b + static_cast<unsigned long long>(g_real) * p.scale_b_gs;
       }
       if constexpr (kChunked) {
@@ -700,7 +707,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
               if constexpr (kKind == 3) {
 #pragma unroll
                 for (uint32_t i = 0; i < 32u; ++i)
-                  if (col0 + i < p.n) acc[j][i] *= row_scale * col_scale[col0 + i];
+                  if (col0 + i < p.n) acc[j][i] *= row_scale * inv_scale_for(col_scale[col0 + i]);
               }
               if (p.out_half)
                 store_cols<8>(static_cast<__half *>(p.C), base, p.m, p.n, col0, acc[j], p.accumulate != 0u);
@@ -729,7 +736,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             if constexpr (kKind == 3) {
 #pragma unroll
               for (uint32_t i = 0; i < 32u; ++i)
-                if (col0 + i < p.n) x[i] *= row_scale * col_scale[col0 + i];
+                if (col0 + i < p.n) x[i] *= row_scale * inv_scale_for(col_scale[col0 + i]);
             }
             if (p.out_half)
               store_cols<32>(static_cast<__half *>(p.C), base, p.m, p.n, col0, x, p.accumulate != 0u);
@@ -861,18 +868,13 @@ __global__ void __launch_bounds__(256) pack_tf32_kernel(
 // Every row of an operand (index mn, all of k) gets a power-of-two scale s that brings its
 // largest magnitude into [2^14, 2^15), half's top binades; then x*s = h0 + h1 with
 // h0 = rn_half(x*s), h1 = rn_half(x*s - h0): two half planes with 11 + 11 mantissa bits, the
-// same as TF32 hi + lo.  row_scale_kernel writes 1/s (what the epilogue multiplies by);
-// when the batch is itself a contraction axis (`shared`), one scale per row covers all batches.
-__device__ __forceinline__ float inv_scale_for(float amax) {
-  int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 127;  // floor(log2(amax)) for normal values
-  e = e < -100 ? -100 : (e > 127 ? 127 : e);
-  return __uint_as_float(static_cast<uint32_t>(e - 14 + 127) << 23);  // 2^(e-14), so that amax / it is in [2^14, 2^15)
-}
-
+// same as TF32 hi + lo.  The scale arrays hold the row maxima themselves; the split kernels and
+// the epilogue both derive 1/s = 2^(floor(log2 max) - 14) from them (inv_scale_for).  When the
+// batch is itself a contraction axis (`shared`), one maximum per row covers all batches.
 // K-major source (k contiguous): one warp per row.
-__global__ void __launch_bounds__(256) row_scale_kmajor_kernel(const float *__restrict__ src, float *__restrict__ inv,
-                                                               uint32_t mn, uint32_t k, unsigned long long ld,
-                                                               unsigned long long src_bs, uint32_t nbatch, int shared) {
+__global__ void __launch_bounds__(256) row_max_kmajor_kernel(const float *__restrict__ src, float *__restrict__ amax_out,
+                                                             uint32_t mn, uint32_t k, unsigned long long ld,
+                                                             unsigned long long src_bs, uint32_t nbatch, int shared) {
   const uint32_t lane = threadIdx.x & 31u;
   const unsigned long long rows = static_cast<unsigned long long>(mn) * (shared ? 1u : nbatch);
   for (unsigned long long r = blockIdx.x * 8ull + (threadIdx.x >> 5); r < rows; r += gridDim.x * 8ull) {
@@ -884,42 +886,47 @@ __global__ void __launch_bounds__(256) row_scale_kmajor_kernel(const float *__re
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if (lane == 0) inv[r] = inv_scale_for(amax);
+    if (lane == 0) amax_out[r] = amax;
   }
 }
 
-// MN-major source (mn contiguous): 32 rows x 8 k-lanes per CTA, coalesced along mn.
-__global__ void __launch_bounds__(256) row_scale_mnmajor_kernel(const float *__restrict__ src, float *__restrict__ inv,
-                                                                uint32_t mn, uint32_t k, unsigned long long ld,
-                                                                unsigned long long src_bs, uint32_t nbatch, int shared) {
+// MN-major source (mn contiguous): 32 rows x 8 k-lanes per CTA, coalesced along mn; the k range
+// is cut into slices over grid.y so that a tall, narrow operand still fills the GPU, and the
+// slices meet in an atomic maximum on the (non-negative) float's bit pattern, which orders
+// like the value: the result does not depend on the order.  amax_out starts zeroed.
+__global__ void __launch_bounds__(256) row_max_mnmajor_kernel(const float *__restrict__ src, float *amax_out,
+                                                              uint32_t mn, uint32_t k, unsigned long long ld,
+                                                              unsigned long long src_bs, uint32_t nbatch, int shared,
+                                                              uint32_t k_slice) {
   __shared__ float buf[8][32];
   const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
   const uint32_t tiles = (mn + 31u) / 32u;
-  const unsigned long long total = static_cast<unsigned long long>(tiles) * (shared ? 1u : nbatch);
+  const unsigned long long total = static_cast<unsigned long long>(tiles) * nbatch;
+  const uint32_t p_lo = blockIdx.y * k_slice, p_hi = p_lo + k_slice < k ? p_lo + k_slice : k;
   for (unsigned long long t = blockIdx.x; t < total; t += gridDim.x) {
-    const unsigned long long b0 = shared ? 0 : t / tiles;
-    const uint32_t i = static_cast<uint32_t>(t - b0 * tiles) * 32u + tx;
+    const unsigned long long b = t / tiles;
+    const uint32_t i = static_cast<uint32_t>(t - b * tiles) * 32u + tx;
     float amax = 0.f;
-    if (i < mn)
-      for (uint32_t b = 0; b < (shared ? nbatch : 1u); ++b) {
-        const float *m0 = src + (b0 + b) * src_bs + i;
-        for (uint32_t p = ty; p < k; p += 8u) amax = fmaxf(amax, fabsf(m0[static_cast<unsigned long long>(p) * ld]));
-      }
+    if (i < mn) {
+      const float *m0 = src + b * src_bs + i;
+      for (uint32_t p = p_lo + ty; p < p_hi; p += 8u) amax = fmaxf(amax, fabsf(m0[static_cast<unsigned long long>(p) * ld]));
+    }
     buf[ty][tx] = amax;
     __syncthreads();
     if (ty == 0 && i < mn) {
 #pragma unroll
       for (uint32_t l = 1; l < 8u; ++l) amax = fmaxf(amax, buf[l][tx]);
-      inv[b0 * mn + i] = inv_scale_for(amax);
+      // NaNs: fmaxf drops them and their bit pattern would not order; the products of such a row are NaN anyway
+      atomicMax(reinterpret_cast<int *>(amax_out) + (shared ? 0ull : b * mn) + i, __float_as_int(amax));
     }
     __syncthreads();
   }
 }
 
 // Writes the two half planes, K-major [b][i][k_pad] (k_pad a multiple of 8: 16-byte rows).
-// Same tiling as pack_tf32_kernel; inv holds 1/s per row ([b][i], or [i] when shared).
+// Same tiling as pack_tf32_kernel; amax holds the row maxima ([b][i], or [i] when shared).
 template <bool kTranspose>
-__global__ void __launch_bounds__(256) pack_f16_kernel(const float *__restrict__ src, const float *__restrict__ inv,
+__global__ void __launch_bounds__(256) pack_f16_kernel(const float *__restrict__ src, const float *__restrict__ amax,
                                                        __half *__restrict__ h0, __half *__restrict__ h1, uint32_t mn,
                                                        uint32_t k, uint32_t k_pad, unsigned long long ld,
                                                        unsigned long long src_bs, uint32_t tiles_mn, uint32_t tiles_k,
@@ -932,7 +939,7 @@ __global__ void __launch_bounds__(256) pack_f16_kernel(const float *__restrict__
     const uint32_t rem = static_cast<uint32_t>(t - b * per_b);
     const uint32_t i0 = (rem % tiles_mn) * 32u, p0 = (rem / tiles_mn) * 32u;
     const float *s = src + b * src_bs;
-    const float *iv = inv + (shared ? 0ull : b * mn);
+    const float *iv = amax + (shared ? 0ull : b * mn);
     const unsigned long long dst_b = b * static_cast<unsigned long long>(mn) * k_pad;
     if (kTranspose) {
 #pragma unroll
@@ -947,7 +954,7 @@ __global__ void __launch_bounds__(256) pack_f16_kernel(const float *__restrict__
       const uint32_t i = i0 + ty + j, pp = p0 + tx;
       if (i < mn && pp < k) {
         const float x = kTranspose ? tile[tx][ty + j] : s[static_cast<unsigned long long>(i) * ld + pp];
-        const float xs = x * (1.f / iv[i]);  // 1/inv is the power-of-two scale: exact
+        const float xs = x * (1.f / inv_scale_for(iv[i]));  // the power-of-two scale: exact
         const __half a = __float2half_rn(xs);
         const unsigned long long o = dst_b + static_cast<unsigned long long>(i) * k_pad + pp;
         h0[o] = a;
@@ -1028,37 +1035,46 @@ __global__ void __launch_bounds__(256) pack_transpose64_kernel(const float *__re
 
 // Fast paths of the 3xFP16 pre-pass.
 //
-// pack_f16_rows_kernel: a K-major source with 16-byte aligned rows and k % 8 == 0.  One CTA per
-// row at a time: the row's largest magnitude (float4 loads, block reduction), then the row once
-// more (it is still in L1 / L2) split into the two half planes with 16-byte stores.  Scale and
-// split in one kernel: 4 bytes read from HBM and 4 written per element.
-__global__ void __launch_bounds__(256) pack_f16_rows_kernel(const float *__restrict__ src, float *__restrict__ inv,
+// pack_f16_rows_kernel: a K-major source with 16-byte aligned rows and k % 8 == 0.  A group of
+// kGroup threads (a whole CTA for long rows, a warp for short ones) takes one row at a time: the
+// row's largest magnitude (float4 loads, reduction), then the row once more (it is still in
+// L1 / L2) split into the two half planes with 16-byte stores.  Maximum and split in one kernel:
+// 4 bytes read from HBM and 4 written per element.
+template <uint32_t kGroup>
+__global__ void __launch_bounds__(256) pack_f16_rows_kernel(const float *__restrict__ src, float *__restrict__ amax_out,
                                                             __half *__restrict__ h0, __half *__restrict__ h1,
                                                             uint32_t mn, uint32_t k, unsigned long long ld,
                                                             unsigned long long src_bs, unsigned long long rows) {
+  static_assert(kGroup == 32 || kGroup == 256, "a warp or the CTA");
   __shared__ float red[8];
-  const uint32_t t = threadIdx.x, lane = t & 31u, warp = t >> 5;
+  const uint32_t t = threadIdx.x % kGroup, lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
   const uint32_t k8 = k >> 3;
-  for (unsigned long long r = blockIdx.x; r < rows; r += gridDim.x) {
+  constexpr uint32_t kPerCta = 256u / kGroup;
+  const unsigned long long first = static_cast<unsigned long long>(blockIdx.x) * kPerCta + threadIdx.x / kGroup;
+  const unsigned long long step = static_cast<unsigned long long>(gridDim.x) * kPerCta;
+  // (for kGroup == 256 every thread of the CTA walks the same rows, so the barriers below are uniform)
+  for (unsigned long long r = first; r < rows; r += step) {
     const unsigned long long b = r / mn, i = r - b * mn;
     const float4 *row = reinterpret_cast<const float4 *>(src + b * src_bs + i * ld);
     float amax = 0.f;
-    for (uint32_t c = t; c < 2u * k8; c += 256u) {
+    for (uint32_t c = t; c < 2u * k8; c += kGroup) {
       const float4 v = row[c];
       amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if (lane == 0) red[warp] = amax;
-    __syncthreads();
-    amax = red[0];
+    if (kGroup == 256) {
+      if (lane == 0) red[warp] = amax;
+      __syncthreads();
+      amax = red[0];
 #pragma unroll
-    for (uint32_t w = 1; w < 8u; ++w) amax = fmaxf(amax, red[w]);
-    const float iv = inv_scale_for(amax), sc = 1.f / iv;
-    if (t == 0) inv[r] = iv;
+      for (uint32_t w = 1; w < 8u; ++w) amax = fmaxf(amax, red[w]);
+    }
+    const float sc = 1.f / inv_scale_for(amax);
+    if (t == 0) amax_out[r] = amax;
     uint4 *d0 = reinterpret_cast<uint4 *>(h0 + r * static_cast<unsigned long long>(k));
     uint4 *d1 = reinterpret_cast<uint4 *>(h1 + r * static_cast<unsigned long long>(k));
-    for (uint32_t c = t; c < k8; c += 256u) {
+    for (uint32_t c = t; c < k8; c += kGroup) {
       const float4 u = row[2u * c], v = row[2u * c + 1u];
       const float x[8] = {u.x * sc, u.y * sc, u.z * sc, u.w * sc, v.x * sc, v.y * sc, v.z * sc, v.w * sc};
       __align__(16) __half a[8], e[8];
@@ -1070,15 +1086,15 @@ __global__ void __launch_bounds__(256) pack_f16_rows_kernel(const float *__restr
       d0[c] = *reinterpret_cast<const uint4 *>(a);
       d1[c] = *reinterpret_cast<const uint4 *>(e);
     }
-    __syncthreads();  // red[] is reused by the next row
+    if (kGroup == 256) __syncthreads();  // red[] is reused by the next row
   }
 }
 
 // pack_f16_transpose64_kernel: an MN-major source with mn % 4 == 0 and k % 8 == 0 whose row
-// scales are already known (row_scale_mnmajor_kernel).  64 x 64 tiles through shared memory:
+// maxima are already known (row_max_mnmajor_kernel).  64 x 64 tiles through shared memory:
 // float4 reads along mn, 16-byte half stores along k.
 __global__ void __launch_bounds__(256) pack_f16_transpose64_kernel(const float *__restrict__ src,
-                                                                   const float *__restrict__ inv,
+                                                                   const float *__restrict__ amax,
                                                                    __half *__restrict__ h0, __half *__restrict__ h1,
                                                                    uint32_t mn, uint32_t k, unsigned long long ld,
                                                                    unsigned long long src_bs, uint32_t tiles_mn,
@@ -1092,7 +1108,7 @@ __global__ void __launch_bounds__(256) pack_f16_transpose64_kernel(const float *
     const uint32_t rem = static_cast<uint32_t>(tl - b * per_b);
     const uint32_t i0 = (rem % tiles_mn) * 64u, p0 = (rem / tiles_mn) * 64u;
     const float *s = src + b * src_bs;
-    const float *iv = inv + (shared ? 0ull : b * mn);
+    const float *iv = amax + (shared ? 0ull : b * mn);
     const unsigned long long dst_b = b * static_cast<unsigned long long>(mn) * k;
 #pragma unroll
     for (uint32_t r = 0; r < 4u; ++r) {
@@ -1110,7 +1126,7 @@ __global__ void __launch_bounds__(256) pack_f16_transpose64_kernel(const float *
       const uint32_t e = t + r * 256u;
       const uint32_t im = e >> 3, pk = (e & 7u) * 8u;
       if (i0 + im < mn && p0 + pk < k) {
-        const float sc = 1.f / iv[i0 + im];
+        const float sc = 1.f / inv_scale_for(iv[i0 + im]);
         __align__(16) __half a[8], d[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -1270,39 +1286,54 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
       ProfScope prof(ctx, kProfPack, stream);
       const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15u) == 0 && v.ld % 4u == 0 &&
                            (v.nbatch <= 1 || v.batch_stride % 4u == 0) && v.k % 8u == 0;
-      if (!v.mn_major && aligned && !shared[o] && v.k >= 512u) {  // (a CTA per row pays only for long rows)
-        // scale and split in one kernel, a row per CTA
+      const unsigned long long scale_rows = static_cast<unsigned long long>(v.mn) * (shared[o] ? 1u : v.nbatch);
+      if (!v.mn_major && aligned && !shared[o]) {
+        // maximum and split in one kernel: a row per CTA, or per warp when rows are short
         const unsigned long long rows = static_cast<unsigned long long>(v.mn) * v.nbatch;
-        pack_f16_rows_kernel<<<static_cast<unsigned>(rows < cap ? rows : cap), 256, 0, stream>>>(
-            src, inv, h0, h1, v.mn, v.k, v.ld, v.batch_stride, rows);
+        if (v.k >= 2048u) {
+          pack_f16_rows_kernel<256><<<static_cast<unsigned>(rows < cap ? rows : cap), 256, 0, stream>>>(
+              src, inv, h0, h1, v.mn, v.k, v.ld, v.batch_stride, rows);
+        } else {
+          const unsigned long long ctas = (rows + 7ull) / 8ull;
+          pack_f16_rows_kernel<32><<<static_cast<unsigned>(ctas < cap ? ctas : cap), 256, 0, stream>>>(
+              src, inv, h0, h1, v.mn, v.k, v.ld, v.batch_stride, rows);
+        }
         ctx->launches += 1;
       } else {
-      if (v.mn_major) {
-        const unsigned long long t = static_cast<unsigned long long>((v.mn + 31u) / 32u) * (shared[o] ? 1u : v.nbatch);
-        row_scale_mnmajor_kernel<<<static_cast<unsigned>(t < cap ? t : cap), 256, 0, stream>>>(
-            src, inv, v.mn, v.k, v.ld, v.batch_stride, v.nbatch, shared[o]);
-      } else {
-        const unsigned long long t = (static_cast<unsigned long long>(v.mn) * (shared[o] ? 1u : v.nbatch) + 7ull) / 8ull;
-        row_scale_kmajor_kernel<<<static_cast<unsigned>(t < cap ? t : cap), 256, 0, stream>>>(
-            src, inv, v.mn, v.k, v.ld, v.batch_stride, v.nbatch, shared[o]);
-      }
-      if (v.mn_major && aligned && v.mn % 4u == 0) {
-        const uint32_t tiles_mn = (v.mn + 63u) / 64u, tiles_k = (v.k + 63u) / 64u;
-        const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
-        pack_f16_transpose64_kernel<<<static_cast<unsigned>(tt < cap ? tt : cap), 256, 0, stream>>>(
-            src, inv, h0, h1, v.mn, v.k, v.ld, v.batch_stride, tiles_mn, tiles_k, tt, shared[o]);
-      } else {
-        const uint32_t tiles_mn = (v.mn + 31u) / 32u, tiles_k = (v.k + 31u) / 32u;
-        const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
-        const unsigned blocks = static_cast<unsigned>(tt < cap ? tt : cap);
-        if (v.mn_major)
-          pack_f16_kernel<true><<<blocks, 256, 0, stream>>>(src, inv, h0, h1, v.mn, v.k, kpad[o], v.ld,
-                                                          v.batch_stride, tiles_mn, tiles_k, tt, shared[o]);
-        else
-          pack_f16_kernel<false><<<blocks, 256, 0, stream>>>(src, inv, h0, h1, v.mn, v.k, kpad[o], v.ld,
-                                                           v.batch_stride, tiles_mn, tiles_k, tt, shared[o]);
-      }
-      ctx->launches += 2;
+        if (v.mn_major) {
+          // k slices over grid.y so that at least ~2 CTAs per SM work on a tall, narrow operand
+          const unsigned long long tiles = static_cast<unsigned long long>((v.mn + 31u) / 32u) * v.nbatch;
+          unsigned long long slices = (2ull * ctx->sm_count + tiles - 1) / tiles;
+          const unsigned long long most = v.k / 64u ? v.k / 64u : 1;
+          if (slices > most) slices = most;
+          if (slices > 1024ull) slices = 1024ull;
+          const uint32_t k_slice = static_cast<uint32_t>((v.k + slices - 1) / slices);
+          const unsigned gy = static_cast<unsigned>((v.k + k_slice - 1) / k_slice);
+          cudaMemsetAsync(inv, 0, scale_rows * sizeof(float), stream);
+          row_max_mnmajor_kernel<<<dim3(static_cast<unsigned>(tiles < cap ? tiles : cap), gy), 256, 0, stream>>>(
+              src, inv, v.mn, v.k, v.ld, v.batch_stride, v.nbatch, shared[o], k_slice);
+        } else {
+          const unsigned long long t = (scale_rows + 7ull) / 8ull;
+          row_max_kmajor_kernel<<<static_cast<unsigned>(t < cap ? t : cap), 256, 0, stream>>>(
+              src, inv, v.mn, v.k, v.ld, v.batch_stride, v.nbatch, shared[o]);
+        }
+        if (v.mn_major && aligned && v.mn % 4u == 0) {
+          const uint32_t tiles_mn = (v.mn + 63u) / 64u, tiles_k = (v.k + 63u) / 64u;
+          const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
+          pack_f16_transpose64_kernel<<<static_cast<unsigned>(tt < cap ? tt : cap), 256, 0, stream>>>(
+              src, inv, h0, h1, v.mn, v.k, v.ld, v.batch_stride, tiles_mn, tiles_k, tt, shared[o]);
+        } else {
+          const uint32_t tiles_mn = (v.mn + 31u) / 32u, tiles_k = (v.k + 31u) / 32u;
+          const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
+          const unsigned blocks = static_cast<unsigned>(tt < cap ? tt : cap);
+          if (v.mn_major)
+            pack_f16_kernel<true><<<blocks, 256, 0, stream>>>(src, inv, h0, h1, v.mn, v.k, kpad[o], v.ld,
+                                                            v.batch_stride, tiles_mn, tiles_k, tt, shared[o]);
+          else
+            pack_f16_kernel<false><<<blocks, 256, 0, stream>>>(src, inv, h0, h1, v.mn, v.k, kpad[o], v.ld,
+                                                             v.batch_stride, tiles_mn, tiles_k, tt, shared[o]);
+        }
+        ctx->launches += 2;
       }
       srcs[o][0] = h0;
       srcs[o][1] = h1;

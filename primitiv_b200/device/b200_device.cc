@@ -56,7 +56,8 @@ B200::Mode mode_from_environment() {
   if (v == "tf32" || v == "TF32" || v == "tf32_fast") return B200::Mode::TF32_FAST;
   if (v == "fp16" || v == "FP16" || v == "half") return B200::Mode::FP16;
   if (v == "3xtf32" || v == "3XTF32" || v == "fp32") return B200::Mode::FP32_3XTF32;
-  PRIMITIV_THROW_ERROR("Unknown PRIMITIV_B200_MODE: '" << v << "' (3xtf32 | tf32 | fp16)");
+  if (v == "3xfp16" || v == "3XFP16") return B200::Mode::FP32_3XFP16;
+  PRIMITIV_THROW_ERROR("Unknown PRIMITIV_B200_MODE: '" << v << "' (3xtf32 | tf32 | fp16 | 3xfp16)");
 }
 
 }  // namespace
@@ -148,7 +149,7 @@ void B200::dump_description() const {
   ::b200_ctx_device(state_->ctx, &dev, &sms);
   std::uint64_t st[4] = {0, 0, 0, 0};
   ::b200_pool_stats(state_->ctx, st);
-  static const char *names[] = {"FP32 (3xTF32)", "TF32 (single pass)", "FP16"};
+  static const char *names[] = {"FP32 (3xTF32)", "TF32 (single pass)", "FP16", "FP32 (3xFP16)"};
   std::cerr << "Device " << this << std::endl;
   std::cerr << "  Type: B200 (sm_100a, libprimitiv_b200)" << std::endl;
   std::cerr << "  GPU ordinal ........ " << dev << std::endl;

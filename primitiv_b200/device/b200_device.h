@@ -30,6 +30,7 @@ public:
     FP32_3XTF32 = 0,  // float storage; matmul = 3 TF32 tensor-core passes, fp32 accuracy (default)
     TF32_FAST = 1,    // float storage; matmul = 1 TF32 pass
     FP16 = 2,         // half storage, fp32 arithmetic, like devices::CUDA16
+    FP32_3XFP16 = 3,  // float storage; matmul = 3 fp16 tensor-core passes on row-scaled half planes, fp32 accuracy
   };
 
   /** Number of GPUs this backend can drive (compute capability 10.x only). */
@@ -39,7 +40,7 @@ public:
    * @param device_id CUDA ordinal of the GPU.
    * @param rng_seed Seed of the device's random fills.
    * @param mode Numeric mode; the environment variable PRIMITIV_B200_MODE
-   *             (3xtf32 | tf32 | fp16) overrides the default when `mode` is not given.
+   *             (3xtf32 | tf32 | fp16 | 3xfp16) overrides the default when `mode` is not given.
    * @throw primitiv::Error if the GPU does not exist or is not a Blackwell part.
    */
   explicit B200(std::uint32_t device_id);

@@ -153,6 +153,7 @@ int main(int argc, char **argv) {
   B200::Mode mode = B200::Mode::TF32_FAST;
   if (mode_name == "3xtf32") mode = B200::Mode::FP32_3XTF32;
   else if (mode_name == "fp16") mode = B200::Mode::FP16;
+  else if (mode_name == "3xfp16") mode = B200::Mode::FP32_3XFP16;
   else if (mode_name != "tf32") {
     std::cerr << "usage: lstm_steps [tf32|3xtf32|fp16] [steps] [repeats] [naive_steps]" << std::endl;
     return 2;

@@ -153,6 +153,7 @@ int main(int argc, char **argv) {
   B200::Mode mode = B200::Mode::FP32_3XTF32;
   if (mode_name == "tf32") mode = B200::Mode::TF32_FAST;
   else if (mode_name == "fp16") mode = B200::Mode::FP16;
+  else if (mode_name == "3xfp16") mode = B200::Mode::FP32_3XFP16;
   else if (mode_name != "3xtf32") {
     std::cerr << "usage: mlp_step [3xtf32|tf32|fp16] [batch] [repeats] [check_batch]" << std::endl;
     return 2;

@@ -765,7 +765,8 @@ int main(int argc, char **argv) {
   const std::string m = argc > 1 ? argv[1] : "3xtf32";
   if (m == "tf32") { mode = B200::Mode::TF32_FAST; g_mm_tol = 2e-3f; }
   else if (m == "fp16") { mode = B200::Mode::FP16; g_half = true; g_tol = 2e-3f; g_mm_tol = 2e-3f; }
-  else if (m != "3xtf32") { std::cerr << "usage: device_parity [3xtf32|tf32|fp16]" << std::endl; return 2; }
+  else if (m == "3xfp16") { mode = B200::Mode::FP32_3XFP16; }
+  else if (m != "3xtf32") { std::cerr << "usage: device_parity [3xtf32|tf32|fp16|3xfp16]" << std::endl; return 2; }
   try {
     Pair p(mode);
     p.dev.dump_description();

@@ -64,6 +64,7 @@ int main(int argc, char **argv) {
     const std::string m = argv[1];
     if (m == "tf32") g_mode = primitiv::devices::B200::Mode::TF32_FAST;
     else if (m == "fp16") g_mode = primitiv::devices::B200::Mode::FP16;
+    else if (m == "3xfp16") g_mode = primitiv::devices::B200::Mode::FP32_3XFP16;
     else if (m != "3xtf32") {
       std::fprintf(stderr, "usage: ref_tensor_tests [3xtf32|tf32|fp16] [--filter=...]\n");
       return 2;

@@ -45,7 +45,7 @@ def test_plugin_fails_loudly_without_a_gpu():
 
 @pytest.mark.gpu
 @needs_plugin
-@pytest.mark.parametrize("mode", ["3xtf32", "tf32", "fp16"])
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32", "fp16", "3xfp16"])
 def test_device_parity_against_reference_naive(mode):
     assert os.path.exists(RUNNER), "tests/cpp/_build/device_parity is not built"
     r = subprocess.run([RUNNER, mode], capture_output=True, text=True, timeout=600)
@@ -115,7 +115,7 @@ def test_recurrent_step_loop_matches_reference_naive(mode, tol):
 
 @pytest.mark.gpu
 @needs_plugin
-@pytest.mark.parametrize("mode,tol", [("3xtf32", 1e-5), ("tf32", 2e-3)])
+@pytest.mark.parametrize("mode,tol", [("3xtf32", 1e-5), ("tf32", 2e-3), ("3xfp16", 1e-5)])
 def test_perceptron_training_step_matches_reference_naive(mode, tol):
     """Two SGD steps of the 784-1024-1024-10 perceptron (softmax cross entropy) at batch 256 on
     both devices: loss and updated weights agree; then one step at a batch above 65535."""
@@ -130,7 +130,7 @@ REF_SUITE = os.path.join(ROOT, "tests", "cpp", "_build", "ref_tensor_tests")
 @pytest.mark.gpu
 @needs_plugin
 @pytest.mark.parametrize("policy", ["0", "2"], ids=["auto", "tensorcore"])
-@pytest.mark.parametrize("mode", ["3xtf32", "tf32", "fp16"])
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32", "fp16", "3xfp16"])
 def test_primitiv_own_tensor_tests_pass_on_b200(mode, policy):
     """The reference's own test/tensor_forward_test.cc, tensor_backward_test.cc and tensor_test.cc
     (compiled from the reference tree, unmodified; 372 cases, each looping over every device in
