@@ -1254,7 +1254,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   const void *a_src[2] = {g.A, nullptr}, *b_src[2] = {g.B, nullptr};
   void *scratch = nullptr;
   if (split16) {
-    // scales (1/s per row) and two half planes per operand, all in one scratch block
+    // row maxima and two half planes per operand, all in one scratch block
     OperandView *views[2] = {&va, &vb};
     const void **srcs[2] = {a_src, b_src};
     const uint32_t rmul[2] = {p.a_rmul, p.b_rmul};
@@ -1276,7 +1276,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     char *cursor = static_cast<char *>(scratch);
     for (int o = 0; o < 2; ++o) {
       OperandView &v = *views[o];
-      float *inv = reinterpret_cast<float *>(cursor);
+      float *amax = reinterpret_cast<float *>(cursor);
       cursor += scale_floats[o] * sizeof(float);
       __half *h0 = reinterpret_cast<__half *>(cursor);
       __half *h1 = h0 + plane_halves[o];
@@ -1292,11 +1292,11 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
         const unsigned long long rows = static_cast<unsigned long long>(v.mn) * v.nbatch;
         if (v.k >= 2048u) {
           pack_f16_rows_kernel<256><<<static_cast<unsigned>(rows < cap ? rows : cap), 256, 0, stream>>>(
-              src, inv, h0, h1, v.mn, v.k, v.ld, v.batch_stride, rows);
+              src, amax, h0, h1, v.mn, v.k, v.ld, v.batch_stride, rows);
         } else {
           const unsigned long long ctas = (rows + 7ull) / 8ull;
           pack_f16_rows_kernel<32><<<static_cast<unsigned>(ctas < cap ? ctas : cap), 256, 0, stream>>>(
-              src, inv, h0, h1, v.mn, v.k, v.ld, v.batch_stride, rows);
+              src, amax, h0, h1, v.mn, v.k, v.ld, v.batch_stride, rows);
         }
         ctx->launches += 1;
       } else {
@@ -1309,28 +1309,28 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
           if (slices > 1024ull) slices = 1024ull;
           const uint32_t k_slice = static_cast<uint32_t>((v.k + slices - 1) / slices);
           const unsigned gy = static_cast<unsigned>((v.k + k_slice - 1) / k_slice);
-          cudaMemsetAsync(inv, 0, scale_rows * sizeof(float), stream);
+          cudaMemsetAsync(amax, 0, scale_rows * sizeof(float), stream);
           row_max_mnmajor_kernel<<<dim3(static_cast<unsigned>(tiles < cap ? tiles : cap), gy), 256, 0, stream>>>(
-              src, inv, v.mn, v.k, v.ld, v.batch_stride, v.nbatch, shared[o], k_slice);
+              src, amax, v.mn, v.k, v.ld, v.batch_stride, v.nbatch, shared[o], k_slice);
         } else {
           const unsigned long long t = (scale_rows + 7ull) / 8ull;
           row_max_kmajor_kernel<<<static_cast<unsigned>(t < cap ? t : cap), 256, 0, stream>>>(
-              src, inv, v.mn, v.k, v.ld, v.batch_stride, v.nbatch, shared[o]);
+              src, amax, v.mn, v.k, v.ld, v.batch_stride, v.nbatch, shared[o]);
         }
         if (v.mn_major && aligned && v.mn % 4u == 0) {
           const uint32_t tiles_mn = (v.mn + 63u) / 64u, tiles_k = (v.k + 63u) / 64u;
           const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
           pack_f16_transpose64_kernel<<<static_cast<unsigned>(tt < cap ? tt : cap), 256, 0, stream>>>(
-              src, inv, h0, h1, v.mn, v.k, v.ld, v.batch_stride, tiles_mn, tiles_k, tt, shared[o]);
+              src, amax, h0, h1, v.mn, v.k, v.ld, v.batch_stride, tiles_mn, tiles_k, tt, shared[o]);
         } else {
           const uint32_t tiles_mn = (v.mn + 31u) / 32u, tiles_k = (v.k + 31u) / 32u;
           const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
           const unsigned blocks = static_cast<unsigned>(tt < cap ? tt : cap);
           if (v.mn_major)
-            pack_f16_kernel<true><<<blocks, 256, 0, stream>>>(src, inv, h0, h1, v.mn, v.k, kpad[o], v.ld,
+            pack_f16_kernel<true><<<blocks, 256, 0, stream>>>(src, amax, h0, h1, v.mn, v.k, kpad[o], v.ld,
                                                             v.batch_stride, tiles_mn, tiles_k, tt, shared[o]);
           else
-            pack_f16_kernel<false><<<blocks, 256, 0, stream>>>(src, inv, h0, h1, v.mn, v.k, kpad[o], v.ld,
+            pack_f16_kernel<false><<<blocks, 256, 0, stream>>>(src, amax, h0, h1, v.mn, v.k, kpad[o], v.ld,
                                                              v.batch_stride, tiles_mn, tiles_k, tt, shared[o]);
         }
         ctx->launches += 2;
@@ -1338,10 +1338,10 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
       srcs[o][0] = h0;
       srcs[o][1] = h1;
       if (o == 0) {
-        p.scale_a = inv;
+        p.scale_a = amax;
         p.scale_a_gs = (!shared[0] && p.a_gmul) ? v.mn : 0u;
       } else {
-        p.scale_b = inv;
+        p.scale_b = amax;
         p.scale_b_gs = (!shared[1] && p.b_gmul) ? v.mn : 0u;
       }
       v.ptr = h0;
