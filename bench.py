@@ -10,7 +10,8 @@ Shape({4096,4096}, batch 8) ~ N(0, 0.02), upstream gradient N(0,1), seeded synth
 data.  With N GPUs every rank holds a full batch-8 shard of its own (weak scaling; the
 products of different batch elements are independent, so the data path has no collective).
 
-`--workload lstm_steps` / `--workload mlp_step` run the graph-level programs of the other named
+`--workload batched_square_3xfp16` runs the default shapes in the opt-in fp32-grade mode on the fp16
+pipe.  `--workload lstm_steps` / `--workload mlp_step` run the graph-level programs of the other named
 configurations (1 GPU).  `--workload batched_square_tf32` runs the same shapes in the single-pass TF32 fast mode, and
 `--workload fp16_broadcast` runs the half-precision workload instead: A {8192,8192}
 broadcast, B {8192,2048} x 32, fp32 accumulation, gA summed over the batch (and, with
