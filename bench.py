@@ -391,10 +391,10 @@ def emit(args, wl, world, ms, prof, launches, sampler, e2e, collectives):
             "frac_of_burst_peak": achieved / burst,
             "note": ("achieved = tensor-issued FLOP/s (%d tensor-core pass(es) x algorithmic 2mnk) / mean "
                      "CUDA-event duration of %d launches; peak = %s bf16 sustained%s; the timed region is a "
-                     "fraction of a second, so the burst figure %.0f is given beside it; traffic = ncu dram "
-                     "bytes of the batch-2 capture scaled to this batch"
+                     "fraction of a second, so the burst figure %.0f is given beside it%s"
                      % (wl.passes, tc_n, peaks["source"],
-                        "" if wl.half else " / 2 (TF32 runs at half the 16-bit rate)", burst)),
+                        "" if div == 1.0 else " / 2 (TF32 runs at half the 16-bit rate)", burst,
+                        "; traffic = ncu dram bytes of the batch-2 capture scaled to this batch" if traffic else "")),
             "algorithmic_tflops_in_kernel": achieved / wl.passes,
             "kernel_ms_per_step": tc_ms / args.steps, "pack_ms_per_step": prof["pack"][0] / args.steps,
         },

@@ -667,6 +667,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         float acc[4][32];
         for (uint32_t c = 0; ok && c < chunks_per_tile; ++c, ++chunk_no) {
           const uint32_t buf = chunk_no & 1u;
+          if (p.accumulate && c + 1u == chunks_per_tile && row_ok && !(kDevKnobs && (p.debug & 32u))) {
+            // The tile's last chunk is in flight: ask L2 for this thread's part of the old C tile,
+            // which the final read-add-write would otherwise fetch from HBM with the tensor core
+            // waiting.  One request per thread and column measured better than one per line or per
+            // sector, and one chunk ahead better than two.
+            const unsigned long long ebytes = p.out_half ? 2u : 4u;
+            const uint32_t first = n0 + col_base;
+            const uint32_t ncols = first < p.n ? (p.n - first < cols_per ? p.n - first : cols_per) : 0u;
+            const char *q = static_cast<const char *>(p.C) + (base + static_cast<unsigned long long>(first) * p.m) * ebytes;
+            for (uint32_t col = 0; col < ncols; ++col)
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(q + static_cast<unsigned long long>(col) * p.m * ebytes));
+          }
           if (!warp_wait(smem_u32(&tmem_full_bar[buf]), (chunk_no >> 1) & 1u, abort_flag, lane)) {
             ok = false;
             break;
@@ -1041,7 +1053,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   p.debug = 0u;
   p.band_m = kBandTilesM;
   if (kDevKnobs) {
-    static const char *dbg = std::getenv("PRIMITIV_B200_TC_DEBUG");
+    const char *dbg = std::getenv("PRIMITIV_B200_TC_DEBUG");  // read per call: A/B runs inside one process
     if (dbg) p.debug = static_cast<uint32_t>(std::atoi(dbg));
     static const char *bd = std::getenv("PRIMITIV_B200_TC_BAND");
     if (bd && std::atoi(bd) > 0) p.band_m = static_cast<uint32_t>(std::atoi(bd));
