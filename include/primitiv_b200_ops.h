@@ -198,6 +198,26 @@ B200_API int b200_seed(b200_ctx *ctx, uint64_t seed);
 B200_API int b200_random(b200_ctx *ctx, int mode, int kind, float p0, float p1, void *y, uint64_t n,
                          void *stream);
 
+/* ---- several GPUs driven by one host thread (the device-group class) ----
+ *
+ * No counterpart in the reference: primitiv binds a tensor to one device (core/parameter.cc:80-97).
+ * These three calls are what a device object that keeps one shard per GPU needs besides the
+ * per-GPU operations above: peer mappings, an ordering point between the GPUs' streams that does
+ * not block the host, and the sum of per-GPU partial results (the gradient of a broadcast
+ * operand, a sum over the batch) read over NVLink with plain loads. */
+
+/* Lets kernels and copies of ctx's GPU read peer's memory.  Same GPU, or already enabled: no-op. */
+B200_API int b200_peer_enable(b200_ctx *ctx, b200_ctx *peer);
+/* Work queued later on any of the n contexts' default streams starts only after all work queued
+ * so far on every one of them has finished.  Asynchronous; contexts on the same GPU share a
+ * stream and need nothing. */
+B200_API int b200_stream_barrier(b200_ctx *const *ctxs, int n);
+/* dst[i] = srcs[0][i] + srcs[1][i] + ... (in that order, fp32 arithmetic, one rounding to the
+ * storage type), on ctx's GPU; srcs may live on peers (b200_peer_enable first, and a
+ * b200_stream_barrier between their producers and this call).  1 <= nsrc <= 16. */
+B200_API int b200_peer_sum(b200_ctx *ctx, int mode, const void *const *srcs, int nsrc, void *dst,
+                           uint64_t n, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -81,6 +81,9 @@ SIGNATURES = {
     "b200_batch_sum_fw": (_int, [_vp, _int, _vp, _vp, _u64, _u32, _vp]),
     "b200_seed": (_int, [_vp, _u64]),
     "b200_random": (_int, [_vp, _int, _int, ctypes.c_float, ctypes.c_float, _vp, _u64, _vp]),
+    "b200_peer_enable": (_int, [_vp, _vp]),
+    "b200_stream_barrier": (_int, [ctypes.POINTER(_vp), _int]),
+    "b200_peer_sum": (_int, [_vp, _int, ctypes.POINTER(_vp), _int, _vp, _u64, _vp]),
 }
 
 

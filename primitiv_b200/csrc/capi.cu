@@ -72,6 +72,7 @@ int b200_ctx_destroy(b200_ctx *ctx) {
   cudaDeviceSynchronize();
   for (cudaStream_t st : ctx->pipe_streams) if (st) cudaStreamDestroy(st);
   for (cudaEvent_t ev : ctx->pipe_events) cudaEventDestroy(ev);
+  if (ctx->barrier_event) cudaEventDestroy(ctx->barrier_event);
   cudaFree(ctx->d_status);
   delete ctx;  // the pool's destructor returns cached blocks
   return B200_OK;

@@ -99,6 +99,7 @@ struct b200_ctx {
   b200::StagingRing staging;     // uploads of host arrays (tensor contents, index lists)
   cudaStream_t pipe_streams[3] = {nullptr, nullptr, nullptr};
   std::vector<cudaEvent_t> pipe_events;
+  cudaEvent_t barrier_event = nullptr;  // b200_stream_barrier: marks this GPU's default stream
 };
 
 namespace b200 {

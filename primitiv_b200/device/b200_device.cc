@@ -142,6 +142,18 @@ B200::~B200() {
 
 ::b200_ctx *B200::context() const { return state_->ctx; }
 
+const void *B200::data(const Tensor &x) {
+  if (&x.device() != this) PRIMITIV_THROW_ERROR("B200::data: the tensor lives on another device.");
+  return in(x);
+}
+
+void *B200::data_for_overwrite(Tensor &x) {
+  if (&x.device() != this) PRIMITIV_THROW_ERROR("B200::data_for_overwrite: the tensor lives on another device.");
+  void *p = get_mutable_handle(x);
+  state_->zero_pending.erase(p);
+  return p;
+}
+
 void B200::set_matmul_path_policy(int policy) { B200_CALL(::b200_set_path_policy(state_->ctx, policy)); }
 
 void B200::dump_description() const {
@@ -230,6 +242,12 @@ void B200::copy_tensor_impl(const Tensor &x, Tensor &y) {
         B200_CALL(::b200_status_poll(src->state_->ctx, nullptr, &code));
       }
       B200_CALL(::b200_copy(state_->ctx, src->imode(), px, imode(), MDATA(y), n, nullptr));
+      if (src->device_id_ != device_id_) {
+        // ... and finish the copy before the caller may release x: the source GPU's pool
+        // orders reuse on its own stream only.
+        int code = 0;
+        B200_CALL(::b200_status_poll(state_->ctx, nullptr, &code));
+      }
       return;
     }
   } else if (x.device().type() == DeviceType::NAIVE) {

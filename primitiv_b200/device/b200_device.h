@@ -66,6 +66,14 @@ public:
   /** Kernel choice for matmul: 0 per problem, 1 CUDA cores, 2 tensor cores whenever eligible. */
   void set_matmul_path_policy(int policy);
 
+  /**
+   * Device pointer of a tensor of this device, for code that launches its own work on it (the
+   * device group's sum over GPUs).  `data` makes a deferred zero-fill happen first;
+   * `data_for_overwrite` drops it, for a caller that writes every element.
+   */
+  const void *data(const Tensor &x);
+  void *data_for_overwrite(Tensor &x);
+
 private:
   struct State;
   std::shared_ptr<State> state_;
@@ -87,100 +95,7 @@ private:
   int imode() const { return static_cast<int>(mode_); }
   std::size_t elem_size() const { return mode_ == Mode::FP16 ? 2 : 4; }
 
-  std::shared_ptr<void> new_handle(const Shape &shape, std::size_t *const allocated_size) override;
-
-  std::vector<float> tensor_to_vector_impl(const Tensor &x) override;
-  std::vector<std::uint32_t> argmax_impl(const Tensor &x, std::uint32_t dim) override;
-  std::vector<std::uint32_t> argmin_impl(const Tensor &x, std::uint32_t dim) override;
-
-  void reset_tensor_impl(float k, Tensor &x) override;
-  void reset_tensor_by_array_impl(const float values[], Tensor &x) override;
-  void copy_tensor_impl(const Tensor &x, Tensor &y) override;
-  void identity_impl(Tensor &y) override;
-
-  void random_bernoulli_impl(float p, Tensor &y) override;
-  void random_uniform_impl(float lower, float upper, Tensor &y) override;
-  void random_normal_impl(float mean, float sd, Tensor &y) override;
-  void random_log_normal_impl(float mean, float sd, Tensor &y) override;
-
-  void pick_fw_impl(const Tensor &x, const std::vector<std::uint32_t> &ids, std::uint32_t dim, Tensor &y) override;
-  void slice_fw_impl(const Tensor &x, std::uint32_t dim, std::uint32_t offset, Tensor &y) override;
-  void concat_fw_impl(const std::vector<const Tensor *> &xs, std::uint32_t dim, Tensor &y) override;
-  void pick_bw_impl(const Tensor &gy, const std::vector<std::uint32_t> &ids, std::uint32_t dim, Tensor &gx) override;
-  void slice_bw_impl(const Tensor &gy, std::uint32_t dim, std::uint32_t offset, Tensor &gx) override;
-
-#define B200_DECL_X(name)                                        \
-  void name##_fw_impl(const Tensor &x, Tensor &y) override;      \
-  void name##_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, Tensor &gx) override;
-  void negate_fw_impl(const Tensor &x, Tensor &y) override;
-  B200_DECL_X(abs) B200_DECL_X(sqrt) B200_DECL_X(exp) B200_DECL_X(log) B200_DECL_X(tanh)
-  B200_DECL_X(sigmoid) B200_DECL_X(softplus) B200_DECL_X(sin) B200_DECL_X(cos) B200_DECL_X(tan)
-  B200_DECL_X(transpose)
-#undef B200_DECL_X
-
-  void permute_dims_fw_impl(const Tensor &x, const std::vector<std::uint32_t> &perm, Tensor &y) override;
-  void permute_dims_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy,
-                            const std::vector<std::uint32_t> &perm, Tensor &gx) override;
-  void flip_fw_impl(const Tensor &x, std::uint32_t dim, Tensor &y) override;
-  void flip_bw_impl(const Tensor &gy, std::uint32_t dim, Tensor &gx) override;
-
-#define B200_DECL_X_CONST(name)                                           \
-  void name##_fw_impl(const Tensor &x, float k, Tensor &y) override;      \
-  void name##_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, float k, Tensor &gx) override;
-  B200_DECL_X_CONST(add_const) B200_DECL_X_CONST(subtract_const_r) B200_DECL_X_CONST(subtract_const_l)
-  B200_DECL_X_CONST(multiply_const) B200_DECL_X_CONST(divide_const_r) B200_DECL_X_CONST(divide_const_l)
-  B200_DECL_X_CONST(pow_const_r) B200_DECL_X_CONST(pow_const_l) B200_DECL_X_CONST(prelu) B200_DECL_X_CONST(elu)
-#undef B200_DECL_X_CONST
-
-  void pown_fw_impl(const Tensor &x, std::int32_t k, Tensor &y) override;
-  void pown_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, std::int32_t k, Tensor &gx) override;
-
-#define B200_DECL_X_SCALAR(name) \
-  void name##_fw_impl(const Tensor &x, const Tensor &k, Tensor &y) override;
-  B200_DECL_X_SCALAR(add_scalar) B200_DECL_X_SCALAR(subtract_scalar_r) B200_DECL_X_SCALAR(subtract_scalar_l)
-  B200_DECL_X_SCALAR(multiply_scalar) B200_DECL_X_SCALAR(divide_scalar_r) B200_DECL_X_SCALAR(divide_scalar_l)
-  B200_DECL_X_SCALAR(pow_scalar_r) B200_DECL_X_SCALAR(pow_scalar_l)
-#undef B200_DECL_X_SCALAR
-
-#define B200_DECL_AB(name)                                                    \
-  void name##_fw_impl(const Tensor &a, const Tensor &b, Tensor &y) override;  \
-  void name##_bw_impl(const Tensor &a, const Tensor &b, const Tensor &y, const Tensor &gy, \
-                      Tensor &ga, Tensor &gb) override;
-  B200_DECL_AB(add) B200_DECL_AB(subtract) B200_DECL_AB(multiply) B200_DECL_AB(divide) B200_DECL_AB(pow)
-  B200_DECL_AB(matmul)
-#undef B200_DECL_AB
-
-  void max_fw_impl(const Tensor &x, std::uint32_t dim, Tensor &y) override;
-  void min_fw_impl(const Tensor &x, std::uint32_t dim, Tensor &y) override;
-  void max_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, std::uint32_t dim, Tensor &gx) override;
-  void min_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, std::uint32_t dim, Tensor &gx) override;
-  void sum_fw_impl(const Tensor &x, std::uint32_t dim, Tensor &y) override;
-  void logsumexp_fw_impl(const Tensor &x, std::uint32_t dim, Tensor &y) override;
-  void broadcast_fw_impl(const Tensor &x, std::uint32_t dim, std::uint32_t size, Tensor &y) override;
-
-  void batch_pick_fw_impl(const Tensor &x, const std::vector<std::uint32_t> &ids, Tensor &y) override;
-  void batch_slice_fw_impl(const Tensor &x, std::uint32_t offset, Tensor &y) override;
-  void batch_concat_fw_impl(const std::vector<const Tensor *> &xs, Tensor &y) override;
-  void batch_sum_fw_impl(const Tensor &x, Tensor &y) override;
-  void batch_pick_bw_impl(const Tensor &gy, const std::vector<std::uint32_t> &ids, Tensor &gx) override;
-  void batch_slice_bw_impl(const Tensor &gy, std::uint32_t offset, Tensor &gx) override;
-
-  void conv2d_fw_impl(const Tensor &x, const Tensor &w, std::uint32_t padding0, std::uint32_t padding1,
-                      std::uint32_t stride0, std::uint32_t stride1, std::uint32_t dilation0,
-                      std::uint32_t dilation1, Tensor &y) override;
-  void conv2d_bw_impl(const Tensor &x, const Tensor &w, const Tensor &y, const Tensor &gy,
-                      std::uint32_t padding0, std::uint32_t padding1, std::uint32_t stride0,
-                      std::uint32_t stride1, std::uint32_t dilation0, std::uint32_t dilation1, Tensor &gx,
-                      Tensor &gw) override;
-  void max_pool2d_fw_impl(const Tensor &x, std::uint32_t window0, std::uint32_t window1, std::uint32_t padding0,
-                          std::uint32_t padding1, std::uint32_t stride0, std::uint32_t stride1, Tensor &y) override;
-  void max_pool2d_bw_impl(const Tensor &x, const Tensor &y, const Tensor &gy, std::uint32_t window0,
-                          std::uint32_t window1, std::uint32_t padding0, std::uint32_t padding1,
-                          std::uint32_t stride0, std::uint32_t stride1, Tensor &gx) override;
-
-  void inplace_multiply_const_impl(float k, Tensor &x) override;
-  void inplace_add_impl(const Tensor &x, Tensor &y) override;
-  void inplace_subtract_impl(const Tensor &x, Tensor &y) override;
+#include "device_overrides.inc"
 };
 
 }  // namespace devices

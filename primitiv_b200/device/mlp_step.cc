@@ -11,13 +11,16 @@
 // batch on the reference's Naive device from the same weights and inputs: losses and updated
 // weights must agree.
 //
-//   mlp_step [3xtf32|tf32|fp16] [batch] [repeats] [check_batch]
+//   mlp_step [3xtf32|tf32|fp16|3xfp16] [batch] [repeats] [check_batch] [gpus]
+// With gpus > 1 the device is a B200Group over GPUs 0 .. gpus-1: the same program, unchanged,
+// with the minibatch cut over the GPUs and the weight gradients summed between them.
 // Prints one JSON object.
 #include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <iostream>
+#include <memory>
 #include <random>
 #include <string>
 #include <vector>
@@ -35,6 +38,7 @@
 #include <primitiv_b200.h>
 
 #include "b200_device.h"
+#include "b200_group.h"
 
 using primitiv::Device;
 using primitiv::Graph;
@@ -42,6 +46,7 @@ using primitiv::Node;
 using primitiv::Parameter;
 using primitiv::Shape;
 using primitiv::devices::B200;
+using primitiv::devices::B200Group;
 using primitiv::devices::Naive;
 using std::vector;
 namespace F = primitiv::functions;
@@ -89,6 +94,10 @@ struct Model {
 };
 
 void sync(Device &dev) {
+  if (B200Group *grp = dynamic_cast<B200Group *>(&dev)) {
+    grp->synchronize();
+    return;
+  }
   B200 *b = dynamic_cast<B200 *>(&dev);
   if (!b) return;
   int code = 0;
@@ -150,17 +159,27 @@ int main(int argc, char **argv) {
   const std::uint32_t batch = argc > 2 ? std::atoi(argv[2]) : 65536;
   const int repeats = argc > 3 ? std::atoi(argv[3]) : 5;
   const std::uint32_t check_batch = argc > 4 ? std::atoi(argv[4]) : 256;
+  const std::uint32_t gpus = argc > 5 ? std::atoi(argv[5]) : 1;
   B200::Mode mode = B200::Mode::FP32_3XTF32;
   if (mode_name == "tf32") mode = B200::Mode::TF32_FAST;
   else if (mode_name == "fp16") mode = B200::Mode::FP16;
   else if (mode_name == "3xfp16") mode = B200::Mode::FP32_3XFP16;
   else if (mode_name != "3xtf32") {
-    std::cerr << "usage: mlp_step [3xtf32|tf32|fp16] [batch] [repeats] [check_batch]" << std::endl;
+    std::cerr << "usage: mlp_step [3xtf32|tf32|fp16|3xfp16] [batch] [repeats] [check_batch] [gpus]" << std::endl;
     return 2;
   }
   try {
     const Data data = make_data(batch > check_batch ? batch : check_batch);
-    B200 dev(0, 0, mode);
+    std::unique_ptr<Device> owned;
+    if (gpus > 1) {
+      std::vector<std::uint32_t> ids;
+      for (std::uint32_t i = 0; i < gpus; ++i) ids.push_back(i);
+      owned.reset(new B200Group(ids, 0, mode));
+    } else {
+      owned.reset(new B200(0, 0, mode));
+    }
+    Device &dev = *owned;
+    B200 &first = gpus > 1 ? static_cast<B200Group &>(dev).shard(0) : static_cast<B200 &>(dev);
     // parity at a small batch: two steps on both devices from the same weights
     double loss_diff = 0, w1_diff = 0, w3_diff = 0, naive_ms = 0;
     if (check_batch > 0) {
@@ -190,22 +209,22 @@ int main(int argc, char **argv) {
     }
     double kind_ms[4] = {0, 0, 0, 0};
     std::uint64_t kind_n[4] = {0, 0, 0, 0};
-    b200_profile_read(dev.context(), kind_ms, kind_n);
-    b200_profile_enable(dev.context(), 1);
+    b200_profile_read(first.context(), kind_ms, kind_n);
+    b200_profile_enable(first.context(), 1);
     train_step(model, data, batch, dev);
-    b200_profile_enable(dev.context(), 0);
-    b200_profile_read(dev.context(), kind_ms, kind_n);
+    b200_profile_enable(first.context(), 0);
+    b200_profile_read(first.context(), kind_ms, kind_n);
     // forward + both backward products of the three layers
     const double flops = 3.0 * 2.0 * (static_cast<double>(kHid) * kIn + static_cast<double>(kHid) * kHid +
                                       static_cast<double>(kOut) * kHid) * batch;
-    std::printf("{\"workload\": \"mlp_step\", \"mode\": \"%s\", \"batch\": %u, \"repeats\": %d, "
+    std::printf("{\"workload\": \"mlp_step\", \"mode\": \"%s\", \"gpus\": %u, \"batch\": %u, \"repeats\": %d, "
                 "\"ms_per_step_mean\": %.4f, \"ms_per_step_best\": %.4f, \"ms_of_best\": {\"graph_build\": %.3f, "
                 "\"upload_forward\": %.3f, \"backward_update\": %.3f}, \"matmul_gflops\": %.1f, \"loss\": %.5f, "
                 "\"check_batch\": %u, \"naive_ms_per_step\": %.2f, \"loss_rel_diff\": %.3e, "
                 "\"w1_rel_diff\": %.3e, \"w3_rel_diff\": %.3e, "
                 "\"device_ms_per_step\": {\"gemm_tc\": %.3f, \"pack\": %.3f, \"gemm_simt\": %.3f, \"other\": %.3f}, "
                 "\"launches_per_step\": {\"gemm_tc\": %llu, \"pack\": %llu, \"gemm_simt\": %llu, \"other\": %llu}}\n",
-                mode_name.c_str(), batch, repeats, sum / repeats, best, fastest.build_ms, fastest.forward_ms,
+                mode_name.c_str(), gpus, batch, repeats, sum / repeats, best, fastest.build_ms, fastest.forward_ms,
                 fastest.rest_ms, flops / (sum / repeats * 1e-3) / 1e9,
                 last_loss, check_batch, naive_ms, loss_diff, w1_diff, w3_diff, kind_ms[0], kind_ms[1], kind_ms[2],
                 kind_ms[3], static_cast<unsigned long long>(kind_n[0]), static_cast<unsigned long long>(kind_n[1]),

@@ -10,7 +10,11 @@
 // follows the reference's rule: 4 for fp32 storage, half of the fp32/half mantissa gap for
 // half storage.
 //
-//   ref_tensor_tests [3xtf32|tf32|fp16] [--filter=<substring of Suite.Name>]
+// With PRIMITIV_B200_GROUP=<ordinal,ordinal,...> the first of the two is a devices::B200Group
+// with one shard per listed ordinal instead ("0,0,0": three shards on GPU 0, which exercises the
+// whole sharding logic, uneven cuts and minibatches smaller than the group included, on one GPU).
+//
+//   ref_tensor_tests [3xtf32|tf32|fp16|3xfp16] [--filter=<substring of Suite.Name>]
 #define MINITEST_MAIN
 #include <gtest/gtest.h>
 
@@ -23,6 +27,7 @@
 #include <primitiv/devices/naive/device.h>
 
 #include "b200_device.h"
+#include "b200_group.h"
 
 namespace {
 primitiv::devices::B200::Mode g_mode = primitiv::devices::B200::Mode::FP32_3XTF32;
@@ -42,7 +47,19 @@ void add_available_cuda_devices(std::vector<primitiv::Device *> &devices) {
   // devices::B200 stands where devices::CUDA / CUDA16 would
   // PRIMITIV_B200_PATH_POLICY=2 sends even the tests' tiny products through the tensor-core kernel
   const char *policy = std::getenv("PRIMITIV_B200_PATH_POLICY");
+  const char *group = std::getenv("PRIMITIV_B200_GROUP");
+  if (group) {
+    std::vector<std::uint32_t> ids;
+    for (const char *p = group; *p; ++p)
+      if (*p >= '0' && *p <= '9') ids.push_back(static_cast<std::uint32_t>(*p - '0'));
+    primitiv::devices::B200Group *dev = new primitiv::devices::B200Group(ids, 1, g_mode);
+    if (policy)
+      for (std::uint32_t i = 0; i < dev->num_shards(); ++i) dev->shard(i).set_matmul_path_policy(std::atoi(policy));
+    devices.emplace_back(dev);
+    dev->dump_description();
+  }
   for (std::uint32_t seed : {1u, 2u}) {
+    if (group && seed == 1u) continue;
     primitiv::devices::B200 *dev = new primitiv::devices::B200(0, seed, g_mode);
     if (policy) dev->set_matmul_path_policy(std::atoi(policy));
     devices.emplace_back(dev);

@@ -23,7 +23,8 @@ needs_plugin = pytest.mark.skipif(not os.path.exists(PLUGIN),
 def test_plugin_exports_the_c_api_constructors():
     lib = ctypes.CDLL(PLUGIN)
     for name in ("primitivCreateB200Device", "primitivCreateB200DeviceWithSeed",
-                 "primitivCreateB200DeviceWithSeedAndMode", "primitivGetNumB200Devices"):
+                 "primitivCreateB200DeviceWithSeedAndMode", "primitivGetNumB200Devices",
+                 "primitivCreateB200GroupDevice", "primitivCreateB200GroupDeviceWithSeedAndMode"):
         assert hasattr(lib, name), name
 
 
@@ -160,3 +161,74 @@ def test_reference_xor_example_trains_on_b200():
     assert r.returncode == 0, (r.stdout + r.stderr)[-2000:]
     losses = [float(l.split(":")[1]) for l in r.stdout.splitlines() if l.strip().startswith("loss:")]
     assert len(losses) == 10 and losses[-1] < losses[0], losses
+
+
+# ---- devices::B200Group: one primitiv Device over several shards -------------------------------
+#
+# "0,0,0" puts three shards on GPU 0: every line of the sharding logic (uneven cuts, minibatches
+# smaller than the group, sums over shards, items moving between shards) runs on a single GPU;
+# "0,1" is the same over two GPUs, where the sums and copies cross NVLink.
+
+GROUP_RUNNER = os.path.join(ROOT, "tests", "cpp", "_build", "group_parity")
+
+
+def _gpu_count():
+    import torch
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _group_lists():
+    lists = ["0,0", "0,0,0"]
+    n = _gpu_count()
+    if n >= 2:
+        lists.append("0,1")
+    if n >= 4:
+        lists.append("0,1,2,3")
+    return lists
+
+
+@pytest.mark.gpu
+@needs_plugin
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32", "fp16", "3xfp16"])
+def test_group_parity_against_reference_naive(mode):
+    """tests/cpp/group_parity.cc: matmul fw / bw in all broadcast combinations, sums over the
+    batch, batch_pick / slice / concat and three training steps through primitiv's Graph on a
+    B200Group against Naive; replicas of unbatched tensors must hold identical bits."""
+    import json
+    assert os.path.exists(GROUP_RUNNER), "tests/cpp/_build/group_parity is not built"
+    for ids in _group_lists():
+        r = subprocess.run([GROUP_RUNNER, mode, ids], capture_output=True, text=True, timeout=600)
+        tail = (r.stdout + r.stderr)[-4000:]
+        assert r.returncode == 0, "%s: %s" % (ids, tail)
+        out = json.loads(r.stdout.strip().splitlines()[-1])
+        assert out["failures"] == 0 and out["checks"] > 200 and out["cross_gpu_sums"] > 50, out
+        assert out["shards"] == len(ids.split(","))
+
+
+@pytest.mark.gpu
+@needs_plugin
+@pytest.mark.parametrize("mode", ["3xtf32", "fp16"])
+def test_primitiv_own_tensor_tests_pass_on_a_group(mode):
+    """The reference's own tensor tests again, with a B200Group as the first GPU device of the list
+    (next to Naive and a plain B200, so tensors are also copied between all three kinds)."""
+    assert os.path.exists(REF_SUITE), "tests/cpp/_build/ref_tensor_tests is not built"
+    for ids in _group_lists()[1:3]:
+        env = dict(os.environ, PRIMITIV_B200_GROUP=ids)
+        r = subprocess.run([REF_SUITE, mode], capture_output=True, text=True, timeout=900, env=env)
+        tail = (r.stdout + r.stderr)[-3000:]
+        assert r.returncode == 0, "%s: %s" % (ids, tail)
+        summary = [l for l in r.stdout.splitlines() if l.startswith("[==========]")][-1]
+        ran, passed, failed = [int(w) for w in summary.replace(",", "").split() if w.isdigit()]
+        assert ran >= 370 and passed == ran and failed == 0, summary
+        assert r.stderr.count("Type: B200Group") >= 3
+
+
+@pytest.mark.gpu
+@needs_plugin
+def test_perceptron_step_on_a_group_of_gpus():
+    """mlp_step unchanged on a B200Group over two GPUs: same loss and weights as Naive at batch 256."""
+    if _gpu_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = _run_json("mlp_step", "3xtf32", 8192, 1, 256, 2)
+    assert out["gpus"] == 2
+    assert out["loss_rel_diff"] < 1e-5 and out["w1_rel_diff"] < 1e-5 and out["w3_rel_diff"] < 1e-5, out
