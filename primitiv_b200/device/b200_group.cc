@@ -35,6 +35,11 @@ struct B200Group::Table {
   std::vector<Tensor> parts;
 };
 
+namespace {
+// sums over GPUs of at least this many bytes are done slice by slice (see sum_over_shards)
+const std::uint64_t kSlicedSumBytes = 1ull << 20;
+}  // namespace
+
 // ---------------------------------------------------------------- construction
 
 B200Group::B200Group(const std::vector<std::uint32_t> &device_ids) { initialize(device_ids, 0, nullptr); }
@@ -171,7 +176,12 @@ std::shared_ptr<void> B200Group::new_handle(const Shape &shape, std::size_t *con
 
 // partials[0 .. count) live on shards 0 .. count-1 and have one shape.  Returns one tensor per
 // shard (all of them, also those without a partial) holding partials[0] + partials[1] + ...
-// added in that order on every shard: the same bits everywhere.
+// added in that order: the same bits everywhere.
+//
+// Small sums (and two GPUs): every GPU reads all partials and adds them itself; (g - 1) x bytes
+// cross NVLink per GPU, in one step.  Large sums on three or more GPUs: GPU r adds only the r-th
+// slice of every partial, then copies the other slices from the GPUs that made them;
+// 2 (g - 1) / g x bytes per GPU, in two steps.
 std::vector<Tensor> B200Group::sum_over_shards(std::vector<Tensor> &partials, std::uint32_t count) {
   std::vector<Tensor> sums(g());
   if (g() == 1) {
@@ -179,16 +189,40 @@ std::vector<Tensor> B200Group::sum_over_shards(std::vector<Tensor> &partials, st
     return sums;
   }
   const Shape shape = partials[0].shape();
+  const std::uint64_t n = shape.size();
+  const std::size_t es = type() == DeviceType::CUDA16 ? 2 : 4;
+  const int imode = static_cast<int>(shards_[0]->mode());
   std::vector<const void *> srcs(count);
   for (std::uint32_t s = 0; s < count; ++s) srcs[s] = shards_[s]->data(partials[s]);
-  GROUP_CALL(::b200_stream_barrier(ctxs_.data(), static_cast<int>(ctxs_.size())));  // partials complete everywhere
+  std::vector<char *> dst(g());
   for (std::uint32_t r = 0; r < g(); ++r) {
     sums[r] = shards_[r]->new_tensor_by_constant(shape, 0);  // the fill is deferred and dropped right here
-    void *dst = shards_[r]->data_for_overwrite(sums[r]);
-    GROUP_CALL(::b200_peer_sum(ctxs_[r], static_cast<int>(shards_[r]->mode()), srcs.data(), static_cast<int>(count),
-                               dst, shape.size(), nullptr));
+    dst[r] = static_cast<char *>(shards_[r]->data_for_overwrite(sums[r]));
   }
-  // nobody reuses a partial's memory before every reader is done with it
+  GROUP_CALL(::b200_stream_barrier(ctxs_.data(), static_cast<int>(ctxs_.size())));  // partials complete everywhere
+  if (g() < 3 || n * es < kSlicedSumBytes) {
+    for (std::uint32_t r = 0; r < g(); ++r) {
+      GROUP_CALL(::b200_peer_sum(ctxs_[r], imode, srcs.data(), static_cast<int>(count), dst[r], n, nullptr));
+    }
+  } else {
+    // slice boundaries on multiples of 8 elements keep every 128-bit access aligned
+    auto cut = [&](std::uint32_t r) { return r >= g() ? n : (static_cast<std::uint64_t>(r) * n / g()) & ~std::uint64_t(7); };
+    std::vector<const void *> shifted(count);
+    for (std::uint32_t r = 0; r < g(); ++r) {
+      for (std::uint32_t s = 0; s < count; ++s) shifted[s] = static_cast<const char *>(srcs[s]) + cut(r) * es;
+      GROUP_CALL(::b200_peer_sum(ctxs_[r], imode, shifted.data(), static_cast<int>(count), dst[r] + cut(r) * es,
+                                 cut(r + 1) - cut(r), nullptr));
+    }
+    GROUP_CALL(::b200_stream_barrier(ctxs_.data(), static_cast<int>(ctxs_.size())));  // every slice is summed
+    for (std::uint32_t r = 0; r < g(); ++r) {
+      for (std::uint32_t s = 0; s < g(); ++s) {
+        if (s == r || cut(s + 1) == cut(s)) continue;
+        const void *from = dst[s] + cut(s) * es;
+        GROUP_CALL(::b200_peer_sum(ctxs_[r], imode, &from, 1, dst[r] + cut(s) * es, cut(s + 1) - cut(s), nullptr));
+      }
+    }
+  }
+  // nobody reuses a partial's (or a slice's) memory before every reader is done with it
   GROUP_CALL(::b200_stream_barrier(ctxs_.data(), static_cast<int>(ctxs_.size())));
   ++cross_gpu_sums_;
   return sums;

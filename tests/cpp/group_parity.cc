@@ -174,6 +174,18 @@ void test_sums(Naive &n, B200Group &g, std::uint32_t batch) {
   }
 }
 
+// A sum over shards large enough (> 1 MiB in either storage type) for the slice-by-slice form
+// that groups of three or more use, with a length that is not a multiple of the slice alignment.
+void test_large_sum(Naive &n, B200Group &g) {
+  const Shape s({1021, 601}, 5), s1({1021, 601});
+  Pair x(s, rnd(s.size()), n, g), y(s1, rnd(s1.size()), n, g);
+  n.inplace_add(x.ref, y.ref);
+  g.inplace_add(x.got, y.got);
+  expect_close(y.ref.to_vector(), y.got.to_vector(), "large inplace_add into unbatched", 10 * g_tol);
+  expect_replicas_equal(g, y.got, "large inplace_add");
+  expect_close(n.batch_sum_fw(x.ref).to_vector(), g.batch_sum_fw(x.got).to_vector(), "large batch_sum", 10 * g_tol);
+}
+
 void test_batch_moves(Naive &n, B200Group &g, std::uint32_t batch) {
   const Shape s({3, 4}, batch);
   const std::string tag = "batch " + std::to_string(batch);
@@ -278,6 +290,7 @@ int main(int argc, char **argv) {
       test_batch_moves(naive, group, batch);
       test_training(naive, group, batch);
     }
+    test_large_sum(naive, group);
     group.synchronize();
     std::printf("{\"mode\": \"%s\", \"shards\": %u, \"checks\": %d, \"failures\": %d, \"cross_gpu_sums\": %llu}\n",
                 mode_name.c_str(), shards, g_checks, g_failures, static_cast<unsigned long long>(group.cross_gpu_sums()));
