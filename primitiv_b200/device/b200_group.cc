@@ -13,6 +13,7 @@
 #include <primitiv/core/error.h>
 
 #include "../../include/primitiv_b200_ops.h"
+#include "batch_partition.h"
 
 #define GROUP_CALL(expr)                                                                     \
   do {                                                                                       \
@@ -98,15 +99,10 @@ void B200Group::dump_description() const {
 
 // ---------------------------------------------------------------- partition
 
+std::uint32_t B200Group::active(std::uint32_t batch) const { return batch_partition::active(g(), batch); }
+
 void B200Group::range(std::uint32_t batch, std::uint32_t r, std::uint32_t *lo, std::uint32_t *hi) const {
-  if (batch == 1) {
-    *lo = 0;
-    *hi = 1;
-    return;
-  }
-  const std::uint64_t n = active(batch);
-  *lo = static_cast<std::uint32_t>(static_cast<std::uint64_t>(r) * batch / n);
-  *hi = static_cast<std::uint32_t>(static_cast<std::uint64_t>(r + 1) * batch / n);
+  batch_partition::range(g(), batch, r, lo, hi);
 }
 
 Shape B200Group::local(const Shape &s, std::uint32_t r) const {
@@ -116,12 +112,7 @@ Shape B200Group::local(const Shape &s, std::uint32_t r) const {
 }
 
 std::uint32_t B200Group::owner(std::uint32_t batch, std::uint32_t item) const {
-  const std::uint32_t n = active(batch);
-  std::uint32_t r = static_cast<std::uint32_t>((static_cast<std::uint64_t>(item) * n) / batch);
-  std::uint32_t lo, hi;
-  for (range(batch, r, &lo, &hi); item < lo; range(batch, r, &lo, &hi)) --r;
-  for (; item >= hi; range(batch, r, &lo, &hi)) ++r;
-  return r;
+  return batch_partition::owner(g(), batch, item);
 }
 
 // ---------------------------------------------------------------- parts of a tensor

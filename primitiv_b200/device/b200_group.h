@@ -78,7 +78,7 @@ private:
 
   std::uint32_t g() const { return static_cast<std::uint32_t>(shards_.size()); }
   // shards that hold a part of a tensor or take part in an operation of this batch size
-  std::uint32_t active(std::uint32_t batch) const { return batch == 1 ? g() : (batch < g() ? batch : g()); }
+  std::uint32_t active(std::uint32_t batch) const;
   void range(std::uint32_t batch, std::uint32_t r, std::uint32_t *lo, std::uint32_t *hi) const;
   Shape local(const Shape &s, std::uint32_t r) const;
   std::uint32_t owner(std::uint32_t batch, std::uint32_t item) const;
