@@ -212,11 +212,12 @@ B200_API int b200_peer_enable(b200_ctx *ctx, b200_ctx *peer);
  * so far on every one of them has finished.  Asynchronous; contexts on the same GPU share a
  * stream and need nothing. */
 B200_API int b200_stream_barrier(b200_ctx *const *ctxs, int n);
-/* dst[i] = srcs[0][i] + srcs[1][i] + ... (in that order, fp32 arithmetic, one rounding to the
- * storage type), on ctx's GPU; srcs may live on peers (b200_peer_enable first, and a
- * b200_stream_barrier between their producers and this call).  1 <= nsrc <= 16. */
+/* dst[i] = (accumulate ? dst[i] : 0) + (srcs[0][i] + srcs[1][i] + ...) (in that order, fp32
+ * arithmetic, one rounding to the storage type), on ctx's GPU; srcs may live on peers
+ * (b200_peer_enable first, and a b200_stream_barrier between their producers and this call).
+ * 1 <= nsrc <= 16. */
 B200_API int b200_peer_sum(b200_ctx *ctx, int mode, const void *const *srcs, int nsrc, void *dst,
-                           uint64_t n, void *stream);
+                           uint64_t n, int accumulate, void *stream);
 
 #ifdef __cplusplus
 }

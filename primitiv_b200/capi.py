@@ -83,7 +83,7 @@ SIGNATURES = {
     "b200_random": (_int, [_vp, _int, _int, ctypes.c_float, ctypes.c_float, _vp, _u64, _vp]),
     "b200_peer_enable": (_int, [_vp, _vp]),
     "b200_stream_barrier": (_int, [ctypes.POINTER(_vp), _int]),
-    "b200_peer_sum": (_int, [_vp, _int, ctypes.POINTER(_vp), _int, _vp, _u64, _vp]),
+    "b200_peer_sum": (_int, [_vp, _int, ctypes.POINTER(_vp), _int, _vp, _u64, _int, _vp]),
 }
 
 

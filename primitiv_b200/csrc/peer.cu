@@ -13,11 +13,11 @@ struct PeerSources {
   const void *p[kMaxPeerSources];
 };
 
-// dst[i] = sum over sources in list order.  Sources may be peer memory: plain 128-bit loads,
+// dst[i] = (accumulate ? dst[i] : 0) + sum over sources in list order.  Sources may be peer memory: plain 128-bit loads,
 // one per source and thread in flight, so a launch keeps nsrc x grid x 16 B outstanding on NVLink.
 template <typename T>
 __global__ void __launch_bounds__(256) peer_sum_kernel(PeerSources srcs, int nsrc, T *__restrict__ dst, u64 n,
-                                                       int vector_ok) {
+                                                       int vector_ok, int accumulate) {
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
   constexpr int N = Vec<T>::N;
@@ -33,6 +33,11 @@ __global__ void __launch_bounds__(256) peer_sum_kernel(PeerSources srcs, int nsr
 #pragma unroll
       for (int i = 0; i < N; ++i) acc[i] += x.get(i);
     }
+    if (accumulate) {
+      x.load(dst + v * N);
+#pragma unroll
+      for (int i = 0; i < N; ++i) acc[i] += x.get(i);
+    }
 #pragma unroll
     for (int i = 0; i < N; ++i) x.set(i, acc[i]);
     x.store(dst + v * N);
@@ -40,6 +45,7 @@ __global__ void __launch_bounds__(256) peer_sum_kernel(PeerSources srcs, int nsr
   for (u64 i = nvec * N + tid; i < n; i += stride) {
     float acc = ld(static_cast<const T *>(srcs.p[0]), i);
     for (int s = 1; s < nsrc; ++s) acc += ld(static_cast<const T *>(srcs.p[s]), i);
+    if (accumulate) acc += ld(dst, i);
     st(dst, i, acc);
   }
 }
@@ -87,7 +93,8 @@ int b200_stream_barrier(b200_ctx *const *ctxs, int n) {
   return B200_OK;
 }
 
-int b200_peer_sum(b200_ctx *ctx, int mode, const void *const *srcs, int nsrc, void *dst, uint64_t n, void *stream) {
+int b200_peer_sum(b200_ctx *ctx, int mode, const void *const *srcs, int nsrc, void *dst, uint64_t n, int accumulate,
+                  void *stream) {
   B200_OPS_PROLOGUE(ctx);
   if (!srcs || nsrc < 1 || nsrc > kMaxPeerSources || (!dst && n)) return B200_ERR_INVALID_ARG;
   if (n == 0) return B200_OK;
@@ -101,7 +108,7 @@ int b200_peer_sum(b200_ctx *ctx, int mode, const void *const *srcs, int nsrc, vo
   B200_DISPATCH_MODE(mode, {
     ProfScope prof(ctx, kProfElementwise, s);
     peer_sum_kernel<T><<<grid_for(ctx, n / Vec<T>::N + 1, 256), 256, 0, s>>>(ps, nsrc, static_cast<T *>(dst), n,
-                                                                            vector_ok);
+                                                                            vector_ok, accumulate);
   });
   B200_OPS_EPILOGUE(ctx);
 }

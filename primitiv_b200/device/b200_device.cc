@@ -147,6 +147,11 @@ const void *B200::data(const Tensor &x) {
   return in(x);
 }
 
+void *B200::data_for_accumulate(Tensor &x, int *accumulate) {
+  if (&x.device() != this) PRIMITIV_THROW_ERROR("B200::data_for_accumulate: the tensor lives on another device.");
+  return out_acc(x, accumulate);
+}
+
 void *B200::data_for_overwrite(Tensor &x) {
   if (&x.device() != this) PRIMITIV_THROW_ERROR("B200::data_for_overwrite: the tensor lives on another device.");
   void *p = get_mutable_handle(x);

@@ -69,10 +69,13 @@ public:
   /**
    * Device pointer of a tensor of this device, for code that launches its own work on it (the
    * device group's sum over GPUs).  `data` makes a deferred zero-fill happen first;
-   * `data_for_overwrite` drops it, for a caller that writes every element.
+   * `data_for_overwrite` drops it, for a caller that writes every element;
+   * `data_for_accumulate` drops it too and then reports *accumulate = 0: a caller that would
+   * add to every element stores instead.
    */
   const void *data(const Tensor &x);
   void *data_for_overwrite(Tensor &x);
+  void *data_for_accumulate(Tensor &x, int *accumulate);
 
 private:
   struct State;

@@ -165,35 +165,28 @@ std::shared_ptr<void> B200Group::new_handle(const Shape &shape, std::size_t *con
 
 // ---------------------------------------------------------------- the meeting point of the GPUs
 
-// partials[0 .. count) live on shards 0 .. count-1 and have one shape.  Returns one tensor per
-// shard (all of them, also those without a partial) holding partials[0] + partials[1] + ...
-// added in that order: the same bits everywhere.
+// partials[0 .. count) live on shards 0 .. count-1 and have one shape; dst[r] is memory of that
+// shape on shard r (every shard, also those without a partial).  On every shard
+//   dst[r] = (accumulate[r] ? dst[r] : 0) + (partials[0] + partials[1] + ...)
+// with the partials added in that order: replicas that were equal stay equal, bit for bit.
 //
 // Small sums (and two GPUs): every GPU reads all partials and adds them itself; (g - 1) x bytes
-// cross NVLink per GPU, in one step.  Large sums on three or more GPUs: GPU r adds only the r-th
-// slice of every partial, then copies the other slices from the GPUs that made them;
-// 2 (g - 1) / g x bytes per GPU, in two steps.
-std::vector<Tensor> B200Group::sum_over_shards(std::vector<Tensor> &partials, std::uint32_t count) {
-  std::vector<Tensor> sums(g());
-  if (g() == 1) {
-    sums[0] = std::move(partials[0]);
-    return sums;
-  }
+// cross NVLink per GPU, in one step.  Large sums on three or more GPUs: GPU r does this only for
+// the r-th slice, then copies the other slices from the GPUs that made them; 2 (g - 1) / g x
+// bytes per GPU, in two steps.
+void B200Group::sum_into(std::vector<Tensor> &partials, std::uint32_t count, const std::vector<char *> &dst,
+                         const std::vector<int> &accumulate) {
   const Shape shape = partials[0].shape();
   const std::uint64_t n = shape.size();
   const std::size_t es = type() == DeviceType::CUDA16 ? 2 : 4;
   const int imode = static_cast<int>(shards_[0]->mode());
   std::vector<const void *> srcs(count);
   for (std::uint32_t s = 0; s < count; ++s) srcs[s] = shards_[s]->data(partials[s]);
-  std::vector<char *> dst(g());
-  for (std::uint32_t r = 0; r < g(); ++r) {
-    sums[r] = shards_[r]->new_tensor_by_constant(shape, 0);  // the fill is deferred and dropped right here
-    dst[r] = static_cast<char *>(shards_[r]->data_for_overwrite(sums[r]));
-  }
   GROUP_CALL(::b200_stream_barrier(ctxs_.data(), static_cast<int>(ctxs_.size())));  // partials complete everywhere
   if (g() < 3 || n * es < kSlicedSumBytes) {
     for (std::uint32_t r = 0; r < g(); ++r) {
-      GROUP_CALL(::b200_peer_sum(ctxs_[r], imode, srcs.data(), static_cast<int>(count), dst[r], n, nullptr));
+      GROUP_CALL(::b200_peer_sum(ctxs_[r], imode, srcs.data(), static_cast<int>(count), dst[r], n, accumulate[r],
+                                 nullptr));
     }
   } else {
     // slice boundaries on multiples of 8 elements keep every 128-bit access aligned
@@ -202,26 +195,41 @@ std::vector<Tensor> B200Group::sum_over_shards(std::vector<Tensor> &partials, st
     for (std::uint32_t r = 0; r < g(); ++r) {
       for (std::uint32_t s = 0; s < count; ++s) shifted[s] = static_cast<const char *>(srcs[s]) + cut(r) * es;
       GROUP_CALL(::b200_peer_sum(ctxs_[r], imode, shifted.data(), static_cast<int>(count), dst[r] + cut(r) * es,
-                                 cut(r + 1) - cut(r), nullptr));
+                                 cut(r + 1) - cut(r), accumulate[r], nullptr));
     }
-    GROUP_CALL(::b200_stream_barrier(ctxs_.data(), static_cast<int>(ctxs_.size())));  // every slice is summed
+    GROUP_CALL(::b200_stream_barrier(ctxs_.data(), static_cast<int>(ctxs_.size())));  // every slice is final
     for (std::uint32_t r = 0; r < g(); ++r) {
       for (std::uint32_t s = 0; s < g(); ++s) {
         if (s == r || cut(s + 1) == cut(s)) continue;
         const void *from = dst[s] + cut(s) * es;
-        GROUP_CALL(::b200_peer_sum(ctxs_[r], imode, &from, 1, dst[r] + cut(s) * es, cut(s + 1) - cut(s), nullptr));
+        GROUP_CALL(::b200_peer_sum(ctxs_[r], imode, &from, 1, dst[r] + cut(s) * es, cut(s + 1) - cut(s), 0, nullptr));
       }
     }
   }
   // nobody reuses a partial's (or a slice's) memory before every reader is done with it
   GROUP_CALL(::b200_stream_barrier(ctxs_.data(), static_cast<int>(ctxs_.size())));
   ++cross_gpu_sums_;
+}
+
+// The same into fresh tensors, one per shard.
+std::vector<Tensor> B200Group::sum_over_shards(std::vector<Tensor> &partials, std::uint32_t count) {
+  std::vector<Tensor> sums(g());
+  if (g() == 1) {
+    sums[0] = std::move(partials[0]);
+    return sums;
+  }
+  std::vector<char *> dst(g());
+  for (std::uint32_t r = 0; r < g(); ++r) {
+    sums[r] = shards_[r]->new_tensor_by_constant(partials[0].shape(), 0);  // the fill is deferred and dropped right here
+    dst[r] = static_cast<char *>(shards_[r]->data_for_overwrite(sums[r]));
+  }
+  sum_into(partials, count, dst, std::vector<int>(g(), 0));
   return sums;
 }
 
 // Where a backward pass adds one gradient.  When the operation runs over a minibatch but the
 // gradient has none (a broadcast operand), each shard adds into a zeroed scratch tensor
-// instead; finish() sums the scratch tensors over the shards and adds the total to every replica.
+// instead; finish() adds the scratch tensors of all shards, in shard order, into every replica.
 class B200Group::GradSink {
 public:
   GradSink(B200Group &dev, Tensor &gx, std::uint32_t op_batch)
@@ -243,12 +251,16 @@ public:
     }
     const std::uint32_t count = dev_.active(op_batch_);
     for (std::uint32_t r = 0; r < count; ++r) at(r);  // a shard that was skipped contributes zeros
-    std::vector<Tensor> sums = dev_.sum_over_shards(cur_, count);
+    // the total lands in the gradient itself: stored where its zero-fill was still pending, added otherwise
+    std::vector<Tensor> parts(dev_.g());
+    std::vector<char *> dst(dev_.g());
+    std::vector<int> accumulate(dev_.g(), 1);
     for (std::uint32_t r = 0; r < dev_.g(); ++r) {
-      Tensor p = dev_.take(table_, shape_, r);
-      dev_.shards_[r]->inplace_add(sums[r], p);
-      table_.parts[r] = std::move(p);
+      parts[r] = dev_.take(table_, shape_, r);
+      dst[r] = static_cast<char *>(dev_.shards_[r]->data_for_accumulate(parts[r], &accumulate[r]));
     }
+    dev_.sum_into(cur_, count, dst, accumulate);
+    for (std::uint32_t r = 0; r < dev_.g(); ++r) table_.parts[r] = std::move(parts[r]);
   }
 
 private:

@@ -86,6 +86,8 @@ private:
   Tensor view(const Tensor &x, std::uint32_t r) const;   // read-only part with its local shape
   Table &table(Tensor &x);                               // for writing; may clone a shared tensor
   Tensor take(Table &t, const Shape &xs, std::uint32_t r);
+  void sum_into(std::vector<Tensor> &partials, std::uint32_t count, const std::vector<char *> &dst,
+                const std::vector<int> &accumulate);
   std::vector<Tensor> sum_over_shards(std::vector<Tensor> &partials, std::uint32_t count);
   Tensor gather(const Tensor &x, const std::vector<std::uint32_t> &items, std::uint32_t r);
 
