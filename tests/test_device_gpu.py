@@ -232,3 +232,18 @@ def test_perceptron_step_on_a_group_of_gpus():
     out = _run_json("mlp_step", "3xtf32", 8192, 1, 256, 2)
     assert out["gpus"] == 2
     assert out["loss_rel_diff"] < 1e-5 and out["w1_rel_diff"] < 1e-5 and out["w3_rel_diff"] < 1e-5, out
+
+
+@pytest.mark.gpu
+@needs_plugin
+def test_reference_xor_example_trains_on_a_group():
+    """examples/xor/xor.cc of the reference again, its device line swapped for a B200Group: the batch of
+    four samples is cut over the shards and the parameter gradients are summed between them."""
+    path = os.path.join(ROOT, "primitiv_b200", "device", "_build", "example_xor_group")
+    assert os.path.exists(path), "example_xor_group is not built"
+    for ids in _group_lists()[:3]:
+        env = dict(os.environ, PRIMITIV_B200_GROUP=ids)
+        r = subprocess.run([path], capture_output=True, text=True, timeout=300, env=env)
+        assert r.returncode == 0, "%s: %s" % (ids, (r.stdout + r.stderr)[-2000:])
+        losses = [float(l.split(":")[1]) for l in r.stdout.splitlines() if l.strip().startswith("loss:")]
+        assert len(losses) == 10 and losses[-1] < losses[0], (ids, losses)
