@@ -159,7 +159,9 @@ B200_API int b200_matmul_bw_host(b200_ctx *ctx, int mode,
  * `red` > 1 sums several operand pairs into one C without atomics (the
  * "a batched, b broadcast" gradient that the reference computes with a serial
  * loop of Sgemm calls, matmul.cu:113-123).
- * force_path: 0 = choose; 1 = CUDA-core kernel; 2 = tensor-core kernel (error if ineligible). */
+ * force_path: 0 = choose; 1 = CUDA-core kernel; 2 = tensor-core kernel (error if ineligible);
+ * 3 = the CUDA-core kernels for one tiny extent (m <= 16 or k <= 16) against large ones (error if
+ * the shape and layout are not one of theirs). */
 B200_API int b200_gemm(b200_ctx *ctx, int mode, int trans_a, int trans_b,
                        const void *A, const void *B, void *C,
                        uint32_t m, uint32_t n, uint32_t k,

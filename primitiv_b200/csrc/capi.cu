@@ -192,10 +192,18 @@ int b200_gemm(b200_ctx *ctx, int mode, int trans_a, int trans_b, const void *A, 
   const bool eligible = b200::gemm_tc_eligible(ctx, g);
   if (force_path == 2) return eligible ? b200::gemm_tc(ctx, g, s) : B200_ERR_INVALID_ARG;
   if (force_path == 1) return b200::gemm_simt(ctx, g, s);
+  if (force_path == 3) return b200::gemm_skinny_eligible(g) ? b200::gemm_skinny(ctx, g, s) : B200_ERR_INVALID_ARG;
   if (ctx->path_policy == 2 && eligible) return b200::gemm_tc(ctx, g, s);
   if (ctx->path_policy == 1) return b200::gemm_simt(ctx, g, s);
   // A 128-row MMA tile on a problem this small is mostly padding; the CUDA-core
   // kernel wins below roughly a tile's worth of work.
+  // One tiny extent against large ones is HBM-bound.  In the fp32-grade modes the tensor-core
+  // path would first pack the large operand into planes (three more passes over it): there the
+  // CUDA-core kernels that stream it once win (320-410 us against 675 us for the three products of
+  // a 10 x 1024 layer over 65536 items) and are exact fp32.  The single-pass modes need no
+  // packing and stay on the tensor-core path.
+  if ((mode == B200_MODE_FP32_3XTF32 || mode == B200_MODE_FP32_3XFP16) && b200::gemm_skinny_eligible(g))
+    return b200::gemm_skinny(ctx, g, s);
   const double macs = static_cast<double>(m) * n * k * groups * red;
   // (a few rows against a long contraction are still worth it: the tensor-core path splits k
   // over all SMs and streams the big operand once, the CUDA-core kernel would run on a few CTAs)

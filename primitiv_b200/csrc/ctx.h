@@ -151,6 +151,9 @@ struct GemmArgs {
 
 // CUDA-core path: any shape, any alignment.
 int gemm_simt(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
+// CUDA-core kernels for products with one tiny extent against large ones (gemm_skinny.cu).
+bool gemm_skinny_eligible(const GemmArgs &g);
+int gemm_skinny(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
 // tcgen05 path.  tc_eligible() says whether the operands meet TMA's alignment rules.
 bool gemm_tc_eligible(const b200_ctx *ctx, const GemmArgs &g);
 int gemm_tc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);

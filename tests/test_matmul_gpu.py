@@ -12,7 +12,7 @@ import torch
 
 import oracle_lib as ol
 import primitiv_b200 as pb
-from gpu_util import MODES, TOL, matmul_bw, matmul_fw
+from gpu_util import MODES, TOL, dev, host, matmul_bw, matmul_fw
 
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
@@ -307,3 +307,78 @@ def test_3xfp16_rows_of_very_different_magnitude(ctx):
     row_err = np.linalg.norm(y - want, axis=1) / np.linalg.norm(want, axis=1)
     col_err = np.linalg.norm(y - want, axis=0) / np.linalg.norm(want, axis=0)
     assert row_err.max() < 1e-5 and col_err.max() < 1e-5, (row_err.max(), col_err.max())
+
+
+# One tiny extent against large ones (a 10-row classifier layer over a large minibatch and its two
+# gradients): in the fp32-grade modes these go to the CUDA-core kernels of gemm_skinny.cu, which
+# stream the large operand once and compute in plain fp32.  (di, dj, dk, ba, bb)
+SKINNY_SHAPES = [
+    (10, 1024, 1, 1, 8192),    # rows / reduce / outer with the layouts matmul_fw / matmul_bw produce
+    (7, 1000, 1, 1, 9001),     # nothing divides anything
+    (3, 64, 1, 1, 8193),       # the smallest staging width
+    (16, 300, 1, 1, 8500),     # the largest tiny extent
+]
+
+
+@pytest.mark.parametrize("mode", ["3xtf32", "3xfp16"])
+@pytest.mark.parametrize("shape", SKINNY_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_skinny_products_run_on_cuda_cores_in_fp32(ctx, shape, mode):
+    di, dj, dk, ba, bb = shape
+    rng = np.random.default_rng(hash(shape) % (2 ** 32))
+    a = rng.uniform(-1, 1, di * dj * ba).astype(np.float32)
+    b = rng.uniform(-1, 1, dj * dk * bb).astype(np.float32)
+    gy = rng.standard_normal(di * dk * max(ba, bb)).astype(np.float32)
+    ctx.profile_read()
+    ctx.profile_enable(True)
+    try:
+        y, ga, gb = _check_all(ctx, mode, a, b, gy, di, dj, dk, ba, bb)
+    finally:
+        ctx.profile_enable(False)
+    prof = ctx.profile_read()
+    assert prof["gemm_tc"][1] == 0 and prof["pack"][1] == 0 and prof["gemm_simt"][1] == 3, prof
+    # plain fp32 arithmetic: an order of magnitude inside the bound of the tensor-core modes
+    y64 = ol.fw_f64(a, b, di, dj, dk, ba, bb)
+    assert ol.rel_err(y, y64) <= 1e-6
+    again = _check_all(ctx, mode, a, b, gy, di, dj, dk, ba, bb)
+    for x, z in zip((y, ga, gb), again):   # fixed summation order: same bits every run
+        assert np.array_equal(x, z)
+
+
+@pytest.mark.parametrize("mode", list(MODES))
+def test_skinny_kernels_forced_in_every_mode(ctx, mode):
+    """force_path = 3 through b200_gemm: the three kernels in every storage type, overwrite and +=;
+    a shape that is none of theirs is refused."""
+    m_, k_, n_ = 10, 512, 4099
+    rng = np.random.default_rng(11)
+    w = rng.uniform(-1, 1, (k_, m_)).astype(np.float32)      # {m, k} column-major
+    x = rng.uniform(-1, 1, (n_, k_)).astype(np.float32)      # {k, n} column-major
+    gy = (0.05 * rng.standard_normal((n_, m_))).astype(np.float32)
+    if mode == "fp16":
+        w, x, gy = ol.round_to_half(w), ol.round_to_half(x), ol.round_to_half(gy)
+    M = MODES[mode]
+    dw, dx, dgy = dev(w, M), dev(x, M), dev(gy, M)
+    for accumulate, fill in ((False, 3.0), (True, 0.25)):
+        base = fill if accumulate else 0.0
+        y = dev(np.full((n_, m_), fill, np.float32), M)
+        gx = dev(np.full((n_, k_), fill, np.float32), M)
+        ctx.gemm(M, 0, 0, dw.data_ptr(), dx.data_ptr(), y.data_ptr(), m_, n_, k_, accumulate=accumulate, force_path=3)
+        ctx.gemm(M, 1, 0, dw.data_ptr(), dgy.data_ptr(), gx.data_ptr(), k_, n_, m_, accumulate=accumulate, force_path=3)
+        torch.cuda.synchronize()
+        assert ctx.status_poll() == 0
+        tol = TOL[mode] if mode == "fp16" else 1e-6
+        assert ol.rel_err(host(y).reshape(n_, m_), base + x.astype(np.float64) @ w.astype(np.float64)) <= tol
+        assert ol.rel_err(host(gx).reshape(n_, k_), base + gy.astype(np.float64) @ w.astype(np.float64).T) <= tol
+        # reduce: C {m, n2} (+)= A {m, k2} . B {n2, k2}^T over a long k2
+        n2, k2 = 300, 9001
+        a2 = (0.05 * rng.standard_normal((k2, m_))).astype(np.float32)
+        b2 = rng.uniform(-1, 1, (k2, n2)).astype(np.float32)
+        if mode == "fp16":
+            a2, b2 = ol.round_to_half(a2), ol.round_to_half(b2)
+        c2 = dev(np.full((n2, m_), fill, np.float32), M)
+        da2, db2 = dev(a2, M), dev(b2, M)
+        ctx.gemm(M, 0, 1, da2.data_ptr(), db2.data_ptr(), c2.data_ptr(), m_, n2, k2, accumulate=accumulate, force_path=3)
+        torch.cuda.synchronize()
+        assert ctx.status_poll() == 0
+        assert ol.rel_err(host(c2).reshape(n2, m_), base + b2.astype(np.float64).T @ a2.astype(np.float64)) <= tol
+    with pytest.raises(pb.B200Error):
+        ctx.gemm(M, 0, 0, dw.data_ptr(), dx.data_ptr(), y.data_ptr(), 64, 64, 64, force_path=3)
