@@ -199,11 +199,11 @@ int b200_gemm(b200_ctx *ctx, int mode, int trans_a, int trans_b, const void *A, 
   // kernel wins below roughly a tile's worth of work.
   // One tiny extent against large ones is HBM-bound.  In the fp32-grade modes the tensor-core
   // path would first pack the large operand into planes (three more passes over it): there the
-  // CUDA-core kernels that stream it once win (320-410 us against 675 us for the three products of
+  // CUDA-core kernels that stream it once win (255-335 us against 675 us for the three products of
   // a 10 x 1024 layer over 65536 items) and are exact fp32.  The single-pass modes need no
   // packing and stay on the tensor-core path where TMA's alignment rules admit the operands; where
   // they do not (ten rows of halves are 20 bytes) the alternative is the general CUDA-core kernel,
-  // which takes 5.8 ms for the reduce shape against 0.2 ms here.
+  // which takes 5.8 ms for the reduce shape against 0.12 ms here.
   if ((mode == B200_MODE_FP32_3XTF32 || mode == B200_MODE_FP32_3XFP16 || !eligible) && b200::gemm_skinny_eligible(g))
     return b200::gemm_skinny(ctx, g, s);
   const double macs = static_cast<double>(m) * n * k * groups * red;

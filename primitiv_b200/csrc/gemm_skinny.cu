@@ -29,6 +29,7 @@ template <typename T, uint32_t MP, uint32_t kCols>
 __global__ void __launch_bounds__(256) skinny_rows_kernel(const T *__restrict__ A, const T *__restrict__ B, T *C,
                                                           uint32_t m, uint32_t n, uint32_t k, u64 a_si, u64 a_sk,
                                                           int accumulate) {
+  constexpr uint32_t kDepth = 4;  // k-steps whose loads are in flight together (8 measured slower)
   extern __shared__ __align__(16) float As[];  // [k][MP], rows past m are zero
   for (uint32_t e = threadIdx.x; e < k * MP; e += blockDim.x) {
     const uint32_t kk = e / MP, i = e % MP;
@@ -43,16 +44,16 @@ __global__ void __launch_bounds__(256) skinny_rows_kernel(const T *__restrict__ 
     for (uint32_t c = 0; c < kCols; ++c)
 #pragma unroll
       for (uint32_t i = 0; i < MP; ++i) acc[c][i] = 0.f;
-    // four k-steps per pass: their loads are issued together (4 x kCols requests of 128 B in flight per warp)
-    for (uint32_t kk0 = lane; kk0 < k; kk0 += 128u) {
-      float b[4][kCols];
+    // kDepth k-steps per pass: their loads are issued together (kDepth x kCols requests of 128 B in flight per warp)
+    for (uint32_t kk0 = lane; kk0 < k; kk0 += 32u * kDepth) {
+      float b[kDepth][kCols];
 #pragma unroll
-      for (uint32_t u = 0; u < 4u; ++u)
+      for (uint32_t u = 0; u < kDepth; ++u)
 #pragma unroll
         for (uint32_t c = 0; c < kCols; ++c)
           b[u][c] = (kk0 + 32u * u < k && j0 + c < n) ? ld(B, (j0 + c) * k + kk0 + 32u * u) : 0.f;
 #pragma unroll
-      for (uint32_t u = 0; u < 4u; ++u) {
+      for (uint32_t u = 0; u < kDepth; ++u) {
         const uint32_t kk = kk0 + 32u * u < k ? kk0 + 32u * u : 0u;  // b is zero there
         const float4 *arow = reinterpret_cast<const float4 *>(As + kk * MP);
 #pragma unroll
@@ -95,6 +96,7 @@ template <typename T, uint32_t MP, uint32_t kCols>
 __global__ void __launch_bounds__(256) skinny_reduce_kernel(const T *__restrict__ A, const T *__restrict__ B,
                                                             float *__restrict__ partial, uint32_t m, uint32_t n,
                                                             uint32_t k, uint32_t slice_len) {
+  constexpr uint32_t kDepth = 4;  // k-steps whose loads are in flight together (8 measured slower)
   extern __shared__ __align__(16) float As[];  // [chunk][MP]
   const uint32_t chunk_cap = kSmemFloats / MP;
   const uint32_t k_lo = blockIdx.y * slice_len;
@@ -113,17 +115,17 @@ __global__ void __launch_bounds__(256) skinny_reduce_kernel(const T *__restrict_
       As[e] = i < m ? ld(A, static_cast<u64>(c0 + kk) * m + i) : 0.f;  // A stored m x k
     }
     __syncthreads();
-    for (uint32_t kk0 = 0; kk0 < len; kk0 += 4u) {
-      float b[4][kCols];
+    for (uint32_t kk0 = 0; kk0 < len; kk0 += kDepth) {
+      float b[kDepth][kCols];
 #pragma unroll
-      for (uint32_t u = 0; u < 4u; ++u)
+      for (uint32_t u = 0; u < kDepth; ++u)
 #pragma unroll
         for (uint32_t c = 0; c < kCols; ++c) {
           const u64 j = jbase + static_cast<u64>(c) * blockDim.x;
           b[u][c] = (kk0 + u < len && j < n) ? ld(B, static_cast<u64>(c0 + kk0 + u) * n + j) : 0.f;  // B stored n x k
         }
 #pragma unroll
-      for (uint32_t u = 0; u < 4u; ++u) {
+      for (uint32_t u = 0; u < kDepth; ++u) {
         const uint32_t kk = kk0 + u < len ? kk0 + u : 0u;  // b is zero there
         const float4 *arow = reinterpret_cast<const float4 *>(As + kk * MP);  // one address per warp: broadcast
 #pragma unroll
@@ -173,10 +175,9 @@ __global__ void __launch_bounds__(256) reduce_final_kernel(const float *__restri
 }
 
 // ---- outer: thread owns two rows, the CTA a strip of columns; A's k values sit in registers ----
-template <typename T, uint32_t KP>
-__global__ void __launch_bounds__(256) skinny_outer_kernel(const T *__restrict__ A, const T *__restrict__ B, T *C,
-                                                           uint32_t m, uint32_t n, uint32_t k, uint32_t strip,
-                                                           int accumulate) {
+template <typename T, uint32_t KP, bool accumulate>
+__global__ void __launch_bounds__(256, 4) skinny_outer_kernel(const T *__restrict__ A, const T *__restrict__ B, T *C,
+                                                              uint32_t m, uint32_t n, uint32_t k, uint32_t strip) {
   extern __shared__ __align__(16) float Bs[];  // [strip][KP], entries past k are zero
   const u64 j_lo = static_cast<u64>(blockIdx.y) * strip;
   const uint32_t cols = n - j_lo < strip ? static_cast<uint32_t>(n - j_lo) : strip;
@@ -251,18 +252,18 @@ static int skinny_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t s) {
     const uint32_t mp = padded(g.m);
     const u64 a_si = g.trans_a ? g.k : 1, a_sk = g.trans_a ? 1 : g.m;
     const size_t smem = static_cast<size_t>(mp) * g.k * sizeof(float);
-    const u64 col_groups = (static_cast<u64>(g.n) + 3) / 4;  // at most 4 columns per warp pass
+    const u64 col_groups = (static_cast<u64>(g.n) + 1) / 2;  // two columns per warp pass (four with mp == 4)
     const u64 want = (col_groups + 7) / 8, cap = static_cast<u64>(ctx->sm_count) * 4;
     const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
     if (mp == 4) skinny_rows_kernel<T, 4, 4><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, a_si, a_sk, g.accumulate);
-    else if (mp == 12) skinny_rows_kernel<T, 12, 4><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, a_si, a_sk, g.accumulate);
+    else if (mp == 12) skinny_rows_kernel<T, 12, 2><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, a_si, a_sk, g.accumulate);
     else skinny_rows_kernel<T, 20, 2><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, a_si, a_sk, g.accumulate);
     ++ctx->launches;
     return static_cast<int>(cudaGetLastError());
   }
   if (kind == kReduce) {
     const uint32_t mp = padded(g.m);
-    const uint32_t cols = mp == 20 ? 2u : 4u;
+    const uint32_t cols = mp == 4 ? 4u : 2u;
     const unsigned gx = static_cast<unsigned>((static_cast<u64>(g.n) + 256ull * cols - 1) / (256ull * cols));
     // about four CTAs per SM, slices of at least 64 k values
     u64 slices = (4ull * ctx->sm_count + gx - 1) / gx;
@@ -278,7 +279,7 @@ static int skinny_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t s) {
     const size_t smem = static_cast<size_t>(chunk) * mp * sizeof(float);
     float *pp = static_cast<float *>(partial);
     if (mp == 4) skinny_reduce_kernel<T, 4, 4><<<dim3(gx, gy), 256, smem, s>>>(A, B, pp, g.m, g.n, g.k, slice_len);
-    else if (mp == 12) skinny_reduce_kernel<T, 12, 4><<<dim3(gx, gy), 256, smem, s>>>(A, B, pp, g.m, g.n, g.k, slice_len);
+    else if (mp == 12) skinny_reduce_kernel<T, 12, 2><<<dim3(gx, gy), 256, smem, s>>>(A, B, pp, g.m, g.n, g.k, slice_len);
     else skinny_reduce_kernel<T, 20, 2><<<dim3(gx, gy), 256, smem, s>>>(A, B, pp, g.m, g.n, g.k, slice_len);
     reduce_final_kernel<T><<<static_cast<unsigned>((count + 31) / 32), dim3(32, 8), 0, s>>>(pp, C, count, gy, g.accumulate);
     ctx->launches += 2;
@@ -291,10 +292,14 @@ static int skinny_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t s) {
     const dim3 grid((g.m + 511u) / 512u, (g.n + strip - 1) / strip);
     if (grid.y > 65535u) return gemm_simt(ctx, g, s);
     const size_t smem = static_cast<size_t>(strip) * kp * sizeof(float);
-    if (kp == 4) skinny_outer_kernel<T, 4><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, strip, g.accumulate);
-    else if (kp == 8) skinny_outer_kernel<T, 8><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, strip, g.accumulate);
-    else if (kp == 12) skinny_outer_kernel<T, 12><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, strip, g.accumulate);
-    else skinny_outer_kernel<T, 16><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, strip, g.accumulate);
+#define B200_OUTER(KP)                                                                                   \
+  (g.accumulate ? skinny_outer_kernel<T, KP, true><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, strip) \
+                : skinny_outer_kernel<T, KP, false><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, strip))
+    if (kp == 4) B200_OUTER(4);
+    else if (kp == 8) B200_OUTER(8);
+    else if (kp == 12) B200_OUTER(12);
+    else B200_OUTER(16);
+#undef B200_OUTER
     ++ctx->launches;
     return static_cast<int>(cudaGetLastError());
   }
