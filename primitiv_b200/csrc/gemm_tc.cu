@@ -724,10 +724,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 for (uint32_t i = 0; i < 32u; ++i)
                   if (col0 + i < p.n) acc[j][i] *= row_scale * inv_scale_for(col_scale[col0 + i]);
               }
-              if (p.out_half)
-                store_cols<8>(static_cast<__half *>(p.C), base, p.m, p.n, col0, acc[j], p.accumulate != 0u);
-              else
-                store_cols<8>(static_cast<float *>(p.C), base, p.m, p.n, col0, acc[j], p.accumulate != 0u);
+              // the three-pass kinds always store fp32 (half storage is the single-pass fp16 kind)
+              store_cols<8>(static_cast<float *>(p.C), base, p.m, p.n, col0, acc[j], p.accumulate != 0u);
             }
           }
         }
