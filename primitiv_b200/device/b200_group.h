@@ -15,8 +15,9 @@
 // GPUs: the gradient of a broadcast operand (matmul_bw and the elementwise backward passes),
 // inplace_add of a minibatch into a tensor without one, batch_sum, and the backward of slice /
 // pick into an unbatched tensor.  Each GPU computes its partial sum into a scratch tensor; then
-// every GPU reads all partials over NVLink (plain peer loads) and adds them in GPU order, so
-// the replicas stay equal.  The batch-moving operations (batch_pick / slice / concat) copy
+// every GPU reads all partials over NVLink (plain peer loads) and adds them, in GPU order, straight
+// into its replica of the result, so the replicas stay equal bit for bit (large sums: each GPU
+// does this for one slice and the slices are then copied between the replicas).  The batch-moving operations (batch_pick / slice / concat) copy
 // items between GPUs as needed.  The host thread never blocks except for those copies and for
 // reads to the host.
 //
@@ -63,7 +64,7 @@ public:
   /** Blocks until every GPU has finished its queued work; throws if a kernel reported a timeout. */
   void synchronize();
 
-  /** Sums over GPUs performed so far (each is one kernel per GPU between two stream barriers). */
+  /** Sums over GPUs performed so far (each: kernels on every GPU between stream barriers, no host block). */
   std::uint64_t cross_gpu_sums() const { return cross_gpu_sums_; }
 
 private:
