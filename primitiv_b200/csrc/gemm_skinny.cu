@@ -26,7 +26,7 @@ __host__ __device__ inline uint32_t padded(uint32_t t) { return t <= 4 ? 4u : (t
 
 // ---- rows: each warp owns kCols columns of B and C; lanes stride over k ----
 template <typename T, uint32_t MP, uint32_t kCols>
-__global__ void __launch_bounds__(256) skinny_rows_kernel(const T *__restrict__ A, const T *__restrict__ B, T *C,
+__global__ void __launch_bounds__(256, MP <= 12 ? 4 : 2) skinny_rows_kernel(const T *__restrict__ A, const T *__restrict__ B, T *C,
                                                           uint32_t m, uint32_t n, uint32_t k, u64 a_si, u64 a_sk,
                                                           int accumulate) {
   constexpr uint32_t kDepth = 4;  // k-steps whose loads are in flight together (8 measured slower)
@@ -69,31 +69,48 @@ __global__ void __launch_bounds__(256) skinny_rows_kernel(const T *__restrict__ 
         }
       }
     }
-    // lanes hold partial sums over their k values: a butterfly leaves the total in every lane
+    // Lanes hold partial sums over their k values.  Three halving steps (lane bits 4, 3, 2): a
+    // lane passes the half of its values that its partner keeps and adds what it receives, so
+    // V values cost V/2 + V/4 + V/8 shuffles instead of 3 V; the V/8 values left are summed over
+    // lane bits 1 and 0 the plain way.  The order of additions is fixed.
+    constexpr uint32_t V = kCols * MP;  // 16, 24 or 40: a multiple of 8
+    float *v = &acc[0][0];
 #pragma unroll
-    for (uint32_t c = 0; c < kCols; ++c)
+    for (uint32_t step = 0; step < 3u; ++step) {
+      const uint32_t off = 16u >> step, half = V >> (step + 1u);
+      const bool upper = (lane & off) != 0u;
 #pragma unroll
-      for (uint32_t i = 0; i < MP; ++i)
+      for (uint32_t i = 0; i < half; ++i) {
+        const float send = upper ? v[i] : v[i + half];
+        const float keep = upper ? v[i + half] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    }
+    constexpr uint32_t R = V / 8u;
 #pragma unroll
-        for (uint32_t off = 16; off > 0; off >>= 1) acc[c][i] += __shfl_xor_sync(0xffffffffu, acc[c][i], off);
-    // every lane holds every total: element e of the kCols x MP block is written by lane e mod 32
-    // (static register indices only)
+    for (uint32_t i = 0; i < R; ++i) {
+      v[i] += __shfl_xor_sync(0xffffffffu, v[i], 2u);
+      v[i] += __shfl_xor_sync(0xffffffffu, v[i], 1u);
+    }
+    // which values this lane ended up with follows from the halves it kept
+    const uint32_t first = ((lane >> 4) & 1u) * (V / 2u) + ((lane >> 3) & 1u) * (V / 4u) + ((lane >> 2) & 1u) * R;
+    if ((lane & 3u) == 0u) {
 #pragma unroll
-    for (uint32_t c = 0; c < kCols; ++c)
-#pragma unroll
-      for (uint32_t i = 0; i < MP; ++i) {
-        if (lane == ((c * MP + i) & 31u) && i < m && j0 + c < n) {
+      for (uint32_t t = 0; t < R; ++t) {
+        const uint32_t e = first + t, c = e / MP, i = e % MP;
+        if (i < m && j0 + c < n) {
           const u64 at = (j0 + c) * m + i;
-          st(C, at, (accumulate ? ld(C, at) : 0.f) + acc[c][i]);
+          st(C, at, (accumulate ? ld(C, at) : 0.f) + v[t]);
         }
       }
+    }
   }
 }
 
 // ---- reduce: thread owns kCols columns j (coalesced along j), the CTA owns a slice of k ----
 // Writes the slice's partial C to partial[slice][j * m + i]; reduce_final_kernel adds the slices in order.
 template <typename T, uint32_t MP, uint32_t kCols>
-__global__ void __launch_bounds__(256) skinny_reduce_kernel(const T *__restrict__ A, const T *__restrict__ B,
+__global__ void __launch_bounds__(256, MP <= 12 ? 4 : 2) skinny_reduce_kernel(const T *__restrict__ A, const T *__restrict__ B,
                                                             float *__restrict__ partial, uint32_t m, uint32_t n,
                                                             uint32_t k, uint32_t slice_len) {
   constexpr uint32_t kDepth = 4;  // k-steps whose loads are in flight together (8 measured slower)
