@@ -10,17 +10,28 @@ Shape({4096,4096}, batch 8) ~ N(0, 0.02), upstream gradient N(0,1), seeded synth
 data.  With N GPUs every rank holds a full batch-8 shard of its own (weak scaling; the
 products of different batch elements are independent, so the data path has no collective).
 
-`--workload batched_square_3xfp16` runs the default shapes in the opt-in fp32-grade mode on the fp16
-pipe.  `--workload lstm_steps` / `--workload mlp_step` run the graph-level programs of the other named
-configurations (1 GPU).  `--workload batched_square_tf32` runs the same shapes in the single-pass TF32 fast mode, and
-`--workload fp16_broadcast` runs the half-precision workload instead: A {8192,8192}
-broadcast, B {8192,2048} x 32, fp32 accumulation, gA summed over the batch (and, with
-N GPUs, all-reduced over NCCL: B, gy, y, gB are batch-sharded 32 per GPU, A is replicated).
-
 Prints ONE JSON line on rank 0.  `value` is algorithmic GFLOP/s (2*m*n*k per product, three
 products per step) over all ranks with operands resident in HBM; `e2e` is the same metric
-through the host-buffer entry points of the C ABI with the host<->device copies inside the
-timed region.
+through the fused host-buffer entry point of the C ABI (b200_matmul_fw_bw_host) with the
+host<->device copies inside the timed region.
+
+Beside the headline the same line carries, at every N:
+  collective_check   untimed parity of the path's one exchange step: the plumbing workload
+                     (W {256,256} broadcast, X {256,64} x 16, gradients pre-filled 0.5) cut over the
+                     N ranks; y and gX gathered, gW all-reduced over NCCL, all compared with an fp64
+                     product computed on the host, and gW compared bit for bit between the ranks;
+  secondary          two timed legs whose backward has that exchange step: `fp16_broadcast`
+                     (A {8192,8192} replicated, B {8192,2048} x 32 per GPU, half storage; the
+                     128 MiB gA partial is all-reduced) and `mlp_products` (the nine products of a
+                     784-1024-1024-10 perceptron step over 65536 items per GPU, 3xTF32; three
+                     weight-gradient all-reduces);
+  tf32_cublas_measured / gpu_comparator   context figures (rank 0): the TF32 rate of the vendor
+                     GEMM on this GPU, and the reference's own CUDA / CUDA16 devices on the same
+                     workloads when they have been built (own process, never linked here).
+
+`--workload batched_square_3xfp16 | batched_square_tf32 | fp16_broadcast` make another workload the
+headline; `--workload lstm_steps | mlp_step` run the graph-level programs of the other named
+configurations (1 GPU).
 
 --impl reference times the reference's own CPU implementation of the path (its Naive
 device compiled from its sources into oracle/_ref, else the C restatement under oracle/)
@@ -38,6 +49,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "matmul_fw_bw_gflops"
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_tc_kernel launch on the batch-2 square case
+# (profiles/gemm_tc_kernel_3xtf32_batch2_ncu_full.md): 1.41 GB overwriting, 1.55 GB accumulating
+NCU_DRAM_BYTES_PER_LAUNCH_BATCH2 = 1.48e9
 
 
 class Workload:
@@ -258,23 +272,79 @@ def run_reference(args, wl, rank):
     print(json.dumps(line), flush=True)
 
 
-def run_ours(args, wl, rank, local_rank, world):
-    import torch
-    import primitiv_b200 as pb
-    from primitiv_b200.sharding import GpuBackend, ShardedMatmul, nccl_all_reduce
+class Rig:
+    """What every leg needs: the context, the process group and the timing rules (barrier +
+    synchronize on both sides, CUDA events on the launching stream, max over ranks)."""
 
-    torch.cuda.set_device(local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    ctx = pb.Context(local_rank)
-    mode = {"FP16": pb.MODE_FP16, "TF32": pb.MODE_TF32, "3xFP16": pb.MODE_FP32_3XFP16}.get(wl.mode_name, pb.MODE_FP32_3XTF32)
+    def __init__(self, rank, local_rank, world):
+        import torch
+        import primitiv_b200 as pb
+        self.torch, self.pb = torch, pb
+        self.rank, self.local_rank, self.world = rank, local_rank, world
+        torch.cuda.set_device(local_rank)
+        self.dist = None
+        if world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            self.dist = dist
+        self.ctx = pb.Context(local_rank)
+
+    def mode(self, name):
+        pb = self.pb
+        return {"FP16": pb.MODE_FP16, "TF32": pb.MODE_TF32, "3xFP16": pb.MODE_FP32_3XFP16}.get(name, pb.MODE_FP32_3XTF32)
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, values):
+        if self.dist is None:
+            return [float(v) for v in values]
+        t = self.torch.tensor(values, device="cuda", dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(v) for v in t]
+
+    def sharded(self, mode):
+        from primitiv_b200.sharding import GpuBackend, ShardedMatmul, nccl_all_reduce
+        return ShardedMatmul(GpuBackend(self.ctx, mode), self.world, self.rank, nccl_all_reduce)
+
+    def timed(self, step, steps, warmup, sm):
+        """W warm-up steps, then exactly K timed steps.  -> dict(ms, prof, launches, collectives, clocks)"""
+        torch, ctx = self.torch, self.ctx
+        for _ in range(warmup):
+            step()
+        self.barrier()
+        sampler = ClockSampler(self.local_rank)
+        sampler.start()
+        ctx.profile_read()
+        ctx.profile_enable(True)
+        launches0, coll0 = ctx.launch_count(), sm.collectives
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        self.barrier()
+        ms = e0.elapsed_time(e1)
+        ctx.profile_enable(False)
+        prof = ctx.profile_read()
+        sampler.stop_flag = True
+        sampler.join(timeout=3)
+        assert ctx.status_poll() == 0, "a kernel reported a bounded-wait timeout"
+        return {"ms": self.max_over_ranks([ms])[0], "prof": prof, "launches": ctx.launch_count() - launches0,
+                "collectives": sm.collectives - coll0, "clocks": sampler.summary()}
+
+
+def workload_tensors(rig, wl):
+    """This rank's shard of the workload: seeded synthetic tensors, a replicated operand the same on every rank."""
+    torch = rig.torch
     dt = torch.float16 if wl.half else torch.float32
     g = torch.Generator(device="cuda")
-    g.manual_seed(1234 + rank)
+    g.manual_seed(1234 + rig.rank)
     shared = torch.Generator(device="cuda")
-    shared.manual_seed(99)            # a replicated operand is the same on every rank
+    shared.manual_seed(99)
     na, nb, ny = wl.di * wl.dj * wl.ba, wl.dj * wl.dk * wl.bb, wl.di * wl.dk * wl.bs
     a = (torch.randn(na, generator=(shared if wl.ba == 1 else g), device="cuda") * wl.sa).to(dt)
     b = (torch.randn(nb, generator=g, device="cuda") * wl.sb).to(dt)
@@ -282,131 +352,342 @@ def run_ours(args, wl, rank, local_rank, world):
     y = torch.empty(ny, device="cuda", dtype=dt)
     ga = torch.zeros(na, device="cuda", dtype=dt)
     gb = torch.zeros(nb, device="cuda", dtype=dt)
+    return a, b, gy, y, ga, gb
+
+
+def run_workload(rig, wl, steps, warmup):
+    """Device-resident leg of one Workload.  -> (result of Rig.timed, the operand tensors)"""
+    a, b, gy, y, ga, gb = workload_tensors(rig, wl)
     # global batch sizes as the sharded orchestration sees them (1 = replicated operand)
-    gba = 1 if wl.ba == 1 else wl.ba * world
-    gbb = 1 if wl.bb == 1 else wl.bb * world
-    sm = ShardedMatmul(GpuBackend(ctx, mode), world, rank, nccl_all_reduce)
+    gba = 1 if wl.ba == 1 else wl.ba * rig.world
+    gbb = 1 if wl.bb == 1 else wl.bb * rig.world
+    sm = rig.sharded(rig.mode(wl.mode_name))
 
     def step():
         sm.forward(a, b, y, wl.di, wl.dj, wl.dk, gba, gbb)
         sm.backward(a, b, gy, ga, gb, wl.di, wl.dj, wl.dk, gba, gbb)
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
+    return rig.timed(step, steps, warmup, sm), (a, b, gy)
 
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    ctx.profile_read()
-    ctx.profile_enable(True)
-    launches0 = ctx.launch_count()
-    coll0 = sm.collectives
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    ctx.profile_enable(False)
-    prof = ctx.profile_read()
-    launches = ctx.launch_count() - launches0
-    collectives = sm.collectives - coll0
-    sampler.stop_flag = True
-    sampler.join(timeout=3)
-    assert ctx.status_poll() == 0, "a kernel reported a bounded-wait timeout"
 
-    # ---- end to end through the host-buffer entry points (pinned host memory) ----
+def tensor_roofline(wl, res, steps, peaks):
+    tc_ms, tc_n = res["prof"]["gemm_tc"]
+    issued_flops_per_launch = float(wl.passes) * wl.flops * steps / max(tc_n, 1)
+    tc_avg_ms = tc_ms / max(tc_n, 1)
+    achieved = issued_flops_per_launch / (tc_avg_ms * 1e-3) / 1e12 if tc_n else 0.0
+    div = 1.0 if (wl.half or wl.mode_name == "3xFP16") else 2.0     # TF32 runs at half the 16-bit rate
+    sustained, burst = peaks["bf16_sustained"] / div, peaks["bf16_burst"] / div
+    return achieved, sustained, burst, tc_ms, tc_n, div
+
+
+def collective_check(rig):
+    """Untimed parity of the exchange step on the plumbing workload: W {256,256} broadcast, X {256,64} x 16
+    U(-1,1), gy N(0,1), gradients pre-filled 0.5, the batch cut over the ranks.  The fp64 products are
+    computed here with numpy (the check must not depend on where the test oracle is built)."""
+    import numpy as np
+    from primitiv_b200.sharding import shard_range
+    torch, dist, world, rank = rig.torch, rig.dist, rig.world, rig.rank
+    di, dj, dk, bb = 256, 256, 64, 16
+    rng = np.random.default_rng(0)
+    w = rng.uniform(-1, 1, di * dj).astype(np.float32)
+    x = rng.uniform(-1, 1, dj * dk * bb).astype(np.float32)
+    gy = rng.standard_normal(di * dk * bb).astype(np.float32)
+    first, count = shard_range(bb, rank, world)
+    cu = lambda v: torch.from_numpy(np.ascontiguousarray(v)).cuda()
+    lw, lx, lgy = cu(w), cu(x[first * dj * dk:(first + count) * dj * dk]), cu(gy[first * di * dk:(first + count) * di * dk])
+    y = torch.empty(di * dk * count, device="cuda")
+    gw = torch.full((di * dj,), 0.5, device="cuda")
+    gx = torch.full((dj * dk * count,), 0.5, device="cuda")
+    sm = rig.sharded(rig.pb.MODE_FP32_3XTF32)
+    rig.ctx.set_path_policy(2)            # the tensor-core kernel, although the problem is small
+    try:
+        sm.forward(lw, lx, y, di, dj, dk, 1, bb)
+        sm.backward(lw, lx, lgy, gw, gx, di, dj, dk, 1, bb)
+    finally:
+        rig.ctx.set_path_policy(0)
+    torch.cuda.synchronize()
+    assert rig.ctx.status_poll() == 0
+
+    def gather(t):
+        if dist is None:
+            return [t]
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t)
+        return parts
+
+    ys, gxs, gws = gather(y), gather(gx), gather(gw)
+    if rank != 0:
+        return None
+    W = w.astype(np.float64).reshape(dj, di).T                      # column-major {di, dj}
+    X = x.astype(np.float64).reshape(bb * dk, dj).T                 # {dj, dk*bb}: the batches are adjacent columns
+    G = gy.astype(np.float64).reshape(bb * dk, di).T                # {di, dk*bb}
+    flat = lambda m: np.ascontiguousarray(m.T).reshape(-1)
+    rel = lambda got, ref: float(np.linalg.norm(got.astype(np.float64) - ref) / np.linalg.norm(ref))
+    errs = {"y": rel(torch.cat(ys).cpu().numpy(), flat(W @ X)),
+            "gW": rel(gws[0].cpu().numpy(), flat(0.5 + G @ X.T)),
+            "gX": rel(torch.cat(gxs).cpu().numpy(), flat(0.5 + W.T @ G))}
+    return {"workload": "W{256,256} broadcast . X{256,64} x 16, gradients pre-filled 0.5, 3xTF32, batch cut over the ranks",
+            "nranks": world, "rel_err": max(errs.values()), "rel_err_by_tensor": errs, "tolerance": 1e-5,
+            "collectives": sm.collectives,
+            "replicas_bit_identical": all(bool(torch.equal(gws[0], g)) for g in gws[1:])}
+
+
+def leg_fp16_broadcast(rig, steps, warmup, peaks):
+    """Secondary leg: the half-precision workload with a replicated A (its gradient partial is all-reduced)."""
+    wl = Workload("fp16_broadcast", 0)
+    res, _ = run_workload(rig, wl, steps, warmup)
+    rig.torch.cuda.empty_cache()
+    ms = res["ms"] / steps
+    achieved, sustained, burst, tc_ms, tc_n, _ = tensor_roofline(wl, res, steps, peaks)
+    return {"workload": wl.label(), "value": wl.flops * rig.world / (ms * 1e-3) / 1e9, "unit": "GFLOP/s",
+            "ms_per_step": ms, "steps": steps, "warmup": warmup, "dtype": wl.dtype, "mode": wl.mode_name,
+            "batch_per_gpu": wl.bs, "scaling": "weak",
+            "collectives_per_step": res["collectives"] / steps,
+            "collective": "all-reduce (sum) of the 128 MiB gA partial over NCCL, started before and waited for "
+                          "after the local gB product" if rig.world > 1 else "none at 1 GPU",
+            "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (kind::f16, cta pair)", "achieved": achieved,
+                         "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst,
+                         "frac_of_sustained_peak": achieved / sustained, "traffic": None,
+                         "note": "tensor-issued = algorithmic FLOP / mean CUDA-event duration of %d launches; peak = %s "
+                                 "bf16 burst (the leg lasts a fraction of a second)" % (tc_n, peaks["source"]),
+                         "kernel_ms_per_step": tc_ms / steps},
+            "gpu_launches": int(res["launches"]), "clocks": res["clocks"]}
+
+
+MLP_LAYERS = ((1024, 784), (1024, 1024), (10, 1024))     # (rows, cols) of W1, W2, W3
+MLP_BATCH = 65536
+
+
+def leg_mlp_products(rig, steps, warmup, peaks):
+    """Secondary leg: the nine products of one 784-1024-1024-10 perceptron step (three forward, three
+    weight gradients summed over the batch and all-reduced, three input gradients), 65536 items per
+    GPU, fp32 via 3xTF32.  Weights Xavier-uniform and replicated, inputs U(0,1), upstream N(0,1)."""
+    torch = rig.torch
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4321 + rig.rank)
+    shared = torch.Generator(device="cuda")
+    shared.manual_seed(77)
+    B = MLP_BATCH
+    ws, gws, acts, gacts = [], [], [], []
+    acts.append(torch.rand(MLP_LAYERS[0][1] * B, generator=g, device="cuda"))
+    for rows, cols in MLP_LAYERS:
+        lim = (6.0 / (rows + cols)) ** 0.5
+        ws.append((torch.rand(rows * cols, generator=shared, device="cuda") * 2 - 1) * lim)
+        gws.append(torch.zeros(rows * cols, device="cuda"))
+        acts.append(torch.empty(rows * B, device="cuda"))
+    gacts = [torch.zeros(a.numel(), device="cuda") for a in acts]
+    gacts[-1] = torch.randn(MLP_LAYERS[-1][0] * B, generator=g, device="cuda")
+    sm = rig.sharded(rig.pb.MODE_FP32_3XTF32)
+    gb = B * rig.world
+
+    def step():
+        for l, (rows, cols) in enumerate(MLP_LAYERS):
+            sm.forward(ws[l], acts[l], acts[l + 1], rows, cols, 1, 1, gb)
+        for l in range(len(MLP_LAYERS) - 1, -1, -1):
+            rows, cols = MLP_LAYERS[l]
+            sm.backward(ws[l], acts[l], gacts[l + 1], gws[l], gacts[l], rows, cols, 1, 1, gb)
+
+    res = rig.timed(step, steps, warmup, sm)
+    same = True
+    if rig.dist is not None:      # replicas of a weight gradient hold the same bits on every rank
+        parts = [torch.empty_like(gws[0]) for _ in range(rig.world)]
+        rig.dist.all_gather(parts, gws[0])
+        same = all(bool(torch.equal(parts[0], p)) for p in parts[1:])
+    del ws, gws, acts, gacts
+    torch.cuda.empty_cache()
+    flops = 3 * sum(2 * r * c * B for r, c in MLP_LAYERS)
+    tc_flops = 3 * sum(2 * r * c * B for r, c in MLP_LAYERS[:2])       # the 10-row layer runs on CUDA cores
+    ms = res["ms"] / steps
+    tc_ms, tc_n = res["prof"]["gemm_tc"]
+    achieved = 3.0 * tc_flops * steps / (tc_ms * 1e-3) / 1e12 if tc_ms else 0.0
+    burst = peaks["bf16_burst"] / 2.0
+    kinds = {k: {"ms_per_step": v[0] / steps, "launches_per_step": v[1] / steps} for k, v in res["prof"].items()}
+    return {"workload": "mlp_784_1024_1024_10_batch%d_per_gpu_nine_products_fp32_3xtf32" % B, "value": flops * rig.world / (ms * 1e-3) / 1e9,
+            "unit": "GFLOP/s", "ms_per_step": ms, "steps": steps, "warmup": warmup, "mode": "3xTF32",
+            "dtype": "tf32x3 (fp32 storage, fp32 accumulate)", "batch_per_gpu": B, "scaling": "weak",
+            "collectives_per_step": res["collectives"] / steps,
+            "collective": "all-reduce (sum) of gW1, gW2, gW3 partials (3.2 MB, 4.2 MB, 41 kB) over NCCL" if rig.world > 1 else "none at 1 GPU",
+            "replicas_bit_identical": same,
+            "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (3xTF32) over the two 1024-row layers", "achieved": achieved,
+                         "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst, "traffic": None,
+                         "note": "tensor-issued FLOP (3 passes) of the six tensor-core products / their summed CUDA-event "
+                                 "time; the 10-row layer's three products are HBM-bound CUDA-core kernels (gemm_simt row)",
+                         "device_ms_by_kernel_kind": kinds},
+            "gpu_launches": int(res["launches"]), "clocks": res["clocks"]}
+
+
+def tf32_cublas_measured(rig):
+    """TF32 rate of the vendor GEMM on this GPU, measured the way MEASURED_PEAKS.json measures bf16
+    (torch.matmul 8192^3, best of 10 = burst; back to back for a second = sustained).  A measurement
+    aid beside the roofline, never on the product path."""
+    torch = rig.torch
+    n = 8192
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn(n, n, device="cuda")
+        b = torch.randn(n, n, device="cuda")
+        c = torch.empty(n, n, device="cuda")
+        for _ in range(3):
+            torch.matmul(a, b, out=c)
+        best = 1e9
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(a, b, out=c)
+            e1.record()
+            e1.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        reps = max(10, int(1000.0 / best))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            torch.matmul(a, b, out=c)
+        e1.record()
+        e1.synchronize()
+        sustained_ms = e0.elapsed_time(e1) / reps
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    del a, b, c
+    torch.cuda.empty_cache()
+    fl = 2.0 * n ** 3
+    return {"burst_tflops": fl / (best * 1e-3) / 1e12, "sustained_tflops": fl / (sustained_ms * 1e-3) / 1e12,
+            "how": "torch.matmul fp32 with TF32 allowed, 8192^3: best of 10 (burst), %d back to back (sustained)" % reps}
+
+
+def gpu_comparator(wl_names):
+    """The reference's own GPU devices (devices::CUDA: cublasSgemm / SgemmBatched, primitiv/devices/cuda/ops/
+    matmul.cu:26-138; devices::CUDA16: cublasHgemm, cuda16/ops/matmul.cu:46-266) on the same workloads, timed
+    with CUDA events in a process of their own.  Built by `make -C oracle ref_cuda` where the reference tree
+    is mounted; the binary travels under baseline/_ref/ and is never linked into this library."""
+    exe = os.path.join(ROOT, "baseline", "_ref", "cuda", "ref_cuda_matmul")
+    if not os.path.exists(exe):
+        return {"unavailable": "baseline/_ref/cuda/ref_cuda_matmul is not built (make -C oracle ref_cuda, needs the reference tree)"}
+    out = {}
+    for name in wl_names:
+        try:
+            r = subprocess.run([exe, name, "5", "2"], capture_output=True, text=True, timeout=600)
+            if r.returncode != 0:
+                out[name] = {"unavailable": "exit %d: %s" % (r.returncode, (r.stderr or r.stdout).strip()[-300:])}
+            else:
+                out[name] = json.loads(r.stdout.strip().splitlines()[-1])
+        except Exception as e:      # noqa: BLE001 -- a comparator that cannot run is reported, not fatal
+            out[name] = {"unavailable": repr(e)[:300]}
+    return out
+
+
+def run_ours(args, wl, rank, local_rank, world):
+    rig = Rig(rank, local_rank, world)
+    peaks = measured_peaks()
+    check = collective_check(rig)
+    res, (a, b, gy) = run_workload(rig, wl, args.steps, args.warmup)
+
+    # ---- end to end through the host-buffer entry point (pinned host memory) ----
     e2e = None
     if not args.skip_e2e:
-        e2e = run_e2e(args, wl, ctx, mode, a, b, gy, barrier, torch)
-    if dist is not None:
-        t = torch.tensor([ms, e2e["ms"] if e2e else 0.0], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t[0])
-        if e2e:
-            e2e["ms"] = float(t[1])
+        e2e = run_e2e(args, wl, rig, a, b, gy)
+        e2e["ms"] = rig.max_over_ranks([e2e["ms"]])[0]
+    del a, b, gy
+    rig.torch.cuda.empty_cache()
+    rig.ctx.pool_release_cached()
+
+    secondary = {}
+    if not args.skip_secondary:
+        if wl.name != "fp16_broadcast":
+            secondary["fp16_broadcast"] = leg_fp16_broadcast(rig, args.secondary_steps, 3, peaks)
+            rig.ctx.pool_release_cached()
+        secondary["mlp_products"] = leg_mlp_products(rig, args.secondary_steps, 3, peaks)
+        rig.ctx.pool_release_cached()
+    extras = {}
+    if rank == 0 and not args.skip_cpu:
+        extras["tf32_cublas_measured"] = tf32_cublas_measured(rig)
+    rig.barrier()
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        extras["gpu_comparator"] = gpu_comparator(["batched_square", "fp16_broadcast"])
     if rank == 0:
-        emit(args, wl, world, ms, prof, launches, sampler, e2e, collectives)
-    if dist is not None:
-        dist.destroy_process_group()
+        emit(args, wl, world, res, e2e, peaks, check, secondary, extras)
+    if rig.dist is not None:
+        rig.barrier()
+        rig.dist.destroy_process_group()
 
 
-def run_e2e(args, wl, ctx, mode, a, b, gy, barrier, torch):
-    """Each rank pushes its own shard through b200_matmul_{fw,bw}_host (no collective on this leg)."""
+def run_e2e(args, wl, rig, a, b, gy):
+    """Each rank pushes its own shard through b200_matmul_fw_bw_host (no collective on this leg): a, b and
+    gy go up once, y, ga and gb come down; the gradients start from zeros (the workload's definition), so
+    the entry point is told so and does not upload them."""
+    torch, ctx = rig.torch, rig.ctx
+    mode = rig.mode(wl.mode_name)
     P = lambda t: t.data_ptr()
-    e2e_steps = max(1, min(args.steps, 3))
+    e2e_steps = max(1, min(args.steps, 5))
     hb = lambda src: src.cpu().pin_memory()
     ha, hbm, hgy = hb(a), hb(b), hb(gy)
     hy = torch.empty(gy.numel(), dtype=gy.dtype).pin_memory()
-    hga = torch.zeros(a.numel(), dtype=a.dtype).pin_memory()
-    hgb = torch.zeros(b.numel(), dtype=b.dtype).pin_memory()
+    hga = torch.empty(a.numel(), dtype=a.dtype).pin_memory()
+    hgb = torch.empty(b.numel(), dtype=b.dtype).pin_memory()
     dims = (wl.di, wl.dj, wl.dk, wl.ba, wl.bb)
 
     def e2e_step():
-        ctx.matmul_fw_host(mode, P(ha), P(hbm), P(hy), *dims)
-        ctx.matmul_bw_host(mode, P(ha), P(hbm), P(hgy), P(hga), P(hgb), *dims)
-        return float(hga[0])  # the step's result is read on the host
+        ctx.matmul_fw_bw_host(mode, P(ha), P(hbm), P(hgy), P(hy), P(hga), P(hgb), *dims,
+                              accumulate_a=False, accumulate_b=False)
+        return float(hga[0]) + float(hy[0])  # the step's results are read on the host
 
-    e2e_step()
-    barrier()
+    for _ in range(2):
+        e2e_step()
+    rig.barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
     for _ in range(e2e_steps):
         e2e_step()
     f1.record()
-    barrier()
+    rig.barrier()
     ba, bb_, by = a.numel() * wl.elem, b.numel() * wl.elem, gy.numel() * wl.elem
     return {"ms": f0.elapsed_time(f1), "steps": e2e_steps,
-            "h2d": (ba + bb_) + (ba + bb_ + by + ba + bb_),   # fw: a, b;  bw: a, b, gy and the gradients added to
-            "d2h": by + ba + bb_}                              # y; ga, gb
+            "h2d": ba + bb_ + by,       # a, b, gy: once each
+            "d2h": by + ba + bb_}       # y; ga, gb
 
 
-def emit(args, wl, world, ms, prof, launches, sampler, e2e, collectives):
-    peaks = measured_peaks()
-    ms_per_step = ms / args.steps
+def emit(args, wl, world, res, e2e, peaks, check, secondary, extras):
+    ms_per_step = res["ms"] / args.steps
     value = wl.flops * world / (ms_per_step * 1e-3) / 1e9
-    tc_ms, tc_n = prof["gemm_tc"]
-    issued_flops_per_launch = float(wl.passes) * wl.flops * args.steps / max(tc_n, 1)
-    tc_avg_ms = tc_ms / max(tc_n, 1)
-    achieved = issued_flops_per_launch / (tc_avg_ms * 1e-3) / 1e12 if tc_n else 0.0
-    div = 1.0 if (wl.half or wl.mode_name == "3xFP16") else 2.0     # TF32 runs at half the 16-bit rate
-    peak, burst = peaks["bf16_sustained"] / div, peaks["bf16_burst"] / div
-    # DRAM bytes of one gemm_tc_kernel launch: ncu capture of the batch-2 square case (1.48 GB, mean of
-    # an overwriting and an accumulating launch, see profiles/), scaled by the batch (independent
-    # products, traffic grows in proportion)
-    traffic = 1.48e9 * wl.bs / 2.0 if wl.name == "batched_square" else None
+    achieved, sustained, burst, tc_ms, tc_n, div = tensor_roofline(wl, res, args.steps, peaks)
+    # DRAM bytes of one gemm_tc_kernel launch: ncu capture of the batch-2 square case (see profiles/),
+    # mean of an overwriting and an accumulating launch, scaled by the batch (independent products:
+    # traffic grows in proportion)
+    traffic = NCU_DRAM_BYTES_PER_LAUNCH_BATCH2 * wl.bs / 2.0 if wl.name == "batched_square" else None
     line = {
         "metric": METRIC, "value": value, "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.config(world),
         "roofline": {
             "bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05, cta pair)", "achieved": achieved,
-            "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
-            "frac_of_burst_peak": achieved / burst,
+            "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst, "traffic": traffic,
+            "frac_of_sustained_peak": achieved / sustained,
             "note": ("achieved = tensor-issued FLOP/s (%d tensor-core pass(es) x algorithmic 2mnk) / mean "
-                     "CUDA-event duration of %d launches; peak = %s bf16 sustained%s; the timed region is a "
-                     "fraction of a second, so the burst figure %.0f is given beside it%s"
+                     "CUDA-event duration of %d launches; peak = %s bf16 burst%s (the timed region is a "
+                     "fraction of a second); the sustained figure is %.0f%s"
                      % (wl.passes, tc_n, peaks["source"],
-                        "" if div == 1.0 else " / 2 (TF32 runs at half the 16-bit rate)", burst,
+                        "" if div == 1.0 else " / 2 (TF32 runs at half the 16-bit rate)", sustained,
                         "; traffic = ncu dram bytes of the batch-2 capture scaled to this batch" if traffic else "")),
             "algorithmic_tflops_in_kernel": achieved / wl.passes,
-            "kernel_ms_per_step": tc_ms / args.steps, "pack_ms_per_step": prof["pack"][0] / args.steps,
+            "kernel_ms_per_step": tc_ms / args.steps, "pack_ms_per_step": res["prof"]["pack"][0] / args.steps,
         },
-        "gpu_launches": int(launches),
-        "collectives_per_step": collectives / max(args.steps, 1),
-        "clocks": sampler.summary(),
+        "gpu_launches": int(res["launches"]),
+        "collectives_per_step": res["collectives"] / max(args.steps, 1),
+        "clocks": res["clocks"],
     }
     if e2e:
         per = e2e["ms"] / e2e["steps"]
         line["e2e"] = {"value": wl.flops * world / (per * 1e-3) / 1e9, "unit": "GFLOP/s",
                        "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
-                       "steps": e2e["steps"], "ms_per_step": per}
+                       "steps": e2e["steps"], "ms_per_step": per,
+                       "entry_point": "b200_matmul_fw_bw_host (pinned host buffers; a, b, gy up once, y, ga, gb down)"}
+    if check is not None:
+        line["collective_check"] = check
+    if secondary:
+        line["secondary"] = secondary
+    line.update(extras)
+    if "tf32_cublas_measured" in extras and div == 2.0:
+        line["roofline"]["frac_of_cublas_tf32_burst"] = achieved / extras["tf32_cublas_measured"]["burst_tflops"]
     if world == 1 and not args.skip_cpu:
         t, kind, cores = cpu_sample(wl)
         line["cpu_baseline"] = {"value": wl.sample_flops / t / 1e9, "unit": "GFLOP/s", "cores": cores,
@@ -478,6 +759,8 @@ def main():
                     help="batch elements per GPU (default: the workload's own, 8 / 32; smaller values are for "
                          "profiler captures and show in config.workload)")
     ap.add_argument("--skip-e2e", action="store_true", help="leave out the host-buffer leg (profiler captures)")
+    ap.add_argument("--skip-secondary", action="store_true", help="leave out the secondary legs (profiler captures)")
+    ap.add_argument("--secondary-steps", type=int, default=8, help="timed steps of each secondary leg")
     ap.add_argument("--skip-cpu", action="store_true", help="leave out the CPU baseline leg (profiler captures)")
     args = ap.parse_args()
     if args.workload in GRAPH_PROGRAMS:

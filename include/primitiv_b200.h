@@ -17,6 +17,13 @@
  *     stream, which is what the reference CUDA device uses for every launch.
  *   - Calls are asynchronous with respect to the host unless stated otherwise.
  *   - One host thread at a time per context (the contract of primitiv::Device).
+ *   - One stream per context at a time.  The pool hands a freed block to the next request
+ *     without waiting for the GPU: reuse is safe because the next user's work is queued on the
+ *     same stream, behind the last reader.  The matrix product frees its packing and split-k
+ *     scratch this way right after its launch.  A caller that moves a context from one stream
+ *     to another must order the two itself (an event, or a synchronisation) at the switch;
+ *     two streams used in alternation on one context race on recycled scratch.  (The reference
+ *     device works on the legacy default stream only, primitiv/devices/cuda/ops/matmul.cu.)
  *   - There is no CPU fallback: if no sm_100 GPU is present, context creation fails.
  */
 #ifndef PRIMITIV_B200_H_
@@ -68,9 +75,18 @@ B200_API int b200_ctx_create(int device_id, b200_ctx **ctx);
 B200_API int b200_ctx_destroy(b200_ctx *ctx);
 B200_API int b200_ctx_device(const b200_ctx *ctx, int *device_id, int *sm_count);
 
-/* Reads and clears the device status word written by a kernel whose bounded wait
- * ran out.  Synchronises `stream`.  *code is 0 when no kernel reported anything. */
+/* Every device-side wait of this library is bounded.  A kernel whose wait ran out gives up,
+ * returns normally and stores B200_ERR_KERNEL_TIMEOUT in the context's status word, which lives
+ * in pinned host memory.  This plays the part of the reference's CUDA_CALL checks
+ * (primitiv/internal/cuda/utils.h:20-48): every entry point that hands results to the host
+ * after waiting for the GPU (b200_download, b200_argminmax, the *_host products) reads the word
+ * and, if it is set, clears it and returns B200_ERR_KERNEL_TIMEOUT instead of 0.
+ *
+ * b200_status_poll waits for `stream`, then reads and clears the word into *code (0 = nothing
+ * was reported).  b200_status_peek does the same without waiting: for callers that have just
+ * synchronised by other means. */
 B200_API int b200_status_poll(b200_ctx *ctx, void *stream, int *code);
+B200_API int b200_status_peek(b200_ctx *ctx, int *code);
 
 /* Exercises the failure-reporting path without any failure: launches a one-warp kernel that
  * waits about a millisecond on a barrier nothing arrives at, gives up, and writes
@@ -150,6 +166,24 @@ B200_API int b200_matmul_bw_host(b200_ctx *ctx, int mode,
                                  uint32_t di, uint32_t dj, uint32_t dk,
                                  uint32_t ba, uint32_t bb);
 
+/* Forward and both gradients of one product from HOST buffers in a single pipelined pass, the
+ * end-to-end form of a training step's use of the path (Device::new_tensor_by_array, matmul_fw,
+ * matmul_bw, Tensor::to_vector in primitiv terms):
+ *     y = a . b ;   ga (+)= gy . b^T ;   gb (+)= a^T . gy
+ * a, b and gy cross the bus once each (the two separate calls above upload a and b twice).
+ * accumulate_a / accumulate_b: 1 = `+=` into the values ga_host / gb_host hold on entry (the
+ * reference's semantics, matmul.cu:67-138; the gradient is uploaded first), 0 = the gradient is
+ * known to start from zeros: it is not uploaded and the kernels store instead of adding.
+ * y_host may be NULL (no forward product); ga_host / gb_host may be NULL (that gradient is
+ * skipped); gy_host may be NULL when both gradients are.  Synchronous: returns when every result
+ * is in host memory.  Pinned host buffers give full bus speed; pageable ones work. */
+B200_API int b200_matmul_fw_bw_host(b200_ctx *ctx, int mode,
+                                    const void *a_host, const void *b_host, const void *gy_host,
+                                    void *y_host, void *ga_host, void *gb_host,
+                                    uint32_t di, uint32_t dj, uint32_t dk,
+                                    uint32_t ba, uint32_t bb,
+                                    int accumulate_a, int accumulate_b);
+
 /* ---- the general contraction underneath (what cublasSgemm / SgemmBatched /
  * Hgemm were to the reference devices) --------------------------------------------------
  *   C[g] = (accumulate ? C[g] : 0) + sum_{r < red} opA(A[g*a_gs + r*a_rs]) . opB(B[g*b_gs + r*b_rs])
@@ -179,7 +213,10 @@ B200_API int b200_gemm(b200_ctx *ctx, int mode, int trans_a, int trans_b,
  * with the hi/lo packing planes, which b200_gemm takes from the pool, placed in a fixed
  * 32 MiB array inside the library's device image (B200_NOALLOC_SCRATCH_BYTES; every GPU that
  * loads the library holds it until the process exits).  It calls no cudaMalloc, cudaFree,
- * pool routine or event creation, and gives bit-identical results to b200_gemm.
+ * pool routine or event creation.  It runs the same kernel in the same accuracy class as
+ * b200_gemm (<= 1e-5 normwise), but always as one pass over k: b200_gemm may cut a long
+ * contraction with few output tiles into k-slices (which needs pool scratch) or pick another
+ * kernel for a small or skinny shape, so the two results can differ in their last bits.
  *
  * Limit: 2 planes x (m + n) x round_up(k, 4) floats, each plane rounded up to 64 floats, must
  * fit the array, i.e. roughly (m + n) * k <= 4 Mi elements (1024 x 1024 x 2048, 2048 x 2048 x

@@ -105,7 +105,8 @@ B200_API int b200_identity(b200_ctx *ctx, int mode, void *y, uint32_t size, void
  * b200_upload copies the array into pinned staging memory of the context and returns: the
  * array may be reused at once, the device copy is ordered on the stream like a kernel, and
  * the stream is not waited for.  b200_download returns when the values are in the host array
- * (it synchronises the stream, like the reference's blocking cudaMemcpy). */
+ * (it synchronises the stream, like the reference's blocking cudaMemcpy); if a kernel's bounded
+ * wait ran out before that point it returns B200_ERR_KERNEL_TIMEOUT once, see b200_status_poll. */
 B200_API int b200_upload(b200_ctx *ctx, int mode, const float *values_host, void *y, uint64_t n, void *stream);
 B200_API int b200_download(b200_ctx *ctx, int mode, const void *x, float *values_host, uint64_t n, void *stream);
 /* y = x, converting between storage types when the modes differ (a copy between two B200 devices). */
@@ -155,7 +156,7 @@ B200_API int b200_reduce_fw(b200_ctx *ctx, int mode, int red, const void *x, voi
 /* max_bw / min_bw: gx[first position equal to y] += gy */
 B200_API int b200_minmax_bw(b200_ctx *ctx, int mode, const void *x, const void *y, const void *gy,
                             void *gx, uint32_t n, uint64_t skip1, uint64_t outputs, void *stream);
-/* argmax / argmin: indices to the HOST; synchronises. */
+/* argmax / argmin: indices to the HOST; synchronises, and reports a wait that ran out like b200_download. */
 B200_API int b200_argminmax(b200_ctx *ctx, int mode, int want_max, const void *x, uint32_t *ids_host,
                             uint32_t n, uint64_t skip1, uint64_t outputs, void *stream);
 /* batch_sum.cc */

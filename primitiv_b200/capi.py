@@ -27,6 +27,7 @@ SIGNATURES = {
     "b200_ctx_destroy": (_int, [_vp]),
     "b200_ctx_device": (_int, [_vp, ctypes.POINTER(_int), ctypes.POINTER(_int)]),
     "b200_status_poll": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
+    "b200_status_peek": (_int, [_vp, ctypes.POINTER(_int)]),
     "b200_selftest_wait_timeout": (_int, [_vp, _vp]),
     "b200_pool_alloc": (_int, [_vp, ctypes.c_size_t, ctypes.POINTER(_vp), ctypes.POINTER(ctypes.c_size_t)]),
     "b200_pool_free": (_int, [_vp, _vp]),
@@ -39,6 +40,7 @@ SIGNATURES = {
     "b200_matmul_bw_ex": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _int, _int, _vp]),
     "b200_matmul_fw_host": (_int, [_vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32]),
     "b200_matmul_bw_host": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32]),
+    "b200_matmul_fw_bw_host": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _int, _int]),
     "b200_gemm": (_int, [_vp, _int, _int, _int, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32,
                          _u64, _u64, _u64, _u64, _u64, _int, _int, _vp]),
     "b200_gemm_3xtf32_noalloc": (_int, [_vp, _int, _int, _vp, _vp, _vp, _u32, _u32, _u32, _int, _vp]),
@@ -206,12 +208,26 @@ class Context:
         _check(lib().b200_matmul_bw(self._h, mode, a, b, gy, ga, gb, di, dj, dk, ba, bb, stream),
                "matmul_bw")
 
+    def matmul_bw_ex(self, mode, a, b, gy, ga, gb, di, dj, dk, ba, bb, accumulate_a=True, accumulate_b=True,
+                     stream=None):
+        """matmul_bw with `+=` (True) or `=` (False) per gradient; ga / gb may be None to skip one."""
+        _check(lib().b200_matmul_bw_ex(self._h, mode, a, b, gy, ga, gb, di, dj, dk, ba, bb,
+                                       int(accumulate_a), int(accumulate_b), stream), "matmul_bw_ex")
+
     def matmul_fw_host(self, mode, a, b, y, di, dj, dk, ba, bb):
         _check(lib().b200_matmul_fw_host(self._h, mode, a, b, y, di, dj, dk, ba, bb), "matmul_fw_host")
 
     def matmul_bw_host(self, mode, a, b, gy, ga, gb, di, dj, dk, ba, bb):
         _check(lib().b200_matmul_bw_host(self._h, mode, a, b, gy, ga, gb, di, dj, dk, ba, bb),
                "matmul_bw_host")
+
+    def matmul_fw_bw_host(self, mode, a, b, gy, y, ga, gb, di, dj, dk, ba, bb, accumulate_a=True, accumulate_b=True):
+        """Forward and both gradients from host buffers in one pipelined pass (addresses as ints, None to skip)."""
+        _check(lib().b200_matmul_fw_bw_host(self._h, mode, a, b, gy, y, ga, gb, di, dj, dk, ba, bb,
+                                            int(accumulate_a), int(accumulate_b)), "matmul_fw_bw_host")
+
+    def selftest_wait_timeout(self, stream=None):
+        _check(lib().b200_selftest_wait_timeout(self._h, stream), "selftest_wait_timeout")
 
     def op(self, name, *args):
         """Calls any other entry point by name (the elementwise / movement / reduction set)."""

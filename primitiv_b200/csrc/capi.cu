@@ -45,12 +45,19 @@ int b200_ctx_create(int device_id, b200_ctx **out) {
   ctx->cc_minor = prop.minor;
   ctx->smem_optin = prop.sharedMemPerBlockOptin;
   DeviceGuard guard(device_id);
-  cudaError_t e = cudaMalloc(&ctx->d_status, 256);
-  if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, 256);
+  void *word = nullptr, *alias = nullptr;
+  cudaError_t e = cudaHostAlloc(&word, 256, cudaHostAllocMapped | cudaHostAllocPortable);
+  if (e == cudaSuccess) {
+    memset(word, 0, 256);
+    e = cudaHostGetDevicePointer(&alias, word, 0);
+    if (e != cudaSuccess) cudaFreeHost(word);
+  }
   if (e != cudaSuccess) {
     delete ctx;
     return static_cast<int>(e);
   }
+  ctx->h_status = static_cast<int *>(word);
+  ctx->d_status = static_cast<int *>(alias);
   void *fn = nullptr;
   cudaDriverEntryPointQueryResult qres;
   if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
@@ -58,7 +65,7 @@ int b200_ctx_create(int device_id, b200_ctx **out) {
     ctx->encode_tiled = reinterpret_cast<b200::EncodeTiledFn>(fn);
   } else {
     cudaGetLastError();
-    cudaFree(ctx->d_status);
+    cudaFreeHost(ctx->h_status);
     delete ctx;
     return B200_ERR_DRIVER;
   }
@@ -73,7 +80,7 @@ int b200_ctx_destroy(b200_ctx *ctx) {
   for (cudaStream_t st : ctx->pipe_streams) if (st) cudaStreamDestroy(st);
   for (cudaEvent_t ev : ctx->pipe_events) cudaEventDestroy(ev);
   if (ctx->barrier_event) cudaEventDestroy(ctx->barrier_event);
-  cudaFree(ctx->d_status);
+  cudaFreeHost(ctx->h_status);
   delete ctx;  // the pool's destructor returns cached blocks
   return B200_OK;
 }
@@ -88,12 +95,14 @@ int b200_ctx_device(const b200_ctx *ctx, int *device_id, int *sm_count) {
 int b200_status_poll(b200_ctx *ctx, void *stream, int *code) {
   if (!ctx || !code) return B200_ERR_INVALID_ARG;
   DeviceGuard guard(ctx->device);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int host = 0;
-  B200_CUDA_TRY(cudaMemcpyAsync(&host, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
-  B200_CUDA_TRY(cudaStreamSynchronize(s));
-  if (host != 0) B200_CUDA_TRY(cudaMemsetAsync(ctx->d_status, 0, sizeof(int), s));
-  *code = host;
+  B200_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  *code = b200::take_status(ctx);
+  return B200_OK;
+}
+
+int b200_status_peek(b200_ctx *ctx, int *code) {
+  if (!ctx || !code) return B200_ERR_INVALID_ARG;
+  *code = b200::take_status(ctx);
   return B200_OK;
 }
 
@@ -247,7 +256,9 @@ int b200_matmul_fw(b200_ctx *ctx, int mode, const void *a, const void *b, void *
   }
   if (ba == 1) {
     // one product over the combined {dj, dk*bb} matrix: b's batches are adjacent columns
-    return b200_gemm(ctx, mode, 0, 0, a, b, y, di, dk * bb, dj, 1, 1, 0, 0, 0, 0, 0, 0, 0, stream);
+    const uint64_t dkb = (uint64_t)dk * bb;
+    if (dkb > 0xffffffffull) return B200_ERR_TOO_LARGE;  // extents are 32-bit, as primitiv's Shape is
+    return b200_gemm(ctx, mode, 0, 0, a, b, y, di, (uint32_t)dkb, dj, 1, 1, 0, 0, 0, 0, 0, 0, 0, stream);
   }
   return b200_gemm(ctx, mode, 0, 0, a, b, y, di, dk, dj, ba, 1, na, 0, bb > 1 ? nb : 0, 0, ny, 0, 0,
                    stream);
@@ -276,6 +287,7 @@ int b200_matmul_bw_ex(b200_ctx *ctx, int mode, const void *a, const void *b, con
     return B200_OK;
   }
   if (ba == 1) {
+    if ((uint64_t)dk * bb > 0xffffffffull) return B200_ERR_TOO_LARGE;
     const uint32_t dkb = dk * bb;
     // ga += gy_all . b_all^T : the batch sum is the tail of one long contraction
     if (ga) {
@@ -354,7 +366,8 @@ int pipe_finish(b200_ctx *ctx, int rc) {
     const cudaError_t e = cudaStreamSynchronize(st);
     if (!rc && e != cudaSuccess) rc = static_cast<int>(e);
   }
-  return rc;
+  const int status = b200::take_status(ctx);  // the results are on the host now: a wait that ran out is an error
+  return rc ? rc : status;
 }
 
 inline const char *cbytes(const void *p, size_t off) { return static_cast<const char *>(p) + off; }
@@ -462,6 +475,100 @@ int b200_matmul_bw_host(b200_ctx *ctx, int mode, const void *a_host, const void 
     // `down` already waits for the last chunk's products: the batch-summed gradients are complete
     if (ba == 1) B200_CUDA_TRY(cudaMemcpyAsync(ga_host, dga.p, sa, cudaMemcpyDeviceToHost, down));
     if (bb == 1) B200_CUDA_TRY(cudaMemcpyAsync(gb_host, dgb.p, sb, cudaMemcpyDeviceToHost, down));
+    return B200_OK;
+  };
+  return pipe_finish(ctx, body());
+}
+
+// Forward and backward of one product from host buffers in ONE pipelined pass: every operand
+// crosses the bus once (a and b serve the forward product and both gradients), a gradient that
+// the caller declares to start from zeros is neither uploaded nor read, and y travels down while
+// the gradients are still being computed.  Per chunk of the batch: a, b up -> forward -> y down;
+// gy (and any gradient to be added to) up -> backward -> batched gradients down.
+int b200_matmul_fw_bw_host(b200_ctx *ctx, int mode, const void *a_host, const void *b_host,
+                           const void *gy_host, void *y_host, void *ga_host, void *gb_host,
+                           uint32_t di, uint32_t dj, uint32_t dk, uint32_t ba, uint32_t bb,
+                           int accumulate_a, int accumulate_b) {
+  int rc = check_matmul(ctx, mode, ba, bb);
+  if (rc) return rc;
+  if (!a_host || !b_host) return B200_ERR_INVALID_ARG;
+  const bool want_bw = ga_host || gb_host;
+  if (want_bw && !gy_host) return B200_ERR_INVALID_ARG;
+  if (!y_host && !want_bw) return B200_OK;
+  DeviceGuard guard(ctx->device);
+  const size_t eb = b200::elem_bytes(mode);
+  const uint32_t bs = ba > bb ? ba : bb;
+  const size_t ia = (size_t)di * dj * eb, ib = (size_t)dj * dk * eb, iy = (size_t)di * dk * eb;  // one item
+  const size_t sa = ia * ba, sb = ib * bb, sy = iy * bs;
+  if (sa == 0 || sb == 0 || sy == 0) {
+    // an empty extent: y (if any) is empty or zero, and nothing is added to the gradients
+    if (y_host && sy && dj == 0) memset(y_host, 0, sy);
+    if (ga_host && !accumulate_a && sa) memset(ga_host, 0, sa);
+    if (gb_host && !accumulate_b && sb) memset(gb_host, 0, sb);
+    return B200_OK;
+  }
+  Scratch da(ctx), db(ctx), dgy(ctx), dy(ctx), dga(ctx), dgb(ctx);
+  if ((rc = da.get(sa)) || (rc = db.get(sb))) return rc;
+  if (y_host && (rc = dy.get(sy))) return rc;
+  if (want_bw && (rc = dgy.get(sy))) return rc;
+  if (ga_host && (rc = dga.get(sa))) return rc;
+  if (gb_host && (rc = dgb.get(sb))) return rc;
+  const size_t per_step = (ba > 1 ? sa : 0) + (bb > 1 ? sb : 0) + (want_bw ? sy : 0);
+  const uint32_t chunks = pipe_chunks(mode, bs, per_step);
+  if ((rc = pipe_prepare(ctx, 4 * chunks))) return rc;
+  cudaStream_t up = ctx->pipe_streams[kPipeUp], run = ctx->pipe_streams[kPipeRun],
+               down = ctx->pipe_streams[kPipeDown];
+  const int acc_a = accumulate_a ? 1 : 0, acc_b = accumulate_b ? 1 : 0;
+  auto body = [&]() -> int {
+    // batch-1 operands, and the batch-1 gradients every chunk adds into, go up first
+    if (ba == 1) {
+      B200_CUDA_TRY(cudaMemcpyAsync(da.p, a_host, sa, cudaMemcpyHostToDevice, up));
+      if (ga_host && acc_a) B200_CUDA_TRY(cudaMemcpyAsync(dga.p, ga_host, sa, cudaMemcpyHostToDevice, up));
+    }
+    if (bb == 1) {
+      B200_CUDA_TRY(cudaMemcpyAsync(db.p, b_host, sb, cudaMemcpyHostToDevice, up));
+      if (gb_host && acc_b) B200_CUDA_TRY(cudaMemcpyAsync(dgb.p, gb_host, sb, cudaMemcpyHostToDevice, up));
+    }
+    for (uint32_t c = 0; c < chunks; ++c) {
+      const uint32_t n0 = (uint32_t)((uint64_t)bs * c / chunks), n1 = (uint32_t)((uint64_t)bs * (c + 1) / chunks);
+      const uint32_t cnt = n1 - n0;
+      const size_t oa = ba > 1 ? ia * n0 : 0, ob = bb > 1 ? ib * n0 : 0, oy = iy * n0;
+      const uint32_t ca = ba > 1 ? cnt : 1, cb = bb > 1 ? cnt : 1;
+      cudaEvent_t operands_up = ctx->pipe_events[4 * c], grads_up = ctx->pipe_events[4 * c + 1],
+                  fw_done = ctx->pipe_events[4 * c + 2], bw_done = ctx->pipe_events[4 * c + 3];
+      if (ba > 1) B200_CUDA_TRY(cudaMemcpyAsync(mbytes(da.p, oa), cbytes(a_host, oa), ia * cnt, cudaMemcpyHostToDevice, up));
+      if (bb > 1) B200_CUDA_TRY(cudaMemcpyAsync(mbytes(db.p, ob), cbytes(b_host, ob), ib * cnt, cudaMemcpyHostToDevice, up));
+      B200_CUDA_TRY(cudaEventRecord(operands_up, up));
+      B200_CUDA_TRY(cudaStreamWaitEvent(run, operands_up, 0));
+      if (y_host) {
+        const int r = b200_matmul_fw(ctx, mode, cbytes(da.p, oa), cbytes(db.p, ob), mbytes(dy.p, oy), di, dj, dk, ca, cb, run);
+        if (r) return r;
+        B200_CUDA_TRY(cudaEventRecord(fw_done, run));
+        B200_CUDA_TRY(cudaStreamWaitEvent(down, fw_done, 0));
+        B200_CUDA_TRY(cudaMemcpyAsync(mbytes(y_host, oy), cbytes(dy.p, oy), iy * cnt, cudaMemcpyDeviceToHost, down));
+      }
+      if (!want_bw) continue;
+      B200_CUDA_TRY(cudaMemcpyAsync(mbytes(dgy.p, oy), cbytes(gy_host, oy), iy * cnt, cudaMemcpyHostToDevice, up));
+      if (ga_host && acc_a && ba > 1)
+        B200_CUDA_TRY(cudaMemcpyAsync(mbytes(dga.p, oa), cbytes(ga_host, oa), ia * cnt, cudaMemcpyHostToDevice, up));
+      if (gb_host && acc_b && bb > 1)
+        B200_CUDA_TRY(cudaMemcpyAsync(mbytes(dgb.p, ob), cbytes(gb_host, ob), ib * cnt, cudaMemcpyHostToDevice, up));
+      B200_CUDA_TRY(cudaEventRecord(grads_up, up));
+      B200_CUDA_TRY(cudaStreamWaitEvent(run, grads_up, 0));
+      // a batch-1 gradient is one array for all chunks: only the first chunk may store into it
+      const int r = b200_matmul_bw_ex(ctx, mode, cbytes(da.p, oa), cbytes(db.p, ob), cbytes(dgy.p, oy),
+                                      ga_host ? mbytes(dga.p, oa) : nullptr, gb_host ? mbytes(dgb.p, ob) : nullptr,
+                                      di, dj, dk, ca, cb, (ba == 1 && c > 0) ? 1 : acc_a,
+                                      (bb == 1 && c > 0) ? 1 : acc_b, run);
+      if (r) return r;
+      B200_CUDA_TRY(cudaEventRecord(bw_done, run));
+      B200_CUDA_TRY(cudaStreamWaitEvent(down, bw_done, 0));
+      if (ga_host && ba > 1) B200_CUDA_TRY(cudaMemcpyAsync(mbytes(ga_host, oa), cbytes(dga.p, oa), ia * cnt, cudaMemcpyDeviceToHost, down));
+      if (gb_host && bb > 1) B200_CUDA_TRY(cudaMemcpyAsync(mbytes(gb_host, ob), cbytes(dgb.p, ob), ib * cnt, cudaMemcpyDeviceToHost, down));
+    }
+    // `down` already waits for the last chunk's products: the batch-summed gradients are complete
+    if (ga_host && ba == 1) B200_CUDA_TRY(cudaMemcpyAsync(ga_host, dga.p, sa, cudaMemcpyDeviceToHost, down));
+    if (gb_host && bb == 1) B200_CUDA_TRY(cudaMemcpyAsync(gb_host, dgb.p, sb, cudaMemcpyDeviceToHost, down));
     return B200_OK;
   };
   return pipe_finish(ctx, body());

@@ -81,7 +81,11 @@ struct b200_ctx {
   int cc_major = 0, cc_minor = 0;
   std::size_t smem_optin = 0;
   b200::Pool pool;
-  int *d_status = nullptr;       // device status word (bounded-wait failures)
+  // Status word of the bounded device-side waits.  It lives in pinned host memory that the
+  // GPU writes through a mapped alias (d_status): a kernel whose wait ran out stores its code
+  // there, and the host reads it after any synchronisation without another copy.
+  int *h_status = nullptr;       // host address
+  int *d_status = nullptr;       // the same word as the kernels address it
   b200::EncodeTiledFn encode_tiled = nullptr;
   std::uint64_t launches = 0;
   bool tc_smem_configured = false;
@@ -163,6 +167,25 @@ int selftest_wait_timeout(b200_ctx *ctx, cudaStream_t stream);
 int gemm_3xtf32_noalloc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
 
 inline int elem_bytes(int mode) { return mode == B200_MODE_FP16 ? 2 : 4; }
+
+// Reads and clears the status word.  Meaningful once the work that may have written it has
+// been waited for; every entry point that synchronises calls this and returns the code, which is
+// how a wait that ran out becomes an error of the next host-visible result.
+inline int take_status(b200_ctx *ctx) {
+  volatile int *w = ctx->h_status;
+  const int code = *w;
+  if (code != 0) *w = 0;
+  return code;
+}
+
+#ifdef __CUDACC__
+// Device side of the same word: a plain store through the mapped alias (every writer stores the
+// same kind of code, so no atomic is needed), made visible to the host before the kernel ends.
+__device__ __forceinline__ void report_status(int *status, int code) {
+  *reinterpret_cast<volatile int *>(status) = code;
+  __threadfence_system();
+}
+#endif
 
 }  // namespace b200
 

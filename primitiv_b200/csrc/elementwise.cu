@@ -535,7 +535,7 @@ int b200_download(b200_ctx *ctx, int mode, const void *x, float *values_host, ui
   if (mode != B200_MODE_FP16) {
     B200_CUDA_TRY(cudaMemcpyAsync(values_host, x, n * sizeof(float), cudaMemcpyDeviceToHost, s));
     B200_CUDA_TRY(cudaStreamSynchronize(s));
-    return B200_OK;
+    return b200::take_status(ctx);  // values computed by a kernel whose wait ran out are not handed over silently
   }
   void *tmp = nullptr;
   int rc = ctx->pool.alloc(n * sizeof(float), &tmp, nullptr);
@@ -547,7 +547,7 @@ int b200_download(b200_ctx *ctx, int mode, const void *x, float *values_host, ui
   if (e == cudaSuccess) e = cudaMemcpyAsync(values_host, tmp, n * sizeof(float), cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   ctx->pool.free(tmp);
-  return static_cast<int>(e);
+  return e == cudaSuccess ? b200::take_status(ctx) : static_cast<int>(e);
 }
 
 int b200_copy(b200_ctx *ctx, int src_mode, const void *x, int dst_mode, void *y, uint64_t n, void *stream) {

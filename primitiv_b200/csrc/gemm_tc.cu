@@ -773,7 +773,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
   // neither CTA of a pair may leave (or free TMEM) while the other can still signal its
   // barriers or read accumulators the shared MMA wrote
   if constexpr (kCtas == 2) cluster_sync_all();
-  if (threadIdx.x == 0 && s_abort) atomicCAS(p.status, 0, B200_ERR_KERNEL_TIMEOUT);
+  if (threadIdx.x == 0 && s_abort) report_status(p.status, B200_ERR_KERNEL_TIMEOUT);
   if (warp == 1) {
     tc_fence_after();
     if constexpr (kCtas == 2)
@@ -1193,7 +1193,7 @@ __global__ void wait_timeout_selftest_kernel(int *status, long long limit_cycles
         break;
       }
     }
-    if (timed_out) atomicCAS(status, 0, B200_ERR_KERNEL_TIMEOUT);
+    if (timed_out) report_status(status, B200_ERR_KERNEL_TIMEOUT);
   }
 }
 

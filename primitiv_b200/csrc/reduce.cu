@@ -225,7 +225,7 @@ int b200_argminmax(b200_ctx *ctx, int mode, int want_max, const void *x, uint32_
     e = cudaMemcpyAsync(ids_host, d_ids, outputs * sizeof(uint32_t), cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   ctx->pool.free(d_ids);
-  return static_cast<int>(e);
+  return e == cudaSuccess ? b200::take_status(ctx) : static_cast<int>(e);
 }
 
 int b200_batch_sum_fw(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t volume, uint32_t batch,

@@ -10,6 +10,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <iostream>
+#include <random>
 #include <string>
 #include <unordered_map>
 
@@ -74,8 +75,11 @@ std::uint32_t B200::num_devices() {
   return n;
 }
 
+// Without a seed the random fills start from the system's entropy source, as the reference's
+// one-argument constructors do (primitiv/devices/cuda/device.cu:111-112): two unseeded devices
+// must not draw the same dropout masks and initial weights.
 B200::B200(std::uint32_t device_id) : device_id_(device_id), mode_(mode_from_environment()) {
-  initialize(0);
+  initialize(std::random_device()());
 }
 
 B200::B200(std::uint32_t device_id, std::uint32_t rng_seed)
@@ -141,6 +145,19 @@ B200::~B200() {
 }
 
 ::b200_ctx *B200::context() const { return state_->ctx; }
+
+// Waits for the device's stream and turns a bounded wait that ran out in some kernel into
+// primitiv::Error, the way the reference's CUDA_CALL does for any failed CUDA call
+// (primitiv/internal/cuda/utils.h:20-48).  The status word is cleared by the read, so the
+// device stays usable: the error is reported once.
+void B200::wait_and_check() {
+  int code = 0;
+  B200_CALL(::b200_status_poll(state_->ctx, nullptr, &code));
+  if (code != 0) {
+    PRIMITIV_THROW_ERROR("B200: a kernel on GPU " << device_id_ << " gave up waiting: "
+                         << ::b200_error_string(code) << " [" << code << "]");
+  }
+}
 
 const void *B200::data(const Tensor &x) {
   if (&x.device() != this) PRIMITIV_THROW_ERROR("B200::data: the tensor lives on another device.");
@@ -243,15 +260,13 @@ void B200::copy_tensor_impl(const Tensor &x, Tensor &y) {
       if (src->device_id_ != device_id_) {
         // The two GPUs' default streams do not order against each other: let the source
         // device finish whatever still writes x before this device reads it.
-        int code = 0;
-        B200_CALL(::b200_status_poll(src->state_->ctx, nullptr, &code));
+        const_cast<B200 *>(src)->wait_and_check();
       }
       B200_CALL(::b200_copy(state_->ctx, src->imode(), px, imode(), MDATA(y), n, nullptr));
       if (src->device_id_ != device_id_) {
         // ... and finish the copy before the caller may release x: the source GPU's pool
         // orders reuse on its own stream only.
-        int code = 0;
-        B200_CALL(::b200_status_poll(state_->ctx, nullptr, &code));
+        wait_and_check();
       }
       return;
     }

@@ -38,7 +38,8 @@ public:
 
   /**
    * @param device_id CUDA ordinal of the GPU.
-   * @param rng_seed Seed of the device's random fills.
+   * @param rng_seed Seed of the device's random fills; without it the seed comes from
+   *                 std::random_device, as in the reference's CUDA device.
    * @param mode Numeric mode; the environment variable PRIMITIV_B200_MODE
    *             (3xtf32 | tf32 | fp16 | 3xfp16) overrides the default when `mode` is not given.
    * @throw primitiv::Error if the GPU does not exist or is not a Blackwell part.
@@ -62,6 +63,14 @@ public:
   Mode mode() const { return mode_; }
   std::uint32_t device_id() const { return device_id_; }
   b200_ctx *context() const;
+
+  /**
+   * Blocks until the device's queued work is done.
+   * @throw primitiv::Error if a kernel reported that one of its bounded waits ran out (once;
+   *        the report is cleared and the device stays usable).  The calls that hand values to
+   *        the host (to_vector, argmax, argmin, copies between GPUs) make the same check.
+   */
+  void wait_and_check();
 
   /** Kernel choice for matmul: 0 per problem, 1 CUDA cores, 2 tensor cores whenever eligible. */
   void set_matmul_path_policy(int policy);

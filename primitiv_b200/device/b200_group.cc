@@ -8,6 +8,7 @@
 
 #include <algorithm>
 #include <iostream>
+#include <random>
 #include <string>
 
 #include <primitiv/core/error.h>
@@ -43,7 +44,11 @@ const std::uint64_t kSlicedSumBytes = 1ull << 20;
 
 // ---------------------------------------------------------------- construction
 
-B200Group::B200Group(const std::vector<std::uint32_t> &device_ids) { initialize(device_ids, 0, nullptr); }
+// unseeded: entropy from the system, like the reference's one-argument CUDA constructor
+// (primitiv/devices/cuda/device.cu:111-112); shard i then draws from seed + i
+B200Group::B200Group(const std::vector<std::uint32_t> &device_ids) {
+  initialize(device_ids, std::random_device()(), nullptr);
+}
 
 B200Group::B200Group(const std::vector<std::uint32_t> &device_ids, std::uint32_t rng_seed) {
   initialize(device_ids, rng_seed, nullptr);
@@ -83,11 +88,16 @@ B200Group::~B200Group() {
 }
 
 void B200Group::synchronize() {
-  for (b200_ctx *c : ctxs_) {
-    int code = 0;
-    GROUP_CALL(::b200_status_poll(c, nullptr, &code));
-    if (code != 0) PRIMITIV_THROW_ERROR("B200Group: a kernel reported a bounded-wait timeout [" << code << "]");
+  // every GPU is waited for before the first report is thrown, so that no shard is left running
+  std::string failed;
+  for (auto &s : shards_) {
+    try {
+      s->wait_and_check();
+    } catch (const primitiv::Error &e) {
+      if (failed.empty()) failed = e.what();
+    }
   }
+  if (!failed.empty()) PRIMITIV_THROW_ERROR("B200Group: " << failed);
 }
 
 void B200Group::dump_description() const {

@@ -9,9 +9,10 @@ an error.  Tensors with batch N hold N / world elements per rank; tensors with b
 each rank adds the same all-reduced partial.
 
 The orchestration is independent of where the arithmetic runs: ``ShardedMatmul`` takes a
-*backend* with four methods (``matmul_fw``, ``matmul_bw``, ``zeros_like``, ``add_``) and an
-``all_reduce`` callable.  ``GpuBackend`` drives the C ABI on this rank's GPU; the CPU tests
-plug in the oracle and a gloo process group to check the orchestration itself.
+*backend* with four methods (``matmul_fw``, ``matmul_bw``, ``scratch_like``, ``add_``) and an
+``all_reduce`` callable that may return a handle with ``wait()`` (an exchange still in
+flight).  ``GpuBackend`` drives the C ABI on this rank's GPU; the CPU tests plug in the
+oracle and a gloo process group to check the orchestration itself.
 """
 
 
@@ -53,15 +54,26 @@ class ShardedMatmul:
             # every gradient is either local to the shard or (ba == bb == 1) replicated work
             bk.matmul_bw(a, b, gy, ga, gb, di, dj, dk, la, lb)
             return
+        # The summed gradient's partial is computed first (stored, not added: the scratch needs
+        # no zero-fill), its all-reduce is started, and the other gradient, which is local to the
+        # shard, is computed while the partials cross the links.  Only then is the reduced sum
+        # added into the replicated gradient: one `+=` of the same bits on every rank
+        # (primitiv/devices/cuda/ops/matmul.cu:127-136 is the single-GPU form of the same sum).
         if a_summed:
-            part = bk.zeros_like(ga)
-            bk.matmul_bw(a, b, gy, part, gb, di, dj, dk, la, lb)   # gb is per batch element: local
-            self.all_reduce(part)
+            part = bk.scratch_like(ga)
+            bk.matmul_bw(a, b, gy, part, None, di, dj, dk, la, lb, acc_a=False)
+            pending = self.all_reduce(part)
+            bk.matmul_bw(a, b, gy, None, gb, di, dj, dk, la, lb)      # gb is per batch element: local
+            if pending is not None:
+                pending.wait()
             bk.add_(ga, part)
         else:
-            part = bk.zeros_like(gb)
-            bk.matmul_bw(a, b, gy, ga, part, di, dj, dk, la, lb)
-            self.all_reduce(part)
+            part = bk.scratch_like(gb)
+            bk.matmul_bw(a, b, gy, None, part, di, dj, dk, la, lb, acc_b=False)
+            pending = self.all_reduce(part)
+            bk.matmul_bw(a, b, gy, ga, None, di, dj, dk, la, lb)
+            if pending is not None:
+                pending.wait()
             bk.add_(gb, part)
         self.collectives += 1
 
@@ -71,22 +83,32 @@ class GpuBackend:
 
     def __init__(self, ctx, mode):
         self.ctx, self.mode = ctx, mode
+        self._scratch = {}
 
     def matmul_fw(self, a, b, y, di, dj, dk, ba, bb):
         self.ctx.matmul_fw(self.mode, a.data_ptr(), b.data_ptr(), y.data_ptr(), di, dj, dk, ba, bb)
 
-    def matmul_bw(self, a, b, gy, ga, gb, di, dj, dk, ba, bb):
-        self.ctx.matmul_bw(self.mode, a.data_ptr(), b.data_ptr(), gy.data_ptr(), ga.data_ptr(), gb.data_ptr(),
-                           di, dj, dk, ba, bb)
+    def matmul_bw(self, a, b, gy, ga, gb, di, dj, dk, ba, bb, acc_a=True, acc_b=True):
+        """ga / gb may be None (that gradient is skipped); acc_* False stores instead of adding."""
+        self.ctx.matmul_bw_ex(self.mode, a.data_ptr(), b.data_ptr(), gy.data_ptr(),
+                              None if ga is None else ga.data_ptr(), None if gb is None else gb.data_ptr(),
+                              di, dj, dk, ba, bb, acc_a, acc_b)
 
-    def zeros_like(self, t):
+    def scratch_like(self, t):
+        """Uninitialised device memory of t's size, kept for the next step (no allocation per step)."""
         import torch
-        return torch.zeros_like(t)
+        key = (t.numel(), t.dtype)
+        if key not in self._scratch:
+            self._scratch[key] = torch.empty_like(t)
+        return self._scratch[key]
 
     def add_(self, dst, src):
         self.ctx.op("b200_inplace_add", self.mode, src.data_ptr(), dst.data_ptr(), dst.numel(), 1, 1, 1.0, None)
 
 
 def nccl_all_reduce(t):
+    """Starts the sum over ranks on NCCL's own stream (it first waits for the work queued so far
+    on the current stream) and returns the handle; handle.wait() makes the current stream, not
+    the host, wait for the result."""
     import torch.distributed as dist
-    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return dist.all_reduce(t, op=dist.ReduceOp.SUM, async_op=True)

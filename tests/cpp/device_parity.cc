@@ -23,6 +23,7 @@
 #include <primitiv/core/functions.h>
 #include <primitiv/core/graph.h>
 #include <primitiv/core/initializer_impl.h>
+#include <primitiv/core/model.h>
 #include <primitiv/core/optimizer_impl.h>
 #include <primitiv/core/parameter.h>
 #include <primitiv/core/shape.h>
@@ -30,6 +31,7 @@
 #include <primitiv/devices/naive/device.h>
 
 #include "b200_device.h"
+#include "../../include/primitiv_b200.h"
 
 using primitiv::Device;
 using primitiv::Shape;
@@ -758,6 +760,83 @@ void test_graph_training(Pair &p) {
   expect(losses[1].back() < losses[1].front(), "training on B200 reduces the loss");
 }
 
+// A kernel whose bounded wait ran out must not hand garbage to the host silently: the next call
+// that returns values to the host throws primitiv::Error (as the reference's CUDA_CALL does for
+// any failed CUDA call, primitiv/internal/cuda/utils.h:20-48), once, and the device stays usable.
+// The wait that runs out here is the library's self-test: a one-warp kernel that waits a
+// millisecond for a barrier nothing arrives at and returns normally.  Nothing faults.
+void test_kernel_timeout_is_reported(Pair &p) {
+  const Shape s({4, 3}, 2);
+  const vector<float> v = on_grid(rnd(s.size()));
+  Tensor t = p.dev.new_tensor_by_vector(s, v);
+  auto thrown_by = [&](const std::function<void()> &f) {
+    try { f(); } catch (const primitiv::Error &) { return true; }
+    return false;
+  };
+  expect(::b200_selftest_wait_timeout(p.dev.context(), nullptr) == 0, "timeout self-test launches");
+  expect(thrown_by([&] { t.to_vector(); }), "to_vector() throws after a kernel's wait ran out");
+  expect(!thrown_by([&] { t.to_vector(); }), "the report is delivered once");
+  expect_close(v, t.to_vector(), "the device still works after the report", g_tol);
+  expect(::b200_selftest_wait_timeout(p.dev.context(), nullptr) == 0, "timeout self-test launches again");
+  expect(thrown_by([&] { t.argmax(0); }), "argmax() throws after a kernel's wait ran out");
+  expect(t.argmax(0).size() == 6, "argmax works afterwards");
+  expect(::b200_selftest_wait_timeout(p.dev.context(), nullptr) == 0, "timeout self-test launches a third time");
+  expect(thrown_by([&] { p.dev.wait_and_check(); }), "wait_and_check() throws after a kernel's wait ran out");
+  expect(!thrown_by([&] { p.dev.wait_and_check(); }), "and not a second time");
+  Tensor y = p.dev.matmul_fw(p.dev.new_tensor_by_vector(Shape({2, 4}), on_grid(rnd(8))), t);
+  expect(y.to_vector().size() == 12, "the next product on the same device succeeds");
+}
+
+// Checkpoint round trip (primitiv/core/model.cc:16-75 over Parameter::save / load, which go
+// through to_vector() and new_tensor_by_array on the device): parameters trained on the B200
+// device are written, read back into fresh parameters on the same device, and must be the same
+// values bit for bit; a Naive-side load of the same file agrees too.
+void test_model_save_load(Pair &p) {
+  using primitiv::Model;
+  using primitiv::Parameter;
+  const std::string path = "/tmp/primitiv_b200_device_parity_model.bin";
+  const vector<float> w = on_grid(rnd(6 * 5)), b = on_grid(rnd(6));
+  vector<float> saved_w, saved_b;
+  {
+    Parameter pw({6, 5}, w, p.dev), pb({6}, b, p.dev);
+    pw.gradient() += p.dev.new_tensor_by_vector(Shape({6, 5}), on_grid(rnd(30)));
+    primitiv::optimizers::SGD opt(0.5f);
+    opt.add(pw, pb);
+    opt.update();
+    Model m;
+    m.add("w", pw);
+    m.add("b", pb);
+    m.save(path, true);
+    saved_w = pw.value().to_vector();
+    saved_b = pb.value().to_vector();
+  }
+  Device *devs[2] = {&p.dev, &p.naive};
+  for (Device *d : devs) {
+    Parameter qw, qb;
+    Model m;
+    m.add("w", qw);
+    m.add("b", qb);
+    m.load(path, true, d);
+    expect(qw.value().to_vector() == saved_w, "Model::load returns the saved weights bit for bit");
+    expect(qb.value().to_vector() == saved_b, "Model::load returns the saved bias bit for bit");
+    expect(&qw.device() == d, "loaded parameter lives on the requested device");
+  }
+  std::remove(path.c_str());
+}
+
+// The one-argument constructor takes its seed from the system's entropy source
+// (primitiv/devices/cuda/device.cu:111-112): two such devices draw different numbers, two
+// devices with the same explicit seed the same ones.
+void test_unseeded_devices_differ() {
+  const Shape s({64, 4});
+  B200 a(0), b(0);
+  expect(a.random_uniform(s, 0.f, 1.f).to_vector() != b.random_uniform(s, 0.f, 1.f).to_vector(),
+         "unseeded devices draw different numbers");
+  B200 c(0, 11), d(0, 11);
+  expect(c.random_uniform(s, 0.f, 1.f).to_vector() == d.random_uniform(s, 0.f, 1.f).to_vector(),
+         "devices with the same seed draw the same numbers");
+}
+
 }  // namespace
 
 int main(int argc, char **argv) {
@@ -783,6 +862,9 @@ int main(int argc, char **argv) {
     test_conv_and_pool(p);
     test_zero_gradients(p);
     test_graph_training(p);
+    test_model_save_load(p);
+    test_kernel_timeout_is_reported(p);
+    test_unseeded_devices_differ();
   } catch (const std::exception &e) {
     std::cerr << "EXCEPTION: " << e.what() << std::endl;
     return 3;

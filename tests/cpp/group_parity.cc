@@ -9,6 +9,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <functional>
 #include <iostream>
 #include <random>
 #include <string>
@@ -25,6 +26,7 @@
 #include <primitiv/devices/naive/device.h>
 
 #include "b200_group.h"
+#include "../../include/primitiv_b200.h"
 
 using primitiv::Device;
 using primitiv::Graph;
@@ -266,6 +268,26 @@ void test_training(Naive &n, B200Group &g, std::uint32_t batch) {
   }
 }
 
+// A bounded wait that ran out on any shard surfaces as primitiv::Error from the group, once
+// (the wait here is the library's self-test kernel, which returns normally after a millisecond).
+void test_kernel_timeout_is_reported(B200Group &group) {
+  const std::uint32_t last = group.num_shards() - 1;
+  const Shape s({3, 2}, 2 * group.num_shards());
+  vector<float> v(s.size(), 0.25f);
+  Tensor t = group.new_tensor_by_vector(s, v);
+  auto thrown_by = [&](const std::function<void()> &f) {
+    try { f(); } catch (const primitiv::Error &) { return true; }
+    return false;
+  };
+  expect(::b200_selftest_wait_timeout(group.shard(last).context(), nullptr) == 0, "timeout self-test launches");
+  expect(thrown_by([&] { t.to_vector(); }), "group to_vector() throws after a shard's kernel gave up waiting");
+  expect(!thrown_by([&] { t.to_vector(); }), "the report is delivered once");
+  expect(::b200_selftest_wait_timeout(group.shard(0).context(), nullptr) == 0, "timeout self-test launches again");
+  expect(thrown_by([&] { group.synchronize(); }), "group synchronize() throws after a shard's kernel gave up waiting");
+  expect(!thrown_by([&] { group.synchronize(); }), "and not a second time");
+  expect(t.to_vector() == v, "the group still works after the report");
+}
+
 }  // namespace
 
 int main(int argc, char **argv) {
@@ -292,6 +314,7 @@ int main(int argc, char **argv) {
     }
     test_large_sum(naive, group);
     group.synchronize();
+    test_kernel_timeout_is_reported(group);
     std::printf("{\"mode\": \"%s\", \"shards\": %u, \"checks\": %d, \"failures\": %d, \"cross_gpu_sums\": %llu}\n",
                 mode_name.c_str(), shards, g_checks, g_failures, static_cast<unsigned long long>(group.cross_gpu_sums()));
   } catch (const std::exception &e) {

@@ -106,6 +106,18 @@ def test_batched_square_gemm_workload_full_size(ctx):
     check_bw(ctx, pb.MODE_FP32_3XTF32, a, b, gy, n, n, n, bs, bs, TOL["3xtf32"], g, prefill=0.0)
 
 
+def test_batched_square_gemm_workload_full_size_3xfp16(ctx):
+    """The same workload in the second fp32-grade mode (row-scaled half planes, three fp16 passes):
+    held to the same 1e-5 bound."""
+    g = _gen(4)
+    n, bs = 4096, 8
+    a = torch.randn(n * n * bs, generator=g, device="cuda") * 0.02
+    b = torch.randn(n * n * bs, generator=g, device="cuda") * 0.02
+    gy = torch.randn(n * n * bs, generator=g, device="cuda")
+    check_fw(ctx, pb.MODE_FP32_3XFP16, a, b, n, n, n, bs, bs, TOL["3xfp16"], g)
+    check_bw(ctx, pb.MODE_FP32_3XFP16, a, b, gy, n, n, n, bs, bs, TOL["3xfp16"], g, prefill=0.5)
+
+
 def test_mlp_layer_shapes_full_batch(ctx):
     """784 -> 1024 -> 1024 -> 10 with batch 65536 (> 65535: no grid.y batch index anywhere), broadcast weights."""
     g = _gen(1)

@@ -221,6 +221,58 @@ def test_host_buffer_entry_points_pipeline_over_batch_chunks(ctx, mode, batches)
     assert ol.rel_err(ga.astype(np.float32), ga64) < tol and ol.rel_err(gb.astype(np.float32), gb64) < tol
 
 
+@pytest.mark.parametrize("accumulate", [True, False], ids=["prefill_0.5", "known_zero"])
+@pytest.mark.parametrize("batches", [(6, 6), (1, 6), (6, 1), (1, 1)], ids=lambda b: "ba%d_bb%d" % b)
+@pytest.mark.parametrize("mode", ["3xtf32", "fp16"])
+def test_fused_host_entry_point(ctx, mode, batches, accumulate):
+    """b200_matmul_fw_bw_host: y, ga and gb of one call against the fp64 oracle.  With the
+    accumulate flags set the gradients start from 0.5 (the reference's `+=`); with them clear the
+    host arrays hold a poison value that must not reach the result (the gradient is declared to
+    start from zeros and is never uploaded)."""
+    di = dj = dk = 512
+    ba, bb = batches
+    bs = max(ba, bb)
+    rng = np.random.default_rng(200 + 10 * ba + bb)
+    half = mode == "fp16"
+    dt = np.float16 if half else np.float32
+    a = rng.uniform(-1, 1, di * dj * ba).astype(np.float32).astype(dt)
+    b = rng.uniform(-1, 1, dj * dk * bb).astype(np.float32).astype(dt)
+    gy = rng.standard_normal(di * dk * bs).astype(np.float32).astype(dt)
+    a32, b32, gy32 = (x.astype(np.float32) for x in (a, b, gy))
+    args = (di, dj, dk, ba, bb)
+    tol = 2e-3 if half else 1e-5
+    start = 0.5 if accumulate else 0.0
+    y = np.full(di * dk * bs, 7.0, dt)
+    ga = np.full(di * dj * ba, 0.5 if accumulate else 1e4, dt)
+    gb = np.full(dj * dk * bb, 0.5 if accumulate else 1e4, dt)
+    ctx.matmul_fw_bw_host(MODES[mode], a.ctypes.data, b.ctypes.data, gy.ctypes.data, y.ctypes.data,
+                          ga.ctypes.data, gb.ctypes.data, *args, accumulate_a=accumulate, accumulate_b=accumulate)
+    ga64, gb64 = ol.bw_f64(a32, b32, gy32, np.full(di * dj * ba, start, np.float32),
+                           np.full(dj * dk * bb, start, np.float32), *args)
+    assert ol.rel_err(y.astype(np.float32), ol.fw_f64(a32, b32, *args)) < tol
+    assert ol.rel_err(ga.astype(np.float32), ga64) < tol and ol.rel_err(gb.astype(np.float32), gb64) < tol
+
+
+def test_fused_host_entry_point_optional_outputs(ctx):
+    """Any of y / ga / gb may be left out; the plumbing workload with pinned host buffers."""
+    c = ol.config1_inputs()
+    args = (c["di"], c["dj"], c["dk"], c["ba"], c["bb"])
+    M = pb.MODE_FP32_3XTF32
+    pin = lambda x: torch.from_numpy(x.copy()).pin_memory()
+    a, b, gy = pin(c["a"]), pin(c["b"]), pin(c["gy"])
+    y = torch.empty(c["di"] * c["dk"] * c["bb"]).pin_memory()
+    ga, gb = pin(c["ga0"]), pin(c["gb0"])
+    P = lambda t: t.data_ptr()
+    ctx.matmul_fw_bw_host(M, P(a), P(b), None, P(y), None, None, *args)               # forward only
+    assert ol.rel_err(y.numpy(), ol.fw_f64(c["a"], c["b"], *args)) < 1e-5
+    ctx.matmul_fw_bw_host(M, P(a), P(b), P(gy), None, P(ga), None, *args)             # ga only, +=
+    ctx.matmul_fw_bw_host(M, P(a), P(b), P(gy), None, None, P(gb), *args)             # gb only, +=
+    ga64, gb64 = ol.bw_f64(c["a"], c["b"], c["gy"], c["ga0"], c["gb0"], *args)
+    assert ol.rel_err(ga.numpy(), ga64) < 1e-5 and ol.rel_err(gb.numpy(), gb64) < 1e-5
+    with pytest.raises(pb.B200Error):   # gradients asked for without an upstream gradient
+        ctx.matmul_fw_bw_host(M, P(a), P(b), None, None, P(ga), None, *args)
+
+
 # Few output tiles against a long contraction: the tensor-core path cuts k into slices for the
 # idle SMs and adds the slices in a fixed order.  (di, dj, dk, ba, bb)
 SPLIT_K_SHAPES = [

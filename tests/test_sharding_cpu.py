@@ -31,12 +31,18 @@ class OracleBackend:
     def matmul_fw(self, a, b, y, di, dj, dk, ba, bb):
         y[:] = ol.fw_naive(a, b, di, dj, dk, ba, bb)
 
-    def matmul_bw(self, a, b, gy, ga, gb, di, dj, dk, ba, bb):
-        ga2, gb2 = ol.bw_naive(a, b, gy, ga, gb, di, dj, dk, ba, bb)
-        ga[:], gb[:] = ga2, gb2
+    def matmul_bw(self, a, b, gy, ga, gb, di, dj, dk, ba, bb, acc_a=True, acc_b=True):
+        # either gradient may be left out; acc_* False means the array holds garbage and is overwritten
+        ga0 = np.zeros(di * dj * ba, np.float32) if (ga is None or not acc_a) else ga
+        gb0 = np.zeros(dj * dk * bb, np.float32) if (gb is None or not acc_b) else gb
+        ga2, gb2 = ol.bw_naive(a, b, gy, ga0, gb0, di, dj, dk, ba, bb)
+        if ga is not None:
+            ga[:] = ga2
+        if gb is not None:
+            gb[:] = gb2
 
-    def zeros_like(self, t):
-        return np.zeros_like(t)
+    def scratch_like(self, t):
+        return np.full_like(t, np.nan)      # uninitialised memory: whoever reads it before writing fails the test
 
     def add_(self, dst, src):
         dst += src
@@ -57,8 +63,9 @@ def _worker(rank, world, port, out_dir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
 
     def all_reduce(arr):
+        # asynchronous, as on the GPU: the handle is waited for only after the local gradient
         t = torch.from_numpy(arr)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return dist.all_reduce(t, op=dist.ReduceOp.SUM, async_op=True)
 
     sm = ShardedMatmul(OracleBackend(), world, rank, all_reduce)
     results = {}

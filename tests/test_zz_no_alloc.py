@@ -4,7 +4,8 @@ loop that bans cudaMalloc / cudaFree because they synchronise the device).
 
 b200_gemm_3xtf32_noalloc keeps its packing planes in a fixed array inside the
 library instead of pool memory.  It is checked here against the ordinary entry
-point (b200_gemm, 3xTF32, tensor-core kernel) on two calls in a row: the second
+point (b200_gemm, 3xTF32, tensor-core kernel; same accuracy class, the last bits may differ
+because b200_gemm may split a long contraction over k) on two calls in a row: the second
 call is smaller and differently shaped than the first, so planes left behind by the
 first call would show up as wrong results if the second call read anything it had
 not written itself.  The file name sorts last on purpose: a run that stops at the
@@ -53,6 +54,23 @@ def _run_pair(ctx, ta, tb, m, n, k, accumulate, seed):
 def test_matches_the_pool_backed_entry_point_on_two_calls_in_a_row(ctx):
     _run_pair(ctx, 0, 0, 512, 384, 1024, accumulate=False, seed=11)
     _run_pair(ctx, 1, 1, 200, 136, 72, accumulate=True, seed=12)
+
+
+def test_a_product_that_fills_the_fixed_array_exactly(ctx):
+    """1024 x 1024 x 2048: two planes of (m + n) * k floats are exactly the 8 Mi floats of the array,
+    the largest case the entry point accepts.  An off-by-one in the plane layout would show here
+    as a wrong last row or as a rejected call."""
+    _run_pair(ctx, 0, 1, 1024, 1024, 2048, accumulate=False, seed=13)
+    _run_pair(ctx, 1, 0, 1024, 1024, 2048, accumulate=True, seed=14)
+
+
+def test_one_column_more_than_fits_is_rejected(ctx):
+    x = torch.zeros(16, device="cuda")
+    launches = ctx.launch_count()
+    with pytest.raises(pb.B200Error) as e:
+        ctx.gemm_3xtf32_noalloc(0, 0, x.data_ptr(), x.data_ptr(), x.data_ptr(), 1024, 1025, 2048)
+    assert e.value.code == 1006
+    assert ctx.launch_count() == launches    # nothing ran, so the small buffer was never read
 
 
 def test_sizes_beyond_the_fixed_array_are_rejected(ctx):
