@@ -64,7 +64,7 @@ class Workload:
             self.ba = self.bb = batch if batch else 8
             self.mode_name, self.passes, self.half = "3xTF32", 3, False
             self.sa, self.sb, self.sgy = 0.02, 0.02, 1.0
-            self.dtype = "tf32x3 (fp32 storage, fp32 accumulate)"
+            self.dtype = "f32 via tf32 + 2 x bf16 correction passes (fp32 storage, fp32 accumulate)"
             self.sample_dk = 64
         elif name == "batched_square_tf32":
             # the same shapes in the single-pass TF32 fast mode (tolerance 2e-3 instead of 1e-5)
@@ -370,12 +370,22 @@ def run_workload(rig, wl, steps, warmup):
     return rig.timed(step, steps, warmup, sm), (a, b, gy)
 
 
+def peak_divisor(mode_name, half):
+    """Measured bf16 peak / this = the peak of the passes a mode issues.  Single-pass fp16 and 3xFP16
+    run on the 16-bit pipe (1).  TF32 runs at half that rate (2).  The fp32 mode issues one TF32 pass
+    and two bf16 correction passes of the same FLOP count: the least time for its 3F issued FLOP is
+    F / (P/2) + 2F / P = 4F / P, so the peak of the mix is 3P/4 (divisor 4/3)."""
+    if half or mode_name == "3xFP16":
+        return 1.0
+    return 4.0 / 3.0 if mode_name == "3xTF32" else 2.0
+
+
 def tensor_roofline(wl, res, steps, peaks):
     tc_ms, tc_n = res["prof"]["gemm_tc"]
     issued_flops_per_launch = float(wl.passes) * wl.flops * steps / max(tc_n, 1)
     tc_avg_ms = tc_ms / max(tc_n, 1)
     achieved = issued_flops_per_launch / (tc_avg_ms * 1e-3) / 1e12 if tc_n else 0.0
-    div = 1.0 if (wl.half or wl.mode_name == "3xFP16") else 2.0     # TF32 runs at half the 16-bit rate
+    div = peak_divisor(wl.mode_name, wl.half)
     sustained, burst = peaks["bf16_sustained"] / div, peaks["bf16_burst"] / div
     return achieved, sustained, burst, tc_ms, tc_n, div
 
@@ -500,11 +510,11 @@ def leg_mlp_products(rig, steps, warmup, peaks):
     ms = res["ms"] / steps
     tc_ms, tc_n = res["prof"]["gemm_tc"]
     achieved = 3.0 * tc_flops * steps / (tc_ms * 1e-3) / 1e12 if tc_ms else 0.0
-    burst = peaks["bf16_burst"] / 2.0
+    burst = peaks["bf16_burst"] / peak_divisor("3xTF32", False)
     kinds = {k: {"ms_per_step": v[0] / steps, "launches_per_step": v[1] / steps} for k, v in res["prof"].items()}
     return {"workload": "mlp_784_1024_1024_10_batch%d_per_gpu_nine_products_fp32_3xtf32" % B, "value": flops * rig.world / (ms * 1e-3) / 1e9,
             "unit": "GFLOP/s", "ms_per_step": ms, "steps": steps, "warmup": warmup, "mode": "3xTF32",
-            "dtype": "tf32x3 (fp32 storage, fp32 accumulate)", "batch_per_gpu": B, "scaling": "weak",
+            "dtype": "f32 via tf32 + 2 x bf16 correction passes (fp32 storage, fp32 accumulate)", "batch_per_gpu": B, "scaling": "weak",
             "collectives_per_step": res["collectives"] / steps,
             "collective": "all-reduce (sum) of gW1, gW2, gW3 partials (3.2 MB, 4.2 MB, 41 kB) over NCCL" if rig.world > 1 else "none at 1 GPU",
             "replicas_bit_identical": same,
@@ -666,7 +676,9 @@ def emit(args, wl, world, res, e2e, peaks, check, secondary, extras):
                      "CUDA-event duration of %d launches; peak = %s bf16 burst%s (the timed region is a "
                      "fraction of a second); the sustained figure is %.0f%s"
                      % (wl.passes, tc_n, peaks["source"],
-                        "" if div == 1.0 else " / 2 (TF32 runs at half the 16-bit rate)", sustained,
+                        "" if div == 1.0 else (" / 2 (TF32 runs at half the 16-bit rate)" if div == 2.0 else
+                                               " x 3/4 (one TF32 pass at half the 16-bit rate plus two bf16 passes at the full rate)"),
+                        sustained,
                         "; traffic = ncu dram bytes of the batch-2 capture scaled to this batch" if traffic else "")),
             "algorithmic_tflops_in_kernel": achieved / wl.passes,
             "kernel_ms_per_step": tc_ms / args.steps, "pack_ms_per_step": res["prof"]["pack"][0] / args.steps,
@@ -688,6 +700,9 @@ def emit(args, wl, world, res, e2e, peaks, check, secondary, extras):
     line.update(extras)
     if "tf32_cublas_measured" in extras and div == 2.0:
         line["roofline"]["frac_of_cublas_tf32_burst"] = achieved / extras["tf32_cublas_measured"]["burst_tflops"]
+    if "tf32_cublas_measured" in extras and wl.mode_name != "FP16":
+        # what one pass of the vendor's TF32 GEMM would deliver on these shapes, at a thousandth of the accuracy
+        line["roofline"]["algorithmic_vs_cublas_tf32_single_pass"] = (achieved / wl.passes) / extras["tf32_cublas_measured"]["burst_tflops"]
     if world == 1 and not args.skip_cpu:
         t, kind, cores = cpu_sample(wl)
         line["cpu_baseline"] = {"value": wl.sample_flops / t / 1e9, "unit": "GFLOP/s", "cores": cores,
@@ -727,7 +742,7 @@ def run_graph_program(args):
     passes = 3.0 if pre[0] == "3xtf32" else 1.0
     flops = out["matmul_gflops"] * 1e9 * ms * 1e-3   # algorithmic matmul FLOP of one step
     peaks = measured_peaks()
-    peak = peaks["bf16_sustained"] / 2.0
+    peak = peaks["bf16_sustained"] / peak_divisor("3xTF32" if passes == 3.0 else "TF32", False)
     achieved = passes * flops / (dev["gemm_tc"] * 1e-3) / 1e12 if dev["gemm_tc"] else 0.0
     line = {
         "metric": METRIC, "value": out["matmul_gflops"], "unit": "GFLOP/s", "n_gpus": 1, "steps": args.steps,

@@ -42,7 +42,8 @@ typedef struct b200_ctx b200_ctx;
 
 /* Numeric modes of the matrix product. */
 enum {
-  B200_MODE_FP32_3XTF32 = 0, /* fp32 storage; each product = 3 TF32 tensor-core passes on hi/lo splits; fp32 accuracy */
+  B200_MODE_FP32_3XTF32 = 0, /* fp32 storage; each product = 3 tensor-core passes on hi/lo splits (hi.hi in TF32, the two
+                              * correction terms in TF32 or bf16, see b200_set_correction_policy); fp32 accuracy */
   B200_MODE_TF32        = 1, /* fp32 storage; one TF32 pass */
   B200_MODE_FP16        = 2, /* half storage, fp32 accumulation, one rounding on store (mirrors primitiv::devices::CUDA16) */
   /* fp32 storage and fp32-grade results on the fp16 tensor pipe: every operand row is scaled by a
@@ -242,6 +243,16 @@ B200_API int b200_set_path_policy(b200_ctx *ctx, int policy);
  * (tcgen05 cta_group::2) whenever the problem has more than 128 rows and at least 128
  * columns, 1 = always one CTA per 128-row tile. */
 B200_API int b200_set_pair_policy(b200_ctx *ctx, int policy);
+
+/* Arithmetic of the two correction passes of B200_MODE_FP32_3XTF32.  With x = hi + lo, hi = x rounded
+ * to TF32, a product is hi.hi + lo.hi + hi.lo.  The last two terms are 2^-11 of the result and need only
+ * a few digits, so by default (0) their operands are carried as bf16 planes and multiplied on the
+ * bf16 pipe, at twice the TF32 rate: 8 tensor-core instructions per 32 elements of k instead of 12,
+ * the same bytes per packed element, and the same <= 1e-5 normwise bound (measured 2e-6).
+ * 1 = all three passes on TF32 planes (the textbook 3xTF32 form; per-product error 2^-22 instead of
+ * 2^-19, which matters only where a single product, not a sum of many, must be right to the last
+ * bits). */
+B200_API int b200_set_correction_policy(b200_ctx *ctx, int policy);
 
 /* Optional per-launch timing.  While enabled, every kernel launch of this context is
  * bracketed by a pair of CUDA events on its stream.  b200_profile_read synchronises the

@@ -46,6 +46,7 @@ SIGNATURES = {
     "b200_gemm_3xtf32_noalloc": (_int, [_vp, _int, _int, _vp, _vp, _vp, _u32, _u32, _u32, _int, _vp]),
     "b200_set_path_policy": (_int, [_vp, _int]),
     "b200_set_pair_policy": (_int, [_vp, _int]),
+    "b200_set_correction_policy": (_int, [_vp, _int]),
     "b200_profile_enable": (_int, [_vp, _int]),
     "b200_profile_read": (_int, [_vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_u64)]),
     "b200_launch_count": (_int, [_vp, ctypes.POINTER(_u64)]),
@@ -160,6 +161,10 @@ class Context:
 
     def set_path_policy(self, policy):
         _check(lib().b200_set_path_policy(self._h, policy), "set_path_policy")
+
+    def set_correction_policy(self, policy):
+        """fp32 mode: 0 = correction passes on the bf16 pipe (default), 1 = TF32 planes throughout."""
+        _check(lib().b200_set_correction_policy(self._h, policy), "set_correction_policy")
 
     def set_pair_policy(self, policy):
         _check(lib().b200_set_pair_policy(self._h, policy), "set_pair_policy")

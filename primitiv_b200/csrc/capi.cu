@@ -156,6 +156,12 @@ int b200_set_pair_policy(b200_ctx *ctx, int policy) {
   return B200_OK;
 }
 
+int b200_set_correction_policy(b200_ctx *ctx, int policy) {
+  if (!ctx || policy < 0 || policy > 1) return B200_ERR_INVALID_ARG;
+  ctx->correction_policy = policy;
+  return B200_OK;
+}
+
 int b200_profile_enable(b200_ctx *ctx, int on) {
   if (!ctx) return B200_ERR_INVALID_ARG;
   ctx->profiling = on != 0;

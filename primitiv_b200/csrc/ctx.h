@@ -93,6 +93,7 @@ struct b200_ctx {
   int debug_stage_cap = 0;       // development: cap on pipeline stages (0 = none)
   int pair_policy = 0;           // 0 = CTA pairs (cta_group::2) when the problem allows, 1 = single CTAs only
   int split_policy = 0;          // 0 = split k over idle CTAs when there are few output tiles, 1 = never
+  int correction_policy = 0;     // fp32 mode: 0 = correction passes on the bf16 pipe, 1 = TF32 planes throughout
   std::uint64_t rng_seed = 0, rng_calls = 0;  // Philox key and fill counter (b200_seed / b200_random)
   // optional per-launch timing (b200_profile_*): event pairs, summed when read
   bool profiling = false;

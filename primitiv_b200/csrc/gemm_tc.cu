@@ -91,6 +91,8 @@ constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s at boost cloc
 struct alignas(64) TcParams {
   CUtensorMap mapA[2];  // [0] = values (or hi plane), [1] = lo plane
   CUtensorMap mapB[2];
+  CUtensorMap mapA8[2];  // kind 4: bf16 planes of the correction passes, [0] = hi8, [1] = lo8
+  CUtensorMap mapB8[2];
   void *C;
   unsigned long long c_gs;
   uint32_t m, n, k;
@@ -106,6 +108,8 @@ struct alignas(64) TcParams {
   uint32_t lbo_a, sbo_a, lbo_b, sbo_b;
   uint32_t layout_a, layout_b;  // descriptor swizzle field
   uint32_t idesc;
+  uint32_t idesc8;          // kind 4: instruction descriptor of the bf16 correction passes
+  uint32_t a8_bytes, b8_bytes;  // kind 4: bytes of one bf16 plane of A / of B in a stage (per CTA)
   uint32_t passes;
   uint32_t chunk_kblocks;  // k-blocks per accumulation chunk
   uint32_t accumulate, out_half, kind_f16;
@@ -266,6 +270,49 @@ __device__ __forceinline__ void mma_stage(uint32_t d_tmem, uint32_t sa, uint32_t
   }
 }
 
+// One k-block of the fp32 mode with bf16 correction passes (kind 4), as one basic block of
+// 8 MMAs: (lo8, hi8) and (hi8, lo8) on the bf16 pipe, two k-steps of 16 each, then (hi, hi) in
+// TF32, four k-steps of 8 -- small terms first, all into the same fp32 accumulator.  A stage
+// holds [A hi | A hi8 | A lo8 | B hi | B hi8 | B lo8]; the bf16 planes are K-major rows of 64
+// bytes under the 64-byte swizzle (descriptor layout 4, 8-row groups 512 bytes apart).
+template <int kCtas>
+__device__ __forceinline__ void mma_stage_mix(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t a_plane,
+                                              uint32_t b_plane, uint32_t a8, uint32_t b8, uint32_t hi_desc,
+                                              uint32_t hi8_desc, uint32_t idesc, uint32_t idesc8, bool first) {
+  uint32_t acc = first ? 0u : 1u;
+  {
+    uint32_t a_lo = ((sa + a_plane + a8) & 0x3FFFFu) >> 4;   // A lo8
+    uint32_t b_lo = ((sb + b_plane) & 0x3FFFFu) >> 4;        // B hi8
+#pragma unroll
+    for (uint32_t ks = 0; ks < 2u; ++ks) {
+      mma_issue<kCtas, true>(d_tmem, a_lo, hi8_desc, b_lo, hi8_desc, idesc8, acc);
+      acc = 1u;
+      a_lo += 2u;  // 32 bytes of k, in 16-byte units
+      b_lo += 2u;
+    }
+  }
+  {
+    uint32_t a_lo = ((sa + a_plane) & 0x3FFFFu) >> 4;        // A hi8
+    uint32_t b_lo = ((sb + b_plane + b8) & 0x3FFFFu) >> 4;   // B lo8
+#pragma unroll
+    for (uint32_t ks = 0; ks < 2u; ++ks) {
+      mma_issue<kCtas, true>(d_tmem, a_lo, hi8_desc, b_lo, hi8_desc, idesc8, 1u);
+      a_lo += 2u;
+      b_lo += 2u;
+    }
+  }
+  {
+    uint32_t a_lo = (sa & 0x3FFFFu) >> 4;                    // A hi
+    uint32_t b_lo = (sb & 0x3FFFFu) >> 4;                    // B hi
+#pragma unroll
+    for (uint32_t ks = 0; ks < kKSteps; ++ks) {
+      mma_issue<kCtas, false>(d_tmem, a_lo, hi_desc, b_lo, hi_desc, idesc, 1u);
+      a_lo += 2u;
+      b_lo += 2u;
+    }
+  }
+}
+
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile(
       "{\n\t"
@@ -421,9 +468,12 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uin
 // single-CTA tile, which is what bounds this kernel.
 template <bool kChunked, int kCtas, int kKind>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ TcParams p) {
-  constexpr int kPasses = (kKind == 0 || kKind == 3) ? 3 : 1;  // kind 0 = 3xTF32, 1 = TF32, 2 = FP16, 3 = 3xFP16
+  // kind 0 = 3xTF32 (hi / lo TF32 planes), 1 = TF32, 2 = FP16, 3 = 3xFP16,
+  // 4 = fp32 via one TF32 pass plus two bf16 correction passes (hi, hi8, lo8 planes)
+  constexpr int kPasses = (kKind == 0 || kKind == 3 || kKind == 4) ? 3 : 1;
   constexpr uint32_t kSubs = kPasses == 1 ? 2u : 1u;  // k-blocks per pipeline stage
-  constexpr bool kF16 = kKind >= 2;
+  constexpr bool kF16 = kKind == 2 || kKind == 3;
+  constexpr bool kMix = kKind == 4;
   static_assert(!kChunked || kPasses == 3, "only the three-pass products are chunked");
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
@@ -500,19 +550,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       // this lane's box: [sub][plane][A boxes..., B boxes...]
       const uint32_t a_boxes = p.a_mn_major ? p.a_chunks : 1u, b_boxes = p.b_mn_major ? p.b_chunks : 1u;
       const uint32_t per_plane = a_boxes + b_boxes;
-      const uint32_t nboxes = kSubs * planes * per_plane;  // <= 32, checked on the host
+      // kind 4: six K-major boxes per stage, lanes 0-2 = A {hi, hi8, lo8}, lanes 3-5 = B {hi, hi8, lo8}
+      const uint32_t nboxes = kMix ? 6u : kSubs * planes * per_plane;  // <= 32, checked on the host
       const bool has_box = lane < nboxes;
-      const uint32_t bsub = lane / (planes * per_plane), brem = lane % (planes * per_plane);
-      const uint32_t bpl = (brem / per_plane) & 1u, bidx = brem % per_plane;
-      const bool is_b = bidx >= a_boxes;
-      const uint32_t bchunk = is_b ? bidx - a_boxes : bidx;
-      const bool box_mn = is_b ? p.b_mn_major != 0u : p.a_mn_major != 0u;
-      const uint32_t box_dst = bsub * p.sub_bytes +
-                               (is_b ? planes * p.a_stage_bytes + bpl * p.b_stage_bytes + bchunk * p.b_chunk_bytes
-                                     : bpl * p.a_stage_bytes + bchunk * p.a_chunk_bytes);
+      const uint32_t bsub = kMix ? 0u : lane / (planes * per_plane), brem = lane % (planes * per_plane);
+      const uint32_t bpl = kMix ? lane % 3u : (brem / per_plane) & 1u, bidx = brem % per_plane;
+      const bool is_b = kMix ? lane >= 3u : bidx >= a_boxes;
+      const uint32_t bchunk = kMix ? 0u : (is_b ? bidx - a_boxes : bidx);
+      const bool box_mn = kMix ? false : (is_b ? p.b_mn_major != 0u : p.a_mn_major != 0u);
+      const uint32_t box_dst =
+          kMix ? (is_b ? 2u * p.a_stage_bytes + (bpl == 0u ? 0u : p.b_stage_bytes + (bpl - 1u) * p.b8_bytes)
+                       : (bpl == 0u ? 0u : p.a_stage_bytes + (bpl - 1u) * p.a8_bytes))
+               : bsub * p.sub_bytes +
+                     (is_b ? planes * p.a_stage_bytes + bpl * p.b_stage_bytes + bchunk * p.b_chunk_bytes
+                           : bpl * p.a_stage_bytes + bchunk * p.a_chunk_bytes);
       const int box_k = static_cast<int>(bsub * p.bk);
       const int box_mn_off = static_cast<int>(box_mn ? bchunk * (is_b ? p.b_chunk_elems : p.a_chunk_elems) : 0u);
-      const CUtensorMap *box_map = is_b ? &p.mapB[bpl] : &p.mapA[bpl];
+      const CUtensorMap *box_map =
+          kMix ? (bpl == 0u ? (is_b ? &p.mapB[0] : &p.mapA[0]) : (is_b ? &p.mapB8[(bpl - 1u) & 1u] : &p.mapA8[(bpl - 1u) & 1u]))
+               : (is_b ? &p.mapB[bpl] : &p.mapA[bpl]);
       for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         uint32_t vg, mt, nt;
         tile_coords(tile, p.tiles_m, p.tiles_n, p.band_m, vg, mt, nt);
@@ -586,6 +642,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       const uint32_t a_plane = p.a_stage_bytes, b_plane = p.b_stage_bytes, b_off = planes * p.a_stage_bytes;
       const uint32_t idesc = p.idesc, nstages = p.stages, dbg = kDevKnobs ? p.debug : 0u;
       const uint32_t chunk_kblocks = p.chunk_kblocks, bn = p.bn;
+      // kind 4: descriptor high half of the bf16 planes (8-row groups 512 bytes apart, 64-byte swizzle)
+      const uint32_t hi8_desc = ((512u >> 4) & 0x3FFFu) | (1u << 14) | (4u << 29);
+      const uint32_t idesc8 = p.idesc8, a8 = p.a8_bytes, b8 = p.b8_bytes;
       for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         uint32_t kb_left = kb_per_tile;
         for (uint32_t c = 0; ok && c < chunks_per_tile; ++c, ++chunk_no) {
@@ -611,8 +670,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 #pragma unroll
               for (uint32_t sub = 0; sub < kSubs; ++sub) {
                 const uint32_t ssa = sa + sub * sub_bytes;
-                mma_stage<kCtas, kF16, kPasses>(d_tmem, ssa, ssa + b_off, a_plane, b_plane, a_hi, b_hi, a_lo_fixed,
-                                                b_lo_fixed, kstep_a, kstep_b, idesc, (it | sub) == 0u);
+                if constexpr (kMix)
+                  mma_stage_mix<kCtas>(d_tmem, ssa, ssa + b_off, a_plane, b_plane, a8, b8, a_hi, hi8_desc, idesc,
+                                       idesc8, it == 0u);
+                else
+                  mma_stage<kCtas, kF16, kPasses>(d_tmem, ssa, ssa + b_off, a_plane, b_plane, a_hi, b_hi, a_lo_fixed,
+                                                  b_lo_fixed, kstep_a, kstep_b, idesc, (it | sub) == 0u);
               }
             }
             // frees the stage (in both CTAs of a pair) when these MMAs retire
@@ -810,7 +873,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
 }
 
 int encode_map(const b200_ctx *ctx, CUtensorMap *map, const void *ptr, const OperandView &v,
-               int ebytes, uint32_t box_mn, uint32_t box_k, CUtensorMapSwizzle swz) {
+               int ebytes, uint32_t box_mn, uint32_t box_k, CUtensorMapSwizzle swz, bool bf16 = false) {
   const uint64_t d0 = v.mn_major ? v.mn : v.k;
   const uint64_t d1 = v.mn_major ? v.k : v.mn;
   const uint32_t nb = v.nbatch > 0 ? v.nbatch : 1;
@@ -818,8 +881,9 @@ int encode_map(const b200_ctx *ctx, CUtensorMap *map, const void *ptr, const Ope
   cuuint64_t strides[2] = {v.ld * ebytes, (nb > 1 ? v.batch_stride : v.ld * d1) * ebytes};
   cuuint32_t box[3] = {v.mn_major ? box_mn : box_k, v.mn_major ? box_k : box_mn, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  const CUtensorMapDataType dt =
-      ebytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const CUtensorMapDataType dt = bf16          ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : ebytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   const CUresult r = ctx->encode_tiled(map, dt, 3, const_cast<void *>(ptr), dims, strides, box, estr,
                                        CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -879,6 +943,9 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   const bool f16 = half_store || split16;                  // what the tensor core is fed: kind::f16
   const int eb = f16 ? 2 : 4;                              // bytes of a tensor-core operand element
   const uint32_t passes = (g.mode == B200_MODE_FP32_3XTF32 || split16) ? 3u : 1u;
+  // fp32 mode: the two correction passes on the bf16 pipe (hi / hi8 / lo8 planes) unless the
+  // context asks for TF32 planes throughout
+  const bool mix = g.mode == B200_MODE_FP32_3XTF32 && ctx->correction_policy == 0;
 
   TcParams p;
   memset(&p, 0, sizeof(p));
@@ -909,8 +976,25 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   stride_pattern(g.b_gs, g.b_rs, g.groups, g.red, &vb.batch_stride, &vb.nbatch, &p.b_gmul, &p.b_rmul);
 
   const void *a_src[2] = {g.A, nullptr}, *b_src[2] = {g.B, nullptr};
+  const void *a_mix[3] = {nullptr, nullptr, nullptr}, *b_mix[3] = {nullptr, nullptr, nullptr};
   void *scratch = nullptr;
-  if (split16) {
+  if (mix) {
+    const MixPlanes la = mix_planes(va), lb = mix_planes(vb);
+    const uint64_t total = la.floats() + lb.floats();
+    float *cursor = nullptr;
+    if (fixed_scratch) {
+      if (total > fixed_elems) return B200_ERR_TOO_LARGE;
+      cursor = fixed_scratch;
+    } else {
+      int rc = ctx->pool.alloc(total * sizeof(float), &scratch, nullptr);
+      if (rc != B200_OK) return rc;
+      cursor = static_cast<float *>(scratch);
+    }
+    pack_mix(ctx, stream, va, cursor, la, a_mix);
+    pack_mix(ctx, stream, vb, cursor + la.floats(), lb, b_mix);
+    a_src[0] = a_mix[0];
+    b_src[0] = b_mix[0];
+  } else if (split16) {
     // row maxima and two half planes per operand, all in one scratch block
     if (fixed_scratch) return B200_ERR_INVALID_ARG;  // the allocation-free entry point is 3xTF32 only
     const F16Planes la = f16_planes(va, p.a_rmul != 0u), lb = f16_planes(vb, p.b_rmul != 0u);
@@ -963,6 +1047,8 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   p.a_stage_bytes = kBM * 128u;
   p.b_stage_bytes = b_rows * 128u;
   p.sub_bytes = planes * (p.a_stage_bytes + p.b_stage_bytes);
+  p.a8_bytes = kBM * 64u;     // kind 4: the two bf16 planes of an operand together fill one TF32 plane's room
+  p.b8_bytes = b_rows * 64u;
   // Single-pass modes issue only four MMAs per k-block: their pipeline stage holds two k-blocks
   // (a k-block past the end of k is zero-filled by TMA and adds nothing), 3xTF32 stages hold one.
   p.subs = passes == 1 ? 2u : 1u;
@@ -1036,6 +1122,8 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   const uint32_t fmt = f16 ? 0u : 2u;  // F16 = 0 (kind::f16), TF32 = 2 (kind::tf32)
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (p.a_mn_major << 15) | (p.b_mn_major << 16) |
             ((p.bn >> 3) << 17) | ((tile_m >> 4) << 24);
+  // bf16 x bf16 -> fp32, both operands K-major (kind::f16 with format 1 = BF16)
+  p.idesc8 = (1u << 4) | (1u << 7) | (1u << 10) | ((p.bn >> 3) << 17) | ((tile_m >> 4) << 24);
   p.passes = passes;
   const bool chunked = passes == 3 && static_cast<uint64_t>(g.red) * p.kblocks > kChunkKBlocks;
   p.chunk_kblocks = chunked ? kChunkKBlocks : g.red * p.kblocks;
@@ -1078,10 +1166,16 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   p.stages = stages;
   const size_t smem_bytes = static_cast<size_t>(stages) * p.stage_bytes + 1024;
 
-  for (int i = 0; i < (passes == 3 ? 2 : 1) && rc == B200_OK; ++i) {
+  for (int i = 0; i < ((passes == 3 && !mix) ? 2 : 1) && rc == B200_OK; ++i) {
     rc = encode_map(ctx, &p.mapA[i], a_src[i], va, eb, p.a_mn_major ? chunk : kBM, p.bk, swz_a);
     if (rc == B200_OK)
       rc = encode_map(ctx, &p.mapB[i], b_src[i], vb, eb, p.b_mn_major ? chunk : b_rows, p.bk, swz_b);
+  }
+  for (int i = 0; mix && i < 2 && rc == B200_OK; ++i) {
+    // the bf16 planes share the packed operand's indexing: rows of bk elements = 64 bytes, 64-byte swizzle
+    rc = encode_map(ctx, &p.mapA8[i], a_mix[1 + i], va, 2, kBM, p.bk, CU_TENSOR_MAP_SWIZZLE_64B, true);
+    if (rc == B200_OK)
+      rc = encode_map(ctx, &p.mapB8[i], b_mix[1 + i], vb, 2, b_rows, p.bk, CU_TENSOR_MAP_SWIZZLE_64B, true);
   }
   if (rc == B200_OK && !ctx->tc_smem_configured) {
     const int max_dyn = static_cast<int>(ctx->smem_optin - 512);
@@ -1101,6 +1195,10 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     allow(gemm_tc_kernel<false, 1, 3>);
     allow(gemm_tc_kernel<true, 2, 3>);
     allow(gemm_tc_kernel<false, 2, 3>);
+    allow(gemm_tc_kernel<true, 1, 4>);
+    allow(gemm_tc_kernel<false, 1, 4>);
+    allow(gemm_tc_kernel<true, 2, 4>);
+    allow(gemm_tc_kernel<false, 2, 4>);
     if (e != cudaSuccess) rc = static_cast<int>(e);
     ctx->tc_smem_configured = (e == cudaSuccess);
   }
@@ -1124,13 +1222,19 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
       cfg.attrs = &attr;
       cfg.numAttrs = 1;
       cudaError_t e;
-      if (split16 && chunked) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, 2, 3>, p);
+      if (mix && chunked) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, 2, 4>, p);
+      else if (mix) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 4>, p);
+      else if (split16 && chunked) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, 2, 3>, p);
       else if (split16) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 3>, p);
       else if (chunked) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, 2, 0>, p);
       else if (passes == 3) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 0>, p);
       else if (!f16) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 1>, p);
       else e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 2>, p);
       rc = static_cast<int>(e);
+    } else if (mix && chunked) {
+      gemm_tc_kernel<true, 1, 4><<<grid, kThreads, smem_bytes, stream>>>(p);
+    } else if (mix) {
+      gemm_tc_kernel<false, 1, 4><<<grid, kThreads, smem_bytes, stream>>>(p);
     } else if (split16 && chunked) {
       gemm_tc_kernel<true, 1, 3><<<grid, kThreads, smem_bytes, stream>>>(p);
     } else if (split16) {
@@ -1225,10 +1329,11 @@ int gemm_3xtf32_noalloc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream) {
   if (ctx->device < 0 || ctx->device >= kMaxDevices) return B200_ERR_INVALID_ARG;
   {
     // The documented limit, checked here so that it does not depend on how the operands end up
-    // being packed: hi and lo planes of both operands, k padded to 4, each plane rounded to 64.
-    const uint64_t kpad = (static_cast<uint64_t>(g.k) + 3ull) & ~3ull;
-    const uint64_t pa = (static_cast<uint64_t>(g.m) * kpad + 63ull) & ~63ull;
-    const uint64_t pb = (static_cast<uint64_t>(g.n) * kpad + 63ull) & ~63ull;
+    // being packed: 8 bytes per operand element (a float plane and two bf16 planes, or two float
+    // planes), k padded to 8, each plane rounded up to 128 elements.
+    const uint64_t kpad = (static_cast<uint64_t>(g.k) + 7ull) & ~7ull;
+    const uint64_t pa = (static_cast<uint64_t>(g.m) * kpad + 127ull) & ~127ull;
+    const uint64_t pb = (static_cast<uint64_t>(g.n) * kpad + 127ull) & ~127ull;
     if (2ull * (pa + pb) > kStaticScratchFloats) return B200_ERR_TOO_LARGE;
   }
   float *&addr = g_static_scratch_addr[ctx->device];

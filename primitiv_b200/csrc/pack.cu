@@ -1,6 +1,7 @@
 // Packing pre-pass of the tensor-core matrix product (see pack.h): the kernels that split fp32
 // operands into TF32 hi / lo planes (3xTF32, and TF32 for operands TMA cannot read where they
 // lie) or into row-scaled half planes (3xFP16), and the host code that picks among them.
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "pack.h"
@@ -356,6 +357,140 @@ __global__ void __launch_bounds__(256) pack_f16_transpose64_kernel(const float *
   }
 }
 
+// ---- pre-pass of the fp32 mode with bf16 correction passes (see MixPlanes in pack.h) ----
+
+struct Mix8 {   // eight consecutive k-elements of one row, split
+  float4 h0, h1;          // hi plane
+  uint4 h8, l8;           // hi8 and lo8 planes (8 bf16 each)
+};
+
+__device__ __forceinline__ uint32_t bf16_pair(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);   // a in the low half: lower address
+  return *reinterpret_cast<const uint32_t *>(&v);
+}
+
+__device__ __forceinline__ Mix8 mix_split8(const float (&x)[8]) {
+  float h[8], l[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    h[j] = rn_tf32(x[j]);
+    l[j] = x[j] - h[j];      // exact in fp32
+  }
+  Mix8 m;
+  m.h0 = make_float4(h[0], h[1], h[2], h[3]);
+  m.h1 = make_float4(h[4], h[5], h[6], h[7]);
+  m.h8 = make_uint4(bf16_pair(x[0], x[1]), bf16_pair(x[2], x[3]), bf16_pair(x[4], x[5]), bf16_pair(x[6], x[7]));
+  m.l8 = make_uint4(bf16_pair(l[0], l[1]), bf16_pair(l[2], l[3]), bf16_pair(l[4], l[5]), bf16_pair(l[6], l[7]));
+  return m;
+}
+
+// A K-major source whose rows need no padding (k % 8 == 0) and whose matrices are back to back is
+// one flat array with the planes' own layout: the split is elementwise, eight elements per thread.
+__global__ void __launch_bounds__(256) pack_mix_flat_kernel(const float4 *__restrict__ src, float4 *__restrict__ hi,
+                                                            uint4 *__restrict__ h8, uint4 *__restrict__ l8,
+                                                            unsigned long long n8) {
+  const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
+  for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
+       i += stride) {
+    const float4 u = src[2 * i], v = src[2 * i + 1];
+    const float x[8] = {u.x, u.y, u.z, u.w, v.x, v.y, v.z, v.w};
+    const Mix8 m = mix_split8(x);
+    hi[2 * i] = m.h0;
+    hi[2 * i + 1] = m.h1;
+    h8[i] = m.h8;
+    l8[i] = m.l8;
+  }
+}
+
+// An MN-major source with mn % 4 == 0 and k % 8 == 0: 64 x 64 tiles through shared memory,
+// float4 reads along mn, 16- and 32-byte writes along k.
+__global__ void __launch_bounds__(256) pack_mix_transpose64_kernel(const float *__restrict__ src, float *__restrict__ hi,
+                                                                   __nv_bfloat16 *__restrict__ h8,
+                                                                   __nv_bfloat16 *__restrict__ l8, uint32_t mn,
+                                                                   uint32_t k, unsigned long long src_bs,
+                                                                   uint32_t tiles_mn, uint32_t tiles_k,
+                                                                   unsigned long long total_tiles) {
+  __shared__ float tile[64][65];  // [k][mn]
+  const uint32_t t = threadIdx.x;
+  for (unsigned long long tl = blockIdx.x; tl < total_tiles; tl += gridDim.x) {
+    const unsigned long long per_b = static_cast<unsigned long long>(tiles_mn) * tiles_k;
+    const unsigned long long b = tl / per_b;
+    const uint32_t rem = static_cast<uint32_t>(tl - b * per_b);
+    const uint32_t i0 = (rem % tiles_mn) * 64u, p0 = (rem / tiles_mn) * 64u;
+    const float *s = src + b * src_bs;
+    const unsigned long long dst_b = b * static_cast<unsigned long long>(mn) * k;
+#pragma unroll
+    for (uint32_t r = 0; r < 4u; ++r) {
+      const uint32_t e = t + r * 256u;
+      const uint32_t pk = e >> 4, im = (e & 15u) * 4u;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p0 + pk < k && i0 + im < mn)
+        v = *reinterpret_cast<const float4 *>(s + static_cast<unsigned long long>(p0 + pk) * mn + i0 + im);
+      tile[pk][im] = v.x; tile[pk][im + 1] = v.y; tile[pk][im + 2] = v.z; tile[pk][im + 3] = v.w;
+    }
+    __syncthreads();
+    // 64 mn-rows x 8 groups of 8 k = 512 groups, 2 per thread
+#pragma unroll
+    for (uint32_t r = 0; r < 2u; ++r) {
+      const uint32_t e = t + r * 256u;
+      const uint32_t im = e >> 3, pk = (e & 7u) * 8u;
+      if (i0 + im < mn && p0 + pk < k) {
+        float x[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = tile[pk + j][im];
+        const Mix8 m = mix_split8(x);
+        const unsigned long long o = dst_b + static_cast<unsigned long long>(i0 + im) * k + p0 + pk;
+        *reinterpret_cast<float4 *>(hi + o) = m.h0;
+        *reinterpret_cast<float4 *>(hi + o + 4) = m.h1;
+        *reinterpret_cast<uint4 *>(h8 + o) = m.h8;
+        *reinterpret_cast<uint4 *>(l8 + o) = m.l8;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Any other source (unaligned, ragged k, strided batches): 32 x 32 tiles, one element per thread
+// and step, row stride k_pad in the planes.  Same indexing as pack_tf32_kernel.
+template <bool kTranspose>
+__global__ void __launch_bounds__(256) pack_mix_kernel(const float *__restrict__ src, float *__restrict__ hi,
+                                                       __nv_bfloat16 *__restrict__ h8, __nv_bfloat16 *__restrict__ l8,
+                                                       uint32_t mn, uint32_t k, uint32_t k_pad, unsigned long long ld,
+                                                       unsigned long long src_bs, uint32_t tiles_mn, uint32_t tiles_k,
+                                                       unsigned long long total_tiles) {
+  __shared__ float tile[32][33];
+  const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;  // 32 x 8
+  for (unsigned long long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    const unsigned long long per_b = static_cast<unsigned long long>(tiles_mn) * tiles_k;
+    const unsigned long long b = t / per_b;
+    const uint32_t rem = static_cast<uint32_t>(t - b * per_b);
+    const uint32_t i0 = (rem % tiles_mn) * 32u, p0 = (rem / tiles_mn) * 32u;
+    const float *s = src + b * src_bs;
+    const unsigned long long dst_b = b * static_cast<unsigned long long>(mn) * k_pad;
+    if (kTranspose) {
+#pragma unroll
+      for (uint32_t j = 0; j < 32u; j += 8u) {
+        const uint32_t i = i0 + tx, pp = p0 + ty + j;
+        tile[ty + j][tx] = (i < mn && pp < k) ? s[static_cast<unsigned long long>(pp) * ld + i] : 0.f;
+      }
+      __syncthreads();
+    }
+#pragma unroll
+    for (uint32_t j = 0; j < 32u; j += 8u) {
+      const uint32_t i = i0 + ty + j, pp = p0 + tx;
+      if (i < mn && pp < k) {
+        const float x = kTranspose ? tile[tx][ty + j] : s[static_cast<unsigned long long>(i) * ld + pp];
+        const float h = rn_tf32(x);
+        const unsigned long long o = dst_b + static_cast<unsigned long long>(i) * k_pad + pp;
+        hi[o] = h;
+        h8[o] = __float2bfloat16_rn(x);
+        l8[o] = __float2bfloat16_rn(x - h);
+      }
+    }
+    if (kTranspose) __syncthreads();
+  }
+}
+
 }  // namespace
 
 Tf32Planes tf32_planes(const OperandView &v) {
@@ -402,6 +537,62 @@ void pack_tf32(b200_ctx *ctx, cudaStream_t stream, OperandView &v, bool two_plan
   ++ctx->launches;
   planes_out[0] = hi;
   planes_out[1] = lo;
+  v.ptr = hi;
+  v.mn_major = false;
+  v.ld = lay.kpad;
+  v.batch_stride = static_cast<uint64_t>(v.mn) * lay.kpad;
+}
+
+MixPlanes mix_planes(const OperandView &v) {
+  MixPlanes lay;
+  lay.kpad = (v.k + 7u) & ~7u;
+  const uint64_t n = static_cast<uint64_t>(v.nbatch) * v.mn * lay.kpad;
+  lay.hi_elems = (n + 63ull) & ~63ull;
+  lay.h8_elems = (n + 127ull) & ~127ull;
+  return lay;
+}
+
+void pack_mix(b200_ctx *ctx, cudaStream_t stream, OperandView &v, float *dst, const MixPlanes &lay,
+              const void *planes_out[3]) {
+  float *hi = dst;
+  __nv_bfloat16 *h8 = reinterpret_cast<__nv_bfloat16 *>(dst + lay.hi_elems);
+  __nv_bfloat16 *l8 = h8 + lay.h8_elems;
+  const bool src_ok = (reinterpret_cast<uintptr_t>(v.ptr) & 15u) == 0 && v.k % 8u == 0 &&
+                      (v.nbatch <= 1 || v.batch_stride % 4u == 0);
+  const bool dense = v.nbatch <= 1 || v.batch_stride == static_cast<uint64_t>(v.mn) * v.k;
+  const float *src = static_cast<const float *>(v.ptr);
+  {
+    ProfScope prof(ctx, kProfPack, stream);
+    if (!v.mn_major && src_ok && dense && v.ld == v.k) {
+      const unsigned long long n8 = static_cast<unsigned long long>(v.nbatch) * v.mn * v.k / 8ull;
+      const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
+      const unsigned long long need = (n8 + 255ull) / 256ull;
+      pack_mix_flat_kernel<<<static_cast<unsigned>(need < cap ? need : cap), 256, 0, stream>>>(
+          reinterpret_cast<const float4 *>(src), reinterpret_cast<float4 *>(hi), reinterpret_cast<uint4 *>(h8),
+          reinterpret_cast<uint4 *>(l8), n8);
+    } else if (v.mn_major && src_ok && v.mn % 4u == 0 && v.ld == v.mn) {
+      const uint32_t tiles_mn = (v.mn + 63u) / 64u, tiles_k = (v.k + 63u) / 64u;
+      const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
+      const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 8ull;
+      pack_mix_transpose64_kernel<<<static_cast<unsigned>(tt < cap ? tt : cap), 256, 0, stream>>>(
+          src, hi, h8, l8, v.mn, v.k, v.batch_stride, tiles_mn, tiles_k, tt);
+    } else {
+      const uint32_t tiles_mn = (v.mn + 31u) / 32u, tiles_k = (v.k + 31u) / 32u;
+      const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
+      const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
+      const unsigned blocks = static_cast<unsigned>(tt < cap ? tt : cap);
+      if (v.mn_major)
+        pack_mix_kernel<true><<<blocks, 256, 0, stream>>>(src, hi, h8, l8, v.mn, v.k, lay.kpad, v.ld, v.batch_stride,
+                                                         tiles_mn, tiles_k, tt);
+      else
+        pack_mix_kernel<false><<<blocks, 256, 0, stream>>>(src, hi, h8, l8, v.mn, v.k, lay.kpad, v.ld, v.batch_stride,
+                                                          tiles_mn, tiles_k, tt);
+    }
+  }
+  ++ctx->launches;
+  planes_out[0] = hi;
+  planes_out[1] = h8;
+  planes_out[2] = l8;
   v.ptr = hi;
   v.mn_major = false;
   v.ld = lay.kpad;

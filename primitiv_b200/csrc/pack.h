@@ -36,6 +36,26 @@ Tf32Planes tf32_planes(const OperandView &v);
 void pack_tf32(b200_ctx *ctx, cudaStream_t stream, OperandView &v, bool two_planes, float *dst,
                const Tf32Planes &lay, const void *planes_out[2]);
 
+// ---- planes of the fp32 mode whose correction passes run on the bf16 pipe -------------------
+// x = hi + lo with hi = rn_tf32(x) exactly as above; the product a.b ~ a_hi.b_hi + a_lo.b_hi + a_hi.b_lo
+// needs the two small terms only to a few digits (they are 2^-11 of the result), so their operands
+// are carried as bf16, which the tensor core multiplies at twice the TF32 rate:
+//   hi  = rn_tf32(x)        float plane, operand of the kind::tf32 pass
+//   hi8 = rn_bf16(x)        bf16 plane,  operand of the kind::f16 correction passes
+//   lo8 = rn_bf16(x - hi)   bf16 plane
+// Same 8 bytes per element as two TF32 planes.  All three are K-major [b][i][kpad] with kpad = k
+// rounded up to 8 (16-byte rows in the bf16 planes), laid out [hi][hi8][lo8] in one block.
+struct MixPlanes {
+  uint64_t hi_elems;   // floats in the hi plane, rounded up to 64
+  uint64_t h8_elems;   // bf16 elements in each of the two bf16 planes, rounded up to 128
+  uint32_t kpad;
+  uint64_t floats() const { return hi_elems + h8_elems; }  // the whole block, in floats
+};
+MixPlanes mix_planes(const OperandView &v);
+// planes_out = {hi, hi8, lo8}; v is rewritten to describe the packed operand (K-major, ld = kpad).
+void pack_mix(b200_ctx *ctx, cudaStream_t stream, OperandView &v, float *dst, const MixPlanes &lay,
+              const void *planes_out[3]);
+
 // ---- half planes of the 3xFP16 mode: [row maxima][h0 plane][h1 plane], rows of kpad halves ----
 struct F16Planes {
   uint64_t plane_halves;  // halves per plane, rounded up to 128

@@ -108,6 +108,48 @@ def test_random_shapes_against_fp64_oracle(ctx, shape, mode):
     _check_all(ctx, mode, a, b, gy, di, dj, dk, ba, bb)
 
 
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_fp32_mode_with_tf32_planes_throughout(ctx, shape):
+    """The fp32 mode runs its two correction passes on bf16 planes by default (every other test of
+    mode 3xtf32 in this file); b200_set_correction_policy(1) keeps all three passes on TF32 planes.
+    Same shapes, same 1e-5 bound, tensor-core kernel forced."""
+    di, dj, dk, ba, bb = shape
+    rng = np.random.default_rng(hash(shape) % (2 ** 32))
+    a = rng.uniform(-1, 1, di * dj * ba).astype(np.float32)
+    b = rng.uniform(-1, 1, dj * dk * bb).astype(np.float32)
+    gy = rng.standard_normal(di * dk * max(ba, bb)).astype(np.float32)
+    ctx.set_correction_policy(1)
+    ctx.set_path_policy(2)
+    try:
+        _check_all(ctx, "3xtf32", a, b, gy, di, dj, dk, ba, bb)
+    finally:
+        ctx.set_correction_policy(0)
+        ctx.set_path_policy(0)
+
+
+def test_correction_policies_per_product_error(ctx):
+    """What the two policies differ in: with positive operands (no cancellation) and a contraction of
+    only 8 terms, every element's relative error is bounded by the per-product error of the
+    split: about 2^-19 with bf16 correction operands, 2^-22 with TF32 ones."""
+    di, dj, dk = 256, 8, 256
+    rng = np.random.default_rng(21)
+    a = rng.uniform(1, 2, di * dj).astype(np.float32)
+    b = rng.uniform(1, 2, dj * dk).astype(np.float32)
+    y64 = ol.fw_f64(a, b, di, dj, dk, 1, 1)
+    worst = {}
+    ctx.set_path_policy(2)
+    try:
+        for policy in (0, 1):
+            ctx.set_correction_policy(policy)
+            y = matmul_fw(ctx, pb.MODE_FP32_3XTF32, a, b, di, dj, dk, 1, 1)
+            worst[policy] = float(np.max(np.abs(y - y64) / np.abs(y64)))
+    finally:
+        ctx.set_correction_policy(0)
+        ctx.set_path_policy(0)
+    assert worst[0] <= 4e-6 and worst[1] <= 1e-6, worst
+    assert worst[1] < worst[0], worst
+
+
 @pytest.mark.parametrize("mode", list(MODES))
 def test_plumbing_workload(ctx, mode):
     """W {256,256} broadcast, X {256,64}x16, gy N(0,1), all from one mt19937(0); gradients pre-filled 0.5."""
