@@ -52,6 +52,8 @@ METRIC = "matmul_fw_bw_gflops"
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemm_tc_kernel launch on the batch-2 square case
 # (profiles/gemm_tc_kernel_3xtf32_batch2_ncu_full.md): 1.41 GB overwriting, 1.55 GB accumulating
 NCU_DRAM_BYTES_PER_LAUNCH_BATCH2 = 1.48e9
+# plane memory the library may keep between the forward and the backward call of a step
+PLANE_CACHE_BYTES = 8 << 30
 
 
 class Workload:
@@ -117,7 +119,9 @@ class Workload:
                 "batch_per_gpu": self.bs, "global_batch": self.bs * n_gpus, "mode": self.mode_name,
                 "flops_per_step_per_gpu": self.flops,
                 "l2": "every batched operand (>= 512 MiB) is larger than L2 (126 MB); no flush needed",
-                "parallelism": "batch-sharded x%d" % n_gpus, "collective": collective}
+                "parallelism": "batch-sharded x%d" % n_gpus, "collective": collective,
+                "operand_planes": "fp32 mode: the planes the forward call packs from a and b are reused by the backward "
+                                  "call of the same step and dropped at the start of the next"}
 
 
 def measured_peaks():
@@ -362,12 +366,20 @@ def run_workload(rig, wl, steps, warmup):
     gba = 1 if wl.ba == 1 else wl.ba * rig.world
     gbb = 1 if wl.bb == 1 else wl.bb * rig.world
     sm = rig.sharded(rig.mode(wl.mode_name))
+    rig.ctx.operand_cache_enable(PLANE_CACHE_BYTES)
 
     def step():
+        # a step starts from operands the library has not seen (in training the weights have just been
+        # updated and the minibatch is new): planes kept from the previous step are dropped.  Within
+        # the step the backward call reuses the planes the forward call packed from the same a and b.
+        rig.ctx.operand_cache_invalidate()
         sm.forward(a, b, y, wl.di, wl.dj, wl.dk, gba, gbb)
         sm.backward(a, b, gy, ga, gb, wl.di, wl.dj, wl.dk, gba, gbb)
 
-    return rig.timed(step, steps, warmup, sm), (a, b, gy)
+    try:
+        return rig.timed(step, steps, warmup, sm), (a, b, gy)
+    finally:
+        rig.ctx.operand_cache_enable(0)
 
 
 def peak_divisor(mode_name, half):
@@ -491,13 +503,18 @@ def leg_mlp_products(rig, steps, warmup, peaks):
     gb = B * rig.world
 
     def step():
+        rig.ctx.operand_cache_invalidate()      # as in run_workload: nothing is carried from step to step
         for l, (rows, cols) in enumerate(MLP_LAYERS):
             sm.forward(ws[l], acts[l], acts[l + 1], rows, cols, 1, 1, gb)
         for l in range(len(MLP_LAYERS) - 1, -1, -1):
             rows, cols = MLP_LAYERS[l]
             sm.backward(ws[l], acts[l], gacts[l + 1], gws[l], gacts[l], rows, cols, 1, 1, gb)
 
-    res = rig.timed(step, steps, warmup, sm)
+    rig.ctx.operand_cache_enable(PLANE_CACHE_BYTES)
+    try:
+        res = rig.timed(step, steps, warmup, sm)
+    finally:
+        rig.ctx.operand_cache_enable(0)
     same = True
     if rig.dist is not None:      # replicas of a weight gradient hold the same bits on every rank
         parts = [torch.empty_like(gws[0]) for _ in range(rig.world)]

@@ -244,6 +244,29 @@ B200_API int b200_set_path_policy(b200_ctx *ctx, int policy);
  * columns, 1 = always one CTA per 128-row tile. */
 B200_API int b200_set_pair_policy(b200_ctx *ctx, int policy);
 
+/* ---- operand-plane cache (fp32 mode; no counterpart in the reference) ------------------------------
+ * In B200_MODE_FP32_3XTF32 every fp32 operand is split into three planes before the tensor cores see it
+ * (4 bytes read and 8 written per element).  A dense operand whose strides are multiples of 8 elements
+ * is split "flat": the planes repeat the array's own layout, so the same planes serve every use of the
+ * array, as either operand of any product.  Inside one call this is automatic (gy feeds both products
+ * of b200_matmul_bw; a, b and gy feed two products each in b200_matmul_fw_bw_host).  Across calls the
+ * library cannot know whether the array has changed in between, so the caller opts in:
+ *
+ *   b200_operand_cache_enable(ctx, max_bytes)   keep planes after the call that packed them, least
+ *        recently used first out above max_bytes of plane memory (pool memory, twice the operands'
+ *        size); 0 switches the cache off and frees it.  Typical use: a training step, where the
+ *        backward product receives the very arrays the forward product read.
+ *   b200_operand_cache_invalidate(ctx, ptr, bytes)   forget planes packed from any array that overlaps
+ *        [ptr, ptr + bytes); ptr == NULL forgets everything.  The caller MUST do this for every
+ *        array it (or anything other than the products of this library) writes while the cache is
+ *        on.  Two cases are handled inside: the output of b200_gemm / b200_matmul_*, and blocks
+ *        returned through b200_pool_free.  primitiv::devices::B200 calls it from the one place
+ *        where it hands out a mutable tensor pointer.
+ *   b200_operand_cache_stats   [0] hits, [1] misses, [2] bytes of planes held, [3] entries. */
+B200_API int b200_operand_cache_enable(b200_ctx *ctx, size_t max_bytes);
+B200_API int b200_operand_cache_invalidate(b200_ctx *ctx, const void *ptr, size_t bytes);
+B200_API int b200_operand_cache_stats(const b200_ctx *ctx, uint64_t stats[4]);
+
 /* Arithmetic of the two correction passes of B200_MODE_FP32_3XTF32.  With x = hi + lo, hi = x rounded
  * to TF32, a product is hi.hi + lo.hi + hi.lo.  The last two terms are 2^-11 of the result and need only
  * a few digits, so by default (0) their operands are carried as bf16 planes and multiplied on the

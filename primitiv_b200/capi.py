@@ -47,6 +47,9 @@ SIGNATURES = {
     "b200_set_path_policy": (_int, [_vp, _int]),
     "b200_set_pair_policy": (_int, [_vp, _int]),
     "b200_set_correction_policy": (_int, [_vp, _int]),
+    "b200_operand_cache_enable": (_int, [_vp, ctypes.c_size_t]),
+    "b200_operand_cache_invalidate": (_int, [_vp, _vp, ctypes.c_size_t]),
+    "b200_operand_cache_stats": (_int, [_vp, ctypes.POINTER(_u64)]),
     "b200_profile_enable": (_int, [_vp, _int]),
     "b200_profile_read": (_int, [_vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_u64)]),
     "b200_launch_count": (_int, [_vp, ctypes.POINTER(_u64)]),
@@ -161,6 +164,19 @@ class Context:
 
     def set_path_policy(self, policy):
         _check(lib().b200_set_path_policy(self._h, policy), "set_path_policy")
+
+    def operand_cache_enable(self, max_bytes):
+        """Keep the packed planes of fp32 operands between calls (0 = off); the caller then owes an
+        operand_cache_invalidate for every array it writes."""
+        _check(lib().b200_operand_cache_enable(self._h, max_bytes), "operand_cache_enable")
+
+    def operand_cache_invalidate(self, ptr=None, nbytes=0):
+        _check(lib().b200_operand_cache_invalidate(self._h, ptr, nbytes), "operand_cache_invalidate")
+
+    def operand_cache_stats(self):
+        arr = (_u64 * 4)()
+        _check(lib().b200_operand_cache_stats(self._h, arr))
+        return dict(hits=arr[0], misses=arr[1], bytes=arr[2], entries=arr[3])
 
     def set_correction_policy(self, policy):
         """fp32 mode: 0 = correction passes on the bf16 pipe (default), 1 = TF32 planes throughout."""

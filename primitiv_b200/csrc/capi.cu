@@ -58,6 +58,8 @@ int b200_ctx_create(int device_id, b200_ctx **out) {
   }
   ctx->h_status = static_cast<int *>(word);
   ctx->d_status = static_cast<int *>(alias);
+  // a block that returns to the pool takes the planes packed from its contents with it
+  ctx->pool.on_free = [ctx](const void *p, std::size_t bytes) { b200::plane_cache_drop_range(ctx, p, bytes); };
   void *fn = nullptr;
   cudaDriverEntryPointQueryResult qres;
   if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
@@ -77,6 +79,8 @@ int b200_ctx_destroy(b200_ctx *ctx) {
   if (!ctx) return B200_OK;
   DeviceGuard guard(ctx->device);
   cudaDeviceSynchronize();
+  b200::plane_cache_drop_range(ctx, nullptr, 0);
+  ctx->pool.on_free = nullptr;
   for (cudaStream_t st : ctx->pipe_streams) if (st) cudaStreamDestroy(st);
   for (cudaEvent_t ev : ctx->pipe_events) cudaEventDestroy(ev);
   if (ctx->barrier_event) cudaEventDestroy(ctx->barrier_event);
@@ -156,8 +160,30 @@ int b200_set_pair_policy(b200_ctx *ctx, int policy) {
   return B200_OK;
 }
 
+int b200_operand_cache_enable(b200_ctx *ctx, size_t max_bytes) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  ctx->planes.cap = max_bytes;
+  if (max_bytes == 0 && ctx->planes.scope == 0) b200::plane_cache_drop_range(ctx, nullptr, 0);
+  return B200_OK;
+}
+
+int b200_operand_cache_invalidate(b200_ctx *ctx, const void *ptr, size_t bytes) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  b200::plane_cache_drop_range(ctx, ptr, ptr ? bytes : 0);
+  return B200_OK;
+}
+
+int b200_operand_cache_stats(const b200_ctx *ctx, uint64_t stats[4]) {
+  if (!ctx || !stats) return B200_ERR_INVALID_ARG;
+  stats[0] = ctx->planes.hits;
+  stats[1] = ctx->planes.misses;
+  stats[2] = ctx->planes.bytes;
+  stats[3] = ctx->planes.entries.size();
+  return B200_OK;
+}
+
 int b200_set_correction_policy(b200_ctx *ctx, int policy) {
-  if (!ctx || policy < 0 || policy > 1) return B200_ERR_INVALID_ARG;
+  if (!ctx || policy < 0 || policy > 2) return B200_ERR_INVALID_ARG;
   ctx->correction_policy = policy;
   return B200_OK;
 }
@@ -204,6 +230,11 @@ int b200_gemm(b200_ctx *ctx, int mode, int trans_a, int trans_b, const void *A, 
   GemmArgs g{mode, trans_a ? 1 : 0, trans_b ? 1 : 0, A, B, C, m, n, k, groups, red,
              a_gs, a_rs, b_gs, b_rs, c_gs, accumulate ? 1 : 0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!ctx->planes.entries.empty()) {
+    // planes packed from the array this product writes are stale from here on
+    const size_t span = ((size_t)(groups - 1) * c_gs + (size_t)m * n) * b200::elem_bytes(mode);
+    b200::plane_cache_drop_range(ctx, C, span);
+  }
   const bool eligible = b200::gemm_tc_eligible(ctx, g);
   if (force_path == 2) return eligible ? b200::gemm_tc(ctx, g, s) : B200_ERR_INVALID_ARG;
   if (force_path == 1) return b200::gemm_simt(ctx, g, s);
@@ -283,6 +314,9 @@ int b200_matmul_bw_ex(b200_ctx *ctx, int mode, const void *a, const void *b, con
   int rc = check_matmul(ctx, mode, ba, bb);
   if (rc) return rc;
   if (!a || !b || !gy) return B200_ERR_INVALID_ARG;
+  // gy is an operand of both products (and a, b may already have planes from the forward call):
+  // operand planes are shared for the duration of the call
+  b200::PlaneScope share(ctx);
   const uint64_t na = (uint64_t)di * dj, nb = (uint64_t)dj * dk, ny = (uint64_t)di * dk;
   if (di == 0 || dj == 0 || dk == 0) {
     // some extent is empty: nothing to add; a gradient that was to be written becomes zeros
@@ -513,6 +547,9 @@ int b200_matmul_fw_bw_host(b200_ctx *ctx, int mode, const void *a_host, const vo
     if (gb_host && !accumulate_b && sb) memset(gb_host, 0, sb);
     return B200_OK;
   }
+  // a and b serve the forward product and a gradient each, gy both gradients: their planes are shared
+  // for the duration of the call (declared before the buffers, so it outlives them)
+  b200::PlaneScope share(ctx);
   Scratch da(ctx), db(ctx), dgy(ctx), dy(ctx), dga(ctx), dgb(ctx);
   if ((rc = da.get(sa)) || (rc = db.get(sb))) return rc;
   if (y_host && (rc = dy.get(sy))) return rc;

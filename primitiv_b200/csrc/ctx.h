@@ -7,6 +7,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <functional>
 #include <map>
 #include <unordered_map>
 #include <vector>
@@ -32,6 +33,9 @@ class Pool {
   // in-use + cached bytes past it behave exactly like a failed cudaMalloc.
   void set_limit(std::size_t bytes) { limit_ = bytes; }
   static std::size_t size_class(std::size_t bytes);
+  // Called with (block, bytes) whenever a block goes back to the pool: whatever was derived from
+  // its contents (cached operand planes) is stale from then on.
+  std::function<void(const void *, std::size_t)> on_free;
 
  private:
   std::map<std::size_t, std::vector<void *>> cached_;
@@ -75,6 +79,30 @@ class StagingRing {
 
 }  // namespace b200
 
+namespace b200 {
+
+// Cache of packed operand planes (fp32 mode).  An entry maps a dense source range of the caller's
+// memory to the block that holds its three planes in the source's own layout.  Entries live
+// while the cache is enabled (b200_operand_cache_enable) or while an entry point that uses an
+// operand more than once is running (scope > 0), and die when their source range is written
+// (b200_operand_cache_invalidate), returned to the pool, or evicted to stay under the byte cap.
+struct PlaneCache {
+  struct Entry {
+    const void *src;
+    std::size_t src_bytes;
+    void *block;
+    std::size_t block_bytes;
+    std::uint64_t stamp;
+  };
+  std::vector<Entry> entries;
+  std::size_t bytes = 0, cap = 0;   // cap == 0: not enabled by the caller
+  int scope = 0;                    // > 0 inside an entry point that shares planes between its products
+  std::uint64_t clock = 0, hits = 0, misses = 0;
+  bool active() const { return cap != 0 || scope > 0; }
+};
+
+}  // namespace b200
+
 struct b200_ctx {
   int device = 0;
   int sm_count = 0;
@@ -93,7 +121,8 @@ struct b200_ctx {
   int debug_stage_cap = 0;       // development: cap on pipeline stages (0 = none)
   int pair_policy = 0;           // 0 = CTA pairs (cta_group::2) when the problem allows, 1 = single CTAs only
   int split_policy = 0;          // 0 = split k over idle CTAs when there are few output tiles, 1 = never
-  int correction_policy = 0;     // fp32 mode: 0 = correction passes on the bf16 pipe, 1 = TF32 planes throughout
+  int correction_policy = 0;     // fp32 mode: 0 = correction passes on the bf16 pipe, flat planes where possible;
+                                 // 1 = TF32 planes throughout; 2 = bf16 correction passes, operands always repacked K-major
   std::uint64_t rng_seed = 0, rng_calls = 0;  // Philox key and fill counter (b200_seed / b200_random)
   // optional per-launch timing (b200_profile_*): event pairs, summed when read
   bool profiling = false;
@@ -105,6 +134,7 @@ struct b200_ctx {
   cudaStream_t pipe_streams[3] = {nullptr, nullptr, nullptr};
   std::vector<cudaEvent_t> pipe_events;
   cudaEvent_t barrier_event = nullptr;  // b200_stream_barrier: marks this GPU's default stream
+  b200::PlaneCache planes;
 };
 
 namespace b200 {
@@ -166,6 +196,18 @@ int gemm_tc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
 int selftest_wait_timeout(b200_ctx *ctx, cudaStream_t stream);
 // 3xTF32 product whose packing planes live in a fixed device array: allocates nothing.
 int gemm_3xtf32_noalloc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
+
+// Operand-plane cache (see PlaneCache).  drop_range forgets every entry whose source overlaps
+// [ptr, ptr + bytes) (everything when ptr is null) and returns its block to the pool.
+void plane_cache_drop_range(b200_ctx *ctx, const void *ptr, std::size_t bytes);
+// Brackets an entry point that hands the same operand to several products.
+struct PlaneScope {
+  b200_ctx *ctx;
+  explicit PlaneScope(b200_ctx *c) : ctx(c) { ++ctx->planes.scope; }
+  ~PlaneScope() {
+    if (--ctx->planes.scope == 0 && ctx->planes.cap == 0) plane_cache_drop_range(ctx, nullptr, 0);
+  }
+};
 
 inline int elem_bytes(int mode) { return mode == B200_MODE_FP16 ? 2 : 4; }
 

@@ -88,6 +88,16 @@ constexpr uint32_t kEpilogueWarps = 8;
 constexpr uint32_t kChunkKBlocks = 8;  // 3xTF32: promote to registers every 8 k-blocks (256 k)
 constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s at boost clock, 4 s at the lowest
 
+struct MixDesc {
+  uint32_t hi, lo_fixed, kstep;
+};
+struct MixBox {
+  uint32_t dst;      // byte offset inside the stage
+  int32_t mn_off;    // element offset along mn from the CTA's first row
+  uint32_t map;      // index into the tensor maps, in the order they lie in TcParams
+  uint32_t flags;    // bit 0: operand B; bit 1: the box is MN-major (coordinates {mn, k} instead of {k, mn})
+};
+
 struct alignas(64) TcParams {
   CUtensorMap mapA[2];  // [0] = values (or hi plane), [1] = lo plane
   CUtensorMap mapB[2];
@@ -110,6 +120,13 @@ struct alignas(64) TcParams {
   uint32_t idesc;
   uint32_t idesc8;          // kind 4: instruction descriptor of the bf16 correction passes
   uint32_t a8_bytes, b8_bytes;  // kind 4: bytes of one bf16 plane of A / of B in a stage (per CTA)
+  // kind 4: the planes of an operand are either K-major repacks or flat copies of the caller's
+  // layout (then MN-major operands stay MN-major), so every plane has its own descriptor fields
+  // ({high half, fixed low bits, k-step in 16-byte units}; [0] = the TF32 plane, [1] = the bf16 planes)
+  // and the TMA boxes of a stage come from a host-built table, one entry per producer lane.
+  MixDesc mix_a[2], mix_b[2];
+  MixBox mix_box[32];
+  uint32_t mix_boxes;
   uint32_t passes;
   uint32_t chunk_kblocks;  // k-blocks per accumulation chunk
   uint32_t accumulate, out_half, kind_f16;
@@ -277,38 +294,39 @@ __device__ __forceinline__ void mma_stage(uint32_t d_tmem, uint32_t sa, uint32_t
 // bytes under the 64-byte swizzle (descriptor layout 4, 8-row groups 512 bytes apart).
 template <int kCtas>
 __device__ __forceinline__ void mma_stage_mix(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t a_plane,
-                                              uint32_t b_plane, uint32_t a8, uint32_t b8, uint32_t hi_desc,
-                                              uint32_t hi8_desc, uint32_t idesc, uint32_t idesc8, bool first) {
+                                              uint32_t b_plane, uint32_t a8, uint32_t b8, const MixDesc &a32,
+                                              const MixDesc &ad8, const MixDesc &b32, const MixDesc &bd8,
+                                              uint32_t idesc, uint32_t idesc8, bool first) {
   uint32_t acc = first ? 0u : 1u;
   {
-    uint32_t a_lo = ((sa + a_plane + a8) & 0x3FFFFu) >> 4;   // A lo8
-    uint32_t b_lo = ((sb + b_plane) & 0x3FFFFu) >> 4;        // B hi8
+    uint32_t a_lo = ad8.lo_fixed | (((sa + a_plane + a8) & 0x3FFFFu) >> 4);   // A lo8
+    uint32_t b_lo = bd8.lo_fixed | (((sb + b_plane) & 0x3FFFFu) >> 4);        // B hi8
 #pragma unroll
     for (uint32_t ks = 0; ks < 2u; ++ks) {
-      mma_issue<kCtas, true>(d_tmem, a_lo, hi8_desc, b_lo, hi8_desc, idesc8, acc);
+      mma_issue<kCtas, true>(d_tmem, a_lo, ad8.hi, b_lo, bd8.hi, idesc8, acc);
       acc = 1u;
-      a_lo += 2u;  // 32 bytes of k, in 16-byte units
-      b_lo += 2u;
+      a_lo += ad8.kstep;
+      b_lo += bd8.kstep;
     }
   }
   {
-    uint32_t a_lo = ((sa + a_plane) & 0x3FFFFu) >> 4;        // A hi8
-    uint32_t b_lo = ((sb + b_plane + b8) & 0x3FFFFu) >> 4;   // B lo8
+    uint32_t a_lo = ad8.lo_fixed | (((sa + a_plane) & 0x3FFFFu) >> 4);        // A hi8
+    uint32_t b_lo = bd8.lo_fixed | (((sb + b_plane + b8) & 0x3FFFFu) >> 4);   // B lo8
 #pragma unroll
     for (uint32_t ks = 0; ks < 2u; ++ks) {
-      mma_issue<kCtas, true>(d_tmem, a_lo, hi8_desc, b_lo, hi8_desc, idesc8, 1u);
-      a_lo += 2u;
-      b_lo += 2u;
+      mma_issue<kCtas, true>(d_tmem, a_lo, ad8.hi, b_lo, bd8.hi, idesc8, 1u);
+      a_lo += ad8.kstep;
+      b_lo += bd8.kstep;
     }
   }
   {
-    uint32_t a_lo = (sa & 0x3FFFFu) >> 4;                    // A hi
-    uint32_t b_lo = (sb & 0x3FFFFu) >> 4;                    // B hi
+    uint32_t a_lo = a32.lo_fixed | ((sa & 0x3FFFFu) >> 4);                    // A hi
+    uint32_t b_lo = b32.lo_fixed | ((sb & 0x3FFFFu) >> 4);                    // B hi
 #pragma unroll
     for (uint32_t ks = 0; ks < kKSteps; ++ks) {
-      mma_issue<kCtas, false>(d_tmem, a_lo, hi_desc, b_lo, hi_desc, idesc, 1u);
-      a_lo += 2u;
-      b_lo += 2u;
+      mma_issue<kCtas, false>(d_tmem, a_lo, a32.hi, b_lo, b32.hi, idesc, 1u);
+      a_lo += a32.kstep;
+      b_lo += b32.kstep;
     }
   }
 }
@@ -550,25 +568,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       // this lane's box: [sub][plane][A boxes..., B boxes...]
       const uint32_t a_boxes = p.a_mn_major ? p.a_chunks : 1u, b_boxes = p.b_mn_major ? p.b_chunks : 1u;
       const uint32_t per_plane = a_boxes + b_boxes;
-      // kind 4: six K-major boxes per stage, lanes 0-2 = A {hi, hi8, lo8}, lanes 3-5 = B {hi, hi8, lo8}
-      const uint32_t nboxes = kMix ? 6u : kSubs * planes * per_plane;  // <= 32, checked on the host
+      // kind 4: this lane's box comes from the host-built table
+      const MixBox mbox = (kMix && lane < p.mix_boxes) ? p.mix_box[lane] : MixBox{0u, 0, 0u, 0u};
+      const uint32_t nboxes = kMix ? p.mix_boxes : kSubs * planes * per_plane;  // <= 32, checked on the host
       const bool has_box = lane < nboxes;
       const uint32_t bsub = kMix ? 0u : lane / (planes * per_plane), brem = lane % (planes * per_plane);
-      const uint32_t bpl = kMix ? lane % 3u : (brem / per_plane) & 1u, bidx = brem % per_plane;
-      const bool is_b = kMix ? lane >= 3u : bidx >= a_boxes;
-      const uint32_t bchunk = kMix ? 0u : (is_b ? bidx - a_boxes : bidx);
-      const bool box_mn = kMix ? false : (is_b ? p.b_mn_major != 0u : p.a_mn_major != 0u);
+      const uint32_t bpl = (brem / per_plane) & 1u, bidx = brem % per_plane;
+      const bool is_b = kMix ? (mbox.flags & 1u) != 0u : bidx >= a_boxes;
+      const uint32_t bchunk = is_b ? bidx - a_boxes : bidx;
+      const bool box_mn = kMix ? (mbox.flags & 2u) != 0u : (is_b ? p.b_mn_major != 0u : p.a_mn_major != 0u);
       const uint32_t box_dst =
-          kMix ? (is_b ? 2u * p.a_stage_bytes + (bpl == 0u ? 0u : p.b_stage_bytes + (bpl - 1u) * p.b8_bytes)
-                       : (bpl == 0u ? 0u : p.a_stage_bytes + (bpl - 1u) * p.a8_bytes))
+          kMix ? mbox.dst
                : bsub * p.sub_bytes +
                      (is_b ? planes * p.a_stage_bytes + bpl * p.b_stage_bytes + bchunk * p.b_chunk_bytes
                            : bpl * p.a_stage_bytes + bchunk * p.a_chunk_bytes);
       const int box_k = static_cast<int>(bsub * p.bk);
-      const int box_mn_off = static_cast<int>(box_mn ? bchunk * (is_b ? p.b_chunk_elems : p.a_chunk_elems) : 0u);
-      const CUtensorMap *box_map =
-          kMix ? (bpl == 0u ? (is_b ? &p.mapB[0] : &p.mapA[0]) : (is_b ? &p.mapB8[(bpl - 1u) & 1u] : &p.mapA8[(bpl - 1u) & 1u]))
-               : (is_b ? &p.mapB[bpl] : &p.mapA[bpl]);
+      const int box_mn_off = kMix ? mbox.mn_off
+                                  : static_cast<int>(box_mn ? bchunk * (is_b ? p.b_chunk_elems : p.a_chunk_elems) : 0u);
+      // the eight tensor maps lie back to back at the head of the parameter block
+      const CUtensorMap *box_map = kMix ? &p.mapA[0] + mbox.map : (is_b ? &p.mapB[bpl] : &p.mapA[bpl]);
       for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         uint32_t vg, mt, nt;
         tile_coords(tile, p.tiles_m, p.tiles_n, p.band_m, vg, mt, nt);
@@ -642,8 +660,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       const uint32_t a_plane = p.a_stage_bytes, b_plane = p.b_stage_bytes, b_off = planes * p.a_stage_bytes;
       const uint32_t idesc = p.idesc, nstages = p.stages, dbg = kDevKnobs ? p.debug : 0u;
       const uint32_t chunk_kblocks = p.chunk_kblocks, bn = p.bn;
-      // kind 4: descriptor high half of the bf16 planes (8-row groups 512 bytes apart, 64-byte swizzle)
-      const uint32_t hi8_desc = ((512u >> 4) & 0x3FFFu) | (1u << 14) | (4u << 29);
+      // kind 4: descriptor fields of each plane kind of each operand, in registers
+      const MixDesc mxa32 = p.mix_a[0], mxa8 = p.mix_a[1], mxb32 = p.mix_b[0], mxb8 = p.mix_b[1];
       const uint32_t idesc8 = p.idesc8, a8 = p.a8_bytes, b8 = p.b8_bytes;
       for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         uint32_t kb_left = kb_per_tile;
@@ -671,8 +689,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
               for (uint32_t sub = 0; sub < kSubs; ++sub) {
                 const uint32_t ssa = sa + sub * sub_bytes;
                 if constexpr (kMix)
-                  mma_stage_mix<kCtas>(d_tmem, ssa, ssa + b_off, a_plane, b_plane, a8, b8, a_hi, hi8_desc, idesc,
-                                       idesc8, it == 0u);
+                  mma_stage_mix<kCtas>(d_tmem, ssa, ssa + b_off, a_plane, b_plane, a8, b8, mxa32, mxa8, mxb32, mxb8,
+                                       idesc, idesc8, it == 0u);
                 else
                   mma_stage<kCtas, kF16, kPasses>(d_tmem, ssa, ssa + b_off, a_plane, b_plane, a_hi, b_hi, a_lo_fixed,
                                                   b_lo_fixed, kstep_a, kstep_b, idesc, (it | sub) == 0u);
@@ -945,7 +963,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   const uint32_t passes = (g.mode == B200_MODE_FP32_3XTF32 || split16) ? 3u : 1u;
   // fp32 mode: the two correction passes on the bf16 pipe (hi / hi8 / lo8 planes) unless the
   // context asks for TF32 planes throughout
-  const bool mix = g.mode == B200_MODE_FP32_3XTF32 && ctx->correction_policy == 0;
+  const bool mix = g.mode == B200_MODE_FP32_3XTF32 && ctx->correction_policy != 1;
 
   TcParams p;
   memset(&p, 0, sizeof(p));
@@ -977,21 +995,60 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
 
   const void *a_src[2] = {g.A, nullptr}, *b_src[2] = {g.B, nullptr};
   const void *a_mix[3] = {nullptr, nullptr, nullptr}, *b_mix[3] = {nullptr, nullptr, nullptr};
+  void *flat_blocks[2] = {nullptr, nullptr};  // flat planes that the cache did not take: freed after the launch
   void *scratch = nullptr;
+  auto release = [&]() {   // stream-ordered reuse: later work queues behind this product
+    if (scratch) ctx->pool.free(scratch);
+    for (void *&blk : flat_blocks) {
+      if (blk) ctx->pool.free(blk);
+      blk = nullptr;
+    }
+    scratch = nullptr;
+  };
+  // kind 4 bookkeeping: the plane pointers of each operand and whether they are flat copies
+  bool a_flat = false, b_flat = false;
   if (mix) {
-    const MixPlanes la = mix_planes(va), lb = mix_planes(vb);
-    const uint64_t total = la.floats() + lb.floats();
+    // An operand that is dense and 32-byte aligned in every stride is packed "flat": the three
+    // planes repeat the caller's layout element for element (the kernel reads either
+    // major-ness), the pre-pass is purely elementwise, and the planes can serve every later
+    // use of the same array, whichever side of whichever product it is on: they go through the
+    // context's plane cache.  Anything else is repacked K-major into scratch for this launch.
+    OperandView *views[2] = {&va, &vb};
+    const void **outs[2] = {a_mix, b_mix};
+    bool *flat[2] = {&a_flat, &b_flat};
+    uint64_t repack_floats = 0;
+    MixPlanes lay[2];
+    for (int o = 0; o < 2; ++o) {
+      // (measured: an MN-major A costs nothing, an MN-major B 20 % of the main loop -- 3.84 against 3.16 ms
+      // on 8 x 4096^3 -- so a B operand that is MN-major in memory is still transposed into K-major planes)
+      *flat[o] = !fixed_scratch && ctx->correction_policy == 0 && mix_flat_ok(*views[o]) &&
+                 !(o == 1 && views[o]->mn_major);
+      if (!*flat[o]) {
+        lay[o] = mix_planes(*views[o]);
+        repack_floats += lay[o].floats();
+      }
+    }
     float *cursor = nullptr;
-    if (fixed_scratch) {
-      if (total > fixed_elems) return B200_ERR_TOO_LARGE;
+    if (repack_floats && fixed_scratch) {
+      if (repack_floats > fixed_elems) return B200_ERR_TOO_LARGE;
       cursor = fixed_scratch;
-    } else {
-      int rc = ctx->pool.alloc(total * sizeof(float), &scratch, nullptr);
+    } else if (repack_floats) {
+      int rc = ctx->pool.alloc(repack_floats * sizeof(float), &scratch, nullptr);
       if (rc != B200_OK) return rc;
       cursor = static_cast<float *>(scratch);
     }
-    pack_mix(ctx, stream, va, cursor, la, a_mix);
-    pack_mix(ctx, stream, vb, cursor + la.floats(), lb, b_mix);
+    for (int o = 0; o < 2; ++o) {
+      if (*flat[o]) {
+        const int rc = mix_flat_planes(ctx, stream, *views[o], outs[o], &flat_blocks[o]);
+        if (rc != B200_OK) {
+          release();
+          return rc;
+        }
+      } else {
+        pack_mix(ctx, stream, *views[o], cursor, lay[o], outs[o]);
+        cursor += lay[o].floats();
+      }
+    }
     a_src[0] = a_mix[0];
     b_src[0] = b_mix[0];
   } else if (split16) {
@@ -1039,7 +1096,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     }
   }
 
-  p.a_mn_major = va.mn_major ? 1u : 0u;
+  p.a_mn_major = va.mn_major ? 1u : 0u;   // (after packing: a K-major repack has cleared the flag, flat planes keep it)
   p.b_mn_major = vb.mn_major ? 1u : 0u;
   p.ksteps = p.bk / umma_k;
   const uint32_t planes = passes == 3 ? 2u : 1u;
@@ -1055,7 +1112,10 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   {
     // the producer warp issues one TMA box per lane and stage
     const uint32_t boxes = planes * ((p.a_mn_major ? kBM / chunk : 1u) + (p.b_mn_major ? b_rows / chunk : 1u));
-    if (p.subs * boxes > 32u) return B200_ERR_INVALID_ARG;
+    if (p.subs * boxes > 32u) {
+      release();
+      return B200_ERR_INVALID_ARG;
+    }
   }
   p.stage_bytes = p.subs * p.sub_bytes;
   p.kblocks = (g.k + p.bk * p.subs - 1) / (p.bk * p.subs);  // pipeline-stage iterations along k
@@ -1122,8 +1182,57 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   const uint32_t fmt = f16 ? 0u : 2u;  // F16 = 0 (kind::f16), TF32 = 2 (kind::tf32)
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (p.a_mn_major << 15) | (p.b_mn_major << 16) |
             ((p.bn >> 3) << 17) | ((tile_m >> 4) << 24);
-  // bf16 x bf16 -> fp32, both operands K-major (kind::f16 with format 1 = BF16)
-  p.idesc8 = (1u << 4) | (1u << 7) | (1u << 10) | ((p.bn >> 3) << 17) | ((tile_m >> 4) << 24);
+  // bf16 x bf16 -> fp32 (kind::f16 with format 1 = BF16), same operand major-ness as the TF32 pass
+  p.idesc8 = (1u << 4) | (1u << 7) | (1u << 10) | (p.a_mn_major << 15) | (p.b_mn_major << 16) |
+             ((p.bn >> 3) << 17) | ((tile_m >> 4) << 24);
+  if (mix) {
+    // Descriptor fields per plane kind.  K-major: rows of 128 bytes (TF32, 128-byte swizzle, 8-row groups
+    // 1024 bytes apart) or 64 bytes (bf16, 64-byte swizzle, groups 512 bytes apart), 32 bytes per k-step.
+    // MN-major: chunks of 128 bytes of mn by bk k-rows, 4096 bytes apart; TF32 under the 32-byte-atom
+    // pattern with k-groups of 4 rows (512 bytes), a k-step of 8 rows = 1024 bytes; bf16 under the
+    // plain 128-byte pattern with k-groups of 8 rows (1024 bytes), a k-step of 16 rows = 2048 bytes.
+    auto desc = [&](bool mn_major, bool tf32) {
+      MixDesc d;
+      const uint32_t sbo = mn_major ? (tf32 ? 512u : 1024u) : (tf32 ? 1024u : 512u);
+      const uint32_t layout = mn_major ? (tf32 ? 1u : 2u) : (tf32 ? 2u : 4u);
+      const uint32_t lbo = mn_major ? p.bk * 128u : 0u;
+      d.hi = ((sbo >> 4) & 0x3FFFu) | (1u << 14) | (layout << 29);
+      d.lo_fixed = ((lbo >> 4) & 0x3FFFu) << 16;
+      d.kstep = (mn_major ? (tf32 ? 1024u : 2048u) : 32u) >> 4;
+      return d;
+    };
+    p.mix_a[0] = desc(va.mn_major, true);
+    p.mix_a[1] = desc(va.mn_major, false);
+    p.mix_b[0] = desc(vb.mn_major, true);
+    p.mix_b[1] = desc(vb.mn_major, false);
+    // TMA boxes of one stage: [A hi | A hi8 | A lo8 | B hi | B hi8 | B lo8]; a K-major plane is one box,
+    // an MN-major plane one box per 128 bytes of mn (32 floats, 64 bf16)
+    uint32_t nb = 0;
+    for (uint32_t o = 0; o < 2u; ++o) {
+      const bool mn = o ? vb.mn_major : va.mn_major;
+      const uint32_t rows = o ? b_rows : kBM;
+      const uint32_t plane32 = o ? p.b_stage_bytes : p.a_stage_bytes, plane8 = o ? p.b8_bytes : p.a8_bytes;
+      const uint32_t base = o ? 2u * p.a_stage_bytes : 0u;
+      for (uint32_t t = 0; t < 3u; ++t) {
+        const uint32_t off = base + (t == 0 ? 0u : plane32 + (t - 1u) * plane8);
+        const uint32_t map = t == 0 ? (o ? 2u : 0u) : (o ? 6u : 4u) + (t - 1u);
+        const uint32_t per = t == 0 ? 32u : 64u;   // mn elements per 128-byte chunk
+        const uint32_t count = mn ? rows / per : 1u;
+        for (uint32_t c = 0; c < count; ++c) {
+          if (nb >= 32u) {
+            release();
+            return B200_ERR_INVALID_ARG;
+          }
+          p.mix_box[nb].dst = off + c * p.bk * 128u;
+          p.mix_box[nb].mn_off = static_cast<int32_t>(c * per);
+          p.mix_box[nb].map = map;
+          p.mix_box[nb].flags = o | (mn ? 2u : 0u);
+          ++nb;
+        }
+      }
+    }
+    p.mix_boxes = nb;
+  }
   p.passes = passes;
   const bool chunked = passes == 3 && static_cast<uint64_t>(g.red) * p.kblocks > kChunkKBlocks;
   p.chunk_kblocks = chunked ? kChunkKBlocks : g.red * p.kblocks;
@@ -1136,7 +1245,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     const uint64_t mn = static_cast<uint64_t>(g.m) * g.n;
     const int arc = ctx->pool.alloc(mn * g.groups * splits * sizeof(float), &partial, nullptr);
     if (arc != B200_OK) {
-      if (scratch) ctx->pool.free(scratch);
+      release();
       return arc;
     }
     p.C = partial;
@@ -1172,10 +1281,13 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
       rc = encode_map(ctx, &p.mapB[i], b_src[i], vb, eb, p.b_mn_major ? chunk : b_rows, p.bk, swz_b);
   }
   for (int i = 0; mix && i < 2 && rc == B200_OK; ++i) {
-    // the bf16 planes share the packed operand's indexing: rows of bk elements = 64 bytes, 64-byte swizzle
-    rc = encode_map(ctx, &p.mapA8[i], a_mix[1 + i], va, 2, kBM, p.bk, CU_TENSOR_MAP_SWIZZLE_64B, true);
+    // the bf16 planes share the packed operand's indexing.  K-major: rows of bk elements = 64 bytes under
+    // the 64-byte swizzle; MN-major: boxes of 64 mn elements = 128 bytes by bk rows, plain 128-byte swizzle
+    rc = encode_map(ctx, &p.mapA8[i], a_mix[1 + i], va, 2, va.mn_major ? 64u : kBM, p.bk,
+                    va.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, true);
     if (rc == B200_OK)
-      rc = encode_map(ctx, &p.mapB8[i], b_mix[1 + i], vb, 2, b_rows, p.bk, CU_TENSOR_MAP_SWIZZLE_64B, true);
+      rc = encode_map(ctx, &p.mapB8[i], b_mix[1 + i], vb, 2, vb.mn_major ? 64u : b_rows, p.bk,
+                      vb.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, true);
   }
   if (rc == B200_OK && !ctx->tc_smem_configured) {
     const int max_dyn = static_cast<int>(ctx->smem_optin - 512);
@@ -1268,7 +1380,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     }
   }
   if (partial) ctx->pool.free(partial);
-  if (scratch) ctx->pool.free(scratch);  // stream-ordered reuse: later work queues behind this GEMM
+  release();
   return rc;
 }
 

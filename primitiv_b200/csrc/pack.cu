@@ -4,6 +4,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <vector>
+
 #include "pack.h"
 
 namespace b200 {
@@ -597,6 +599,98 @@ void pack_mix(b200_ctx *ctx, cudaStream_t stream, OperandView &v, float *dst, co
   v.mn_major = false;
   v.ld = lay.kpad;
   v.batch_stride = static_cast<uint64_t>(v.mn) * lay.kpad;
+}
+
+// ------------------------------ flat planes and their cache ------------------------------
+
+bool mix_flat_ok(const OperandView &v) {
+  if (reinterpret_cast<uintptr_t>(v.ptr) & 31u) return false;
+  const uint64_t inner = v.mn_major ? v.mn : v.k;
+  if (v.ld != inner || inner % 8u) return false;                                        // dense, 32-byte rows
+  if (v.nbatch > 1 && v.batch_stride != static_cast<uint64_t>(v.mn) * v.k) return false;  // matrices back to back
+  return true;
+}
+
+void plane_cache_drop_range(b200_ctx *ctx, const void *ptr, std::size_t bytes) {
+  PlaneCache &pc = ctx->planes;
+  if (pc.entries.empty()) return;
+  // collect first, free afterwards: returning a block to the pool calls back into this function
+  std::vector<void *> blocks;
+  const char *lo = static_cast<const char *>(ptr), *hi = lo + bytes;
+  for (std::size_t i = 0; i < pc.entries.size();) {
+    const PlaneCache::Entry &e = pc.entries[i];
+    const char *s0 = static_cast<const char *>(e.src), *s1 = s0 + e.src_bytes;
+    if (!ptr || (s0 < hi && lo < s1)) {
+      blocks.push_back(e.block);
+      pc.bytes -= e.block_bytes;
+      pc.entries[i] = pc.entries.back();
+      pc.entries.pop_back();
+    } else {
+      ++i;
+    }
+  }
+  for (void *b : blocks) ctx->pool.free(b);   // stream-ordered reuse: queued products that read them run first
+}
+
+int mix_flat_planes(b200_ctx *ctx, cudaStream_t stream, const OperandView &v, const void *planes_out[3],
+                    void **owned_block) {
+  PlaneCache &pc = ctx->planes;
+  const uint64_t n = static_cast<uint64_t>(v.nbatch > 1 ? v.nbatch : 1u) * v.mn * v.k;
+  const uint64_t hi_elems = (n + 63ull) & ~63ull, h8_elems = (n + 127ull) & ~127ull;
+  const std::size_t block_bytes = hi_elems * sizeof(float) + 2 * h8_elems * sizeof(__nv_bfloat16);
+  auto planes_of = [&](void *block) {
+    float *hi = static_cast<float *>(block);
+    __nv_bfloat16 *h8 = reinterpret_cast<__nv_bfloat16 *>(hi + hi_elems);
+    planes_out[0] = hi;
+    planes_out[1] = h8;
+    planes_out[2] = h8 + h8_elems;
+  };
+  *owned_block = nullptr;
+  if (pc.active()) {
+    for (PlaneCache::Entry &e : pc.entries) {
+      if (e.src == v.ptr && e.src_bytes == n * sizeof(float)) {
+        e.stamp = ++pc.clock;
+        ++pc.hits;
+        planes_of(e.block);
+        return B200_OK;
+      }
+    }
+    ++pc.misses;
+  }
+  void *block = nullptr;
+  const int rc = ctx->pool.alloc(block_bytes, &block, nullptr);
+  if (rc != B200_OK) return rc;
+  planes_of(block);
+  {
+    ProfScope prof(ctx, kProfPack, stream);
+    const unsigned long long n8 = n / 8ull;
+    const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
+    const unsigned long long need = (n8 + 255ull) / 256ull;
+    pack_mix_flat_kernel<<<static_cast<unsigned>(need < cap ? need : cap), 256, 0, stream>>>(
+        static_cast<const float4 *>(v.ptr), reinterpret_cast<float4 *>(const_cast<void *>(planes_out[0])),
+        reinterpret_cast<uint4 *>(const_cast<void *>(planes_out[1])),
+        reinterpret_cast<uint4 *>(const_cast<void *>(planes_out[2])), n8);
+  }
+  ++ctx->launches;
+  // inside an entry point that shares planes (scope) without a caller-set cap, keep at most 4 GiB
+  const std::size_t cap = pc.cap ? pc.cap : (std::size_t(4) << 30);
+  if (!pc.active() || block_bytes > cap) {
+    *owned_block = block;
+    return B200_OK;
+  }
+  while (pc.bytes + block_bytes > cap && !pc.entries.empty()) {   // least recently used first
+    std::size_t oldest = 0;
+    for (std::size_t i = 1; i < pc.entries.size(); ++i)
+      if (pc.entries[i].stamp < pc.entries[oldest].stamp) oldest = i;
+    void *old = pc.entries[oldest].block;
+    pc.bytes -= pc.entries[oldest].block_bytes;
+    pc.entries[oldest] = pc.entries.back();
+    pc.entries.pop_back();
+    ctx->pool.free(old);
+  }
+  pc.entries.push_back({v.ptr, static_cast<std::size_t>(n * sizeof(float)), block, block_bytes, ++pc.clock});
+  pc.bytes += block_bytes;
+  return B200_OK;
 }
 
 F16Planes f16_planes(const OperandView &v, bool shared) {

@@ -56,6 +56,17 @@ MixPlanes mix_planes(const OperandView &v);
 void pack_mix(b200_ctx *ctx, cudaStream_t stream, OperandView &v, float *dst, const MixPlanes &lay,
               const void *planes_out[3]);
 
+// Flat form of the same three planes: element e of the caller's array <-> element e of each plane,
+// so the planes keep the operand's major-ness and serve any later use of the same array.  Possible
+// when the operand is dense and every stride is a multiple of 8 elements (TMA needs 16-byte rows in
+// the bf16 planes too).
+bool mix_flat_ok(const OperandView &v);
+// Finds the operand's flat planes in the context's plane cache, or packs them (one elementwise
+// pass) and offers them to the cache.  planes_out = {hi, hi8, lo8}.  *owned_block is the block the
+// caller has to return to the pool after its launch, or null when the cache keeps it.
+int mix_flat_planes(b200_ctx *ctx, cudaStream_t stream, const OperandView &v, const void *planes_out[3],
+                    void **owned_block);
+
 // ---- half planes of the 3xFP16 mode: [row maxima][h0 plane][h1 plane], rows of kpad halves ----
 struct F16Planes {
   uint64_t plane_halves;  // halves per plane, rounded up to 128

@@ -66,6 +66,7 @@ int Pool::free(void *ptr) {
   const std::size_t cls = it->second;
   in_use_.erase(it);
   bytes_in_use_ -= cls;
+  if (on_free) on_free(ptr, cls);   // may free further blocks (planes derived from this one)
   cached_[cls].push_back(ptr);
   bytes_cached_ += cls;
   return B200_OK;

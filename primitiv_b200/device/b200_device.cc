@@ -50,6 +50,9 @@ struct B200::State {
 
 namespace {
 
+// plane memory the device may keep between products (pool memory; least recently used out first)
+const std::size_t kPlaneCacheBytes = std::size_t(8) << 30;
+
 B200::Mode mode_from_environment() {
   const char *e = std::getenv("PRIMITIV_B200_MODE");
   if (!e) return B200::Mode::FP32_3XTF32;
@@ -101,6 +104,14 @@ void B200::initialize(std::uint32_t rng_seed) {
   }
   state_->mode = imode();
   B200_CALL(::b200_seed(state_->ctx, rng_seed));
+  // The split planes of an fp32 operand are kept from the forward product for the backward one
+  // (and for any other product that reads the same tensor); every write goes through out() /
+  // out_acc() below, which forget the planes of what is written.
+  B200_CALL(::b200_operand_cache_enable(state_->ctx, kPlaneCacheBytes));
+}
+
+void B200::written(const void *p, const Tensor &x) {
+  ::b200_operand_cache_invalidate(state_->ctx, p, elem_size() * static_cast<std::size_t>(x.shape().size()));
 }
 
 void B200::materialize(const void *ptr) {
@@ -122,6 +133,7 @@ const void *B200::in(const Tensor &x) {
 void *B200::out(Tensor &x) {
   void *p = get_mutable_handle(x);  // may clone a shared tensor (copy-on-write) through copy_tensor_impl
   materialize(p);
+  written(p, x);
   return p;
 }
 
@@ -136,6 +148,7 @@ void *B200::out_acc(Tensor &x, int *accumulate) {
       *accumulate = 0;  // the kernel stores where it would have added to zeros
     }
   }
+  written(p, x);
   return p;
 }
 
@@ -173,6 +186,7 @@ void *B200::data_for_overwrite(Tensor &x) {
   if (&x.device() != this) PRIMITIV_THROW_ERROR("B200::data_for_overwrite: the tensor lives on another device.");
   void *p = get_mutable_handle(x);
   state_->zero_pending.erase(p);
+  written(p, x);
   return p;
 }
 
@@ -235,6 +249,7 @@ std::vector<std::uint32_t> B200::argmin_impl(const Tensor &x, std::uint32_t dim)
 
 void B200::reset_tensor_impl(float k, Tensor &x) {
   void *p = get_mutable_handle(x);
+  written(p, x);
   if (k == 0.f) {
     state_->zero_pending[p] = x.shape().size();  // deferred: see in() / out_acc()
     return;

@@ -103,6 +103,7 @@ private:
   void *out(Tensor &x);
   void *out_acc(Tensor &x, int *accumulate);
   void materialize(const void *ptr);
+  void written(const void *p, const Tensor &x);  // x is about to be written: planes packed from it are stale
   void unary_bw(int op, const Tensor &x, const Tensor &y, const Tensor &gy, float k, std::int32_t ik, Tensor &gx);
   int imode() const { return static_cast<int>(mode_); }
   std::size_t elem_size() const { return mode_ == Mode::FP16 ? 2 : 4; }

@@ -150,6 +150,107 @@ def test_correction_policies_per_product_error(ctx):
     assert worst[1] < worst[0], worst
 
 
+def _cuda(x):
+    return torch.from_numpy(np.ascontiguousarray(x, np.float32)).cuda()
+
+
+@pytest.mark.parametrize("batches", [(1, 4), (4, 4), (4, 1), (1, 1)], ids=lambda b: "ba%d_bb%d" % b)
+def test_operand_cache_shares_planes_between_forward_and_backward(ctx, batches):
+    """With the cache on, a step packs each of a, b, gy once (three misses) and every other use of
+    them finds the planes (three hits: a and b in the backward call, gy in its second product); the
+    planes are read in whichever major-ness the product needs, and the results are the oracle's."""
+    di, dj, dk = 384, 256, 512
+    ba, bb = batches
+    bs = max(ba, bb)
+    rng = np.random.default_rng(31 + ba * 10 + bb)
+    a = rng.uniform(-1, 1, di * dj * ba).astype(np.float32)
+    b = rng.uniform(-1, 1, dj * dk * bb).astype(np.float32)
+    gy = rng.standard_normal(di * dk * bs).astype(np.float32)
+    da, db, dgy = _cuda(a), _cuda(b), _cuda(gy)
+    y = torch.empty(di * dk * bs, device="cuda")
+    ga, gb = torch.full((di * dj * ba,), 0.5, device="cuda"), torch.full((dj * dk * bb,), 0.5, device="cuda")
+    M = pb.MODE_FP32_3XTF32
+    ctx.set_path_policy(2)
+    ctx.operand_cache_enable(1 << 30)
+    try:
+        s0 = ctx.operand_cache_stats()
+        ctx.matmul_fw(M, da.data_ptr(), db.data_ptr(), y.data_ptr(), di, dj, dk, ba, bb)
+        ctx.matmul_bw(M, da.data_ptr(), db.data_ptr(), dgy.data_ptr(), ga.data_ptr(), gb.data_ptr(), di, dj, dk, ba, bb)
+        torch.cuda.synchronize()
+        s1 = ctx.operand_cache_stats()
+        assert (s1["misses"] - s0["misses"], s1["hits"] - s0["hits"]) == (3, 3), (s0, s1)
+        assert s1["entries"] == 3 and s1["bytes"] >= 2 * 4 * (a.size + b.size + gy.size)
+    finally:
+        ctx.operand_cache_enable(0)
+        ctx.set_path_policy(0)
+    assert ctx.operand_cache_stats()["entries"] == 0
+    half = np.full
+    ga64, gb64 = ol.bw_f64(a, b, gy, half(a.size, 0.5, np.float32), half(b.size, 0.5, np.float32), di, dj, dk, ba, bb)
+    assert ol.rel_err(y.cpu().numpy(), ol.fw_f64(a, b, di, dj, dk, ba, bb)) <= 1e-5
+    assert ol.rel_err(ga.cpu().numpy(), ga64) <= 1e-5 and ol.rel_err(gb.cpu().numpy(), gb64) <= 1e-5
+
+
+def test_operand_cache_forgets_what_is_written(ctx):
+    """Planes go stale in three ways, and each is handled: the caller writes an operand and says so
+    (invalidate), a product of this library overwrites an array that was an operand before, and a
+    block goes back to the pool."""
+    n = 256
+    rng = np.random.default_rng(41)
+    a, b, c, a2 = (rng.uniform(-1, 1, n * n).astype(np.float32) for _ in range(4))
+    da, db, dc = _cuda(a), _cuda(b), _cuda(c)
+    y, z = torch.empty(n * n, device="cuda"), torch.empty(n * n, device="cuda")
+    M = pb.MODE_FP32_3XTF32
+    fw = lambda p, q, r: ctx.matmul_fw(M, p.data_ptr(), q.data_ptr(), r.data_ptr(), n, n, n, 1, 1)
+    ref = lambda p, q: ol.fw_f64(p, q, n, n, n, 1, 1)
+    ctx.set_path_policy(2)
+    ctx.operand_cache_enable(1 << 30)
+    try:
+        fw(da, db, y)                                   # y = a.b, planes of a and b kept
+        fw(y, dc, z)                                    # z = y.c, planes of y kept
+        da.copy_(_cuda(a2))                             # the caller rewrites a ...
+        ctx.operand_cache_invalidate(da.data_ptr(), da.numel() * 4)   # ... and says so
+        fw(da, db, y)                                   # y = a2.b: writes y, so y's planes are dropped here
+        fw(y, dc, z)
+        torch.cuda.synchronize()
+        y2 = ref(a2, b)
+        assert ol.rel_err(y.cpu().numpy(), y2) <= 1e-5
+        assert ol.rel_err(z.cpu().numpy(), ref(y2.astype(np.float32), c)) <= 1e-5
+        # a pool block used as an operand, freed, handed out again with other contents
+        p1, _ = ctx.pool_alloc(n * n * 4)
+        ctx.op("b200_upload", M, a.ctypes.data, p1, n * n, None)
+        ctx.matmul_fw(M, p1, db.data_ptr(), y.data_ptr(), n, n, n, 1, 1)
+        ctx.pool_free(p1)
+        p2, _ = ctx.pool_alloc(n * n * 4)
+        assert p2 == p1                                 # same block, as the pool promises
+        ctx.op("b200_upload", M, c.ctypes.data, p2, n * n, None)
+        ctx.matmul_fw(M, p2, db.data_ptr(), y.data_ptr(), n, n, n, 1, 1)
+        torch.cuda.synchronize()
+        ctx.pool_free(p2)
+        assert ol.rel_err(y.cpu().numpy(), ref(c, b)) <= 1e-5
+    finally:
+        ctx.operand_cache_enable(0)
+        ctx.set_path_policy(0)
+
+
+def test_backward_call_packs_the_upstream_gradient_once(ctx):
+    """Without the cache: inside one b200_matmul_bw call gy still serves both products from one set of
+    planes (one hit), and nothing is kept afterwards."""
+    di = dj = dk = 256
+    rng = np.random.default_rng(43)
+    a, b, gy = (rng.uniform(-1, 1, di * dj).astype(np.float32) for _ in range(3))
+    ctx.set_path_policy(2)
+    try:
+        s0 = ctx.operand_cache_stats()
+        ga, gb = matmul_bw(ctx, pb.MODE_FP32_3XTF32, a, b, gy, np.zeros(di * dj, np.float32), np.zeros(dj * dk, np.float32),
+                           di, dj, dk, 1, 1)
+        s1 = ctx.operand_cache_stats()
+    finally:
+        ctx.set_path_policy(0)
+    assert s1["hits"] - s0["hits"] == 1 and s1["misses"] - s0["misses"] == 3 and s1["entries"] == 0, (s0, s1)
+    ga64, gb64 = ol.bw_f64(a, b, gy, np.zeros(di * dj, np.float32), np.zeros(dj * dk, np.float32), di, dj, dk, 1, 1)
+    assert ol.rel_err(ga, ga64) <= 1e-5 and ol.rel_err(gb, gb64) <= 1e-5
+
+
 @pytest.mark.parametrize("mode", list(MODES))
 def test_plumbing_workload(ctx, mode):
     """W {256,256} broadcast, X {256,64}x16, gy N(0,1), all from one mt19937(0); gradients pre-filled 0.5."""
