@@ -244,6 +244,31 @@ B200_API int b200_set_path_policy(b200_ctx *ctx, int policy);
  * columns, 1 = always one CTA per 128-row tile. */
 B200_API int b200_set_pair_policy(b200_ctx *ctx, int policy);
 
+/* ---- launch policy (no counterpart in the reference, which pays one blocking-free but serial launch per
+ * operation on the caller's thread) -------------------------------------------------------------------------
+ * b200_set_async_launch(ctx, 1): kernel launches of this context are issued by a worker thread.  An entry
+ * point then does its bookkeeping on the caller's thread as before, copies the kernel arguments into a
+ * ring and returns; the worker issues the launches in program order.  A graph-level step of thousands of
+ * 3-microsecond kernels is bound by the driver's launch call; this takes that call off the caller's thread
+ * (the recurrent loop of the benchmark: 13.2 -> 9 ms).  Everything else that is ordered on a stream (copies,
+ * b200_download, b200_status_poll, the *_host products) first lets the worker catch up, so results never
+ * depend on the setting.  What does: work the CALLER queues on the same stream by other means (its own
+ * kernels, another library) is ordered against this library's launches only after a call that drains the
+ * queue (b200_status_poll, b200_download).  Hence off by default; primitiv::devices::B200, whose tensors
+ * nothing else touches, switches it on.  A launch that fails is reported by the next draining call.
+ *
+ * b200_set_dependent_launch(ctx, on): programmatic dependent launch, on by default.  Every kernel of the
+ * library begins by releasing the grid queued behind it and then waits for the grid in front of it to
+ * finish (griddepcontrol), and is launched with the programmatic-serialization attribute: a chain of small
+ * kernels overlaps each launch latency with the predecessor's execution.  Results do not depend on it. */
+B200_API int b200_set_async_launch(b200_ctx *ctx, int on);
+/* Returns when every launch queued so far has been handed to the driver (it does not wait for the GPU):
+ * from then on, work queued on the same stream by anyone else runs after it.  Two contexts on one GPU
+ * share the default stream but not a launch queue; whoever makes one read what the other computed calls
+ * this on the producer first.  A no-op without the queue. */
+B200_API int b200_launch_flush(b200_ctx *ctx);
+B200_API int b200_set_dependent_launch(b200_ctx *ctx, int on);
+
 /* ---- operand-plane cache (fp32 mode; no counterpart in the reference) ------------------------------
  * In B200_MODE_FP32_3XTF32 every fp32 operand is split into three planes before the tensor cores see it
  * (4 bytes read and 8 written per element).  A dense operand whose strides are multiples of 8 elements

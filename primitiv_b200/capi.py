@@ -47,6 +47,9 @@ SIGNATURES = {
     "b200_set_path_policy": (_int, [_vp, _int]),
     "b200_set_pair_policy": (_int, [_vp, _int]),
     "b200_set_correction_policy": (_int, [_vp, _int]),
+    "b200_set_async_launch": (_int, [_vp, _int]),
+    "b200_set_dependent_launch": (_int, [_vp, _int]),
+    "b200_launch_flush": (_int, [_vp]),
     "b200_operand_cache_enable": (_int, [_vp, ctypes.c_size_t]),
     "b200_operand_cache_invalidate": (_int, [_vp, _vp, ctypes.c_size_t]),
     "b200_operand_cache_stats": (_int, [_vp, ctypes.POINTER(_u64)]),
@@ -164,6 +167,13 @@ class Context:
 
     def set_path_policy(self, policy):
         _check(lib().b200_set_path_policy(self._h, policy), "set_path_policy")
+
+    def set_async_launch(self, on):
+        """Kernel launches issued by a worker thread (see include/primitiv_b200.h); drained by status_poll()."""
+        _check(lib().b200_set_async_launch(self._h, int(on)), "set_async_launch")
+
+    def set_dependent_launch(self, on):
+        _check(lib().b200_set_dependent_launch(self._h, int(on)), "set_dependent_launch")
 
     def operand_cache_enable(self, max_bytes):
         """Keep the packed planes of fp32 operands between calls (0 = off); the caller then owes an

@@ -60,6 +60,8 @@ int b200_ctx_create(int device_id, b200_ctx **out) {
   ctx->d_status = static_cast<int *>(alias);
   // a block that returns to the pool takes the planes packed from its contents with it
   ctx->pool.on_free = [ctx](const void *p, std::size_t bytes) { b200::plane_cache_drop_range(ctx, p, bytes); };
+  ctx->pool.before_release = [ctx]() { b200::queue_drain(ctx); };
+  ctx->staging.before_copy = [ctx]() { b200::queue_drain(ctx); };
   void *fn = nullptr;
   cudaDriverEntryPointQueryResult qres;
   if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
@@ -78,6 +80,8 @@ int b200_ctx_create(int device_id, b200_ctx **out) {
 int b200_ctx_destroy(b200_ctx *ctx) {
   if (!ctx) return B200_OK;
   DeviceGuard guard(ctx->device);
+  delete ctx->queue;   // issues what is still queued, then stops the worker
+  ctx->queue = nullptr;
   cudaDeviceSynchronize();
   b200::plane_cache_drop_range(ctx, nullptr, 0);
   ctx->pool.on_free = nullptr;
@@ -99,9 +103,10 @@ int b200_ctx_device(const b200_ctx *ctx, int *device_id, int *sm_count) {
 int b200_status_poll(b200_ctx *ctx, void *stream, int *code) {
   if (!ctx || !code) return B200_ERR_INVALID_ARG;
   DeviceGuard guard(ctx->device);
+  b200::queue_drain(ctx);
   B200_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   *code = b200::take_status(ctx);
-  return B200_OK;
+  return b200::take_launch_error(ctx);
 }
 
 int b200_status_peek(b200_ctx *ctx, int *code) {
@@ -160,6 +165,29 @@ int b200_set_pair_policy(b200_ctx *ctx, int policy) {
   return B200_OK;
 }
 
+int b200_set_async_launch(b200_ctx *ctx, int on) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  if (on && !ctx->queue) {
+    ctx->queue = new (std::nothrow) b200::LaunchQueue(ctx->device);
+    if (!ctx->queue) return B200_ERR_OUT_OF_MEMORY;
+  }
+  if (!on) b200::queue_drain(ctx);
+  ctx->async = on != 0;
+  return B200_OK;
+}
+
+int b200_launch_flush(b200_ctx *ctx) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  b200::queue_drain(ctx);
+  return B200_OK;
+}
+
+int b200_set_dependent_launch(b200_ctx *ctx, int on) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  ctx->pdl = on != 0;
+  return B200_OK;
+}
+
 int b200_operand_cache_enable(b200_ctx *ctx, size_t max_bytes) {
   if (!ctx) return B200_ERR_INVALID_ARG;
   ctx->planes.cap = max_bytes;
@@ -198,6 +226,7 @@ int b200_profile_read(b200_ctx *ctx, double ms[4], uint64_t launches[4]) {
   if (!ctx || !ms || !launches) return B200_ERR_INVALID_ARG;
   DeviceGuard guard(ctx->device);
   for (int i = 0; i < b200::kProfKinds; ++i) { ms[i] = 0.0; launches[i] = 0; }
+  b200::queue_drain(ctx);
   B200_CUDA_TRY(cudaDeviceSynchronize());
   for (auto &r : ctx->prof) {
     float t = 0.f;
@@ -287,6 +316,7 @@ int b200_matmul_fw(b200_ctx *ctx, int mode, const void *a, const void *b, void *
   if (ny == 0) return B200_OK;  // an empty result (primitiv's Shape never has a zero extent)
   if (dj == 0) {                // an empty contraction: y = 0
     DeviceGuard guard(ctx->device);
+    b200::queue_drain(ctx);
     B200_CUDA_TRY(cudaMemsetAsync(y, 0, ny * (ba > bb ? ba : bb) * b200::elem_bytes(mode),
                                   static_cast<cudaStream_t>(stream)));
     return B200_OK;
@@ -321,6 +351,7 @@ int b200_matmul_bw_ex(b200_ctx *ctx, int mode, const void *a, const void *b, con
   if (di == 0 || dj == 0 || dk == 0) {
     // some extent is empty: nothing to add; a gradient that was to be written becomes zeros
     DeviceGuard guard(ctx->device);
+    b200::queue_drain(ctx);
     const size_t eb = b200::elem_bytes(mode);
     if (ga && !acc_a && na) B200_CUDA_TRY(cudaMemsetAsync(ga, 0, na * ba * eb, static_cast<cudaStream_t>(stream)));
     if (gb && !acc_b && nb) B200_CUDA_TRY(cudaMemsetAsync(gb, 0, nb * bb * eb, static_cast<cudaStream_t>(stream)));
@@ -422,6 +453,7 @@ int b200_matmul_fw_host(b200_ctx *ctx, int mode, const void *a_host, const void 
   if (rc) return rc;
   if (!a_host || !b_host || !y_host) return B200_ERR_INVALID_ARG;
   DeviceGuard guard(ctx->device);
+  b200::InlineLaunches inline_launches(ctx);  // three streams and events: everything on this thread
   const size_t eb = b200::elem_bytes(mode);
   const uint32_t bs = ba > bb ? ba : bb;
   const size_t ia = (size_t)di * dj * eb, ib = (size_t)dj * dk * eb, iy = (size_t)di * dk * eb;  // one item
@@ -464,6 +496,7 @@ int b200_matmul_bw_host(b200_ctx *ctx, int mode, const void *a_host, const void 
   if (rc) return rc;
   if (!a_host || !b_host || !gy_host || !ga_host || !gb_host) return B200_ERR_INVALID_ARG;
   DeviceGuard guard(ctx->device);
+  b200::InlineLaunches inline_launches(ctx);  // three streams and events: everything on this thread
   const size_t eb = b200::elem_bytes(mode);
   const uint32_t bs = ba > bb ? ba : bb;
   const size_t ia = (size_t)di * dj * eb, ib = (size_t)dj * dk * eb, iy = (size_t)di * dk * eb;
@@ -536,6 +569,7 @@ int b200_matmul_fw_bw_host(b200_ctx *ctx, int mode, const void *a_host, const vo
   if (want_bw && !gy_host) return B200_ERR_INVALID_ARG;
   if (!y_host && !want_bw) return B200_OK;
   DeviceGuard guard(ctx->device);
+  b200::InlineLaunches inline_launches(ctx);  // three streams and events: everything on this thread
   const size_t eb = b200::elem_bytes(mode);
   const uint32_t bs = ba > bb ? ba : bb;
   const size_t ia = (size_t)di * dj * eb, ib = (size_t)dj * dk * eb, iy = (size_t)di * dk * eb;  // one item

@@ -29,6 +29,7 @@ struct ConvGeom {
 template <typename T>
 __global__ void __launch_bounds__(kBlock) im2col_kernel(const T *__restrict__ x, T *__restrict__ col, ConvGeom g,
                                                         u64 per_batch, u64 total, u64 x_volume, int x_batched) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   const u64 P = static_cast<u64>(g.Ho) * g.Wo;
   for (u64 t = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
@@ -52,6 +53,7 @@ __global__ void __launch_bounds__(kBlock) im2col_kernel(const T *__restrict__ x,
 template <typename T>
 __global__ void __launch_bounds__(kBlock) col2im_kernel(const T *__restrict__ gcol, T *gx, ConvGeom g, u64 x_volume,
                                                         u64 total, u64 col_per_batch) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   const u64 P = static_cast<u64>(g.Ho) * g.Wo;
   for (u64 t = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
@@ -87,6 +89,7 @@ struct PoolGeom {
 template <typename T>
 __global__ void __launch_bounds__(kBlock) max_pool2d_fw_kernel(const T *__restrict__ x, T *__restrict__ y, PoolGeom g,
                                                                u64 total) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   const u64 ys = static_cast<u64>(g.Ho) * g.Wo, xs = static_cast<u64>(g.H) * g.W;
   for (u64 t = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
@@ -113,6 +116,7 @@ __global__ void __launch_bounds__(kBlock) max_pool2d_fw_kernel(const T *__restri
 template <typename T>
 __global__ void __launch_bounds__(kBlock) max_pool2d_bw_kernel(const T *__restrict__ x, const T *__restrict__ y,
                                                                const T *__restrict__ gy, T *gx, PoolGeom g, u64 total) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   const u64 ys = static_cast<u64>(g.Ho) * g.Wo, xs = static_cast<u64>(g.H) * g.W;
   for (u64 t = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
@@ -177,8 +181,7 @@ int b200_im2col(b200_ctx *ctx, int mode, const void *x, void *col, uint32_t H, u
   const u64 per_batch = static_cast<u64>(Ho) * Wo * kh * kw * C, total = per_batch * batch;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    im2col_kernel<T><<<grid_for(ctx, total, kBlock), kBlock, 0, s>>>(
-        static_cast<const T *>(x), static_cast<T *>(col), g, per_batch, total, static_cast<u64>(H) * W * C, x_batched);
+    b200::launch(ctx, im2col_kernel<T>, dim3(grid_for(ctx, total, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(col), g, per_batch, total, static_cast<u64>(H) * W * C, x_batched);
   });
   B200_OPS_EPILOGUE(ctx);
 }
@@ -194,7 +197,7 @@ int b200_col2im(b200_ctx *ctx, int mode, const void *gcol, void *gx, uint32_t H,
   const u64 col_per_batch = static_cast<u64>(Ho) * Wo * kh * kw * C;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    col2im_kernel<T><<<grid_for(ctx, total, kBlock), kBlock, 0, s>>>(static_cast<const T *>(gcol), static_cast<T *>(gx),
+    b200::launch(ctx, col2im_kernel<T>, dim3(grid_for(ctx, total, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(gcol), static_cast<T *>(gx),
                                                                    g, x_volume, total, col_per_batch);
   });
   B200_OPS_EPILOGUE(ctx);
@@ -210,7 +213,7 @@ int b200_max_pool2d_fw(b200_ctx *ctx, int mode, const void *x, void *y, uint32_t
   if (total == 0) return B200_OK;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    max_pool2d_fw_kernel<T><<<grid_for(ctx, total, kBlock), kBlock, 0, s>>>(static_cast<const T *>(x),
+    b200::launch(ctx, max_pool2d_fw_kernel<T>, dim3(grid_for(ctx, total, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x),
                                                                            static_cast<T *>(y), g, total);
   });
   B200_OPS_EPILOGUE(ctx);
@@ -227,8 +230,7 @@ int b200_max_pool2d_bw(b200_ctx *ctx, int mode, const void *x, const void *y, co
   if (total == 0) return B200_OK;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    max_pool2d_bw_kernel<T><<<grid_for(ctx, total, kBlock), kBlock, 0, s>>>(
-        static_cast<const T *>(x), static_cast<const T *>(y), static_cast<const T *>(gy), static_cast<T *>(gx), g, total);
+    b200::launch(ctx, max_pool2d_bw_kernel<T>, dim3(grid_for(ctx, total, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<const T *>(y), static_cast<const T *>(gy), static_cast<T *>(gx), g, total);
   });
   B200_OPS_EPILOGUE(ctx);
 }

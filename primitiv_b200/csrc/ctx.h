@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "../../include/primitiv_b200.h"
+#include "launch.h"
 
 namespace b200 {
 
@@ -36,6 +37,9 @@ class Pool {
   // Called with (block, bytes) whenever a block goes back to the pool: whatever was derived from
   // its contents (cached operand planes) is stale from then on.
   std::function<void(const void *, std::size_t)> on_free;
+  // Called before cached blocks are handed back to the driver: the context uses it to issue
+  // launches that are still waiting in its launch queue and may read those blocks.
+  std::function<void()> before_release;
 
  private:
   std::map<std::size_t, std::vector<void *>> cached_;
@@ -68,6 +72,8 @@ class StagingRing {
   int upload(void *dst, const void *src, std::size_t bytes, cudaStream_t stream);
   // waits for every pending DMA out of the ring
   void drain();
+  // Called before each copy is queued on the stream (the context lets its launch queue catch up).
+  std::function<void()> before_copy;
 
  private:
   char *base_ = nullptr;
@@ -135,6 +141,13 @@ struct b200_ctx {
   std::vector<cudaEvent_t> pipe_events;
   cudaEvent_t barrier_event = nullptr;  // b200_stream_barrier: marks this GPU's default stream
   b200::PlaneCache planes;
+  // launch policy (launch.h): programmatic dependent launch on every kernel; kernel launches issued
+  // by a worker thread when the caller has asked for it
+  bool pdl = true;
+  bool async = false;
+  int inline_depth = 0;            // > 0 inside an entry point that interleaves launches with other stream work
+  b200::LaunchQueue *queue = nullptr;
+  int launch_error = 0;            // first error of a launch issued on the caller's thread
 };
 
 namespace b200 {
@@ -165,6 +178,7 @@ struct ProfScope {
   cudaEvent_t stop = nullptr;
   ProfScope(b200_ctx *c, int kind, cudaStream_t s) : ctx(c), stream(s) {
     if (!c->profiling) return;
+    queue_drain(c);  // (launches are not deferred while profiling; this covers the moment it is switched on)
     cudaEvent_t start;
     if (cudaEventCreate(&start) != cudaSuccess) return;
     if (cudaEventCreate(&stop) != cudaSuccess) { cudaEventDestroy(start); stop = nullptr; return; }
@@ -214,6 +228,18 @@ inline int elem_bytes(int mode) { return mode == B200_MODE_FP16 ? 2 : 4; }
 // Reads and clears the status word.  Meaningful once the work that may have written it has
 // been waited for; every entry point that synchronises calls this and returns the code, which is
 // how a wait that ran out becomes an error of the next host-visible result.
+// First error of a kernel launch since the last call (launches return nothing to their entry
+// point once a worker thread issues them); cleared by the read.  Call after queue_drain.
+inline int take_launch_error(b200_ctx *ctx) {
+  int e = ctx->launch_error;
+  ctx->launch_error = 0;
+  if (ctx->queue) {
+    const int q = ctx->queue->take_error();
+    if (e == 0) e = q;
+  }
+  return e;
+}
+
 inline int take_status(b200_ctx *ctx) {
   volatile int *w = ctx->h_status;
   const int code = *w;
@@ -230,6 +256,19 @@ __device__ __forceinline__ void report_status(int *status, int code) {
 }
 #endif
 
+}  // namespace b200
+
+namespace b200 {
+// Marks an entry point that mixes kernel launches with copies, events or several streams: launches
+// inside it are issued on the caller's thread, after the worker has caught up.
+struct InlineLaunches {
+  b200_ctx *ctx;
+  explicit InlineLaunches(b200_ctx *c) : ctx(c) {
+    queue_drain(c);
+    ++c->inline_depth;
+  }
+  ~InlineLaunches() { --ctx->inline_depth; }
+};
 }  // namespace b200
 
 #define B200_CUDA_TRY(expr)                     \

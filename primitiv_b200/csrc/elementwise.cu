@@ -83,6 +83,7 @@ __device__ __forceinline__ float unary_d(float x, float y, float gy, float k, in
 template <typename T, int OP>
 __global__ void __launch_bounds__(kBlock) unary_fw_kernel(const T *__restrict__ x, T *__restrict__ y,
                                                           u64 n, float k, int ik, int vec) {
+  pdl_enter();
   const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   constexpr int N = Vec<T>::N;
@@ -101,6 +102,7 @@ template <typename T, int OP>
 __global__ void __launch_bounds__(kBlock) unary_bw_kernel(const T *__restrict__ x, const T *__restrict__ y,
                                                           const T *__restrict__ gy, T *__restrict__ gx,
                                                           u64 n, float k, int ik, int vec, int accumulate) {
+  pdl_enter();
   const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   constexpr int N = Vec<T>::N;
@@ -150,6 +152,7 @@ template <typename T, int OP>
 __global__ void __launch_bounds__(kBlock) binary_fw_kernel(const T *__restrict__ a, const T *__restrict__ b,
                                                            T *__restrict__ y, u64 volume, u64 total,
                                                            int a_batched, int b_batched, int vec) {
+  pdl_enter();
   const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   constexpr int N = Vec<T>::N;
@@ -175,6 +178,7 @@ template <typename T, int OP>
 __global__ void __launch_bounds__(kBlock) binary_bw_flat_kernel(const T *__restrict__ a, const T *__restrict__ b,
                                                                 const T *__restrict__ y, const T *__restrict__ gy,
                                                                 T *ga, T *gb, u64 total, int acc_a, int acc_b) {
+  pdl_enter();
   // ga and gb are deliberately not __restrict__: for x + x (or x * x) they are the same array,
   // and the two updates of an element must then happen one after the other.
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
@@ -195,6 +199,7 @@ __global__ void __launch_bounds__(256) binary_bw_mixed_kernel(const T *__restric
                                                               T *ga, T *gb, float *partial, u64 volume,
                                                               uint32_t batch, uint32_t slice_len, int a_batched,
                                                               int acc_batched, int acc_summed) {
+  pdl_enter();
   __shared__ float buf[kSumLanes][32];
   T *g_batched = a_batched ? ga : gb, *g_summed = a_batched ? gb : ga;
   for (u64 tile = blockIdx.x; tile * 32ull < volume; tile += gridDim.x) {
@@ -224,6 +229,7 @@ template <typename T, int OP>
 __global__ void __launch_bounds__(kBlock) scalar_fw_kernel(const T *__restrict__ x, const T *__restrict__ k,
                                                            T *__restrict__ y, u64 volume, u64 total,
                                                            int x_batched, int k_batched) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 e = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
     const u64 n = e / volume, i = e - n * volume;
@@ -236,6 +242,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBlock) inplace_add_kernel(const T *__restrict__ x, T *__restrict__ y,
                                                              u64 volume, uint32_t bx, uint32_t by, float sign,
                                                              int vec) {
+  pdl_enter();
   const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   constexpr int N = Vec<T>::N;
@@ -260,6 +267,7 @@ __global__ void __launch_bounds__(kBlock) inplace_add_kernel(const T *__restrict
 
 template <typename T>
 __global__ void __launch_bounds__(kBlock) fill_kernel(T *__restrict__ y, u64 n, float value, int vec) {
+  pdl_enter();
   const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   constexpr int N = Vec<T>::N;
@@ -274,6 +282,7 @@ __global__ void __launch_bounds__(kBlock) fill_kernel(T *__restrict__ y, u64 n, 
 // in place, so no __restrict__ / read-only loads here
 template <typename T>
 __global__ void __launch_bounds__(kBlock) scale_kernel(T *x, u64 n, float k) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 i = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
     st(x, i, ld(x, i) * k);
@@ -281,6 +290,7 @@ __global__ void __launch_bounds__(kBlock) scale_kernel(T *x, u64 n, float k) {
 
 template <typename T>
 __global__ void __launch_bounds__(kBlock) identity_kernel(T *__restrict__ y, uint32_t size) {
+  pdl_enter();
   const u64 total = static_cast<u64>(size) * size;
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 e = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride)
@@ -289,6 +299,7 @@ __global__ void __launch_bounds__(kBlock) identity_kernel(T *__restrict__ y, uin
 
 template <typename S, typename D>
 __global__ void __launch_bounds__(kBlock) convert_kernel(const S *__restrict__ x, D *__restrict__ y, u64 n) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 i = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) st(y, i, ld(x, i));
 }
@@ -304,7 +315,7 @@ void launch_unary_fw(b200_ctx *ctx, cudaStream_t s, int op, const void *x, void 
                      int ik, int vec) {
   const unsigned grid = grid_for(ctx, n / (vec ? Vec<T>::N : 1) + 1, kBlock);
   switch (op) {
-#define X(OP) case OP: unary_fw_kernel<T, OP><<<grid, kBlock, 0, s>>>(static_cast<const T *>(x), static_cast<T *>(y), n, k, ik, vec); break;
+#define X(OP) case OP: b200::launch(ctx, unary_fw_kernel<T, OP>, dim3(grid), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y), n, k, ik, vec); break;
     B200_UNARY_OPS(X)
 #undef X
   }
@@ -315,7 +326,7 @@ void launch_unary_bw(b200_ctx *ctx, cudaStream_t s, int op, const void *x, const
                      void *gx, u64 n, float k, int ik, int vec, int accumulate) {
   const unsigned grid = grid_for(ctx, n / (vec ? Vec<T>::N : 1) + 1, kBlock);
   switch (op) {
-#define X(OP) case OP: unary_bw_kernel<T, OP><<<grid, kBlock, 0, s>>>(static_cast<const T *>(x), static_cast<const T *>(y), static_cast<const T *>(gy), static_cast<T *>(gx), n, k, ik, vec, accumulate); break;
+#define X(OP) case OP: b200::launch(ctx, unary_bw_kernel<T, OP>, dim3(grid), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<const T *>(y), static_cast<const T *>(gy), static_cast<T *>(gx), n, k, ik, vec, accumulate); break;
     B200_UNARY_OPS(X)
 #undef X
   }
@@ -326,7 +337,7 @@ void launch_scalar_fw(b200_ctx *ctx, cudaStream_t s, int op, const void *x, cons
                       u64 volume, u64 total, int x_batched, int k_batched) {
   const unsigned grid = grid_for(ctx, total, kBlock);
   switch (op) {
-#define X(OP) case OP: scalar_fw_kernel<T, OP><<<grid, kBlock, 0, s>>>(static_cast<const T *>(x), static_cast<const T *>(k), static_cast<T *>(y), volume, total, x_batched, k_batched); break;
+#define X(OP) case OP: b200::launch(ctx, scalar_fw_kernel<T, OP>, dim3(grid), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<const T *>(k), static_cast<T *>(y), volume, total, x_batched, k_batched); break;
     B200_SCALAR_OPS(X)
 #undef X
   }
@@ -338,7 +349,7 @@ void launch_binary_fw(b200_ctx *ctx, cudaStream_t s, int op, const void *a, cons
   const int vec = aligned16(a) && aligned16(b) && aligned16(y) && volume % Vec<T>::N == 0;
   const unsigned grid = grid_for(ctx, total / (vec ? Vec<T>::N : 1) + 1, kBlock);
   switch (op) {
-#define X(OP) case OP: binary_fw_kernel<T, OP><<<grid, kBlock, 0, s>>>(static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(y), volume, total, a_batched, b_batched, vec); break;
+#define X(OP) case OP: b200::launch(ctx, binary_fw_kernel<T, OP>, dim3(grid), dim3(kBlock), 0, s, 1u, static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(y), volume, total, a_batched, b_batched, vec); break;
     B200_BINARY_OPS(X)
 #undef X
   }
@@ -355,7 +366,7 @@ int launch_binary_bw(b200_ctx *ctx, cudaStream_t s, int op, const void *a, const
     const u64 total = volume * batch;
     const unsigned grid = grid_for(ctx, total, kBlock);
     switch (op) {
-#define X(OP) case OP: binary_bw_flat_kernel<T, OP><<<grid, kBlock, 0, s>>>(pa, pb, py, pgy, pga, pgb, total, acc_a, acc_b); break;
+#define X(OP) case OP: b200::launch(ctx, binary_bw_flat_kernel<T, OP>, dim3(grid), dim3(kBlock), 0, s, 1u, pa, pb, py, pgy, pga, pgb, total, acc_a, acc_b); break;
       B200_BINARY_OPS(X)
 #undef X
     }
@@ -369,12 +380,12 @@ int launch_binary_bw(b200_ctx *ctx, cudaStream_t s, int op, const void *a, const
   }
   const dim3 grid(bs.tiles, bs.slices), block(32, kSumLanes);
   switch (op) {
-#define X(OP) case OP: binary_bw_mixed_kernel<T, OP><<<grid, block, 0, s>>>(pa, pb, py, pgy, pga, pgb, static_cast<float *>(partial), volume, batch, bs.slice_len, a_batched, a_batched ? acc_a : acc_b, a_batched ? acc_b : acc_a); break;
+#define X(OP) case OP: b200::launch(ctx, binary_bw_mixed_kernel<T, OP>, dim3(grid), dim3(block), 0, s, 1u, pa, pb, py, pgy, pga, pgb, static_cast<float *>(partial), volume, batch, bs.slice_len, a_batched, a_batched ? acc_a : acc_b, a_batched ? acc_b : acc_a); break;
     B200_BINARY_OPS(X)
 #undef X
   }
   if (bs.slices > 1) {
-    batch_final_kernel<T><<<grid_for(ctx, volume, 256), 256, 0, s>>>(static_cast<const float *>(partial),
+    b200::launch(ctx, batch_final_kernel<T>, dim3(grid_for(ctx, volume, 256)), dim3(256), 0, s, 1u, static_cast<const float *>(partial),
                                                                      a_batched ? pgb : pga, volume, bs.slices, 1.f,
                                                                      a_batched ? acc_b : acc_a);
     ++ctx->launches;
@@ -463,8 +474,7 @@ int b200_inplace_add(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t v
     } else {
       const int vec = aligned16(x) && aligned16(y) && volume % Vec<T>::N == 0;
       const u64 work = volume * by / (vec ? Vec<T>::N : 1) + 1;
-      inplace_add_kernel<T><<<grid_for(ctx, work, kBlock), kBlock, 0, s>>>(
-          static_cast<const T *>(x), static_cast<T *>(y), volume, bx, by, sign, vec);
+      b200::launch(ctx, inplace_add_kernel<T>, dim3(grid_for(ctx, work, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y), volume, bx, by, sign, vec);
     }
   });
   B200_OPS_EPILOGUE(ctx);
@@ -476,7 +486,7 @@ int b200_inplace_multiply_const(b200_ctx *ctx, int mode, void *x, uint64_t n, fl
   if (!x) return B200_ERR_INVALID_ARG;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    scale_kernel<T><<<grid_for(ctx, n, kBlock), kBlock, 0, s>>>(static_cast<T *>(x), n, k);
+    b200::launch(ctx, scale_kernel<T>, dim3(grid_for(ctx, n, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<T *>(x), n, k);
   });
   B200_OPS_EPILOGUE(ctx);
 }
@@ -488,8 +498,7 @@ int b200_fill(b200_ctx *ctx, int mode, void *y, uint64_t n, float value, void *s
   const int vec = aligned16(y);
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    fill_kernel<T><<<grid_for(ctx, n / (vec ? Vec<T>::N : 1) + 1, kBlock), kBlock, 0, s>>>(
-        static_cast<T *>(y), n, value, vec);
+    b200::launch(ctx, fill_kernel<T>, dim3(grid_for(ctx, n / (vec ? Vec<T>::N : 1) + 1, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<T *>(y), n, value, vec);
   });
   B200_OPS_EPILOGUE(ctx);
 }
@@ -500,8 +509,7 @@ int b200_identity(b200_ctx *ctx, int mode, void *y, uint32_t size, void *stream)
   if (!y) return B200_ERR_INVALID_ARG;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    identity_kernel<T><<<grid_for(ctx, static_cast<u64>(size) * size, kBlock), kBlock, 0, s>>>(
-        static_cast<T *>(y), size);
+    b200::launch(ctx, identity_kernel<T>, dim3(grid_for(ctx, static_cast<u64>(size) * size, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<T *>(y), size);
   });
   B200_OPS_EPILOGUE(ctx);
 }
@@ -519,8 +527,7 @@ int b200_upload(b200_ctx *ctx, int mode, const float *values_host, void *y, uint
   if (rc) return rc;
   rc = ctx->staging.upload(tmp, values_host, n * sizeof(float), s);
   if (rc == B200_OK) {
-    convert_kernel<float, __half><<<grid_for(ctx, n, kBlock), kBlock, 0, s>>>(
-        static_cast<const float *>(tmp), static_cast<__half *>(y), n);
+    b200::launch(ctx, convert_kernel<float, __half>, dim3(grid_for(ctx, n, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const float *>(tmp), static_cast<__half *>(y), n);
     ++ctx->launches;
     rc = static_cast<int>(cudaGetLastError());
   }
@@ -533,16 +540,19 @@ int b200_download(b200_ctx *ctx, int mode, const void *x, float *values_host, ui
   if (n == 0) return B200_OK;
   if (!values_host || !x) return B200_ERR_INVALID_ARG;
   if (mode != B200_MODE_FP16) {
+    b200::queue_drain(ctx);
     B200_CUDA_TRY(cudaMemcpyAsync(values_host, x, n * sizeof(float), cudaMemcpyDeviceToHost, s));
     B200_CUDA_TRY(cudaStreamSynchronize(s));
-    return b200::take_status(ctx);  // values computed by a kernel whose wait ran out are not handed over silently
+    const int launch_rc = b200::take_launch_error(ctx);
+    const int status = b200::take_status(ctx);
+    return launch_rc ? launch_rc : status;  // values computed by a kernel whose wait ran out are not handed over silently
   }
   void *tmp = nullptr;
   int rc = ctx->pool.alloc(n * sizeof(float), &tmp, nullptr);
   if (rc) return rc;
-  convert_kernel<__half, float><<<grid_for(ctx, n, kBlock), kBlock, 0, s>>>(
-      static_cast<const __half *>(x), static_cast<float *>(tmp), n);
+  b200::launch(ctx, convert_kernel<__half, float>, dim3(grid_for(ctx, n, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const __half *>(x), static_cast<float *>(tmp), n);
   ++ctx->launches;
+  b200::queue_drain(ctx);
   cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) e = cudaMemcpyAsync(values_host, tmp, n * sizeof(float), cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
@@ -557,14 +567,15 @@ int b200_copy(b200_ctx *ctx, int src_mode, const void *x, int dst_mode, void *y,
   const bool sh = src_mode == B200_MODE_FP16, dh = dst_mode == B200_MODE_FP16;
   if (sh == dh) {
     // cudaMemcpyDefault: also right when x lives on another GPU of this process (unified addressing)
+    b200::queue_drain(ctx);
     B200_CUDA_TRY(cudaMemcpyAsync(y, x, n * (sh ? 2 : 4), cudaMemcpyDefault, s));
     return B200_OK;
   }
   const unsigned grid = grid_for(ctx, n, kBlock);
   if (sh)
-    convert_kernel<__half, float><<<grid, kBlock, 0, s>>>(static_cast<const __half *>(x), static_cast<float *>(y), n);
+    b200::launch(ctx, convert_kernel<__half, float>, dim3(grid), dim3(kBlock), 0, s, 1u, static_cast<const __half *>(x), static_cast<float *>(y), n);
   else
-    convert_kernel<float, __half><<<grid, kBlock, 0, s>>>(static_cast<const float *>(x), static_cast<__half *>(y), n);
+    b200::launch(ctx, convert_kernel<float, __half>, dim3(grid), dim3(kBlock), 0, s, 1u, static_cast<const float *>(x), static_cast<__half *>(y), n);
   B200_OPS_EPILOGUE(ctx);
 }
 

@@ -30,6 +30,7 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(
     uint32_t m, uint32_t n, uint32_t k, uint32_t red,
     uint64_t a_gs, uint64_t a_rs, uint64_t b_gs, uint64_t b_rs, uint64_t c_gs,
     int accumulate, uint32_t tiles_m, uint32_t tiles_n) {
+  pdl_enter();
   __shared__ float As[TK][TM + 1];
   __shared__ float Bs[TK][TN + 1];
 
@@ -119,7 +120,7 @@ int launch(b200_ctx *ctx, const GemmArgs &a, cudaStream_t s) {
   T *C = static_cast<T *>(a.C);
   ProfScope prof(ctx, kProfGemmSimt, s);
 #define B200_SIMT_LAUNCH(TA, TB)                                                              \
-  gemm_simt_kernel<T, TA, TB><<<grid, block, 0, s>>>(A, B, C, a.m, a.n, a.k, a.red, a.a_gs, \
+  b200::launch(ctx, gemm_simt_kernel<T, TA, TB>, dim3(grid), dim3(block), 0, s, 1u, A, B, C, a.m, a.n, a.k, a.red, a.a_gs, \
                                                      a.a_rs, a.b_gs, a.b_rs, a.c_gs,        \
                                                      a.accumulate, tiles_m, tiles_n)
   if (a.trans_a) {

@@ -29,6 +29,7 @@ template <typename T, uint32_t MP, uint32_t kCols>
 __global__ void __launch_bounds__(256, MP <= 12 ? 4 : 2) skinny_rows_kernel(const T *__restrict__ A, const T *__restrict__ B, T *C,
                                                           uint32_t m, uint32_t n, uint32_t k, u64 a_si, u64 a_sk,
                                                           int accumulate) {
+  pdl_enter();
   constexpr uint32_t kDepth = 4;  // k-steps whose loads are in flight together (8 measured slower)
   extern __shared__ __align__(16) float As[];  // [k][MP], rows past m are zero
   for (uint32_t e = threadIdx.x; e < k * MP; e += blockDim.x) {
@@ -113,6 +114,7 @@ template <typename T, uint32_t MP, uint32_t kCols>
 __global__ void __launch_bounds__(256, MP <= 12 ? 4 : 2) skinny_reduce_kernel(const T *__restrict__ A, const T *__restrict__ B,
                                                             float *__restrict__ partial, uint32_t m, uint32_t n,
                                                             uint32_t k, uint32_t slice_len) {
+  pdl_enter();
   constexpr uint32_t kDepth = 4;  // k-steps whose loads are in flight together (8 measured slower)
   extern __shared__ __align__(16) float As[];  // [chunk][MP]
   const uint32_t chunk_cap = kSmemFloats / MP;
@@ -176,6 +178,7 @@ __global__ void __launch_bounds__(256, MP <= 12 ? 4 : 2) skinny_reduce_kernel(co
 template <typename T>
 __global__ void __launch_bounds__(256) reduce_final_kernel(const float *__restrict__ partial, T *C, u64 count,
                                                            uint32_t slices, int accumulate) {
+  pdl_enter();
   __shared__ float buf[8][32];
   const u64 e = static_cast<u64>(blockIdx.x) * 32u + threadIdx.x;
   float t = 0.f;
@@ -195,6 +198,7 @@ __global__ void __launch_bounds__(256) reduce_final_kernel(const float *__restri
 template <typename T, uint32_t KP, bool accumulate>
 __global__ void __launch_bounds__(256, 4) skinny_outer_kernel(const T *__restrict__ A, const T *__restrict__ B, T *C,
                                                               uint32_t m, uint32_t n, uint32_t k, uint32_t strip) {
+  pdl_enter();
   extern __shared__ __align__(16) float Bs[];  // [strip][KP], entries past k are zero
   const u64 j_lo = static_cast<u64>(blockIdx.y) * strip;
   const uint32_t cols = n - j_lo < strip ? static_cast<uint32_t>(n - j_lo) : strip;
@@ -272,9 +276,9 @@ static int skinny_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t s) {
     const u64 col_groups = (static_cast<u64>(g.n) + 1) / 2;  // two columns per warp pass (four with mp == 4)
     const u64 want = (col_groups + 7) / 8, cap = static_cast<u64>(ctx->sm_count) * 4;
     const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
-    if (mp == 4) skinny_rows_kernel<T, 4, 4><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, a_si, a_sk, g.accumulate);
-    else if (mp == 12) skinny_rows_kernel<T, 12, 2><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, a_si, a_sk, g.accumulate);
-    else skinny_rows_kernel<T, 20, 2><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, a_si, a_sk, g.accumulate);
+    if (mp == 4) b200::launch(ctx, skinny_rows_kernel<T, 4, 4>, dim3(grid), dim3(256), smem, s, 1u, A, B, C, g.m, g.n, g.k, a_si, a_sk, g.accumulate);
+    else if (mp == 12) b200::launch(ctx, skinny_rows_kernel<T, 12, 2>, dim3(grid), dim3(256), smem, s, 1u, A, B, C, g.m, g.n, g.k, a_si, a_sk, g.accumulate);
+    else b200::launch(ctx, skinny_rows_kernel<T, 20, 2>, dim3(grid), dim3(256), smem, s, 1u, A, B, C, g.m, g.n, g.k, a_si, a_sk, g.accumulate);
     ++ctx->launches;
     return static_cast<int>(cudaGetLastError());
   }
@@ -295,10 +299,10 @@ static int skinny_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t s) {
     const uint32_t chunk = slice_len < kSmemFloats / mp ? slice_len : kSmemFloats / mp;
     const size_t smem = static_cast<size_t>(chunk) * mp * sizeof(float);
     float *pp = static_cast<float *>(partial);
-    if (mp == 4) skinny_reduce_kernel<T, 4, 4><<<dim3(gx, gy), 256, smem, s>>>(A, B, pp, g.m, g.n, g.k, slice_len);
-    else if (mp == 12) skinny_reduce_kernel<T, 12, 2><<<dim3(gx, gy), 256, smem, s>>>(A, B, pp, g.m, g.n, g.k, slice_len);
-    else skinny_reduce_kernel<T, 20, 2><<<dim3(gx, gy), 256, smem, s>>>(A, B, pp, g.m, g.n, g.k, slice_len);
-    reduce_final_kernel<T><<<static_cast<unsigned>((count + 31) / 32), dim3(32, 8), 0, s>>>(pp, C, count, gy, g.accumulate);
+    if (mp == 4) b200::launch(ctx, skinny_reduce_kernel<T, 4, 4>, dim3(gx, gy), dim3(256), smem, s, 1u, A, B, pp, g.m, g.n, g.k, slice_len);
+    else if (mp == 12) b200::launch(ctx, skinny_reduce_kernel<T, 12, 2>, dim3(gx, gy), dim3(256), smem, s, 1u, A, B, pp, g.m, g.n, g.k, slice_len);
+    else b200::launch(ctx, skinny_reduce_kernel<T, 20, 2>, dim3(gx, gy), dim3(256), smem, s, 1u, A, B, pp, g.m, g.n, g.k, slice_len);
+    b200::launch(ctx, reduce_final_kernel<T>, dim3(static_cast<unsigned>((count + 31) / 32)), dim3(32, 8), 0, s, 1u, pp, C, count, gy, g.accumulate);
     ctx->launches += 2;
     ctx->pool.free(partial);  // stream-ordered reuse
     return static_cast<int>(cudaGetLastError());
@@ -310,8 +314,8 @@ static int skinny_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t s) {
     if (grid.y > 65535u) return gemm_simt(ctx, g, s);
     const size_t smem = static_cast<size_t>(strip) * kp * sizeof(float);
 #define B200_OUTER(KP)                                                                                   \
-  (g.accumulate ? skinny_outer_kernel<T, KP, true><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, strip) \
-                : skinny_outer_kernel<T, KP, false><<<grid, 256, smem, s>>>(A, B, C, g.m, g.n, g.k, strip))
+  (g.accumulate ? b200::launch(ctx, skinny_outer_kernel<T, KP, true>, dim3(grid), dim3(256), smem, s, 1u, A, B, C, g.m, g.n, g.k, strip) \
+                : b200::launch(ctx, skinny_outer_kernel<T, KP, false>, dim3(grid), dim3(256), smem, s, 1u, A, B, C, g.m, g.n, g.k, strip))
     if (kp == 4) B200_OUTER(4);
     else if (kp == 8) B200_OUTER(8);
     else if (kp == 12) B200_OUTER(12);

@@ -502,6 +502,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
 
+  pdl_release_next();   // the grid queued behind this one may be scheduled as room becomes free
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -544,6 +545,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
   if constexpr (kCtas == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  // barriers and tensor memory are set up; nothing above touched global memory.  From here on the
+  // operands (and the old C) must be what the grid in front of this one left behind.
+  pdl_wait_previous();
 
   const uint32_t tiles_per_group = p.tiles_m * p.tiles_n;
   const uint32_t total_tiles = tiles_per_group * p.groups;
@@ -877,6 +881,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ partial, T *__restrict__ C,
                                                             unsigned long long mn, uint32_t groups, uint32_t splits,
                                                             unsigned long long c_gs, int accumulate) {
+  pdl_enter();
   const unsigned long long total = mn * groups;
   for (unsigned long long idx = blockIdx.x * 256ull + threadIdx.x; idx < total;
        idx += static_cast<unsigned long long>(gridDim.x) * 256ull) {
@@ -1320,45 +1325,32 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     const unsigned grid = static_cast<unsigned>((launch_tiles < units ? launch_tiles : units) * ctas);
     ProfScope prof(ctx, kProfGemmTc, stream);
     if (ctas == 2) {
-      cudaLaunchConfig_t cfg;
-      memset(&cfg, 0, sizeof(cfg));
-      cfg.gridDim = dim3(grid);
-      cfg.blockDim = dim3(kThreads);
-      cfg.dynamicSmemBytes = smem_bytes;
-      cfg.stream = stream;
-      cudaLaunchAttribute attr;
-      attr.id = cudaLaunchAttributeClusterDimension;
-      attr.val.clusterDim.x = 2;
-      attr.val.clusterDim.y = 1;
-      attr.val.clusterDim.z = 1;
-      cfg.attrs = &attr;
-      cfg.numAttrs = 1;
-      cudaError_t e;
-      if (mix && chunked) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, 2, 4>, p);
-      else if (mix) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 4>, p);
-      else if (split16 && chunked) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, 2, 3>, p);
-      else if (split16) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 3>, p);
-      else if (chunked) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true, 2, 0>, p);
-      else if (passes == 3) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 0>, p);
-      else if (!f16) e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 1>, p);
-      else e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, 2, 2>, p);
-      rc = static_cast<int>(e);
+      // clusters of two CTAs along x (a pair per 256-row tile)
+      const dim3 gd(grid), bd(kThreads);
+      if (mix && chunked) b200::launch(ctx, gemm_tc_kernel<true, 2, 4>, gd, bd, smem_bytes, stream, 2u, p);
+      else if (mix) b200::launch(ctx, gemm_tc_kernel<false, 2, 4>, gd, bd, smem_bytes, stream, 2u, p);
+      else if (split16 && chunked) b200::launch(ctx, gemm_tc_kernel<true, 2, 3>, gd, bd, smem_bytes, stream, 2u, p);
+      else if (split16) b200::launch(ctx, gemm_tc_kernel<false, 2, 3>, gd, bd, smem_bytes, stream, 2u, p);
+      else if (chunked) b200::launch(ctx, gemm_tc_kernel<true, 2, 0>, gd, bd, smem_bytes, stream, 2u, p);
+      else if (passes == 3) b200::launch(ctx, gemm_tc_kernel<false, 2, 0>, gd, bd, smem_bytes, stream, 2u, p);
+      else if (!f16) b200::launch(ctx, gemm_tc_kernel<false, 2, 1>, gd, bd, smem_bytes, stream, 2u, p);
+      else b200::launch(ctx, gemm_tc_kernel<false, 2, 2>, gd, bd, smem_bytes, stream, 2u, p);
     } else if (mix && chunked) {
-      gemm_tc_kernel<true, 1, 4><<<grid, kThreads, smem_bytes, stream>>>(p);
+      b200::launch(ctx, gemm_tc_kernel<true, 1, 4>, dim3(grid), dim3(kThreads), smem_bytes, stream, 1u, p);
     } else if (mix) {
-      gemm_tc_kernel<false, 1, 4><<<grid, kThreads, smem_bytes, stream>>>(p);
+      b200::launch(ctx, gemm_tc_kernel<false, 1, 4>, dim3(grid), dim3(kThreads), smem_bytes, stream, 1u, p);
     } else if (split16 && chunked) {
-      gemm_tc_kernel<true, 1, 3><<<grid, kThreads, smem_bytes, stream>>>(p);
+      b200::launch(ctx, gemm_tc_kernel<true, 1, 3>, dim3(grid), dim3(kThreads), smem_bytes, stream, 1u, p);
     } else if (split16) {
-      gemm_tc_kernel<false, 1, 3><<<grid, kThreads, smem_bytes, stream>>>(p);
+      b200::launch(ctx, gemm_tc_kernel<false, 1, 3>, dim3(grid), dim3(kThreads), smem_bytes, stream, 1u, p);
     } else if (chunked) {
-      gemm_tc_kernel<true, 1, 0><<<grid, kThreads, smem_bytes, stream>>>(p);
+      b200::launch(ctx, gemm_tc_kernel<true, 1, 0>, dim3(grid), dim3(kThreads), smem_bytes, stream, 1u, p);
     } else if (passes == 3) {
-      gemm_tc_kernel<false, 1, 0><<<grid, kThreads, smem_bytes, stream>>>(p);
+      b200::launch(ctx, gemm_tc_kernel<false, 1, 0>, dim3(grid), dim3(kThreads), smem_bytes, stream, 1u, p);
     } else if (!f16) {
-      gemm_tc_kernel<false, 1, 1><<<grid, kThreads, smem_bytes, stream>>>(p);
+      b200::launch(ctx, gemm_tc_kernel<false, 1, 1>, dim3(grid), dim3(kThreads), smem_bytes, stream, 1u, p);
     } else {
-      gemm_tc_kernel<false, 1, 2><<<grid, kThreads, smem_bytes, stream>>>(p);
+      b200::launch(ctx, gemm_tc_kernel<false, 1, 2>, dim3(grid), dim3(kThreads), smem_bytes, stream, 1u, p);
     }
     ++ctx->launches;
     if (rc == B200_OK) rc = static_cast<int>(cudaGetLastError());
@@ -1368,11 +1360,11 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
       const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 8ull;
       const unsigned blocks = static_cast<unsigned>(need < cap ? need : cap);
       if (half_store)
-        splitk_reduce_kernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const float *>(partial),
+        b200::launch(ctx, splitk_reduce_kernel<__half>, dim3(blocks), dim3(256), 0, stream, 1u, static_cast<const float *>(partial),
                                                                    static_cast<__half *>(g.C), mn, g.groups, splits,
                                                                    g.c_gs, g.accumulate);
       else
-        splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float *>(partial),
+        b200::launch(ctx, splitk_reduce_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1u, static_cast<const float *>(partial),
                                                                   static_cast<float *>(g.C), mn, g.groups, splits,
                                                                   g.c_gs, g.accumulate);
       ++ctx->launches;
@@ -1397,6 +1389,7 @@ namespace {
 // reports through the status word exactly as gemm_tc_kernel does when one of its waits
 // runs out.  Nothing faults or traps: the kernel returns normally.
 __global__ void wait_timeout_selftest_kernel(int *status, long long limit_cycles) {
+  pdl_enter();
   __shared__ __align__(8) uint64_t bar;
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bar), 1);
@@ -1416,7 +1409,7 @@ __global__ void wait_timeout_selftest_kernel(int *status, long long limit_cycles
 }  // namespace
 
 int selftest_wait_timeout(b200_ctx *ctx, cudaStream_t stream) {
-  wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>(ctx->d_status, 2000000ll);  // about a millisecond
+  b200::launch(ctx, wait_timeout_selftest_kernel, dim3(1), dim3(32), 0, stream, 1u, ctx->d_status, 2000000ll);  // about a millisecond
   ++ctx->launches;
   return static_cast<int>(cudaGetLastError());
 }

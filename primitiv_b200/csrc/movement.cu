@@ -17,6 +17,7 @@ constexpr unsigned kBlock = 256;
 template <typename T>
 __global__ void __launch_bounds__(kBlock) slice_fw_kernel(const T *__restrict__ x, T *__restrict__ y, u64 base,
                                                           u64 span, u64 skip, u64 off, u64 total) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 e = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
     const u64 r = e / span, j = e - r * span;
@@ -30,6 +31,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBlock) slice_bw_flat_kernel(const T *__restrict__ gy, T *gx, u64 span, u64 skip,
                                                                u64 off, u64 per_batch, u64 x_volume, u64 total,
                                                                int gy_batched) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 t = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
     const u64 n = t / per_batch, e = t - n * per_batch;
@@ -44,6 +46,7 @@ __global__ void __launch_bounds__(kBlock) slice_bw_flat_kernel(const T *__restri
 template <typename T>
 __global__ void __launch_bounds__(256) slice_bw_sum_kernel(const T *__restrict__ gy, T *gx, u64 span, u64 skip,
                                                            u64 off, u64 per_batch, uint32_t batch) {
+  pdl_enter();
   __shared__ float buf[kSumLanes][32];
   for (u64 tile = blockIdx.x; tile * 32ull < per_batch; tile += gridDim.x) {
     const u64 e = tile * 32ull + threadIdx.x;
@@ -64,6 +67,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBlock) concat_part_kernel(const T *__restrict__ x, T *__restrict__ y, u64 span,
                                                              u64 skip, u64 off, u64 per_batch, u64 y_volume,
                                                              u64 total, int x_batched) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 t = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
     const u64 n = t / per_batch, e = t - n * per_batch;
@@ -77,6 +81,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBlock) pick_fw_kernel(const T *__restrict__ x, const uint32_t *__restrict__ ids,
                                                          T *__restrict__ y, u64 base, u64 skip, u64 per_batch,
                                                          u64 x_volume, u64 total, int x_batched, int ids_batched) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 t = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
     const u64 n = t / per_batch, e = t - n * per_batch;
@@ -91,6 +96,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBlock) pick_bw_kernel(const T *__restrict__ gy, const uint32_t *__restrict__ ids,
                                                          T *gx, u64 base, u64 skip, u64 per_batch, u64 x_volume,
                                                          uint32_t batch, int gx_batched, int ids_batched) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 e = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; e < per_batch; e += stride) {
     const u64 r = e / base, i = e - r * base;
@@ -108,6 +114,7 @@ __global__ void __launch_bounds__(kBlock) pick_bw_flat_kernel(const T *__restric
                                                               const uint32_t *__restrict__ ids, T *gx, u64 base,
                                                               u64 skip, u64 per_batch, u64 x_volume, u64 total,
                                                               int ids_batched) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 t = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
     const u64 n = t / per_batch, e = t - n * per_batch;
@@ -121,6 +128,7 @@ __global__ void __launch_bounds__(kBlock) pick_bw_flat_kernel(const T *__restric
 template <typename T>
 __global__ void __launch_bounds__(kBlock) broadcast_fw_kernel(const T *__restrict__ x, T *__restrict__ y, u64 skip1,
                                                               u64 size, u64 total_out) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   const u64 skip2 = skip1 * size;
   for (u64 o = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; o < total_out; o += stride) {
@@ -134,6 +142,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBlock) batch_pick_fw_kernel(const T *__restrict__ x,
                                                                const uint32_t *__restrict__ ids, T *__restrict__ y,
                                                                u64 volume, u64 total) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 t = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
     const u64 n = t / volume, i = t - n * volume;
@@ -146,6 +155,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBlock) batch_pick_bw_kernel(const T *__restrict__ gy,
                                                                const uint32_t *__restrict__ ids, T *gx, u64 volume,
                                                                uint32_t n_ids) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 i = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; i < volume; i += stride) {
     for (uint32_t n = 0; n < n_ids; ++n) {
@@ -160,6 +170,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) transpose_kernel(const T *__restrict__ x, T *y, uint32_t d1, uint32_t d2,
                                                         uint32_t tiles1, uint32_t tiles2, u64 total_tiles,
                                                         int accumulate) {
+  pdl_enter();
   __shared__ float tile[32][33];
   const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
   const u64 ms = static_cast<u64>(d1) * d2;
@@ -197,6 +208,7 @@ struct PermuteArgs {
 template <typename T>
 __global__ void __launch_bounds__(kBlock) permute_kernel(const T *__restrict__ src, T *dst, PermuteArgs a, u64 volume,
                                                          u64 total, int backward) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 t = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
     const u64 n = t / volume;
@@ -219,6 +231,7 @@ __global__ void __launch_bounds__(kBlock) permute_kernel(const T *__restrict__ s
 template <typename T>
 __global__ void __launch_bounds__(kBlock) flip_kernel(const T *__restrict__ x, T *y, u64 skip, u64 n, u64 total,
                                                       int accumulate) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 e = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
     const u64 lo = e % skip, j = (e / skip) % n, hi = e / (skip * n);
@@ -256,8 +269,7 @@ int b200_slice_fw(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t base
   if (!x || !y || offset + y_dim > x_dim) return B200_ERR_INVALID_ARG;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    slice_fw_kernel<T><<<grid_for(ctx, total, kBlock), kBlock, 0, s>>>(
-        static_cast<const T *>(x), static_cast<T *>(y), base, span, skip, base * offset, total);
+    b200::launch(ctx, slice_fw_kernel<T>, dim3(grid_for(ctx, total, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y), base, span, skip, base * offset, total);
   });
   B200_OPS_EPILOGUE(ctx);
 }
@@ -272,14 +284,12 @@ int b200_slice_bw(b200_ctx *ctx, int mode, const void *gy, void *gx, uint64_t ba
   B200_DISPATCH_MODE(mode, {
     if (bx > 1 || by == 1) {
       const u64 total = per_batch * bx;
-      slice_bw_flat_kernel<T><<<grid_for(ctx, total, kBlock), kBlock, 0, s>>>(
-          static_cast<const T *>(gy), static_cast<T *>(gx), span, skip, base * offset, per_batch, skip * repeat,
+      b200::launch(ctx, slice_bw_flat_kernel<T>, dim3(grid_for(ctx, total, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(gy), static_cast<T *>(gx), span, skip, base * offset, per_batch, skip * repeat,
           total, by > 1);
     } else {
       const u64 tiles = (per_batch + 31ull) / 32ull;
       const u64 cap = static_cast<u64>(ctx->sm_count) * 16ull;
-      slice_bw_sum_kernel<T><<<static_cast<unsigned>(tiles < cap ? tiles : cap), dim3(32, kSumLanes), 0, s>>>(
-          static_cast<const T *>(gy), static_cast<T *>(gx), span, skip, base * offset, per_batch, by);
+      b200::launch(ctx, slice_bw_sum_kernel<T>, dim3(static_cast<unsigned>(tiles < cap ? tiles : cap)), dim3(32, kSumLanes), 0, s, 1u, static_cast<const T *>(gy), static_cast<T *>(gx), span, skip, base * offset, per_batch, by);
     }
   });
   B200_OPS_EPILOGUE(ctx);
@@ -294,8 +304,7 @@ int b200_concat_part(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t b
   if (!x || !y || offset + x_dim > y_dim) return B200_ERR_INVALID_ARG;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    concat_part_kernel<T><<<grid_for(ctx, total, kBlock), kBlock, 0, s>>>(
-        static_cast<const T *>(x), static_cast<T *>(y), span, skip, base * offset, per_batch, skip * repeat,
+    b200::launch(ctx, concat_part_kernel<T>, dim3(grid_for(ctx, total, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y), span, skip, base * offset, per_batch, skip * repeat,
         total, x_batched);
   });
   B200_OPS_EPILOGUE(ctx);
@@ -314,8 +323,7 @@ int b200_pick_fw(b200_ctx *ctx, int mode, const void *x, const uint32_t *ids_hos
   if (rc) return rc;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    pick_fw_kernel<T><<<grid_for(ctx, total, kBlock), kBlock, 0, s>>>(
-        static_cast<const T *>(x), ids.get(), static_cast<T *>(y), base, skip, per_batch, skip * repeat, total,
+    b200::launch(ctx, pick_fw_kernel<T>, dim3(grid_for(ctx, total, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), ids.get(), static_cast<T *>(y), base, skip, per_batch, skip * repeat, total,
         x_batched, n_ids > 1);
   });
   B200_OPS_EPILOGUE(ctx);
@@ -336,13 +344,11 @@ int b200_pick_bw(b200_ctx *ctx, int mode, const void *gy, const uint32_t *ids_ho
   B200_DISPATCH_MODE(mode, {
     if (gx_batched) {
       const u64 total = per_batch * batch;
-      pick_bw_flat_kernel<T><<<grid_for(ctx, total, kBlock), kBlock, 0, s>>>(
-          static_cast<const T *>(gy), ids.get(), static_cast<T *>(gx), base, skip, per_batch, skip * repeat, total,
+      b200::launch(ctx, pick_bw_flat_kernel<T>, dim3(grid_for(ctx, total, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(gy), ids.get(), static_cast<T *>(gx), base, skip, per_batch, skip * repeat, total,
           n_ids > 1);
     } else {
       // a batch-1 gx can receive several items at the same place: one thread per (r, i), items in order
-      pick_bw_kernel<T><<<grid_for(ctx, per_batch, kBlock), kBlock, 0, s>>>(
-          static_cast<const T *>(gy), ids.get(), static_cast<T *>(gx), base, skip, per_batch, skip * repeat, batch,
+      b200::launch(ctx, pick_bw_kernel<T>, dim3(grid_for(ctx, per_batch, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(gy), ids.get(), static_cast<T *>(gx), base, skip, per_batch, skip * repeat, batch,
           gx_batched, n_ids > 1);
     }
   });
@@ -357,8 +363,7 @@ int b200_broadcast_fw(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t 
   if (!x || !y || skip1 == 0) return B200_ERR_INVALID_ARG;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    broadcast_fw_kernel<T><<<grid_for(ctx, total_out, kBlock), kBlock, 0, s>>>(
-        static_cast<const T *>(x), static_cast<T *>(y), skip1, size, total_out);
+    b200::launch(ctx, broadcast_fw_kernel<T>, dim3(grid_for(ctx, total_out, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y), skip1, size, total_out);
   });
   B200_OPS_EPILOGUE(ctx);
 }
@@ -374,8 +379,7 @@ int b200_batch_pick_fw(b200_ctx *ctx, int mode, const void *x, const uint32_t *i
   if (rc) return rc;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    batch_pick_fw_kernel<T><<<grid_for(ctx, total, kBlock), kBlock, 0, s>>>(
-        static_cast<const T *>(x), ids.get(), static_cast<T *>(y), volume, total);
+    b200::launch(ctx, batch_pick_fw_kernel<T>, dim3(grid_for(ctx, total, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), ids.get(), static_cast<T *>(y), volume, total);
   });
   B200_OPS_EPILOGUE(ctx);
 }
@@ -390,8 +394,7 @@ int b200_batch_pick_bw(b200_ctx *ctx, int mode, const void *gy, const uint32_t *
   if (rc) return rc;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    batch_pick_bw_kernel<T><<<grid_for(ctx, volume, kBlock), kBlock, 0, s>>>(
-        static_cast<const T *>(gy), ids.get(), static_cast<T *>(gx), volume, n_ids);
+    b200::launch(ctx, batch_pick_bw_kernel<T>, dim3(grid_for(ctx, volume, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(gy), ids.get(), static_cast<T *>(gx), volume, n_ids);
   });
   B200_OPS_EPILOGUE(ctx);
 }
@@ -407,7 +410,7 @@ int b200_transpose(b200_ctx *ctx, int mode, const void *x, void *y, uint32_t d1,
   const unsigned grid = static_cast<unsigned>(tiles < cap ? tiles : cap);
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    transpose_kernel<T><<<grid, 256, 0, s>>>(static_cast<const T *>(x), static_cast<T *>(y), d1, d2, t1, t2, tiles,
+    b200::launch(ctx, transpose_kernel<T>, dim3(grid), dim3(256), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y), d1, d2, t1, t2, tiles,
                                              accumulate);
   });
   B200_OPS_EPILOGUE(ctx);
@@ -439,7 +442,7 @@ int b200_permute_dims(b200_ctx *ctx, int mode, const void *x, void *y, uint32_t 
   if (total == 0) return B200_OK;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    permute_kernel<T><<<grid_for(ctx, total, kBlock), kBlock, 0, s>>>(static_cast<const T *>(x), static_cast<T *>(y),
+    b200::launch(ctx, permute_kernel<T>, dim3(grid_for(ctx, total, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y),
                                                                       a, volume, total, backward);
   });
   B200_OPS_EPILOGUE(ctx);
@@ -452,7 +455,7 @@ int b200_flip(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t skip, ui
   if (!x || !y || skip == 0 || n == 0) return B200_ERR_INVALID_ARG;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    flip_kernel<T><<<grid_for(ctx, total, kBlock), kBlock, 0, s>>>(static_cast<const T *>(x), static_cast<T *>(y),
+    b200::launch(ctx, flip_kernel<T>, dim3(grid_for(ctx, total, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y),
                                                                    skip, n, total, accumulate);
   });
   B200_OPS_EPILOGUE(ctx);

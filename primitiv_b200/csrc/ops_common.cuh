@@ -97,6 +97,7 @@ __device__ __forceinline__ float combine_batch_lanes(float v, float (*buf)[32]) 
 template <typename T>
 __global__ void __launch_bounds__(256) batch_final_kernel(const float *__restrict__ partial, T *y, u64 volume,
                                                           unsigned slices, float scale, int accumulate) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 i = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; i < volume; i += stride) {
     float t = 0.f;
@@ -111,6 +112,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) batch_sum_tile_kernel(const T *__restrict__ x, T *y, float *partial,
                                                              u64 volume, uint32_t batch, uint32_t slice_len,
                                                              float scale, int accumulate) {
+  pdl_enter();
   __shared__ float buf[kSumLanes][32];
   for (u64 tile = blockIdx.x; tile * 32ull < volume; tile += gridDim.x) {
     const u64 i = tile * 32ull + threadIdx.x;
@@ -137,11 +139,10 @@ int launch_batch_sum(b200_ctx *ctx, cudaStream_t s, const void *x, void *y, u64 
     const int rc = ctx->pool.alloc(static_cast<size_t>(bs.slices) * volume * sizeof(float), &partial, nullptr);
     if (rc != B200_OK) return rc;
   }
-  batch_sum_tile_kernel<T><<<dim3(bs.tiles, bs.slices), dim3(32, kSumLanes), 0, s>>>(
-      static_cast<const T *>(x), static_cast<T *>(y), static_cast<float *>(partial), volume, batch, bs.slice_len,
+  b200::launch(ctx, batch_sum_tile_kernel<T>, dim3(bs.tiles, bs.slices), dim3(32, kSumLanes), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y), static_cast<float *>(partial), volume, batch, bs.slice_len,
       scale, accumulate);
   if (bs.slices > 1) {
-    batch_final_kernel<T><<<grid_for(ctx, volume, 256), 256, 0, s>>>(static_cast<const float *>(partial),
+    b200::launch(ctx, batch_final_kernel<T>, dim3(grid_for(ctx, volume, 256)), dim3(256), 0, s, 1u, static_cast<const float *>(partial),
                                                                      static_cast<T *>(y), volume, bs.slices, scale,
                                                                      accumulate);
     ++ctx->launches;

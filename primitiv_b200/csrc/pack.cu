@@ -34,6 +34,7 @@ __global__ void __launch_bounds__(256) pack_tf32_kernel(
     const float *__restrict__ src, float *__restrict__ hi, float *__restrict__ lo, uint32_t mn,
     uint32_t k, uint32_t k_pad, unsigned long long src_bs, uint32_t tiles_mn, uint32_t tiles_k,
     unsigned long long total_tiles) {
+  pdl_enter();
   __shared__ float tile[32][33];
   const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;  // 32 x 8
   for (unsigned long long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
@@ -91,6 +92,7 @@ __global__ void __launch_bounds__(256) pack_tf32_kernel(
 __global__ void __launch_bounds__(256) row_max_kmajor_kernel(const float *__restrict__ src, float *__restrict__ amax_out,
                                                              uint32_t mn, uint32_t k, unsigned long long ld,
                                                              unsigned long long src_bs, uint32_t nbatch, int shared) {
+  pdl_enter();
   const uint32_t lane = threadIdx.x & 31u;
   const unsigned long long rows = static_cast<unsigned long long>(mn) * (shared ? 1u : nbatch);
   for (unsigned long long r = blockIdx.x * 8ull + (threadIdx.x >> 5); r < rows; r += gridDim.x * 8ull) {
@@ -114,6 +116,7 @@ __global__ void __launch_bounds__(256) row_max_mnmajor_kernel(const float *__res
                                                               uint32_t mn, uint32_t k, unsigned long long ld,
                                                               unsigned long long src_bs, uint32_t nbatch, int shared,
                                                               uint32_t k_slice) {
+  pdl_enter();
   __shared__ float buf[8][32];
   const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
   const uint32_t tiles = (mn + 31u) / 32u;
@@ -147,6 +150,7 @@ __global__ void __launch_bounds__(256) pack_f16_kernel(const float *__restrict__
                                                        uint32_t k, uint32_t k_pad, unsigned long long ld,
                                                        unsigned long long src_bs, uint32_t tiles_mn, uint32_t tiles_k,
                                                        unsigned long long total_tiles, int shared) {
+  pdl_enter();
   __shared__ float tile[32][33];
   const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;  // 32 x 8
   for (unsigned long long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
@@ -188,6 +192,7 @@ __global__ void __launch_bounds__(256) pack_f16_kernel(const float *__restrict__
 // split is purely elementwise.
 __global__ void __launch_bounds__(256) pack_flat_kernel(const float4 *__restrict__ src, float4 *__restrict__ hi,
                                                         float4 *__restrict__ lo, unsigned long long n4) {
+  pdl_enter();
   const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
   for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
        i += stride) {
@@ -208,6 +213,7 @@ __global__ void __launch_bounds__(256) pack_transpose64_kernel(const float *__re
                                                                float *__restrict__ lo, uint32_t mn, uint32_t k,
                                                                unsigned long long src_bs, uint32_t tiles_mn,
                                                                uint32_t tiles_k, unsigned long long total_tiles) {
+  pdl_enter();
   __shared__ float tile[64][65];  // [k][mn]
   const uint32_t t = threadIdx.x;
   for (unsigned long long tl = blockIdx.x; tl < total_tiles; tl += gridDim.x) {
@@ -261,6 +267,7 @@ __global__ void __launch_bounds__(256) pack_f16_rows_kernel(const float *__restr
                                                             __half *__restrict__ h0, __half *__restrict__ h1,
                                                             uint32_t mn, uint32_t k, unsigned long long ld,
                                                             unsigned long long src_bs, unsigned long long rows) {
+  pdl_enter();
   static_assert(kGroup == 32 || kGroup == 256, "a warp or the CTA");
   __shared__ float red[8];
   const uint32_t t = threadIdx.x % kGroup, lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
@@ -316,6 +323,7 @@ __global__ void __launch_bounds__(256) pack_f16_transpose64_kernel(const float *
                                                                    unsigned long long src_bs, uint32_t tiles_mn,
                                                                    uint32_t tiles_k, unsigned long long total_tiles,
                                                                    int shared) {
+  pdl_enter();
   __shared__ float tile[64][65];  // [k][mn]
   const uint32_t t = threadIdx.x;
   for (unsigned long long tl = blockIdx.x; tl < total_tiles; tl += gridDim.x) {
@@ -391,6 +399,7 @@ __device__ __forceinline__ Mix8 mix_split8(const float (&x)[8]) {
 __global__ void __launch_bounds__(256) pack_mix_flat_kernel(const float4 *__restrict__ src, float4 *__restrict__ hi,
                                                             uint4 *__restrict__ h8, uint4 *__restrict__ l8,
                                                             unsigned long long n8) {
+  pdl_enter();
   const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
   for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
        i += stride) {
@@ -412,6 +421,7 @@ __global__ void __launch_bounds__(256) pack_mix_transpose64_kernel(const float *
                                                                    uint32_t k, unsigned long long src_bs,
                                                                    uint32_t tiles_mn, uint32_t tiles_k,
                                                                    unsigned long long total_tiles) {
+  pdl_enter();
   __shared__ float tile[64][65];  // [k][mn]
   const uint32_t t = threadIdx.x;
   for (unsigned long long tl = blockIdx.x; tl < total_tiles; tl += gridDim.x) {
@@ -460,6 +470,7 @@ __global__ void __launch_bounds__(256) pack_mix_kernel(const float *__restrict__
                                                        uint32_t mn, uint32_t k, uint32_t k_pad, unsigned long long ld,
                                                        unsigned long long src_bs, uint32_t tiles_mn, uint32_t tiles_k,
                                                        unsigned long long total_tiles) {
+  pdl_enter();
   __shared__ float tile[32][33];
   const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;  // 32 x 8
   for (unsigned long long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
@@ -515,24 +526,22 @@ void pack_tf32(b200_ctx *ctx, cudaStream_t stream, OperandView &v, bool two_plan
       const unsigned long long n4 = static_cast<unsigned long long>(v.nbatch) * v.mn * v.k / 4ull;
       const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
       const unsigned long long need = (n4 + 255ull) / 256ull;
-      pack_flat_kernel<<<static_cast<unsigned>(need < cap ? need : cap), 256, 0, stream>>>(
-          static_cast<const float4 *>(v.ptr), reinterpret_cast<float4 *>(hi), reinterpret_cast<float4 *>(lo), n4);
+      b200::launch(ctx, pack_flat_kernel, dim3(static_cast<unsigned>(need < cap ? need : cap)), dim3(256), 0, stream, 1u, static_cast<const float4 *>(v.ptr), reinterpret_cast<float4 *>(hi), reinterpret_cast<float4 *>(lo), n4);
     } else if (v.mn_major && src_ok && v.mn % 4u == 0) {
       const uint32_t tiles_mn = (v.mn + 63u) / 64u, tiles_k = (v.k + 63u) / 64u;
       const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
       const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 8ull;
-      pack_transpose64_kernel<<<static_cast<unsigned>(tt < cap ? tt : cap), 256, 0, stream>>>(
-          static_cast<const float *>(v.ptr), hi, lo, v.mn, v.k, v.batch_stride, tiles_mn, tiles_k, tt);
+      b200::launch(ctx, pack_transpose64_kernel, dim3(static_cast<unsigned>(tt < cap ? tt : cap)), dim3(256), 0, stream, 1u, static_cast<const float *>(v.ptr), hi, lo, v.mn, v.k, v.batch_stride, tiles_mn, tiles_k, tt);
     } else {
       const uint32_t tiles_mn = (v.mn + 31u) / 32u, tiles_k = (v.k + 31u) / 32u;
       const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
       const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
       const unsigned blocks = static_cast<unsigned>(tt < cap ? tt : cap);
       if (v.mn_major)
-        pack_tf32_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const float *>(v.ptr), hi, lo, v.mn, v.k,
+        b200::launch(ctx, pack_tf32_kernel<true>, dim3(blocks), dim3(256), 0, stream, 1u, static_cast<const float *>(v.ptr), hi, lo, v.mn, v.k,
                                                           lay.kpad, v.batch_stride, tiles_mn, tiles_k, tt);
       else
-        pack_tf32_kernel<false><<<blocks, 256, 0, stream>>>(static_cast<const float *>(v.ptr), hi, lo, v.mn, v.k,
+        b200::launch(ctx, pack_tf32_kernel<false>, dim3(blocks), dim3(256), 0, stream, 1u, static_cast<const float *>(v.ptr), hi, lo, v.mn, v.k,
                                                            lay.kpad, v.batch_stride, tiles_mn, tiles_k, tt);
     }
   }
@@ -569,25 +578,23 @@ void pack_mix(b200_ctx *ctx, cudaStream_t stream, OperandView &v, float *dst, co
       const unsigned long long n8 = static_cast<unsigned long long>(v.nbatch) * v.mn * v.k / 8ull;
       const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
       const unsigned long long need = (n8 + 255ull) / 256ull;
-      pack_mix_flat_kernel<<<static_cast<unsigned>(need < cap ? need : cap), 256, 0, stream>>>(
-          reinterpret_cast<const float4 *>(src), reinterpret_cast<float4 *>(hi), reinterpret_cast<uint4 *>(h8),
+      b200::launch(ctx, pack_mix_flat_kernel, dim3(static_cast<unsigned>(need < cap ? need : cap)), dim3(256), 0, stream, 1u, reinterpret_cast<const float4 *>(src), reinterpret_cast<float4 *>(hi), reinterpret_cast<uint4 *>(h8),
           reinterpret_cast<uint4 *>(l8), n8);
     } else if (v.mn_major && src_ok && v.mn % 4u == 0 && v.ld == v.mn) {
       const uint32_t tiles_mn = (v.mn + 63u) / 64u, tiles_k = (v.k + 63u) / 64u;
       const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
       const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 8ull;
-      pack_mix_transpose64_kernel<<<static_cast<unsigned>(tt < cap ? tt : cap), 256, 0, stream>>>(
-          src, hi, h8, l8, v.mn, v.k, v.batch_stride, tiles_mn, tiles_k, tt);
+      b200::launch(ctx, pack_mix_transpose64_kernel, dim3(static_cast<unsigned>(tt < cap ? tt : cap)), dim3(256), 0, stream, 1u, src, hi, h8, l8, v.mn, v.k, v.batch_stride, tiles_mn, tiles_k, tt);
     } else {
       const uint32_t tiles_mn = (v.mn + 31u) / 32u, tiles_k = (v.k + 31u) / 32u;
       const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
       const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
       const unsigned blocks = static_cast<unsigned>(tt < cap ? tt : cap);
       if (v.mn_major)
-        pack_mix_kernel<true><<<blocks, 256, 0, stream>>>(src, hi, h8, l8, v.mn, v.k, lay.kpad, v.ld, v.batch_stride,
+        b200::launch(ctx, pack_mix_kernel<true>, dim3(blocks), dim3(256), 0, stream, 1u, src, hi, h8, l8, v.mn, v.k, lay.kpad, v.ld, v.batch_stride,
                                                          tiles_mn, tiles_k, tt);
       else
-        pack_mix_kernel<false><<<blocks, 256, 0, stream>>>(src, hi, h8, l8, v.mn, v.k, lay.kpad, v.ld, v.batch_stride,
+        b200::launch(ctx, pack_mix_kernel<false>, dim3(blocks), dim3(256), 0, stream, 1u, src, hi, h8, l8, v.mn, v.k, lay.kpad, v.ld, v.batch_stride,
                                                           tiles_mn, tiles_k, tt);
     }
   }
@@ -666,8 +673,7 @@ int mix_flat_planes(b200_ctx *ctx, cudaStream_t stream, const OperandView &v, co
     const unsigned long long n8 = n / 8ull;
     const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
     const unsigned long long need = (n8 + 255ull) / 256ull;
-    pack_mix_flat_kernel<<<static_cast<unsigned>(need < cap ? need : cap), 256, 0, stream>>>(
-        static_cast<const float4 *>(v.ptr), reinterpret_cast<float4 *>(const_cast<void *>(planes_out[0])),
+    b200::launch(ctx, pack_mix_flat_kernel, dim3(static_cast<unsigned>(need < cap ? need : cap)), dim3(256), 0, stream, 1u, static_cast<const float4 *>(v.ptr), reinterpret_cast<float4 *>(const_cast<void *>(planes_out[0])),
         reinterpret_cast<uint4 *>(const_cast<void *>(planes_out[1])),
         reinterpret_cast<uint4 *>(const_cast<void *>(planes_out[2])), n8);
   }
@@ -718,12 +724,10 @@ void pack_f16(b200_ctx *ctx, cudaStream_t stream, OperandView &v, const F16Plane
       // maximum and split in one kernel: a row per CTA, or per warp when rows are short
       const unsigned long long rows = static_cast<unsigned long long>(v.mn) * v.nbatch;
       if (v.k >= 2048u) {
-        pack_f16_rows_kernel<256><<<static_cast<unsigned>(rows < cap ? rows : cap), 256, 0, stream>>>(
-            src, amax, h0, h1, v.mn, v.k, v.ld, v.batch_stride, rows);
+        b200::launch(ctx, pack_f16_rows_kernel<256>, dim3(static_cast<unsigned>(rows < cap ? rows : cap)), dim3(256), 0, stream, 1u, src, amax, h0, h1, v.mn, v.k, v.ld, v.batch_stride, rows);
       } else {
         const unsigned long long ctas = (rows + 7ull) / 8ull;
-        pack_f16_rows_kernel<32><<<static_cast<unsigned>(ctas < cap ? ctas : cap), 256, 0, stream>>>(
-            src, amax, h0, h1, v.mn, v.k, v.ld, v.batch_stride, rows);
+        b200::launch(ctx, pack_f16_rows_kernel<32>, dim3(static_cast<unsigned>(ctas < cap ? ctas : cap)), dim3(256), 0, stream, 1u, src, amax, h0, h1, v.mn, v.k, v.ld, v.batch_stride, rows);
       }
       ctx->launches += 1;
     } else {
@@ -736,28 +740,26 @@ void pack_f16(b200_ctx *ctx, cudaStream_t stream, OperandView &v, const F16Plane
         if (slices > 1024ull) slices = 1024ull;
         const uint32_t k_slice = static_cast<uint32_t>((v.k + slices - 1) / slices);
         const unsigned gy = static_cast<unsigned>((v.k + k_slice - 1) / k_slice);
+        queue_drain(ctx);
         cudaMemsetAsync(amax, 0, scale_rows * sizeof(float), stream);
-        row_max_mnmajor_kernel<<<dim3(static_cast<unsigned>(tiles < cap ? tiles : cap), gy), 256, 0, stream>>>(
-            src, amax, v.mn, v.k, v.ld, v.batch_stride, v.nbatch, lay.shared, k_slice);
+        b200::launch(ctx, row_max_mnmajor_kernel, dim3(static_cast<unsigned>(tiles < cap ? tiles : cap), gy), dim3(256), 0, stream, 1u, src, amax, v.mn, v.k, v.ld, v.batch_stride, v.nbatch, lay.shared, k_slice);
       } else {
         const unsigned long long t = (scale_rows + 7ull) / 8ull;
-        row_max_kmajor_kernel<<<static_cast<unsigned>(t < cap ? t : cap), 256, 0, stream>>>(
-            src, amax, v.mn, v.k, v.ld, v.batch_stride, v.nbatch, lay.shared);
+        b200::launch(ctx, row_max_kmajor_kernel, dim3(static_cast<unsigned>(t < cap ? t : cap)), dim3(256), 0, stream, 1u, src, amax, v.mn, v.k, v.ld, v.batch_stride, v.nbatch, lay.shared);
       }
       if (v.mn_major && aligned && v.mn % 4u == 0) {
         const uint32_t tiles_mn = (v.mn + 63u) / 64u, tiles_k = (v.k + 63u) / 64u;
         const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
-        pack_f16_transpose64_kernel<<<static_cast<unsigned>(tt < cap ? tt : cap), 256, 0, stream>>>(
-            src, amax, h0, h1, v.mn, v.k, v.ld, v.batch_stride, tiles_mn, tiles_k, tt, lay.shared);
+        b200::launch(ctx, pack_f16_transpose64_kernel, dim3(static_cast<unsigned>(tt < cap ? tt : cap)), dim3(256), 0, stream, 1u, src, amax, h0, h1, v.mn, v.k, v.ld, v.batch_stride, tiles_mn, tiles_k, tt, lay.shared);
       } else {
         const uint32_t tiles_mn = (v.mn + 31u) / 32u, tiles_k = (v.k + 31u) / 32u;
         const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
         const unsigned blocks = static_cast<unsigned>(tt < cap ? tt : cap);
         if (v.mn_major)
-          pack_f16_kernel<true><<<blocks, 256, 0, stream>>>(src, amax, h0, h1, v.mn, v.k, lay.kpad, v.ld,
+          b200::launch(ctx, pack_f16_kernel<true>, dim3(blocks), dim3(256), 0, stream, 1u, src, amax, h0, h1, v.mn, v.k, lay.kpad, v.ld,
                                                           v.batch_stride, tiles_mn, tiles_k, tt, lay.shared);
         else
-          pack_f16_kernel<false><<<blocks, 256, 0, stream>>>(src, amax, h0, h1, v.mn, v.k, lay.kpad, v.ld,
+          b200::launch(ctx, pack_f16_kernel<false>, dim3(blocks), dim3(256), 0, stream, 1u, src, amax, h0, h1, v.mn, v.k, lay.kpad, v.ld,
                                                            v.batch_stride, tiles_mn, tiles_k, tt, lay.shared);
       }
       ctx->launches += 2;

@@ -18,6 +18,7 @@ struct PeerSources {
 template <typename T>
 __global__ void __launch_bounds__(256) peer_sum_kernel(PeerSources srcs, int nsrc, T *__restrict__ dst, u64 n,
                                                        int vector_ok, int accumulate) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
   constexpr int N = Vec<T>::N;
@@ -76,6 +77,7 @@ int b200_stream_barrier(b200_ctx *const *ctxs, int n) {
   if (!ctxs || n < 1) return B200_ERR_INVALID_ARG;
   for (int i = 0; i < n; ++i)
     if (!ctxs[i]) return B200_ERR_INVALID_ARG;
+  for (int i = 0; i < n; ++i) b200::queue_drain(ctxs[i]);   // launches still waiting in a context's launch queue
   bool one_gpu = true;
   for (int i = 1; i < n; ++i) one_gpu = one_gpu && ctxs[i]->device == ctxs[0]->device;
   if (one_gpu) return B200_OK;  // one default stream: already ordered
@@ -107,7 +109,7 @@ int b200_peer_sum(b200_ctx *ctx, int mode, const void *const *srcs, int nsrc, vo
   }
   B200_DISPATCH_MODE(mode, {
     ProfScope prof(ctx, kProfElementwise, s);
-    peer_sum_kernel<T><<<grid_for(ctx, n / Vec<T>::N + 1, 256), 256, 0, s>>>(ps, nsrc, static_cast<T *>(dst), n,
+    b200::launch(ctx, peer_sum_kernel<T>, dim3(grid_for(ctx, n / Vec<T>::N + 1, 256)), dim3(256), 0, s, 1u, ps, nsrc, static_cast<T *>(dst), n,
                                                                             vector_ok, accumulate);
   });
   B200_OPS_EPILOGUE(ctx);

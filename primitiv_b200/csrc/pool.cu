@@ -76,6 +76,7 @@ void Pool::release_cached() {
   bool any = false;
   for (auto &kv : cached_) any = any || !kv.second.empty();
   if (!any) return;
+  if (before_release) before_release();   // launches a worker thread has not issued yet
   cudaDeviceSynchronize();  // cached blocks may still be read by queued kernels
   for (auto &kv : cached_) {
     for (void *p : kv.second) cudaFree(p);
@@ -140,6 +141,7 @@ int StagingRing::upload(void *dst, const void *src, std::size_t bytes, cudaStrea
     }
     char *stage = base_ + static_cast<std::size_t>(slot) * kSlotBytes;
     std::memcpy(stage, from, n);
+    if (before_copy) before_copy();   // stream order is program order: queued launches are issued first
     cudaError_t e = cudaMemcpyAsync(to, stage, n, cudaMemcpyHostToDevice, stream);
     if (e == cudaSuccess) e = cudaEventRecord(events_[slot], stream);
     if (e != cudaSuccess) return static_cast<int>(e);

@@ -34,6 +34,7 @@ __device__ __forceinline__ float u01_open_high(uint32_t x) { return (x >> 8) * 5
 template <typename T>
 __global__ void __launch_bounds__(kBlock) random_kernel(T *__restrict__ y, u64 n, int kind, float p0, float p1,
                                                         uint2 key, u64 call) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   const u64 blocks = (n + 3) / 4;
   for (u64 b = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; b < blocks; b += stride) {
@@ -92,7 +93,7 @@ int b200_random(b200_ctx *ctx, int mode, int kind, float p0, float p1, void *y, 
   const u64 call = ctx->rng_calls++;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    random_kernel<T><<<grid_for(ctx, (n + 3) / 4, kBlock), kBlock, 0, s>>>(static_cast<T *>(y), n, kind, p0, p1, key,
+    b200::launch(ctx, random_kernel<T>, dim3(grid_for(ctx, (n + 3) / 4, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<T *>(y), n, kind, p0, p1, key,
                                                                            call);
   });
   B200_OPS_EPILOGUE(ctx);

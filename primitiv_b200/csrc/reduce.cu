@@ -65,6 +65,7 @@ __device__ __forceinline__ float reduce_serial(const T *x, u64 first, u64 step, 
 template <typename T, int RED>
 __global__ void __launch_bounds__(kBlock) reduce_thread_kernel(const T *__restrict__ x, T *__restrict__ y,
                                                                uint32_t n, u64 skip1, u64 outputs) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 o = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; o < outputs; o += stride) {
     const u64 first = (o / skip1) * skip1 * n + o % skip1;
@@ -75,6 +76,7 @@ __global__ void __launch_bounds__(kBlock) reduce_thread_kernel(const T *__restri
 template <typename T, int RED>
 __global__ void __launch_bounds__(kBlock) reduce_warp_kernel(const T *__restrict__ x, T *__restrict__ y, uint32_t n,
                                                              u64 outputs) {
+  pdl_enter();
   const uint32_t lane = threadIdx.x & 31u;
   const u64 warp = (static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const u64 nwarps = (static_cast<u64>(gridDim.x) * blockDim.x) >> 5;
@@ -127,6 +129,7 @@ __device__ __forceinline__ uint32_t first_extreme(const T *x, u64 first, u64 ste
 template <typename T>
 __global__ void __launch_bounds__(kBlock) argminmax_kernel(const T *__restrict__ x, uint32_t *__restrict__ ids,
                                                            uint32_t n, u64 skip1, u64 outputs, int want_max) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 o = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; o < outputs; o += stride) {
     const u64 first = (o / skip1) * skip1 * n + o % skip1;
@@ -139,6 +142,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBlock) minmax_bw_kernel(const T *__restrict__ x, const T *__restrict__ y,
                                                            const T *__restrict__ gy, T *gx, uint32_t n, u64 skip1,
                                                            u64 outputs) {
+  pdl_enter();
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   for (u64 o = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; o < outputs; o += stride) {
     const u64 first = (o / skip1) * skip1 * n + o % skip1;
@@ -157,10 +161,9 @@ template <typename T, int RED>
 void launch_reduce(b200_ctx *ctx, cudaStream_t s, const void *x, void *y, uint32_t n, u64 skip1, u64 outputs) {
   if (skip1 == 1 && n >= 64) {
     const unsigned grid = grid_for(ctx, outputs * 32ull, kBlock);
-    reduce_warp_kernel<T, RED><<<grid, kBlock, 0, s>>>(static_cast<const T *>(x), static_cast<T *>(y), n, outputs);
+    b200::launch(ctx, reduce_warp_kernel<T, RED>, dim3(grid), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y), n, outputs);
   } else {
-    reduce_thread_kernel<T, RED><<<grid_for(ctx, outputs, kBlock), kBlock, 0, s>>>(
-        static_cast<const T *>(x), static_cast<T *>(y), n, skip1, outputs);
+    b200::launch(ctx, reduce_thread_kernel<T, RED>, dim3(grid_for(ctx, outputs, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y), n, skip1, outputs);
   }
 }
 
@@ -195,8 +198,7 @@ int b200_minmax_bw(b200_ctx *ctx, int mode, const void *x, const void *y, const 
   if (!x || !y || !gy || !gx || n == 0 || skip1 == 0) return B200_ERR_INVALID_ARG;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    minmax_bw_kernel<T><<<grid_for(ctx, outputs, kBlock), kBlock, 0, s>>>(
-        static_cast<const T *>(x), static_cast<const T *>(y), static_cast<const T *>(gy), static_cast<T *>(gx), n,
+    b200::launch(ctx, minmax_bw_kernel<T>, dim3(grid_for(ctx, outputs, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<const T *>(y), static_cast<const T *>(gy), static_cast<T *>(gx), n,
         skip1, outputs);
   });
   B200_OPS_EPILOGUE(ctx);
@@ -213,13 +215,12 @@ int b200_argminmax(b200_ctx *ctx, int mode, int want_max, const void *x, uint32_
   {
     ProfScope prof(ctx, kProfElementwise, s);
     if (mode == B200_MODE_FP16)
-      argminmax_kernel<__half><<<grid_for(ctx, outputs, kBlock), kBlock, 0, s>>>(
-          static_cast<const __half *>(x), static_cast<uint32_t *>(d_ids), n, skip1, outputs, want_max);
+      b200::launch(ctx, argminmax_kernel<__half>, dim3(grid_for(ctx, outputs, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const __half *>(x), static_cast<uint32_t *>(d_ids), n, skip1, outputs, want_max);
     else
-      argminmax_kernel<float><<<grid_for(ctx, outputs, kBlock), kBlock, 0, s>>>(
-          static_cast<const float *>(x), static_cast<uint32_t *>(d_ids), n, skip1, outputs, want_max);
+      b200::launch(ctx, argminmax_kernel<float>, dim3(grid_for(ctx, outputs, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const float *>(x), static_cast<uint32_t *>(d_ids), n, skip1, outputs, want_max);
   }
   ++ctx->launches;
+  b200::queue_drain(ctx);
   cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess)
     e = cudaMemcpyAsync(ids_host, d_ids, outputs * sizeof(uint32_t), cudaMemcpyDeviceToHost, s);

@@ -108,7 +108,16 @@ void B200::initialize(std::uint32_t rng_seed) {
   // (and for any other product that reads the same tensor); every write goes through out() /
   // out_acc() below, which forget the planes of what is written.
   B200_CALL(::b200_operand_cache_enable(state_->ctx, kPlaneCacheBytes));
+  // Kernel launches go through the library's worker thread: nothing but this class queues work
+  // on the device's stream, and every call that hands values to the host drains the queue.
+  // PRIMITIV_B200_ASYNC=0 keeps them on the calling thread.
+  const char *async = std::getenv("PRIMITIV_B200_ASYNC");
+  set_async_launch(!(async && std::string(async) == "0"));
+  const char *pdl = std::getenv("PRIMITIV_B200_DEPENDENT_LAUNCH");   // 0 switches programmatic dependent launch off
+  if (pdl && std::string(pdl) == "0") B200_CALL(::b200_set_dependent_launch(state_->ctx, 0));
 }
+
+void B200::set_async_launch(bool on) { B200_CALL(::b200_set_async_launch(state_->ctx, on ? 1 : 0)); }
 
 void B200::written(const void *p, const Tensor &x) {
   ::b200_operand_cache_invalidate(state_->ctx, p, elem_size() * static_cast<std::size_t>(x.shape().size()));
@@ -272,12 +281,20 @@ void B200::copy_tensor_impl(const Tensor &x, Tensor &y) {
     if (src->device_id_ == device_id_ || src->mode_ == mode_) {
       // a zero-fill still pending on x is the source device's to launch
       const void *px = const_cast<B200 *>(src)->in(x);
+      if (src != this) {
+        // whatever still computes x may be waiting in the source device's launch queue: hand it to the
+        // driver before this device queues the copy behind it (one GPU: one default stream)
+        B200_CALL(::b200_launch_flush(src->state_->ctx));
+      }
       if (src->device_id_ != device_id_) {
         // The two GPUs' default streams do not order against each other: let the source
         // device finish whatever still writes x before this device reads it.
         const_cast<B200 *>(src)->wait_and_check();
       }
       B200_CALL(::b200_copy(state_->ctx, src->imode(), px, imode(), MDATA(y), n, nullptr));
+      // ... and the copy itself (a converting kernel when the modes differ) is handed to the driver before
+      // the source device may queue anything that overwrites x
+      if (src != this) B200_CALL(::b200_launch_flush(state_->ctx));
       if (src->device_id_ != device_id_) {
         // ... and finish the copy before the caller may release x: the source GPU's pool
         // orders reuse on its own stream only.

@@ -72,6 +72,12 @@ public:
    */
   void wait_and_check();
 
+  /**
+   * Whether kernel launches are issued by the library's worker thread (default, see
+   * b200_set_async_launch) or on the calling thread.  Results are the same either way.
+   */
+  void set_async_launch(bool on);
+
   /** Kernel choice for matmul: 0 per problem, 1 CUDA cores, 2 tensor cores whenever eligible. */
   void set_matmul_path_policy(int policy);
 

@@ -65,6 +65,9 @@ void B200Group::initialize(const std::vector<std::uint32_t> &ids, std::uint32_t 
   for (std::size_t i = 0; i < ids.size(); ++i) {
     const std::uint32_t seed = rng_seed + static_cast<std::uint32_t>(i);
     shards_.emplace_back(mode ? new B200(ids[i], seed, *mode) : new B200(ids[i], seed));
+    // the group orders its GPUs' streams against each other with events and launches peer sums itself:
+    // its shards launch on the calling thread
+    shards_.back()->set_async_launch(false);
     ctxs_.push_back(shards_.back()->context());
   }
   for (std::size_t i = 0; i < ids.size(); ++i) {

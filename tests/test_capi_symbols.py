@@ -67,3 +67,25 @@ def test_pool_size_classes():
         prev = c
     # the 205 MB activation of the MLP workload takes a 224 MiB block, not 256 MiB
     assert f(784 * 65536 * 4) == 224 << 20
+
+
+def test_every_kernel_takes_part_in_dependent_launch():
+    """Kernels are launched with the programmatic-serialization attribute, which lets a grid start
+    before the one in front of it has finished: each kernel must therefore wait for its predecessor
+    (pdl_enter, or pdl_wait_previous after a set-up that touches no global memory) before anything
+    else.  A kernel without the wait would race; this keeps one from slipping in."""
+    csrc = os.path.join(ROOT, "primitiv_b200", "csrc")
+    missing, raw = [], []
+    for name in sorted(os.listdir(csrc)):
+        if not name.endswith((".cu", ".cuh")):
+            continue
+        text = open(os.path.join(csrc, name)).read()
+        if "<<<" in text:
+            raw.append(name)          # every launch goes through b200::launch
+        for m in re.finditer(r"__global__", text):
+            brace = text.index("{", m.end())      # no brace occurs inside a kernel's signature
+            body = text[brace:brace + 4000]
+            if "pdl_enter();" not in body[:200] and "pdl_wait_previous();" not in body:
+                missing.append((name, text[m.start():m.start() + 120].split("(")[0][-60:]))
+    assert not raw, raw
+    assert not missing, missing
