@@ -620,9 +620,13 @@ def run_ours(args, wl, rank, local_rank, world):
 
     secondary = {}
     if not args.skip_secondary:
+        # a second of idling before each leg: every leg starts from the same power and clock state
+        # instead of inheriting the cap the previous one ran into
         if wl.name != "fp16_broadcast":
+            time.sleep(1.0)
             secondary["fp16_broadcast"] = leg_fp16_broadcast(rig, args.secondary_steps, 3, peaks)
             rig.ctx.pool_release_cached()
+        time.sleep(1.0)
         secondary["mlp_products"] = leg_mlp_products(rig, args.secondary_steps, 3, peaks)
         rig.ctx.pool_release_cached()
     extras = {}
@@ -729,7 +733,7 @@ def emit(args, wl, world, res, e2e, peaks, check, secondary, extras):
 
 
 GRAPH_PROGRAMS = {
-    # workload -> (binary under primitiv_b200/device/_build, arguments before the repeat count, what it is)
+    # workload -> (binary under tests/cpp/_build, arguments before the repeat count, what it is)
     "lstm_steps": ("lstm_steps", ["tf32", "50"],
                    "50 LSTM steps (E 512, H 1024, batch 64) forward + backward through primitiv's Graph, TF32 fast mode"),
     "mlp_step": ("mlp_step", ["3xtf32", "65536"],
@@ -744,7 +748,7 @@ def run_graph_program(args):
     because host work is part of what it measures."""
     import subprocess
     binary, pre, what = GRAPH_PROGRAMS[args.workload]
-    path = os.path.join(ROOT, "primitiv_b200", "device", "_build", binary)
+    path = os.path.join(ROOT, "tests", "cpp", "_build", binary)
     if not os.path.exists(path):
         print(json.dumps({"workload": args.workload, "unavailable": "%s is not built (needs the primitiv headers)" % path}))
         return

@@ -108,11 +108,12 @@ void B200::initialize(std::uint32_t rng_seed) {
   // (and for any other product that reads the same tensor); every write goes through out() /
   // out_acc() below, which forget the planes of what is written.
   B200_CALL(::b200_operand_cache_enable(state_->ctx, kPlaneCacheBytes));
-  // Kernel launches go through the library's worker thread: nothing but this class queues work
-  // on the device's stream, and every call that hands values to the host drains the queue.
-  // PRIMITIV_B200_ASYNC=0 keeps them on the calling thread.
+  // PRIMITIV_B200_ASYNC=1 moves the kernel launches to the library's worker thread (nothing but this
+  // class queues work on the device's stream, and every call that hands values to the host drains
+  // the queue).  Off by default: with dependent launches on, the graph-level loops measured here are
+  // no longer bound by the launch call, and the worker costs a spinning core.
   const char *async = std::getenv("PRIMITIV_B200_ASYNC");
-  set_async_launch(!(async && std::string(async) == "0"));
+  if (async && std::string(async) == "1") set_async_launch(true);
   const char *pdl = std::getenv("PRIMITIV_B200_DEPENDENT_LAUNCH");   // 0 switches programmatic dependent launch off
   if (pdl && std::string(pdl) == "0") B200_CALL(::b200_set_dependent_launch(state_->ctx, 0));
 }

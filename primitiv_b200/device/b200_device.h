@@ -73,8 +73,9 @@ public:
   void wait_and_check();
 
   /**
-   * Whether kernel launches are issued by the library's worker thread (default, see
-   * b200_set_async_launch) or on the calling thread.  Results are the same either way.
+   * Whether kernel launches are issued by the library's worker thread (see b200_set_async_launch;
+   * also switched on by PRIMITIV_B200_ASYNC=1) or on the calling thread (default).  Results are
+   * the same either way.
    */
   void set_async_launch(bool on);
 

@@ -3,7 +3,7 @@
 
 Run where the reference sources are mounted and `make -C oracle ref` has been run:
 
-    python tests/golden/make_golden.py --ref /root/reference
+    python tests/golden/make_golden.py --ref <primitiv source tree>
 
 Writes, next to this script:
 
@@ -173,7 +173,7 @@ def ref_naive_cases():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="the primitiv source tree the vectors are taken from")
     args = ap.parse_args()
     rd = lambda p: open(os.path.join(args.ref, p)).read()
     cases = forward_cases(rd("test/tensor_forward_test.cc"))

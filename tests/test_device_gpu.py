@@ -59,7 +59,7 @@ def test_device_parity_against_reference_naive(mode):
 @needs_plugin
 def test_primitiv_c_api_runs_matmul_on_b200():
     """primitiv's unmodified C API (primitivApplyTensorMatmul) on a device made by the new constructor."""
-    capi = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libprimitiv_c.so"), mode=ctypes.RTLD_GLOBAL)
+    capi = ctypes.CDLL(os.path.join(ROOT, "baseline", "_ref", "framework", "libprimitiv_c.so"), mode=ctypes.RTLD_GLOBAL)
     plug = ctypes.CDLL(PLUGIN, mode=ctypes.RTLD_GLOBAL)
     vp = ctypes.c_void_p
     dev = vp()
@@ -96,7 +96,7 @@ def test_primitiv_c_api_runs_matmul_on_b200():
 
 def _run_json(binary, *args):
     import json
-    path = os.path.join(ROOT, "primitiv_b200", "device", "_build", binary)
+    path = os.path.join(ROOT, "tests", "cpp", "_build", binary)
     assert os.path.exists(path), "%s is not built" % path
     r = subprocess.run([path] + [str(a) for a in args], capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
