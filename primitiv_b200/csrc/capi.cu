@@ -1,12 +1,32 @@
 // extern "C" entry points of libprimitiv_b200.so: context, pool, and the mapping of
 // primitiv's matmul_fw / matmul_bw onto the general contraction.
+#include <cstdio>
 #include <cstring>
 #include <new>
+
+#include <nvtx3/nvToolsExt.h>
 
 #include "ctx.h"
 
 using b200::DeviceGuard;
 using b200::GemmArgs;
+
+namespace {
+
+// NVTX range round one product (packing, the kernel, a split-k reduction), named by its shape,
+// so that a timeline shows which launches belong to which matmul_fw / matmul_bw call.  The
+// header-only NVTX does nothing but test a pointer unless a profiler has attached itself.
+struct GemmRange {
+  GemmRange(int mode, int ta, int tb, uint32_t m, uint32_t n, uint32_t k, uint32_t groups, uint32_t red, int acc) {
+    char name[96];
+    std::snprintf(name, sizeof(name), "b200_gemm %s%s %ux%ux%u g%u r%u mode%d%s", ta ? "T" : "N", tb ? "T" : "N", m, n, k,
+                  groups, red, mode, acc ? " +=" : "");
+    nvtxRangePushA(name);
+  }
+  ~GemmRange() { nvtxRangePop(); }
+};
+
+}  // namespace
 
 extern "C" {
 
@@ -256,6 +276,7 @@ int b200_gemm(b200_ctx *ctx, int mode, int trans_a, int trans_b, const void *A, 
   if (m == 0 || n == 0 || groups == 0) return B200_OK;
   if (k == 0 || red == 0) return B200_ERR_INVALID_ARG;
   DeviceGuard guard(ctx->device);
+  GemmRange range(mode, trans_a, trans_b, m, n, k, groups, red, accumulate);
   GemmArgs g{mode, trans_a ? 1 : 0, trans_b ? 1 : 0, A, B, C, m, n, k, groups, red,
              a_gs, a_rs, b_gs, b_rs, c_gs, accumulate ? 1 : 0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -11,6 +11,7 @@
 //   outer   k <= 16, A stored k x m, B stored k x n:                    gX += W^T . gy
 // Arithmetic is fp32 FMA in a fixed order (no atomics): results do not depend on the launch.
 #include <cstdint>
+#include <cstdlib>
 
 #include "ops_common.cuh"
 
@@ -247,6 +248,225 @@ __global__ void __launch_bounds__(256, 4) skinny_outer_kernel(const T *__restric
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Fast forms of the three kernels for fp32 storage with 16-byte aligned, 4-divisible extents (the
+// shapes a layer of a few rows over a large minibatch produces).  They move 128 bits per access,
+// keep the tiny operand in registers where the kernels above re-read it from shared memory for
+// every loaded element (24 bytes of shared memory per 4-byte element of the large operand), and
+// need no warp reduction per column pair where a different split of the work avoids it.
+
+// rows, k <= 1024: the CTA's 8 warps split k, 128 values each, 4 consecutive ones per lane, and
+// every lane keeps its 4 x MP values of A in registers for the whole launch.  All warps walk the
+// CTA's columns together, four at a time (the next four already in flight): one 128-bit load per
+// lane and column, 4 MP FMAs, and a halving reduction across the warp (V/2 + V/4 + V/8 + V/4
+// shuffles for V = 4 MP values).  The warps' sums over their k-slices meet in shared memory, one
+// tile of 32 columns at a time, and are added in warp order: no atomics, a fixed order.
+template <uint32_t MP>
+__global__ void __launch_bounds__(256, 2) skinny_rows_reg_kernel(const float *__restrict__ A, const float *__restrict__ B,
+                                                                 float *C, uint32_t m, uint32_t n, uint32_t k, u64 a_si,
+                                                                 u64 a_sk, int accumulate) {
+  pdl_enter();
+  static_assert(MP % 2 == 0 && MP <= 16, "rows padded to an even count");
+  constexpr uint32_t V = 4 * MP, R = V / 8;   // values per four columns; values a lane keeps after three halvings
+  __shared__ float part[2][8][32 * MP];       // [buffer][warp][column in tile][row]
+  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+  const uint32_t kk0 = warp * 128u + lane * 4u;
+  float w[4][MP];
+#pragma unroll
+  for (uint32_t t = 0; t < 4u; ++t)
+#pragma unroll
+    for (uint32_t i = 0; i < MP; ++i) w[t][i] = (i < m && kk0 + t < k) ? A[i * a_si + (kk0 + t) * a_sk] : 0.f;
+  const bool live = kk0 < k;   // k % 4 == 0: a lane's four values are all inside or all outside
+  const uint32_t tiles = (n + 31u) / 32u;
+  uint32_t buf = 0;
+  for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, buf ^= 1u) {
+    const u64 j0 = static_cast<u64>(tile) * 32u;
+    float4 nxt[4];
+#pragma unroll
+    for (uint32_t u = 0; u < 4u; ++u)
+      nxt[u] = (live && j0 + u < n) ? *reinterpret_cast<const float4 *>(B + (j0 + u) * k + kk0) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t c0 = 0; c0 < 32u; c0 += 4u) {
+      float4 b[4];
+#pragma unroll
+      for (uint32_t u = 0; u < 4u; ++u) b[u] = nxt[u];
+      if (c0 + 4u < 32u) {
+#pragma unroll
+        for (uint32_t u = 0; u < 4u; ++u)
+          nxt[u] = (live && j0 + c0 + 4u + u < n) ? *reinterpret_cast<const float4 *>(B + (j0 + c0 + 4u + u) * k + kk0)
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      float v[V];   // v[u * MP + i]
+#pragma unroll
+      for (uint32_t u = 0; u < 4u; ++u)
+#pragma unroll
+        for (uint32_t i = 0; i < MP; ++i) {
+          float t = w[0][i] * b[u].x;
+          t += w[1][i] * b[u].y;
+          t += w[2][i] * b[u].z;
+          t += w[3][i] * b[u].w;
+          v[u * MP + i] = t;
+        }
+      // three halving steps (lane bits 4, 3, 2): a lane sends the half its partner keeps
+#pragma unroll
+      for (uint32_t step = 0; step < 3u; ++step) {
+        const uint32_t off = 16u >> step, half = V >> (step + 1u);
+        const bool upper = (lane & off) != 0u;
+#pragma unroll
+        for (uint32_t i = 0; i < half; ++i) {
+          const float send = upper ? v[i] : v[i + half];
+          const float keep = upper ? v[i + half] : v[i];
+          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+      }
+#pragma unroll
+      for (uint32_t i = 0; i < R; ++i) {
+        v[i] += __shfl_xor_sync(0xffffffffu, v[i], 2u);
+        v[i] += __shfl_xor_sync(0xffffffffu, v[i], 1u);
+      }
+      const uint32_t first = ((lane >> 4) & 1u) * (V / 2u) + ((lane >> 3) & 1u) * (V / 4u) + ((lane >> 2) & 1u) * R;
+      if ((lane & 3u) == 0u) {
+#pragma unroll
+        for (uint32_t t = 0; t < R; ++t) part[buf][warp][c0 * MP + first + t] = v[t];
+      }
+    }
+    __syncthreads();   // (the other buffer is free again once every warp has passed this point)
+    // 32 columns x m rows of C are contiguous: warps' sums added in warp order
+    for (uint32_t e = threadIdx.x; e < 32u * m; e += blockDim.x) {
+      const uint32_t c = e / m, i = e - c * m;
+      if (j0 + c < n) {
+        float t = 0.f;
+#pragma unroll
+        for (uint32_t wv = 0; wv < 8u; ++wv) t += part[buf][wv][c * MP + i];
+        const u64 at = (j0 + c) * m + i;
+        C[at] = (accumulate ? C[at] : 0.f) + t;
+      }
+    }
+  }
+}
+
+// reduce, n % 4 == 0: a thread owns four consecutive columns (one 128-bit load per k value), the
+// CTA a slice of k; A's slice is staged in shared memory and broadcast.
+template <uint32_t MP>
+__global__ void __launch_bounds__(256, 2) skinny_reduce4_kernel(const float *__restrict__ A, const float *__restrict__ B,
+                                                                float *__restrict__ partial, uint32_t m, uint32_t n,
+                                                                uint32_t k, uint32_t slice_len) {
+  pdl_enter();
+  constexpr uint32_t kDepth = 8;   // k values whose 128-bit loads are in flight together: 32 KB per CTA
+  constexpr uint32_t AP = (MP + 3u) & ~3u;   // staged row length: whole 128-bit words
+  extern __shared__ __align__(16) float As[];  // [chunk][AP]
+  const uint32_t chunk_cap = kSmemFloats / AP;
+  const uint32_t k_lo = blockIdx.y * slice_len;
+  const uint32_t k_hi = k_lo + slice_len < k ? k_lo + slice_len : k;
+  const u64 j = (static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x) * 4u;
+  const bool col_ok = j < n;   // n % 4 == 0: all four columns or none
+  float acc[4][MP];
+#pragma unroll
+  for (uint32_t c = 0; c < 4u; ++c)
+#pragma unroll
+    for (uint32_t i = 0; i < MP; ++i) acc[c][i] = 0.f;
+  for (uint32_t c0 = k_lo; c0 < k_hi; c0 += chunk_cap) {
+    const uint32_t len = k_hi - c0 < chunk_cap ? k_hi - c0 : chunk_cap;
+    __syncthreads();
+    for (uint32_t e = threadIdx.x; e < len * AP; e += blockDim.x) {
+      const uint32_t kk = e / AP, i = e % AP;
+      As[e] = i < m ? A[static_cast<u64>(c0 + kk) * m + i] : 0.f;  // A stored m x k
+    }
+    __syncthreads();
+    for (uint32_t kk0 = 0; kk0 < len; kk0 += kDepth) {
+      float4 b[kDepth];
+#pragma unroll
+      for (uint32_t u = 0; u < kDepth; ++u)
+        b[u] = (kk0 + u < len && col_ok) ? *reinterpret_cast<const float4 *>(B + static_cast<u64>(c0 + kk0 + u) * n + j)
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);   // B stored n x k
+#pragma unroll
+      for (uint32_t u = 0; u < kDepth; ++u) {
+        const uint32_t kk = kk0 + u < len ? kk0 + u : 0u;  // b is zero there
+        const float4 *arow = reinterpret_cast<const float4 *>(As + kk * AP);  // one address per warp: broadcast
+        float a[AP];
+#pragma unroll
+        for (uint32_t q = 0; q < AP / 4; ++q) {
+          const float4 t = arow[q];
+          a[4 * q] = t.x; a[4 * q + 1] = t.y; a[4 * q + 2] = t.z; a[4 * q + 3] = t.w;
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < MP; ++i) {
+          acc[0][i] += a[i] * b[u].x;
+          acc[1][i] += a[i] * b[u].y;
+          acc[2][i] += a[i] * b[u].z;
+          acc[3][i] += a[i] * b[u].w;
+        }
+      }
+    }
+  }
+  if (col_ok) {
+    float *out = partial + static_cast<u64>(blockIdx.y) * m * n;
+#pragma unroll
+    for (uint32_t c = 0; c < 4u; ++c)
+#pragma unroll
+      for (uint32_t i = 0; i < MP; ++i)
+        if (i < m) out[(j + c) * m + i] = acc[c][i];
+  }
+}
+
+// outer, m % 4 == 0: a lane owns four consecutive rows of C (one 128-bit store per column) with
+// their K values of A in registers for the whole launch; a warp owns 128 rows, the CTA's eight
+// warps 1024 rows and a strip of 64 columns at a time, whose K values of B are staged in shared
+// memory once per strip and read as broadcasts.  Per column and lane: K / 4 shared loads, 4 K FMAs,
+// one 128-bit store.
+template <uint32_t K, bool accumulate>
+__global__ void __launch_bounds__(256, 2) skinny_outer4_kernel(const float *__restrict__ A, const float *__restrict__ B,
+                                                               float *C, uint32_t m, uint32_t n) {
+  pdl_enter();
+  constexpr uint32_t KP = (K + 3u) & ~3u, kStrip = 64;
+  __shared__ __align__(16) float Bs[kStrip * KP];
+  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+  const uint32_t i0 = (blockIdx.y * 8u + warp) * 128u + lane * 4u;
+  const bool row_ok = i0 < m;   // m % 4 == 0
+  float a[4][K];
+#pragma unroll
+  for (uint32_t r = 0; r < 4u; ++r)
+#pragma unroll
+    for (uint32_t kk = 0; kk < K; ++kk) a[r][kk] = row_ok ? A[static_cast<u64>(i0 + r) * K + kk] : 0.f;  // A stored k x m
+  const uint32_t strips = (n + kStrip - 1) / kStrip;
+  for (uint32_t strip = blockIdx.x; strip < strips; strip += gridDim.x) {
+    const u64 j_lo = static_cast<u64>(strip) * kStrip;
+    const uint32_t cols = n - j_lo < kStrip ? static_cast<uint32_t>(n - j_lo) : kStrip;
+    __syncthreads();   // the previous strip's readers are done
+    for (uint32_t e = threadIdx.x; e < cols * KP; e += blockDim.x) {
+      const uint32_t c = e / KP, kk = e % KP;
+      Bs[e] = kk < K ? B[(j_lo + c) * K + kk] : 0.f;  // B stored k x n
+    }
+    __syncthreads();
+    if (!row_ok) continue;
+    for (uint32_t c0 = 0; c0 < cols; c0 += 4u) {
+      float4 old[4];
+#pragma unroll
+      for (uint32_t u = 0; u < 4u; ++u)
+        old[u] = (accumulate && c0 + u < cols) ? *reinterpret_cast<const float4 *>(C + (j_lo + c0 + u) * m + i0)
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (uint32_t u = 0; u < 4u; ++u) {
+        if (c0 + u < cols) {
+          const float4 *bcol = reinterpret_cast<const float4 *>(Bs + (c0 + u) * KP);  // broadcast
+          float bv[KP];
+#pragma unroll
+          for (uint32_t q = 0; q < KP / 4; ++q) {
+            const float4 t = bcol[q];
+            bv[4 * q] = t.x; bv[4 * q + 1] = t.y; bv[4 * q + 2] = t.z; bv[4 * q + 3] = t.w;
+          }
+          float t[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (uint32_t kk = 0; kk < K; ++kk)
+#pragma unroll
+            for (uint32_t r = 0; r < 4u; ++r) t[r] += a[r][kk] * bv[kk];
+          *reinterpret_cast<float4 *>(C + (j_lo + c0 + u) * m + i0) =
+              make_float4(old[u].x + t[0], old[u].y + t[1], old[u].z + t[2], old[u].w + t[3]);
+        }
+      }
+    }
+  }
+}
+
 }  // namespace
 
 // Which of the three kernels takes this product, if any.
@@ -269,6 +489,36 @@ static int skinny_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t s) {
   T *C = static_cast<T *>(g.C);
   const SkinnyKind kind = skinny_kind(g);
   ProfScope prof(ctx, kProfGemmSimt, s);
+#ifdef PRIMITIV_B200_DEV_KNOBS
+  static const bool fast_off = std::getenv("PRIMITIV_B200_SKINNY_FAST") && std::atoi(std::getenv("PRIMITIV_B200_SKINNY_FAST")) == 0;
+  const bool kFloat = sizeof(T) == 4 && !fast_off;
+#else
+  constexpr bool kFloat = sizeof(T) == 4;
+#endif
+  auto aligned = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (kind == kRows && kFloat && g.k % 4u == 0 && g.k <= 1024u && aligned(g.B)) {
+    // the small operand in registers, 128-bit loads of the large one (see skinny_rows_reg_kernel)
+    const u64 a_si = g.trans_a ? g.k : 1, a_sk = g.trans_a ? 1 : g.m;
+    const uint32_t tiles = (g.n + 31u) / 32u;
+    const uint32_t cap = static_cast<uint32_t>(ctx->sm_count) * 2u;
+    const dim3 grid(tiles < cap ? tiles : cap), block(256);
+    const float *Af = reinterpret_cast<const float *>(A), *Bf = reinterpret_cast<const float *>(B);
+    float *Cf = reinterpret_cast<float *>(C);
+#define B200_ROWS_REG(MPV) b200::launch(ctx, skinny_rows_reg_kernel<MPV>, grid, block, 0, s, 1u, Af, Bf, Cf, g.m, g.n, g.k, a_si, a_sk, g.accumulate)
+    switch ((g.m + 1u) & ~1u) {
+      case 2: B200_ROWS_REG(2); break;
+      case 4: B200_ROWS_REG(4); break;
+      case 6: B200_ROWS_REG(6); break;
+      case 8: B200_ROWS_REG(8); break;
+      case 10: B200_ROWS_REG(10); break;
+      case 12: B200_ROWS_REG(12); break;
+      case 14: B200_ROWS_REG(14); break;
+      default: B200_ROWS_REG(16); break;
+    }
+#undef B200_ROWS_REG
+    ++ctx->launches;
+    return static_cast<int>(cudaGetLastError());
+  }
   if (kind == kRows) {
     const uint32_t mp = padded(g.m);
     const u64 a_si = g.trans_a ? g.k : 1, a_sk = g.trans_a ? 1 : g.m;
@@ -280,6 +530,41 @@ static int skinny_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t s) {
     else if (mp == 12) b200::launch(ctx, skinny_rows_kernel<T, 12, 2>, dim3(grid), dim3(256), smem, s, 1u, A, B, C, g.m, g.n, g.k, a_si, a_sk, g.accumulate);
     else b200::launch(ctx, skinny_rows_kernel<T, 20, 2>, dim3(grid), dim3(256), smem, s, 1u, A, B, C, g.m, g.n, g.k, a_si, a_sk, g.accumulate);
     ++ctx->launches;
+    return static_cast<int>(cudaGetLastError());
+  }
+  if (kind == kReduce && kFloat && g.n % 4u == 0 && aligned(g.B)) {
+    // four consecutive columns per thread, 128-bit loads (see skinny_reduce4_kernel)
+    const uint32_t mp2 = (g.m + 1u) & ~1u, ap = (mp2 + 3u) & ~3u;
+    const unsigned gx = static_cast<unsigned>((static_cast<u64>(g.n) / 4u + 255u) / 256u);
+    u64 slices = (2ull * ctx->sm_count + gx - 1) / gx;   // two CTAs per SM
+    if (slices > g.k / 64) slices = g.k / 64;
+    if (slices < 1) slices = 1;
+    const uint32_t slice_len = static_cast<uint32_t>((g.k + slices - 1) / slices);
+    const unsigned gy = (g.k + slice_len - 1) / slice_len;
+    const u64 count = static_cast<u64>(g.m) * g.n;
+    void *partial = nullptr;
+    const int rc = ctx->pool.alloc(static_cast<size_t>(gy) * count * sizeof(float), &partial, nullptr);
+    if (rc != B200_OK) return rc;
+    const uint32_t chunk = slice_len < kSmemFloats / ap ? slice_len : kSmemFloats / ap;
+    const size_t smem = static_cast<size_t>(chunk) * ap * sizeof(float);
+    float *pp = static_cast<float *>(partial);
+    const float *Af = reinterpret_cast<const float *>(A), *Bf = reinterpret_cast<const float *>(B);
+    const dim3 grid(gx, gy), block(256);
+#define B200_REDUCE4(MPV) b200::launch(ctx, skinny_reduce4_kernel<MPV>, grid, block, smem, s, 1u, Af, Bf, pp, g.m, g.n, g.k, slice_len)
+    switch (mp2) {
+      case 2: B200_REDUCE4(2); break;
+      case 4: B200_REDUCE4(4); break;
+      case 6: B200_REDUCE4(6); break;
+      case 8: B200_REDUCE4(8); break;
+      case 10: B200_REDUCE4(10); break;
+      case 12: B200_REDUCE4(12); break;
+      case 14: B200_REDUCE4(14); break;
+      default: B200_REDUCE4(16); break;
+    }
+#undef B200_REDUCE4
+    b200::launch(ctx, reduce_final_kernel<T>, dim3(static_cast<unsigned>((count + 31) / 32)), dim3(32, 8), 0, s, 1u, pp, C, count, gy, g.accumulate);
+    ctx->launches += 2;
+    ctx->pool.free(partial);  // stream-ordered reuse
     return static_cast<int>(cudaGetLastError());
   }
   if (kind == kReduce) {
@@ -305,6 +590,31 @@ static int skinny_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t s) {
     b200::launch(ctx, reduce_final_kernel<T>, dim3(static_cast<unsigned>((count + 31) / 32)), dim3(32, 8), 0, s, 1u, pp, C, count, gy, g.accumulate);
     ctx->launches += 2;
     ctx->pool.free(partial);  // stream-ordered reuse
+    return static_cast<int>(cudaGetLastError());
+  }
+  if (kind == kOuter && kFloat && g.m % 4u == 0 && aligned(g.C)) {
+    // four consecutive rows per lane, 128-bit stores, k compiled in (see skinny_outer4_kernel)
+    const unsigned row_groups = (g.m + 1023u) / 1024u;
+    const unsigned strips = (g.n + 63u) / 64u;
+    unsigned gx = static_cast<unsigned>(ctx->sm_count) * 2u / row_groups;
+    if (gx < 1) gx = 1;
+    if (gx > strips) gx = strips;
+    const dim3 grid(gx, row_groups), block(256);
+    const float *Af = reinterpret_cast<const float *>(A), *Bf = reinterpret_cast<const float *>(B);
+    float *Cf = reinterpret_cast<float *>(C);
+#define B200_OUTER4(KV)                                                                                          \
+  case KV:                                                                                                       \
+    if (g.accumulate) b200::launch(ctx, skinny_outer4_kernel<KV, true>, grid, block, 0, s, 1u, Af, Bf, Cf, g.m, g.n); \
+    else b200::launch(ctx, skinny_outer4_kernel<KV, false>, grid, block, 0, s, 1u, Af, Bf, Cf, g.m, g.n);        \
+    break;
+    switch (g.k) {
+      B200_OUTER4(1) B200_OUTER4(2) B200_OUTER4(3) B200_OUTER4(4) B200_OUTER4(5) B200_OUTER4(6) B200_OUTER4(7) B200_OUTER4(8)
+      B200_OUTER4(9) B200_OUTER4(10) B200_OUTER4(11) B200_OUTER4(12) B200_OUTER4(13) B200_OUTER4(14) B200_OUTER4(15)
+      B200_OUTER4(16)
+      default: return B200_ERR_INVALID_ARG;
+    }
+#undef B200_OUTER4
+    ++ctx->launches;
     return static_cast<int>(cudaGetLastError());
   }
   if (kind == kOuter) {
