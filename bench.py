@@ -50,8 +50,8 @@ sys.path.insert(0, ROOT)
 
 METRIC = "matmul_fw_bw_gflops"
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemm_tc_kernel launch on the batch-2 square case
-# (profiles/gemm_tc_kernel_3xtf32_batch2_ncu_full.md): 1.41 GB overwriting, 1.55 GB accumulating
-NCU_DRAM_BYTES_PER_LAUNCH_BATCH2 = 1.48e9
+# (profiles/gemm_tc_kernel_fp32_mix_batch2_ncu_full.md): 1.38 GB overwriting, 1.51 GB accumulating
+NCU_DRAM_BYTES_PER_LAUNCH_BATCH2 = 1.47e9
 # plane memory the library may keep between the forward and the backward call of a step
 PLANE_CACHE_BYTES = 8 << 30
 
