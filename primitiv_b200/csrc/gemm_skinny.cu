@@ -13,6 +13,7 @@
 #include <cstdint>
 #include <cstdlib>
 
+#include "mbar.cuh"
 #include "ops_common.cuh"
 
 namespace b200 {
@@ -255,6 +256,18 @@ __global__ void __launch_bounds__(256, 4) skinny_outer_kernel(const T *__restric
 // every loaded element (24 bytes of shared memory per 4-byte element of the large operand), and
 // need no warp reduction per column pair where a different split of the work avoids it.
 
+// Packed fp32 arithmetic (sm_100: two independent fp32 FMAs per instruction, round-to-nearest each,
+// the same results as two scalar FMAs).  These kernels are bound by instruction issue, ten FMAs per
+// loaded element, so halving the FMA instructions is most of what there is to win.
+typedef unsigned long long f32x2;   // {low float, high float}
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ void fma2(f32x2 &acc, f32x2 a, f32x2 b) { asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b)); }
+
 // rows, k <= 1024: the CTA's 8 warps split k, 128 values each, 4 consecutive ones per lane, and
 // every lane keeps its 4 x MP values of A in registers for the whole launch.  All warps walk the
 // CTA's columns together, four at a time (the next four already in flight): one 128-bit load per
@@ -271,11 +284,16 @@ __global__ void __launch_bounds__(256, 2) skinny_rows_reg_kernel(const float *__
   __shared__ float part[2][8][32 * MP];       // [buffer][warp][column in tile][row]
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
   const uint32_t kk0 = warp * 128u + lane * 4u;
-  float w[4][MP];
+  f32x2 w[4][MP / 2];   // rows (2p, 2p + 1) of A at the lane's four k values
 #pragma unroll
   for (uint32_t t = 0; t < 4u; ++t)
 #pragma unroll
-    for (uint32_t i = 0; i < MP; ++i) w[t][i] = (i < m && kk0 + t < k) ? A[i * a_si + (kk0 + t) * a_sk] : 0.f;
+    for (uint32_t pr = 0; pr < MP / 2; ++pr) {
+      const uint32_t i = 2u * pr;
+      const float lo = (i < m && kk0 + t < k) ? A[i * a_si + (kk0 + t) * a_sk] : 0.f;
+      const float hi = (i + 1u < m && kk0 + t < k) ? A[(i + 1u) * a_si + (kk0 + t) * a_sk] : 0.f;
+      w[t][pr] = pack2(lo, hi);
+    }
   const bool live = kk0 < k;   // k % 4 == 0: a lane's four values are all inside or all outside
   const uint32_t tiles = (n + 31u) / 32u;
   uint32_t buf = 0;
@@ -297,15 +315,19 @@ __global__ void __launch_bounds__(256, 2) skinny_rows_reg_kernel(const float *__
       }
       float v[V];   // v[u * MP + i]
 #pragma unroll
-      for (uint32_t u = 0; u < 4u; ++u)
+      for (uint32_t u = 0; u < 4u; ++u) {
+        const f32x2 bx = pack2(b[u].x, b[u].x), by = pack2(b[u].y, b[u].y), bz = pack2(b[u].z, b[u].z),
+                    bw = pack2(b[u].w, b[u].w);
 #pragma unroll
-        for (uint32_t i = 0; i < MP; ++i) {
-          float t = w[0][i] * b[u].x;
-          t += w[1][i] * b[u].y;
-          t += w[2][i] * b[u].z;
-          t += w[3][i] * b[u].w;
-          v[u * MP + i] = t;
+        for (uint32_t pr = 0; pr < MP / 2; ++pr) {
+          f32x2 t = pack2(0.f, 0.f);
+          fma2(t, w[0][pr], bx);
+          fma2(t, w[1][pr], by);
+          fma2(t, w[2][pr], bz);
+          fma2(t, w[3][pr], bw);
+          unpack2(t, v[u * MP + 2u * pr], v[u * MP + 2u * pr + 1u]);
         }
+      }
       // three halving steps (lane bits 4, 3, 2): a lane sends the half its partner keeps
 #pragma unroll
       for (uint32_t step = 0; step < 3u; ++step) {
@@ -359,11 +381,11 @@ __global__ void __launch_bounds__(256, 2) skinny_reduce4_kernel(const float *__r
   const uint32_t k_hi = k_lo + slice_len < k ? k_lo + slice_len : k;
   const u64 j = (static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x) * 4u;
   const bool col_ok = j < n;   // n % 4 == 0: all four columns or none
-  float acc[4][MP];
+  f32x2 acc[4][MP / 2];   // rows (2p, 2p + 1) of the four columns
 #pragma unroll
   for (uint32_t c = 0; c < 4u; ++c)
 #pragma unroll
-    for (uint32_t i = 0; i < MP; ++i) acc[c][i] = 0.f;
+    for (uint32_t pr = 0; pr < MP / 2; ++pr) acc[c][pr] = pack2(0.f, 0.f);
   for (uint32_t c0 = k_lo; c0 < k_hi; c0 += chunk_cap) {
     const uint32_t len = k_hi - c0 < chunk_cap ? k_hi - c0 : chunk_cap;
     __syncthreads();
@@ -381,19 +403,23 @@ __global__ void __launch_bounds__(256, 2) skinny_reduce4_kernel(const float *__r
 #pragma unroll
       for (uint32_t u = 0; u < kDepth; ++u) {
         const uint32_t kk = kk0 + u < len ? kk0 + u : 0u;  // b is zero there
-        const float4 *arow = reinterpret_cast<const float4 *>(As + kk * AP);  // one address per warp: broadcast
-        float a[AP];
+        // one address per warp: broadcast; a 128-bit load is two ready-made pairs of A's rows
+        const ulonglong2 *arow = reinterpret_cast<const ulonglong2 *>(As + kk * AP);
+        f32x2 a[AP / 2];
 #pragma unroll
         for (uint32_t q = 0; q < AP / 4; ++q) {
-          const float4 t = arow[q];
-          a[4 * q] = t.x; a[4 * q + 1] = t.y; a[4 * q + 2] = t.z; a[4 * q + 3] = t.w;
+          const ulonglong2 t = arow[q];
+          a[2 * q] = t.x;
+          a[2 * q + 1] = t.y;
         }
+        const f32x2 bx = pack2(b[u].x, b[u].x), by = pack2(b[u].y, b[u].y), bz = pack2(b[u].z, b[u].z),
+                    bw = pack2(b[u].w, b[u].w);
 #pragma unroll
-        for (uint32_t i = 0; i < MP; ++i) {
-          acc[0][i] += a[i] * b[u].x;
-          acc[1][i] += a[i] * b[u].y;
-          acc[2][i] += a[i] * b[u].z;
-          acc[3][i] += a[i] * b[u].w;
+        for (uint32_t pr = 0; pr < MP / 2; ++pr) {
+          fma2(acc[0][pr], a[pr], bx);
+          fma2(acc[1][pr], a[pr], by);
+          fma2(acc[2][pr], a[pr], bz);
+          fma2(acc[3][pr], a[pr], bw);
         }
       }
     }
@@ -403,9 +429,146 @@ __global__ void __launch_bounds__(256, 2) skinny_reduce4_kernel(const float *__r
 #pragma unroll
     for (uint32_t c = 0; c < 4u; ++c)
 #pragma unroll
-      for (uint32_t i = 0; i < MP; ++i)
-        if (i < m) out[(j + c) * m + i] = acc[c][i];
+      for (uint32_t pr = 0; pr < MP / 2; ++pr) {
+        float lo, hi;
+        unpack2(acc[c][pr], lo, hi);
+        if (2u * pr < m) out[(j + c) * m + 2u * pr] = lo;
+        if (2u * pr + 1u < m) out[(j + c) * m + 2u * pr + 1u] = hi;
+      }
   }
+}
+
+// reduce through a shared-memory ring: the CTA owns a slice of k and up to 1024 columns.  One
+// producer thread streams the slice of B (rows of n contiguous floats) into a four-stage ring with
+// bulk copies, eight rows = 32 KB per stage, 128 KB in flight per SM, so the consumers never wait on
+// a load of their own; the sixteen consumer warps own two columns per thread and read B with one
+// 64-bit shared load per k value, A's slice as broadcasts.  One CTA per SM.
+constexpr uint32_t kRingStages = 4, kRingRows = 8, kRingCols = 1024;
+constexpr size_t kRingBytes = static_cast<size_t>(kRingStages) * kRingRows * kRingCols * sizeof(float);
+
+template <uint32_t MP>
+__global__ void __launch_bounds__(544, 1) skinny_reduce_ring_kernel(const float *__restrict__ A, const float *__restrict__ B,
+                                                                    float *__restrict__ partial, uint32_t m, uint32_t n,
+                                                                    uint32_t k, uint32_t slice_len, int *status) {
+  pdl_enter();
+  constexpr uint32_t AP = (MP + 3u) & ~3u;
+  extern __shared__ __align__(128) unsigned char ring_smem[];
+  float *stages = reinterpret_cast<float *>(ring_smem);                 // [stage][row][cols]
+  float *As = stages + kRingStages * kRingRows * kRingCols;             // [row of the slice][AP]
+  __shared__ __align__(8) uint64_t full_bar[kRingStages];
+  __shared__ __align__(8) uint64_t empty_bar[kRingStages];
+  __shared__ int s_abort;
+  volatile int *abort_flag = &s_abort;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t col0 = blockIdx.x * kRingCols;
+  const uint32_t cols = n - col0 < kRingCols ? n - col0 : kRingCols;    // a multiple of 4
+  const uint32_t k_lo = blockIdx.y * slice_len;
+  const uint32_t k_hi = k_lo + slice_len < k ? k_lo + slice_len : k;
+  const uint32_t rows_total = k_hi - k_lo;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (uint32_t st = 0; st < kRingStages; ++st) {
+      ring::init(ring::smem_addr(&full_bar[st]), 1);
+      ring::init(ring::smem_addr(&empty_bar[st]), 16);
+    }
+    ring::fence_init();
+  }
+  for (uint32_t e = threadIdx.x; e < rows_total * AP; e += blockDim.x) {
+    const uint32_t r = e / AP, i = e % AP;
+    As[e] = i < m ? A[static_cast<u64>(k_lo + r) * m + i] : 0.f;  // A stored m x k
+  }
+  __syncthreads();
+  if (warp == 16u) {
+    // ---- producer ----
+    if (lane == 0u) {
+      uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
+      for (uint32_t r0 = 0; r0 < rows_total; r0 += kRingRows) {
+        if (!ring::wait(ring::smem_addr(&empty_bar[stage]), phase ^ 1u, abort_flag)) break;
+        const uint32_t nrows = rows_total - r0 < kRingRows ? rows_total - r0 : kRingRows;
+        const uint32_t bar = ring::smem_addr(&full_bar[stage]);
+        const uint32_t dst = ring::smem_addr(stages + static_cast<size_t>(stage) * kRingRows * kRingCols);
+        const float *src = B + static_cast<u64>(k_lo + r0) * n + col0;  // B stored n x k
+        ring::arrive_expect_tx(bar, nrows * cols * 4u);
+        armed |= 1u << stage;
+        armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+        if (cols == n) {
+          ring::bulk_load(dst, src, nrows * cols * 4u, bar);     // the rows are adjacent in memory: one copy
+        } else {
+          for (uint32_t r = 0; r < nrows; ++r)
+            ring::bulk_load(dst + r * cols * 4u, src + static_cast<u64>(r) * n, cols * 4u, bar);
+        }
+        if (++stage == kRingStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (*abort_flag) {
+        // let the copies in flight land before the CTA gives its shared memory up
+        for (uint32_t st = 0; st < kRingStages; ++st)
+          if (armed & (1u << st)) ring::wait_quiet(ring::smem_addr(&full_bar[st]), (armed_parity >> st) & 1u);
+      }
+    }
+  } else {
+    // ---- consumers: sixteen warps, two columns per thread ----
+    const uint32_t j = threadIdx.x * 2u;
+    const bool col_ok = j < cols;
+    f32x2 acc[2][MP / 2];   // rows (2p, 2p + 1) of the two columns
+#pragma unroll
+    for (uint32_t c = 0; c < 2u; ++c)
+#pragma unroll
+      for (uint32_t pr = 0; pr < MP / 2; ++pr) acc[c][pr] = pack2(0.f, 0.f);
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    for (uint32_t r0 = 0; ok && r0 < rows_total; r0 += kRingRows) {
+      uint32_t got = 1u;
+      if (lane == 0u) got = ring::wait(ring::smem_addr(&full_bar[stage]), phase, abort_flag) ? 1u : 0u;
+      if (!__shfl_sync(0xffffffffu, got, 0)) {
+        ok = false;
+        break;
+      }
+      const uint32_t nrows = rows_total - r0 < kRingRows ? rows_total - r0 : kRingRows;
+      const float *st_base = stages + static_cast<size_t>(stage) * kRingRows * kRingCols;
+#pragma unroll 4
+      for (uint32_t r = 0; r < nrows; ++r) {
+        const float2 b = col_ok ? *reinterpret_cast<const float2 *>(st_base + r * cols + j) : make_float2(0.f, 0.f);
+        // one address per warp: broadcast; a 128-bit load is two ready-made pairs of A's rows
+        const ulonglong2 *arow = reinterpret_cast<const ulonglong2 *>(As + (r0 + r) * AP);
+        f32x2 a[AP / 2];
+#pragma unroll
+        for (uint32_t q = 0; q < AP / 4; ++q) {
+          const ulonglong2 t = arow[q];
+          a[2 * q] = t.x;
+          a[2 * q + 1] = t.y;
+        }
+        const f32x2 bx = pack2(b.x, b.x), by = pack2(b.y, b.y);
+#pragma unroll
+        for (uint32_t pr = 0; pr < MP / 2; ++pr) {
+          fma2(acc[0][pr], a[pr], bx);
+          fma2(acc[1][pr], a[pr], by);
+        }
+      }
+      __syncwarp();
+      if (lane == 0u) ring::arrive(ring::smem_addr(&empty_bar[stage]));
+      if (++stage == kRingStages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    }
+    if (ok && col_ok) {
+      float *out = partial + static_cast<u64>(blockIdx.y) * m * n;
+#pragma unroll
+      for (uint32_t c = 0; c < 2u; ++c)
+#pragma unroll
+        for (uint32_t pr = 0; pr < MP / 2; ++pr) {
+          float lo, hi;
+          unpack2(acc[c][pr], lo, hi);
+          if (2u * pr < m) out[static_cast<u64>(col0 + j + c) * m + 2u * pr] = lo;
+          if (2u * pr + 1u < m) out[static_cast<u64>(col0 + j + c) * m + 2u * pr + 1u] = hi;
+        }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && s_abort) report_status(status, B200_ERR_KERNEL_TIMEOUT);
 }
 
 // outer, m % 4 == 0: a lane owns four consecutive rows of C (one 128-bit store per column) with
@@ -422,11 +585,16 @@ __global__ void __launch_bounds__(256, 2) skinny_outer4_kernel(const float *__re
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
   const uint32_t i0 = (blockIdx.y * 8u + warp) * 128u + lane * 4u;
   const bool row_ok = i0 < m;   // m % 4 == 0
-  float a[4][K];
+  f32x2 a[4][KP / 2];   // pairs of consecutive k values of the lane's four rows (zero past K)
 #pragma unroll
   for (uint32_t r = 0; r < 4u; ++r)
 #pragma unroll
-    for (uint32_t kk = 0; kk < K; ++kk) a[r][kk] = row_ok ? A[static_cast<u64>(i0 + r) * K + kk] : 0.f;  // A stored k x m
+    for (uint32_t q = 0; q < KP / 2; ++q) {
+      const float lo = (row_ok && 2u * q < K) ? A[static_cast<u64>(i0 + r) * K + 2u * q] : 0.f;  // A stored k x m
+      const float hi = (row_ok && 2u * q + 1u < K) ? A[static_cast<u64>(i0 + r) * K + 2u * q + 1u] : 0.f;
+      a[r][q] = pack2(lo, hi);
+    }
+  constexpr uint32_t KH = (K + 1u) / 2u;   // pairs that hold at least one live k value
   const uint32_t strips = (n + kStrip - 1) / kStrip;
   for (uint32_t strip = blockIdx.x; strip < strips; strip += gridDim.x) {
     const u64 j_lo = static_cast<u64>(strip) * kStrip;
@@ -447,18 +615,25 @@ __global__ void __launch_bounds__(256, 2) skinny_outer4_kernel(const float *__re
 #pragma unroll
       for (uint32_t u = 0; u < 4u; ++u) {
         if (c0 + u < cols) {
-          const float4 *bcol = reinterpret_cast<const float4 *>(Bs + (c0 + u) * KP);  // broadcast
-          float bv[KP];
+          const ulonglong2 *bcol = reinterpret_cast<const ulonglong2 *>(Bs + (c0 + u) * KP);  // broadcast
+          f32x2 bv[KP / 2];   // the column's k values in pairs (zero past K)
 #pragma unroll
           for (uint32_t q = 0; q < KP / 4; ++q) {
-            const float4 t = bcol[q];
-            bv[4 * q] = t.x; bv[4 * q + 1] = t.y; bv[4 * q + 2] = t.z; bv[4 * q + 3] = t.w;
+            const ulonglong2 t = bcol[q];
+            bv[2 * q] = t.x;
+            bv[2 * q + 1] = t.y;
           }
-          float t[4] = {0.f, 0.f, 0.f, 0.f};
+          // even and odd k values accumulate side by side and meet at the end
+          float t[4];
 #pragma unroll
-          for (uint32_t kk = 0; kk < K; ++kk)
+          for (uint32_t r = 0; r < 4u; ++r) {
+            f32x2 s2 = pack2(0.f, 0.f);
 #pragma unroll
-            for (uint32_t r = 0; r < 4u; ++r) t[r] += a[r][kk] * bv[kk];
+            for (uint32_t q = 0; q < KH; ++q) fma2(s2, a[r][q], bv[q]);
+            float lo, hi;
+            unpack2(s2, lo, hi);
+            t[r] = lo + hi;
+          }
           *reinterpret_cast<float4 *>(C + (j_lo + c0 + u) * m + i0) =
               make_float4(old[u].x + t[0], old[u].y + t[1], old[u].z + t[2], old[u].w + t[3]);
         }
@@ -531,6 +706,51 @@ static int skinny_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t s) {
     else b200::launch(ctx, skinny_rows_kernel<T, 20, 2>, dim3(grid), dim3(256), smem, s, 1u, A, B, C, g.m, g.n, g.k, a_si, a_sk, g.accumulate);
     ++ctx->launches;
     return static_cast<int>(cudaGetLastError());
+  }
+  if (kind == kReduce && kFloat && g.n % 4u == 0 && aligned(g.B)) {
+    // the large operand through a shared-memory ring filled by bulk copies (skinny_reduce_ring_kernel),
+    // when a slice of A fits beside the ring; otherwise four columns per thread with direct loads
+    const uint32_t mp2r = (g.m + 1u) & ~1u, apr = (mp2r + 3u) & ~3u;
+    const unsigned rgx = (g.n + kRingCols - 1) / kRingCols;
+    u64 rslices = static_cast<u64>(ctx->sm_count) / rgx;   // one CTA per SM
+    if (rslices < 1) rslices = 1;
+    if (rslices > g.k / 64) rslices = g.k / 64 ? g.k / 64 : 1;
+    // (the kernel needs n % 2 == 0 for its 64-bit loads and 16-byte rows for the bulk copies: n % 4 == 0 gives both)
+    const uint32_t rslice_len = static_cast<uint32_t>((g.k + rslices - 1) / rslices);
+    const unsigned rgy = (g.k + rslice_len - 1) / rslice_len;
+    const size_t a_bytes = static_cast<size_t>(rslice_len) * apr * sizeof(float);
+    const size_t ring_smem = kRingBytes + a_bytes;
+    if (ring_smem + 1024 <= ctx->smem_optin) {
+      const u64 count = static_cast<u64>(g.m) * g.n;
+      void *partial = nullptr;
+      const int rc = ctx->pool.alloc(static_cast<size_t>(rgy) * count * sizeof(float), &partial, nullptr);
+      if (rc != B200_OK) return rc;
+      float *pp = static_cast<float *>(partial);
+      const float *Af = reinterpret_cast<const float *>(A), *Bf = reinterpret_cast<const float *>(B);
+      const dim3 grid(rgx, rgy), block(544);
+      cudaError_t attr = cudaSuccess;
+#define B200_RING(MPV)                                                                                                   \
+  case MPV:                                                                                                              \
+    attr = cudaFuncSetAttribute(skinny_reduce_ring_kernel<MPV>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+                                static_cast<int>(ctx->smem_optin - 1024));                                               \
+    if (attr == cudaSuccess)                                                                                             \
+      b200::launch(ctx, skinny_reduce_ring_kernel<MPV>, grid, block, ring_smem, s, 1u, Af, Bf, pp, g.m, g.n, g.k, rslice_len, \
+                   ctx->d_status);                                                                                       \
+    break;
+      switch (mp2r) {
+        B200_RING(2) B200_RING(4) B200_RING(6) B200_RING(8) B200_RING(10) B200_RING(12) B200_RING(14) B200_RING(16)
+        default: attr = cudaErrorInvalidValue; break;
+      }
+#undef B200_RING
+      if (attr != cudaSuccess) {
+        ctx->pool.free(partial);
+        return static_cast<int>(attr);
+      }
+      b200::launch(ctx, reduce_final_kernel<T>, dim3(static_cast<unsigned>((count + 31) / 32)), dim3(32, 8), 0, s, 1u, pp, C, count, rgy, g.accumulate);
+      ctx->launches += 2;
+      ctx->pool.free(partial);  // stream-ordered reuse
+      return static_cast<int>(cudaGetLastError());
+    }
   }
   if (kind == kReduce && kFloat && g.n % 4u == 0 && aligned(g.B)) {
     // four consecutive columns per thread, 128-bit loads (see skinny_reduce4_kernel)
