@@ -27,7 +27,10 @@ Beside the headline the same line carries, at every N:
                      weight-gradient all-reduces);
   tf32_cublas_measured / gpu_comparator   context figures (rank 0): the TF32 rate of the vendor
                      GEMM on this GPU, and the reference's own CUDA / CUDA16 devices on the same
-                     workloads when they have been built (own process, never linked here).
+                     workloads when they have been built (own process, never linked here);
+  graph_programs     (1 GPU) the recurrent step loop and one perceptron training step as whole
+                     programs through primitiv's Graph on devices::B200, each beside the same model
+                     code on the reference's devices::CUDA.
 
 `--workload batched_square_3xfp16 | batched_square_tf32 | fp16_broadcast` make another workload the
 headline; `--workload lstm_steps | mlp_step` run the graph-level programs of the other named
@@ -603,6 +606,57 @@ def gpu_comparator(wl_names):
     return out
 
 
+def graph_legs():
+    """The two graph-level configurations (the recurrent step loop, one perceptron training step) as whole
+    programs through primitiv's Graph: on devices::B200 (tests/cpp/_build, with a parity check against the
+    reference's Naive device on a short prefix / small batch inside the program) and, beside each, the same
+    model code on the reference's devices::CUDA (baseline/_ref/cuda/ref_cuda_graphs).  Wall clock inside the
+    programs, host work included; each runs in a process of its own on GPU 0."""
+    def run(cmd):
+        if not os.path.exists(cmd[0]):
+            return {"unavailable": "%s is not built (needs the reference tree at build time)" % os.path.relpath(cmd[0], ROOT)}
+        try:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+            if r.returncode != 0:
+                return {"unavailable": "exit %d: %s" % (r.returncode, (r.stderr or r.stdout).strip()[-300:])}
+            return json.loads(r.stdout.strip().splitlines()[-1])
+        except Exception as e:      # noqa: BLE001 -- a leg that cannot run is reported, not fatal
+            return {"unavailable": repr(e)[:300]}
+
+    ours = os.path.join(ROOT, "tests", "cpp", "_build")
+    ref = os.path.join(ROOT, "baseline", "_ref", "cuda", "ref_cuda_graphs")
+    out = {}
+    # devices::CUDA puts the batch index of its broadcasting elementwise kernels in gridDim.y
+    # (primitiv/devices/cuda/ops/common.h:118-151), which ends at 65535: at the configuration's 65536 items
+    # the bias additions are never launched and nothing reports it (the loss then differs in the second
+    # digit).  The perceptron step is therefore compared at 32768 items as well, where the reference runs.
+    for name, mine, theirs, key in (
+            ("lstm_steps", ["tf32", "50", "5", "2"], ["lstm_steps", "50", "5"], "ms_per_loop_mean"),
+            ("mlp_step", ["3xtf32", "65536", "3", "256"], ["mlp_step", "65536", "3"], "ms_per_step_mean"),
+            ("mlp_step_batch32768", ["3xtf32", "32768", "3", "0"], ["mlp_step", "32768", "3"], "ms_per_step_mean")):
+        program = name.split("_batch")[0]
+        b200 = run([os.path.join(ours, program)] + mine)
+        time.sleep(1.0)
+        cuda = run([ref] + theirs)
+        time.sleep(1.0)
+        leg = {"what": GRAPH_PROGRAMS[program][2] if name == program else "the same step at 32768 items",
+               "b200": b200, "reference_cuda": cuda}
+        if key in b200 and key in cuda:
+            leg["ms"] = {"b200": b200[key], "reference_cuda": cuda[key]}
+            leg["speedup_vs_reference_cuda"] = cuda[key] / b200[key]
+            if "ms_of_best" in b200 and "ms_of_best" in cuda:    # the part of the step that is device work
+                leg["backward_update_ms"] = {"b200": b200["ms_of_best"]["backward_update"],
+                                             "reference_cuda": cuda["ms_of_best"]["backward_update"]}
+            if b200.get("loss") and cuda.get("loss"):
+                diff = abs(b200["loss"] - cuda["loss"]) / abs(cuda["loss"])
+                leg["loss_rel_diff_vs_reference_cuda"] = diff
+                if diff > 1e-2:
+                    leg["note"] = ("the reference device did not compute this configuration: its elementwise kernels "
+                                   "index the batch with gridDim.y, which ends at 65535")
+        out[name] = leg
+    return out
+
+
 def run_ours(args, wl, rank, local_rank, world):
     rig = Rig(rank, local_rank, world)
     peaks = measured_peaks()
@@ -635,6 +689,8 @@ def run_ours(args, wl, rank, local_rank, world):
     rig.barrier()
     if rank == 0 and world == 1 and not args.skip_cpu:
         extras["gpu_comparator"] = gpu_comparator(["batched_square", "fp16_broadcast"])
+        if not args.skip_secondary:
+            extras["graph_programs"] = graph_legs()
     if rank == 0:
         emit(args, wl, world, res, e2e, peaks, check, secondary, extras)
     if rig.dist is not None:

@@ -114,6 +114,19 @@ B200_API size_t b200_pool_size_class(size_t bytes);
  * a failed cudaMalloc (release cached blocks, retry once, then
  * B200_ERR_OUT_OF_MEMORY), without touching the GPU's real memory limit. */
 B200_API int b200_pool_set_limit(b200_ctx *ctx, size_t bytes);
+/* Debugging aid for out-of-bounds writes: with `bytes` > 0 (rounded up to 256) every block
+ * the pool takes from the driver carries that many bytes of a fixed pattern in front of and
+ * behind the part the caller sees; 0 switches it off.  Only while no block is handed out
+ * (B200_ERR_INVALID_ARG otherwise); cached blocks are released.  b200_pool_check_guards waits
+ * for `stream`, inspects the bands of every block, handed out or cached, restores the
+ * pattern, and reports the number of blocks with a damaged band, the lowest such block (the
+ * pointer b200_pool_alloc returned) and which side was hit (1 front, 2 back, 3 both).
+ * Blocks come from cudaMalloc, so a store a little past the end of an output does not
+ * fault; this is how such a store is found.  primitiv::devices::B200 switches the bands on
+ * when PRIMITIV_B200_POOL_GUARD is set and checks them at every host synchronisation
+ * (=1) or before every operation as well (=2), throwing primitiv::Error. */
+B200_API int b200_pool_set_guard(b200_ctx *ctx, size_t bytes);
+B200_API int b200_pool_check_guards(b200_ctx *ctx, void *stream, uint64_t *damaged_blocks, void **first_block, int *side);
 
 /* ---- the hot path -----------------------------------------------------------------
  * b200_matmul_fw replaces Device::matmul_fw_impl (primitiv/core/device.h:464;

@@ -35,6 +35,8 @@ SIGNATURES = {
     "b200_pool_stats": (_int, [_vp, ctypes.POINTER(_u64)]),
     "b200_pool_set_limit": (_int, [_vp, ctypes.c_size_t]),
     "b200_pool_size_class": (ctypes.c_size_t, [ctypes.c_size_t]),
+    "b200_pool_set_guard": (_int, [_vp, ctypes.c_size_t]),
+    "b200_pool_check_guards": (_int, [_vp, _vp, ctypes.POINTER(_u64), ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_int)]),
     "b200_matmul_fw": (_int, [_vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp]),
     "b200_matmul_bw": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp]),
     "b200_matmul_bw_ex": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _int, _int, _vp]),
@@ -225,6 +227,15 @@ class Context:
 
     def pool_set_limit(self, nbytes):
         _check(lib().b200_pool_set_limit(self._h, nbytes))
+
+    def pool_set_guard(self, nbytes):
+        _check(lib().b200_pool_set_guard(self._h, nbytes))
+
+    def pool_check_guards(self, stream=None):
+        """-> (number of blocks with a damaged guard band, lowest such block or None, side bits)."""
+        n, first, side = _u64(0), ctypes.c_void_p(None), ctypes.c_int(0)
+        _check(lib().b200_pool_check_guards(self._h, stream, ctypes.byref(n), ctypes.byref(first), ctypes.byref(side)))
+        return n.value, first.value, side.value
 
     def pool_stats(self):
         arr = (_u64 * 4)()

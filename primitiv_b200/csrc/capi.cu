@@ -173,6 +173,19 @@ int b200_pool_set_limit(b200_ctx *ctx, size_t bytes) {
   return B200_OK;
 }
 
+int b200_pool_set_guard(b200_ctx *ctx, size_t bytes) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  DeviceGuard guard(ctx->device);
+  b200::plane_cache_drop_range(ctx, nullptr, 0);   // cached planes are pool blocks too
+  return ctx->pool.set_guard(bytes);
+}
+
+int b200_pool_check_guards(b200_ctx *ctx, void *stream, uint64_t *damaged_blocks, void **first_block, int *side) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  DeviceGuard guard(ctx->device);
+  return b200::pool_check_guards(ctx, static_cast<cudaStream_t>(stream), damaged_blocks, first_block, side);
+}
+
 int b200_set_path_policy(b200_ctx *ctx, int policy) {
   if (!ctx || policy < 0 || policy > 2) return B200_ERR_INVALID_ARG;
   ctx->path_policy = policy;

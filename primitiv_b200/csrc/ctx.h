@@ -34,6 +34,13 @@ class Pool {
   // in-use + cached bytes past it behave exactly like a failed cudaMalloc.
   void set_limit(std::size_t bytes) { limit_ = bytes; }
   static std::size_t size_class(std::size_t bytes);
+  // Debug aid: `bytes` (rounded up to 256) of a known pattern in front of and behind every block,
+  // checked by pool_check_guards().  Only while the pool holds no block at all.
+  int set_guard(std::size_t bytes);
+  std::size_t guard() const { return guard_; }
+  // Every block the pool owns, handed out or cached: (pointer the caller sees, class size).
+  void blocks(std::vector<std::pair<void *, std::size_t>> *out) const;
+  static constexpr unsigned char kGuardByte = 0xA5;
   // Called with (block, bytes) whenever a block goes back to the pool: whatever was derived from
   // its contents (cached operand planes) is stale from then on.
   std::function<void(const void *, std::size_t)> on_free;
@@ -44,7 +51,7 @@ class Pool {
  private:
   std::map<std::size_t, std::vector<void *>> cached_;
   std::unordered_map<void *, std::size_t> in_use_;
-  std::size_t bytes_in_use_ = 0, bytes_cached_ = 0, limit_ = 0;
+  std::size_t bytes_in_use_ = 0, bytes_cached_ = 0, limit_ = 0, guard_ = 0;
   std::uint64_t n_malloc_ = 0, n_hit_ = 0;
   int raw_alloc(std::size_t bytes, void **ptr);
 };
@@ -62,10 +69,17 @@ namespace b200 {
 // A copy from pageable memory makes the CUDA runtime wait for the stream first; staging
 // through pinned slots keeps uploads asynchronous: the host copies into a slot, queues the
 // DMA and an event, and only waits when it comes round to a slot whose DMA is still pending.
+//
+// One core copies into pinned memory at 8-9 GB/s, a sixth of what the bus then moves.  An upload
+// of kGangBytes or more is therefore staged half a ring at a time with a few helper threads
+// copying side by side (started on first use, asleep otherwise), while the DMA of the other half
+// is in flight.
+class CopyGang;
 class StagingRing {
  public:
   static constexpr std::size_t kSlotBytes = 1u << 20;
   static constexpr int kSlots = 16;
+  static constexpr std::size_t kGangBytes = 8u << 20;
   ~StagingRing();
   // dst (device) <- src (host, any kind), bytes; ordered on `stream`.  The source may be
   // reused as soon as this returns.
@@ -80,7 +94,9 @@ class StagingRing {
   cudaEvent_t events_[kSlots] = {};
   bool pending_[kSlots] = {};
   int next_ = 0;
+  CopyGang *gang_ = nullptr;
   int prepare();
+  int upload_wave(char *to, const char *from, std::size_t bytes, cudaStream_t stream);
 };
 
 }  // namespace b200
@@ -206,6 +222,8 @@ int gemm_skinny(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
 // tcgen05 path.  tc_eligible() says whether the operands meet TMA's alignment rules.
 bool gemm_tc_eligible(const b200_ctx *ctx, const GemmArgs &g);
 int gemm_tc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
+// Checks (and re-arms) the guard bands of every pool block; see b200_pool_check_guards.
+int pool_check_guards(b200_ctx *ctx, cudaStream_t stream, std::uint64_t *damaged, void **first, int *side);
 // Launches a kernel whose only wait runs out (see b200_selftest_wait_timeout).
 int selftest_wait_timeout(b200_ctx *ctx, cudaStream_t stream);
 // 3xTF32 product whose packing planes live in a fixed device array: allocates nothing.

@@ -52,6 +52,7 @@ namespace {
 
 // plane memory the device may keep between products (pool memory; least recently used out first)
 const std::size_t kPlaneCacheBytes = std::size_t(8) << 30;
+const std::size_t kPoolGuardBytes = 256;
 
 B200::Mode mode_from_environment() {
   const char *e = std::getenv("PRIMITIV_B200_MODE");
@@ -103,6 +104,14 @@ void B200::initialize(std::uint32_t rng_seed) {
                          << ::b200_error_string(rc) << " [" << rc << "]");
   }
   state_->mode = imode();
+  // Debugging aid: PRIMITIV_B200_POOL_GUARD=1 puts guard bands round every block of the memory pool
+  // and checks them whenever the host waits for the device; =2 checks before every operation as
+  // well, so that a store outside a tensor is reported at the operation after the one that did it.
+  const char *guard = std::getenv("PRIMITIV_B200_POOL_GUARD");
+  if (guard && (std::string(guard) == "1" || std::string(guard) == "2")) {
+    B200_CALL(::b200_pool_set_guard(state_->ctx, kPoolGuardBytes));
+    guard_level_ = guard[0] - '0';
+  }
   B200_CALL(::b200_seed(state_->ctx, rng_seed));
   // The split planes of an fp32 operand are kept from the forward product for the backward one
   // (and for any other product that reads the same tensor); every write goes through out() /
@@ -118,9 +127,22 @@ void B200::initialize(std::uint32_t rng_seed) {
   if (pdl && std::string(pdl) == "0") B200_CALL(::b200_set_dependent_launch(state_->ctx, 0));
 }
 
+void B200::check_pool_guards() {
+  std::uint64_t damaged = 0;
+  void *first = nullptr;
+  int side = 0;
+  B200_CALL(::b200_pool_check_guards(state_->ctx, nullptr, &damaged, &first, &side));
+  if (damaged != 0) {
+    PRIMITIV_THROW_ERROR("B200: a kernel on GPU " << device_id_ << " wrote outside its tensor: " << damaged
+                         << " block(s) of the memory pool have a damaged guard band, the lowest at " << first
+                         << (side == 1 ? " (in front of it)" : side == 2 ? " (behind it)" : " (on both sides)"));
+  }
+}
+
 void B200::set_async_launch(bool on) { B200_CALL(::b200_set_async_launch(state_->ctx, on ? 1 : 0)); }
 
 void B200::written(const void *p, const Tensor &x) {
+  if (guard_level_ >= 2) check_pool_guards();
   ::b200_operand_cache_invalidate(state_->ctx, p, elem_size() * static_cast<std::size_t>(x.shape().size()));
 }
 
@@ -180,6 +202,7 @@ void B200::wait_and_check() {
     PRIMITIV_THROW_ERROR("B200: a kernel on GPU " << device_id_ << " gave up waiting: "
                          << ::b200_error_string(code) << " [" << code << "]");
   }
+  if (guard_level_ >= 1) check_pool_guards();
 }
 
 const void *B200::data(const Tensor &x) {
@@ -236,6 +259,7 @@ std::shared_ptr<void> B200::new_handle(const Shape &shape, std::size_t *const al
 std::vector<float> B200::tensor_to_vector_impl(const Tensor &x) {
   std::vector<float> ret(x.shape().size());
   B200_CALL(::b200_download(state_->ctx, imode(), CDATA(x), ret.data(), ret.size(), nullptr));
+  if (guard_level_ >= 1) check_pool_guards();
   return ret;
 }
 

@@ -98,8 +98,10 @@ private:
   std::shared_ptr<State> state_;
   std::uint32_t device_id_;
   Mode mode_;
+  int guard_level_ = 0;  // PRIMITIV_B200_POOL_GUARD: 0 off, 1 check at host synchronisation, 2 before every operation too
 
   void initialize(std::uint32_t rng_seed);
+  void check_pool_guards();
 
   // Tensor -> device pointer.  primitiv zero-fills every gradient right before the first `+=`
   // into it (primitiv/core/graph.cc:191-212).  reset_tensor(0) therefore only notes the

@@ -151,6 +151,29 @@ def test_primitiv_own_tensor_tests_pass_on_b200(mode, policy):
 
 @pytest.mark.gpu
 @needs_plugin
+@pytest.mark.parametrize("program", ["device_parity", "ref_tensor_tests"])
+@pytest.mark.parametrize("mode", ["3xtf32", "fp16"])
+def test_no_operation_writes_outside_its_tensor(mode, program):
+    """Both suites again with guard bands round every block of the memory pool, checked before
+    every operation (PRIMITIV_B200_POOL_GUARD=2): a kernel that stored past either end of a tensor
+    or of its scratch would make the next operation throw."""
+    path = os.path.join(ROOT, "tests", "cpp", "_build", program)
+    assert os.path.exists(path), "%s is not built" % path
+    env = dict(os.environ, PRIMITIV_B200_POOL_GUARD="2", PRIMITIV_B200_PATH_POLICY="2" if program == "ref_tensor_tests" else "0")
+    r = subprocess.run([path, mode], capture_output=True, text=True, timeout=1200, env=env)
+    tail = (r.stdout + r.stderr)[-3000:]
+    assert r.returncode == 0, tail
+    assert "guard band" not in r.stdout + r.stderr, tail
+    if program == "device_parity":
+        assert "0 failures" in r.stdout, tail
+    else:
+        summary = [l for l in r.stdout.splitlines() if l.startswith("[==========]")][-1]
+        ran, passed, failed = [int(w) for w in summary.replace(",", "").split() if w.isdigit()]
+        assert ran >= 370 and passed == ran and failed == 0, summary
+
+
+@pytest.mark.gpu
+@needs_plugin
 def test_reference_xor_example_trains_on_b200():
     """examples/xor/xor.cc of the reference, compiled from the reference tree with only its device
     line swapped (a forced include turns `devices::Naive dev;` into a B200 on GPU 0): Graph,
