@@ -25,8 +25,10 @@ Beside the headline the same line carries, at every N:
                      128 MiB gA partial is all-reduced) and `mlp_products` (the nine products of a
                      784-1024-1024-10 perceptron step over 65536 items per GPU, 3xTF32; three
                      weight-gradient all-reduces);
-  tf32_cublas_measured / gpu_comparator   context figures (rank 0): the TF32 rate of the vendor
-                     GEMM on this GPU, and the reference's own CUDA / CUDA16 devices on the same
+  tf32_cublas_measured / l2_ingest_measured / gpu_comparator   context figures (rank 0): the TF32 rate
+                     of the vendor GEMM on this GPU, the rate at which an SM takes operand tiles in
+                     from L2 (the second ceiling of the tensor-core kernels), and the reference's own
+                     CUDA / CUDA16 devices on the same
                      workloads when they have been built (own process, never linked here);
   graph_programs     (1 GPU) the recurrent step loop and one perceptron training step as whole
                      programs through primitiv's Graph on devices::B200, each beside the same model
@@ -686,6 +688,14 @@ def run_ours(args, wl, rank, local_rank, world):
     extras = {}
     if rank == 0 and not args.skip_cpu:
         extras["tf32_cublas_measured"] = tf32_cublas_measured(rig)
+        per_clk, gbs = rig.ctx.measure_l2_ingest()
+        extras["l2_ingest_measured"] = {
+            "bytes_per_clk_per_sm": per_clk, "gb_per_s_per_sm": gbs,
+            "needed_at_full_tensor_rate": 64.0,
+            "tensor_utilisation_ceiling": min(1.0, per_clk / 64.0),
+            "note": "bulk copies L2 -> shared memory and nothing else, 128 KB in flight per SM (b200_measure_l2_ingest); "
+                    "the 256 x 256 pair tiles of the fp32, TF32 and half-precision kinds need 64 B per SM clock at full "
+                    "tensor rate, so their tensor-pipe utilisation cannot exceed the ratio"}
     rig.barrier()
     if rank == 0 and world == 1 and not args.skip_cpu:
         extras["gpu_comparator"] = gpu_comparator(["batched_square", "fp16_broadcast"])

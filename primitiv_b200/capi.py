@@ -35,6 +35,7 @@ SIGNATURES = {
     "b200_pool_stats": (_int, [_vp, ctypes.POINTER(_u64)]),
     "b200_pool_set_limit": (_int, [_vp, ctypes.c_size_t]),
     "b200_pool_size_class": (ctypes.c_size_t, [ctypes.c_size_t]),
+    "b200_measure_l2_ingest": (_int, [_vp, _vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]),
     "b200_pool_set_guard": (_int, [_vp, ctypes.c_size_t]),
     "b200_pool_check_guards": (_int, [_vp, _vp, ctypes.POINTER(_u64), ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_int)]),
     "b200_matmul_fw": (_int, [_vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp]),
@@ -227,6 +228,12 @@ class Context:
 
     def pool_set_limit(self, nbytes):
         _check(lib().b200_pool_set_limit(self._h, nbytes))
+
+    def measure_l2_ingest(self, stream=None):
+        """-> (bytes per SM clock, GB/s per SM) that bulk copies from L2 into shared memory reach on this GPU."""
+        a, b = ctypes.c_double(0), ctypes.c_double(0)
+        _check(lib().b200_measure_l2_ingest(self._h, stream, ctypes.byref(a), ctypes.byref(b)), "measure_l2_ingest")
+        return a.value, b.value
 
     def pool_set_guard(self, nbytes):
         _check(lib().b200_pool_set_guard(self._h, nbytes))

@@ -141,6 +141,12 @@ int b200_selftest_wait_timeout(b200_ctx *ctx, void *stream) {
   return b200::selftest_wait_timeout(ctx, static_cast<cudaStream_t>(stream));
 }
 
+int b200_measure_l2_ingest(b200_ctx *ctx, void *stream, double *bytes_per_clock_per_sm, double *gb_per_s_per_sm) {
+  if (!ctx) return B200_ERR_INVALID_ARG;
+  DeviceGuard guard(ctx->device);
+  return b200::measure_l2_ingest(ctx, static_cast<cudaStream_t>(stream), bytes_per_clock_per_sm, gb_per_s_per_sm);
+}
+
 int b200_pool_alloc(b200_ctx *ctx, size_t bytes, void **ptr, size_t *allocated) {
   if (!ctx) return B200_ERR_INVALID_ARG;
   DeviceGuard guard(ctx->device);

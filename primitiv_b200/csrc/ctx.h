@@ -224,6 +224,8 @@ bool gemm_tc_eligible(const b200_ctx *ctx, const GemmArgs &g);
 int gemm_tc(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream);
 // Checks (and re-arms) the guard bands of every pool block; see b200_pool_check_guards.
 int pool_check_guards(b200_ctx *ctx, cudaStream_t stream, std::uint64_t *damaged, void **first, int *side);
+// Streams L2-resident data into every SM's shared memory and reports the rate; see b200_measure_l2_ingest.
+int measure_l2_ingest(b200_ctx *ctx, cudaStream_t stream, double *bytes_per_clock_per_sm, double *gb_per_s_per_sm);
 // Launches a kernel whose only wait runs out (see b200_selftest_wait_timeout).
 int selftest_wait_timeout(b200_ctx *ctx, cudaStream_t stream);
 // 3xTF32 product whose packing planes live in a fixed device array: allocates nothing.

@@ -18,15 +18,12 @@ namespace {
 constexpr unsigned kBlock = 256;
 
 struct SumOp {
-  __device__ static float init() { return 0.f; }
   __device__ static float merge(float a, float b) { return a + b; }
 };
 struct MaxOp {
-  __device__ static float init() { return -INFINITY; }
   __device__ static float merge(float a, float b) { return fmaxf(a, b); }
 };
 struct MinOp {
-  __device__ static float init() { return INFINITY; }
   __device__ static float merge(float a, float b) { return fminf(a, b); }
 };
 

@@ -608,3 +608,11 @@ def test_skinny_kernels_forced_in_every_mode(ctx, mode):
         assert ol.rel_err(host(c2).reshape(n2, m_), base + b2.astype(np.float64).T @ a2.astype(np.float64)) <= tol
     with pytest.raises(pb.B200Error):
         ctx.gemm(M, 0, 0, dw.data_ptr(), dx.data_ptr(), y.data_ptr(), 64, 64, 64, force_path=3)
+
+
+def test_l2_ingest_measurement_is_sane(ctx):
+    """The measurement aid streams L2-resident data into every SM and reports the rate: a few tens of bytes
+    per SM clock on this GPU generation, and its bounded waits must not have run out."""
+    per_clk, gbs = ctx.measure_l2_ingest()
+    assert 16.0 < per_clk < 200.0 and 20.0 < gbs < 400.0, (per_clk, gbs)
+    assert ctx.status_poll() == 0
