@@ -254,7 +254,9 @@ B200_API int b200_set_path_policy(b200_ctx *ctx, int policy);
 
 /* Tile shape of the tensor-core kernel: 0 (default) = a pair of CTAs per 256-row tile
  * (tcgen05 cta_group::2) whenever the problem has more than 128 rows and at least 128
- * columns, 1 = always one CTA per 128-row tile. */
+ * columns, 256 x 512 per pair for large half-precision products and 256 x 256 otherwise;
+ * 1 = always one CTA per 128-row tile; 2 = pairs, never the 256 x 512 tile; 3 = pairs, the
+ * 256 x 512 tile whenever the product has 512 columns (test hook). */
 B200_API int b200_set_pair_policy(b200_ctx *ctx, int policy);
 
 /* ---- launch policy (no counterpart in the reference, which pays one blocking-free but serial launch per

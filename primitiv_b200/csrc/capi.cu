@@ -199,7 +199,7 @@ int b200_set_path_policy(b200_ctx *ctx, int policy) {
 }
 
 int b200_set_pair_policy(b200_ctx *ctx, int policy) {
-  if (!ctx || policy < 0 || policy > 1) return B200_ERR_INVALID_ARG;
+  if (!ctx || policy < 0 || policy > 3) return B200_ERR_INVALID_ARG;
   ctx->pair_policy = policy;
   return B200_OK;
 }

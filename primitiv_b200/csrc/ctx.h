@@ -141,7 +141,7 @@ struct b200_ctx {
   bool tc_smem_configured = false;
   int path_policy = 0;           // 0 = choose per problem, 1 = CUDA-core kernel, 2 = tensor-core kernel when eligible
   int debug_stage_cap = 0;       // development: cap on pipeline stages (0 = none)
-  int pair_policy = 0;           // 0 = CTA pairs (cta_group::2) when the problem allows, 1 = single CTAs only
+  int pair_policy = 0;           // see b200_set_pair_policy
   int split_policy = 0;          // 0 = split k over idle CTAs when there are few output tiles, 1 = never
   int correction_policy = 0;     // fp32 mode: 0 = correction passes on the bf16 pipe, flat planes where possible;
                                  // 1 = TF32 planes throughout; 2 = bf16 correction passes, operands always repacked K-major

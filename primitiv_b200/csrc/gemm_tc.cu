@@ -363,6 +363,33 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// The same load without the wait, and the wait as a statement that "produces" the registers, so
+// that nothing which uses them can be scheduled in front of it: several loads can then be in
+// flight behind one wait.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+
 // ---- CTA-pair (cta_group::2) forms.  Two CTAs of a cluster share one MMA: the leader
 // (cluster rank 0) issues it for both, each CTA stages its own 128 rows of A and its own
 // half of B's rows, and holds the 128 accumulator rows of its half of M in its own TMEM. ----
@@ -484,15 +511,26 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uin
 // CTA's TMEM receives the 128 accumulator rows of its half of M for all bn columns.  Per
 // CTA that is a third less shared-memory fill and operand traffic per FLOP than the
 // single-CTA tile, which is what bounds this kernel.
-template <bool kChunked, int kCtas, int kKind>
+//
+// kWide (half storage, pairs only): a 256 x 512 tile per pair.  Each CTA stages its 128 rows of A and
+// 128 rows of B for each of the two 256-column halves; a k-block is two runs of four MMAs (left half
+// into TMEM columns 0-255, right half into 256-511) that share the A tile.  Per FLOP that is a
+// quarter less to take in from L2, which is what bounds the 256 x 256 form (an SM takes in 56-58
+// bytes per clock where that form needs 64).  The accumulator fills the tensor memory, so there is
+// no second buffer to hide the epilogue behind: the epilogue warps therefore first drain their 256
+// columns into registers (as packed halves), hand the tensor memory back, and only then go to
+// global memory while the next tile's main loop is already running.
+template <bool kChunked, int kCtas, int kKind, bool kWide = false>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ TcParams p) {
   // kind 0 = 3xTF32 (hi / lo TF32 planes), 1 = TF32, 2 = FP16, 3 = 3xFP16,
   // 4 = fp32 via one TF32 pass plus two bf16 correction passes (hi, hi8, lo8 planes)
   constexpr int kPasses = (kKind == 0 || kKind == 3 || kKind == 4) ? 3 : 1;
-  constexpr uint32_t kSubs = kPasses == 1 ? 2u : 1u;  // k-blocks per pipeline stage
+  constexpr uint32_t kSubs = (kPasses == 1 && !kWide) ? 2u : 1u;  // k-blocks per pipeline stage
   constexpr bool kF16 = kKind == 2 || kKind == 3;
   constexpr bool kMix = kKind == 4;
+  constexpr bool kTable = kMix || kWide;   // the TMA boxes of a stage come from the host-built table
   static_assert(!kChunked || kPasses == 3, "only the three-pass products are chunked");
+  static_assert(!kWide || (kCtas == 2 && kKind == 2 && !kChunked), "the wide tile is a pair form for half storage");
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
   __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
@@ -573,30 +611,32 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       const uint32_t a_boxes = p.a_mn_major ? p.a_chunks : 1u, b_boxes = p.b_mn_major ? p.b_chunks : 1u;
       const uint32_t per_plane = a_boxes + b_boxes;
       // kind 4: this lane's box comes from the host-built table
-      const MixBox mbox = (kMix && lane < p.mix_boxes) ? p.mix_box[lane] : MixBox{0u, 0, 0u, 0u};
-      const uint32_t nboxes = kMix ? p.mix_boxes : kSubs * planes * per_plane;  // <= 32, checked on the host
+      const MixBox mbox = (kTable && lane < p.mix_boxes) ? p.mix_box[lane] : MixBox{0u, 0, 0u, 0u};
+      const uint32_t nboxes = kTable ? p.mix_boxes : kSubs * planes * per_plane;  // <= 32, checked on the host
       const bool has_box = lane < nboxes;
-      const uint32_t bsub = kMix ? 0u : lane / (planes * per_plane), brem = lane % (planes * per_plane);
+      const uint32_t bsub = kTable ? 0u : lane / (planes * per_plane), brem = lane % (planes * per_plane);
       const uint32_t bpl = (brem / per_plane) & 1u, bidx = brem % per_plane;
-      const bool is_b = kMix ? (mbox.flags & 1u) != 0u : bidx >= a_boxes;
+      const bool is_b = kTable ? (mbox.flags & 1u) != 0u : bidx >= a_boxes;
       const uint32_t bchunk = is_b ? bidx - a_boxes : bidx;
-      const bool box_mn = kMix ? (mbox.flags & 2u) != 0u : (is_b ? p.b_mn_major != 0u : p.a_mn_major != 0u);
+      const bool box_mn = kTable ? (mbox.flags & 2u) != 0u : (is_b ? p.b_mn_major != 0u : p.a_mn_major != 0u);
       const uint32_t box_dst =
-          kMix ? mbox.dst
+          kTable ? mbox.dst
                : bsub * p.sub_bytes +
                      (is_b ? planes * p.a_stage_bytes + bpl * p.b_stage_bytes + bchunk * p.b_chunk_bytes
                            : bpl * p.a_stage_bytes + bchunk * p.a_chunk_bytes);
       const int box_k = static_cast<int>(bsub * p.bk);
-      const int box_mn_off = kMix ? mbox.mn_off
-                                  : static_cast<int>(box_mn ? bchunk * (is_b ? p.b_chunk_elems : p.a_chunk_elems) : 0u);
+      const int box_mn_off = kTable ? mbox.mn_off
+                                    : static_cast<int>(box_mn ? bchunk * (is_b ? p.b_chunk_elems : p.a_chunk_elems) : 0u);
       // the eight tensor maps lie back to back at the head of the parameter block
-      const CUtensorMap *box_map = kMix ? &p.mapA[0] + mbox.map : (is_b ? &p.mapB[bpl] : &p.mapA[bpl]);
+      const CUtensorMap *box_map = kTable ? &p.mapA[0] + mbox.map : (is_b ? &p.mapB[bpl] : &p.mapA[bpl]);
+      // rows of B this CTA contributes to one MMA (the wide tile stages two such sets, 256 columns apart)
+      const uint32_t b_rank_rows = kWide ? b_rows / 2u : b_rows;
       for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         uint32_t vg, mt, nt;
         tile_coords(tile, p.tiles_m, p.tiles_n, p.band_m, vg, mt, nt);
         const uint32_t g = vg / splits, split = vg - g * splits;  // split-K: this tile's slice of k
         const int m0 = static_cast<int>(mt * (kBM * kCtas) + cta_rank * kBM);
-        const int n0 = static_cast<int>(nt * p.bn + cta_rank * b_rows);
+        const int n0 = static_cast<int>(nt * p.bn + cta_rank * b_rank_rows);
         const int mn = (is_b ? n0 : m0) + box_mn_off;
         for (uint32_t r = 0; ok && r < red; ++r) {
           const int z = static_cast<int>(is_b ? g * p.b_gmul + r * p.b_rmul : g * p.a_gmul + r * p.a_rmul);
@@ -670,8 +710,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       for (uint32_t tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         uint32_t kb_left = kb_per_tile;
         for (uint32_t c = 0; ok && c < chunks_per_tile; ++c, ++chunk_no) {
-          const uint32_t buf = chunk_no & 1u;
-          const uint32_t buf_phase = (chunk_no >> 1) & 1u;
+          const uint32_t buf = kWide ? 0u : chunk_no & 1u;   // the wide tile's accumulator is the whole tensor memory
+          const uint32_t buf_phase = kWide ? chunk_no & 1u : (chunk_no >> 1) & 1u;
           if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abort_flag))) {
             ok = false;
             break;
@@ -692,10 +732,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 #pragma unroll
               for (uint32_t sub = 0; sub < kSubs; ++sub) {
                 const uint32_t ssa = sa + sub * sub_bytes;
-                if constexpr (kMix)
+                if constexpr (kMix) {
                   mma_stage_mix<kCtas>(d_tmem, ssa, ssa + b_off, a_plane, b_plane, a8, b8, mxa32, mxa8, mxb32, mxb8,
                                        idesc, idesc8, it == 0u);
-                else
+                } else if constexpr (kWide) {
+                  // left and right 256 columns: same A tile, B rows 0-127 and 128-255 of the stage
+                  mma_stage<kCtas, kF16, kPasses>(d_tmem, ssa, ssa + b_off, a_plane, b_plane, a_hi, b_hi, a_lo_fixed,
+                                                  b_lo_fixed, kstep_a, kstep_b, idesc, it == 0u);
+                  mma_stage<kCtas, kF16, kPasses>(d_tmem + 256u, ssa, ssa + b_off + (b_plane >> 1), a_plane, b_plane, a_hi,
+                                                  b_hi, a_lo_fixed, b_lo_fixed, kstep_a, kstep_b, idesc, it == 0u);
+                } else
                   mma_stage<kCtas, kF16, kPasses>(d_tmem, ssa, ssa + b_off, a_plane, b_plane, a_hi, b_hi, a_lo_fixed,
                                                   b_lo_fixed, kstep_a, kstep_b, idesc, (it | sub) == 0u);
               }
@@ -757,7 +803,51 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         if (row < p.m) row_scale = inv_scale_for(p.scale_a[static_cast<unsigned long long>(g_real) * p.scale_a_gs + row]);
         col_scale = p.scale_b + static_cast<unsigned long long>(g_real) * p.scale_b_gs;
       }
-      if constexpr (kChunked) {
+      if constexpr (kWide) {
+        if (!warp_wait(smem_u32(&tmem_full_bar[0]), chunk_no & 1u, abort_flag, lane)) {
+          ok = false;
+          break;
+        }
+        ++chunk_no;
+        tc_fence_after();
+        // this thread's 256 columns of its row, rounded to half and packed in pairs: 128 registers
+        uint32_t pk[8][16];
+#pragma unroll
+        for (uint32_t j = 0; j < 8u; j += 2u) {   // two loads of 32 columns in flight behind each wait
+          uint32_t v0[32], v1[32];
+          tmem_ld32_issue(tmem_base + lane_addr + col_base + j * 32u, v0);
+          tmem_ld32_issue(tmem_base + lane_addr + col_base + j * 32u + 32u, v1);
+          tmem_ld_wait(v0);
+          tmem_ld_wait(v1);
+#pragma unroll
+          for (uint32_t i = 0; i < 16u; ++i) {
+            const __half2 h0 = __floats2half2_rn(__uint_as_float(v0[2u * i]), __uint_as_float(v0[2u * i + 1u]));
+            const __half2 h1 = __floats2half2_rn(__uint_as_float(v1[2u * i]), __uint_as_float(v1[2u * i + 1u]));
+            pk[j][i] = *reinterpret_cast<const uint32_t *>(&h0);
+            pk[j + 1u][i] = *reinterpret_cast<const uint32_t *>(&h1);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(empty0);   // the next tile's main loop may start
+        if (row_ok) {
+          const bool acc_now = p.accumulate != 0u;
+#pragma unroll
+          for (uint32_t j = 0; j < 8u; ++j) {
+            const uint32_t col0 = n0 + col_base + j * 32u;
+            if (col0 < p.n) {
+              float x[32];
+#pragma unroll
+              for (uint32_t i = 0; i < 16u; ++i) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&pk[j][i]));
+                x[2u * i] = f.x;
+                x[2u * i + 1u] = f.y;
+              }
+              store_cols<8>(static_cast<__half *>(p.C), base, p.m, p.n, col0, x, acc_now);
+            }
+          }
+        }
+      } else if constexpr (kChunked) {
         float acc[4][32];
         for (uint32_t c = 0; ok && c < chunks_per_tile; ++c, ++chunk_no) {
           const uint32_t buf = chunk_no & 1u;
@@ -987,6 +1077,19 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   const uint32_t ctas = (ctx->pair_policy != 1 && g.m > kBM && p.bn >= 128u && ctx->sm_count >= 2) ? 2u : 1u;
   const uint32_t tile_m = kBM * ctas;
   p.tiles_m = (g.m + tile_m - 1) / tile_m;
+  // Half storage, pairs: a 256 x 512 tile per pair (see gemm_tc_kernel, kWide) for long contractions
+  // of problems that still fill the GPU four times over with tiles of that size.  Each tile pays
+  // about 6 us at its end that the 256 x 256 form hides behind its second accumulator buffer, and
+  // earns 5 % in its main loop: measured on 8192 x 8192 x 65536 halves, +4 % at k = 65536, -2.5 % at
+  // k = 8192, break-even near 12 K.  pair_policy 2 = never, 3 = whenever n allows (tests).
+  bool wide = false;
+  if (half_store && ctas == 2u && !fixed_scratch && g.n >= 512u && ctx->pair_policy != 2) {
+    const uint64_t wide_tiles = static_cast<uint64_t>(p.tiles_m) * ((g.n + 511u) / 512u) * g.groups;
+    const uint64_t k_total = static_cast<uint64_t>(g.k) * g.red;
+    wide = ctx->pair_policy == 3 ||
+           (k_total >= 16384u && wide_tiles >= 4ull * static_cast<uint64_t>(ctx->sm_count / 2));
+  }
+  if (wide) p.bn = 512u;
   p.tiles_n = (g.n + p.bn - 1) / p.bn;
   const uint64_t total_tiles = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * g.groups;
   if (total_tiles > 0x7fffffffull) return B200_ERR_TOO_LARGE;
@@ -1113,7 +1216,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   p.b8_bytes = b_rows * 64u;
   // Single-pass modes issue only four MMAs per k-block: their pipeline stage holds two k-blocks
   // (a k-block past the end of k is zero-filled by TMA and adds nothing), 3xTF32 stages hold one.
-  p.subs = passes == 1 ? 2u : 1u;
+  p.subs = (passes == 1 && !wide) ? 2u : 1u;   // (a wide stage is one k-block: 16 KB of A, 32 KB of B)
   {
     // the producer warp issues one TMA box per lane and stage
     const uint32_t boxes = planes * ((p.a_mn_major ? kBM / chunk : 1u) + (p.b_mn_major ? b_rows / chunk : 1u));
@@ -1131,7 +1234,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   {
     const uint64_t units = static_cast<uint64_t>(ctx->sm_count) / ctas;
     static const char *sp = kDevKnobs ? std::getenv("PRIMITIV_B200_TC_SPLIT") : nullptr;  // 0 = never split
-    const bool allow = !(sp && std::atoi(sp) == 0) && ctx->split_policy != 1;
+    const bool allow = !(sp && std::atoi(sp) == 0) && ctx->split_policy != 1 && !wide;   // (the wide epilogue stores halves only)
     if (!fixed_scratch && allow && total_tiles * 2 <= units && p.kblocks >= 16u) {
       uint64_t want = units / total_tiles;
       if (want > p.kblocks / 4u) want = p.kblocks / 4u;
@@ -1185,8 +1288,9 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     p.kstep_b_bytes = umma_k * eb;
   }
   const uint32_t fmt = f16 ? 0u : 2u;  // F16 = 0 (kind::f16), TF32 = 2 (kind::tf32)
+  const uint32_t mma_n = wide ? 256u : p.bn;   // columns of one instruction
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (p.a_mn_major << 15) | (p.b_mn_major << 16) |
-            ((p.bn >> 3) << 17) | ((tile_m >> 4) << 24);
+            ((mma_n >> 3) << 17) | ((tile_m >> 4) << 24);
   // bf16 x bf16 -> fp32 (kind::f16 with format 1 = BF16), same operand major-ness as the TF32 pass
   p.idesc8 = (1u << 4) | (1u << 7) | (1u << 10) | (p.a_mn_major << 15) | (p.b_mn_major << 16) |
              ((p.bn >> 3) << 17) | ((tile_m >> 4) << 24);
@@ -1238,6 +1342,25 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     }
     p.mix_boxes = nb;
   }
+  if (wide) {
+    // TMA boxes of one stage: [A | B rows for the left 256 columns | B rows for the right 256 columns];
+    // a K-major tile is one box of 128 rows, an MN-major tile one box per 64 elements (128 bytes) of mn
+    uint32_t nb = 0;
+    auto add = [&](uint32_t dst, uint32_t mn_off, uint32_t map, uint32_t flags) {
+      p.mix_box[nb].dst = dst;
+      p.mix_box[nb].mn_off = static_cast<int32_t>(mn_off);
+      p.mix_box[nb].map = map;
+      p.mix_box[nb].flags = flags;
+      ++nb;
+    };
+    const uint32_t a_cnt = va.mn_major ? kBM / chunk : 1u, b_cnt = vb.mn_major ? 128u / chunk : 1u;
+    for (uint32_t c = 0; c < a_cnt; ++c) add(c * p.bk * 128u, c * chunk, 0u, va.mn_major ? 2u : 0u);
+    for (uint32_t h = 0; h < 2u; ++h)
+      for (uint32_t c = 0; c < b_cnt; ++c)
+        add(p.a_stage_bytes + h * (p.b_stage_bytes >> 1) + c * p.bk * 128u, h * 256u + c * chunk, 2u,
+            1u | (vb.mn_major ? 2u : 0u));
+    p.mix_boxes = nb;
+  }
   p.passes = passes;
   const bool chunked = passes == 3 && static_cast<uint64_t>(g.red) * p.kblocks > kChunkKBlocks;
   p.chunk_kblocks = chunked ? kChunkKBlocks : g.red * p.kblocks;
@@ -1259,7 +1382,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     p.out_half = 0u;
   }
   p.status = ctx->d_status;
-  p.tmem_cols = p.bn * 2u;  // 128, 256 or 512: powers of two
+  p.tmem_cols = wide ? 512u : p.bn * 2u;  // 128, 256 or 512: powers of two
   p.debug = 0u;
   p.band_m = kBandTilesM;
   if (kDevKnobs) {
@@ -1283,7 +1406,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   for (int i = 0; i < ((passes == 3 && !mix) ? 2 : 1) && rc == B200_OK; ++i) {
     rc = encode_map(ctx, &p.mapA[i], a_src[i], va, eb, p.a_mn_major ? chunk : kBM, p.bk, swz_a);
     if (rc == B200_OK)
-      rc = encode_map(ctx, &p.mapB[i], b_src[i], vb, eb, p.b_mn_major ? chunk : b_rows, p.bk, swz_b);
+      rc = encode_map(ctx, &p.mapB[i], b_src[i], vb, eb, p.b_mn_major ? chunk : (wide ? 128u : b_rows), p.bk, swz_b);
   }
   for (int i = 0; mix && i < 2 && rc == B200_OK; ++i) {
     // the bf16 planes share the packed operand's indexing.  K-major: rows of bk elements = 64 bytes under
@@ -1316,6 +1439,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     allow(gemm_tc_kernel<false, 1, 4>);
     allow(gemm_tc_kernel<true, 2, 4>);
     allow(gemm_tc_kernel<false, 2, 4>);
+    allow(gemm_tc_kernel<false, 2, 2, true>);
     if (e != cudaSuccess) rc = static_cast<int>(e);
     ctx->tc_smem_configured = (e == cudaSuccess);
   }
@@ -1334,6 +1458,7 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
       else if (chunked) b200::launch(ctx, gemm_tc_kernel<true, 2, 0>, gd, bd, smem_bytes, stream, 2u, p);
       else if (passes == 3) b200::launch(ctx, gemm_tc_kernel<false, 2, 0>, gd, bd, smem_bytes, stream, 2u, p);
       else if (!f16) b200::launch(ctx, gemm_tc_kernel<false, 2, 1>, gd, bd, smem_bytes, stream, 2u, p);
+      else if (wide) b200::launch(ctx, gemm_tc_kernel<false, 2, 2, true>, gd, bd, smem_bytes, stream, 2u, p);
       else b200::launch(ctx, gemm_tc_kernel<false, 2, 2>, gd, bd, smem_bytes, stream, 2u, p);
     } else if (mix && chunked) {
       b200::launch(ctx, gemm_tc_kernel<true, 1, 4>, dim3(grid), dim3(kThreads), smem_bytes, stream, 1u, p);

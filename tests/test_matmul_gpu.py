@@ -616,3 +616,40 @@ def test_l2_ingest_measurement_is_sane(ctx):
     per_clk, gbs = ctx.measure_l2_ingest()
     assert 16.0 < per_clk < 200.0 and 20.0 < gbs < 400.0, (per_clk, gbs)
     assert ctx.status_poll() == 0
+
+
+@pytest.mark.parametrize("dims", [(300, 200, 1100, 1, 1), (512, 264, 520, 1, 3), (260, 72, 2048, 2, 2), (1024, 136, 512, 1, 1)])
+def test_half_precision_wide_tile_matches_the_regular_tile(ctx, dims):
+    """Half storage, 256 x 512 tiles per CTA pair (pair policy 3 forces them wherever the product has 512
+    columns; by default only large products take them) against 256 x 256 tiles (policy 2): all three
+    products, ragged edges in every dimension, every operand major-ness.  An overwriting product gives the
+    same bits (same instructions in the same order per output element); an accumulating one rounds the
+    product to half before adding the old value, so it may differ from the regular tile by one rounding."""
+    di, dj, dk, ba, bb = dims
+    rng = np.random.default_rng(sum(dims))
+    bs = max(ba, bb)
+    a = ol.round_to_half(rng.standard_normal(di * dj * ba).astype(np.float32))
+    b = ol.round_to_half(rng.standard_normal(dj * dk * bb).astype(np.float32))
+    gy = ol.round_to_half(rng.standard_normal(di * dk * bs).astype(np.float32))
+    m = MODES["fp16"]
+    out = {}
+    ctx.set_path_policy(2)
+    try:
+        for pair in (2, 3):
+            ctx.set_pair_policy(pair)
+            y = matmul_fw(ctx, m, a, b, di, dj, dk, ba, bb)
+            ga0 = np.full(di * dj * ba, 0.5, np.float32)
+            gb0 = np.full(dj * dk * bb, 0.5, np.float32)
+            ga, gb = matmul_bw(ctx, m, a, b, gy, ga0, gb0, di, dj, dk, ba, bb)
+            out[pair] = (y, ga, gb)
+    finally:
+        ctx.set_pair_policy(0)
+        ctx.set_path_policy(0)
+    assert np.array_equal(out[2][0], out[3][0])
+    y64 = ol.fw_f64(a, b, di, dj, dk, ba, bb)
+    ga64, gb64 = ol.bw_f64(a, b, gy, np.full(di * dj * ba, 0.5, np.float32), np.full(dj * dk * bb, 0.5, np.float32),
+                           di, dj, dk, ba, bb)
+    for got, want in zip(out[3], (y64, ga64, gb64)):
+        assert ol.rel_err(got, want) <= TOL["fp16"]
+    for i in (1, 2):
+        assert ol.rel_err(out[3][i], out[2][i].astype(np.float64)) <= 1e-3
