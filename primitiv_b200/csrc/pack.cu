@@ -395,21 +395,34 @@ __device__ __forceinline__ Mix8 mix_split8(const float (&x)[8]) {
 }
 
 // A K-major source whose rows need no padding (k % 8 == 0) and whose matrices are back to back is
-// one flat array with the planes' own layout: the split is elementwise, eight elements per thread.
+// one flat array with the planes' own layout: the split is elementwise.  Four elements per thread
+// and access (one 128-bit load, one 128-bit and two 64-bit stores, all fully coalesced), four such
+// accesses in flight per thread; the source is read once and marked so in the cache.
 __global__ void __launch_bounds__(256) pack_mix_flat_kernel(const float4 *__restrict__ src, float4 *__restrict__ hi,
-                                                            uint4 *__restrict__ h8, uint4 *__restrict__ l8,
-                                                            unsigned long long n8) {
+                                                            uint2 *__restrict__ h8, uint2 *__restrict__ l8,
+                                                            unsigned long long n4) {
   pdl_enter();
-  const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
-  for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
-       i += stride) {
-    const float4 u = src[2 * i], v = src[2 * i + 1];
-    const float x[8] = {u.x, u.y, u.z, u.w, v.x, v.y, v.z, v.w};
-    const Mix8 m = mix_split8(x);
-    hi[2 * i] = m.h0;
-    hi[2 * i + 1] = m.h1;
-    h8[i] = m.h8;
-    l8[i] = m.l8;
+  constexpr unsigned kUnroll = 4;
+  const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x * kUnroll;
+  for (unsigned long long base = static_cast<unsigned long long>(blockIdx.x) * blockDim.x * kUnroll + threadIdx.x;
+       base < n4; base += stride) {
+    float4 x[kUnroll];
+#pragma unroll
+    for (unsigned u = 0; u < kUnroll; ++u) {
+      const unsigned long long i = base + static_cast<unsigned long long>(u) * blockDim.x;
+      x[u] = i < n4 ? __ldcs(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (unsigned u = 0; u < kUnroll; ++u) {
+      const unsigned long long i = base + static_cast<unsigned long long>(u) * blockDim.x;
+      if (i < n4) {
+        const float4 v = x[u];
+        const float4 h = make_float4(rn_tf32(v.x), rn_tf32(v.y), rn_tf32(v.z), rn_tf32(v.w));
+        hi[i] = h;
+        h8[i] = make_uint2(bf16_pair(v.x, v.y), bf16_pair(v.z, v.w));
+        l8[i] = make_uint2(bf16_pair(v.x - h.x, v.y - h.y), bf16_pair(v.z - h.z, v.w - h.w));   // differences exact in fp32
+      }
+    }
   }
 }
 
@@ -575,11 +588,11 @@ void pack_mix(b200_ctx *ctx, cudaStream_t stream, OperandView &v, float *dst, co
   {
     ProfScope prof(ctx, kProfPack, stream);
     if (!v.mn_major && src_ok && dense && v.ld == v.k) {
-      const unsigned long long n8 = static_cast<unsigned long long>(v.nbatch) * v.mn * v.k / 8ull;
+      const unsigned long long n4 = static_cast<unsigned long long>(v.nbatch) * v.mn * v.k / 4ull;
       const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
-      const unsigned long long need = (n8 + 255ull) / 256ull;
-      b200::launch(ctx, pack_mix_flat_kernel, dim3(static_cast<unsigned>(need < cap ? need : cap)), dim3(256), 0, stream, 1u, reinterpret_cast<const float4 *>(src), reinterpret_cast<float4 *>(hi), reinterpret_cast<uint4 *>(h8),
-          reinterpret_cast<uint4 *>(l8), n8);
+      const unsigned long long need = (n4 + 1023ull) / 1024ull;
+      b200::launch(ctx, pack_mix_flat_kernel, dim3(static_cast<unsigned>(need < cap ? need : cap)), dim3(256), 0, stream, 1u, reinterpret_cast<const float4 *>(src), reinterpret_cast<float4 *>(hi), reinterpret_cast<uint2 *>(h8),
+          reinterpret_cast<uint2 *>(l8), n4);
     } else if (v.mn_major && src_ok && v.mn % 4u == 0 && v.ld == v.mn) {
       const uint32_t tiles_mn = (v.mn + 63u) / 64u, tiles_k = (v.k + 63u) / 64u;
       const unsigned long long tt = static_cast<unsigned long long>(tiles_mn) * tiles_k * v.nbatch;
@@ -670,12 +683,12 @@ int mix_flat_planes(b200_ctx *ctx, cudaStream_t stream, const OperandView &v, co
   planes_of(block);
   {
     ProfScope prof(ctx, kProfPack, stream);
-    const unsigned long long n8 = n / 8ull;
+    const unsigned long long n4 = n / 4ull;
     const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
-    const unsigned long long need = (n8 + 255ull) / 256ull;
+    const unsigned long long need = (n4 + 1023ull) / 1024ull;
     b200::launch(ctx, pack_mix_flat_kernel, dim3(static_cast<unsigned>(need < cap ? need : cap)), dim3(256), 0, stream, 1u, static_cast<const float4 *>(v.ptr), reinterpret_cast<float4 *>(const_cast<void *>(planes_out[0])),
-        reinterpret_cast<uint4 *>(const_cast<void *>(planes_out[1])),
-        reinterpret_cast<uint4 *>(const_cast<void *>(planes_out[2])), n8);
+        reinterpret_cast<uint2 *>(const_cast<void *>(planes_out[1])),
+        reinterpret_cast<uint2 *>(const_cast<void *>(planes_out[2])), n4);
   }
   ++ctx->launches;
   // inside an entry point that shares planes (scope) without a caller-set cap, keep at most 4 GiB
