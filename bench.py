@@ -692,10 +692,9 @@ def run_ours(args, wl, rank, local_rank, world):
         extras["l2_ingest_measured"] = {
             "bytes_per_clk_per_sm": per_clk, "gb_per_s_per_sm": gbs,
             "needed_at_full_tensor_rate": 64.0,
-            "tensor_utilisation_ceiling": min(1.0, per_clk / 64.0),
-            "note": "bulk copies L2 -> shared memory and nothing else, 128 KB in flight per SM (b200_measure_l2_ingest); "
-                    "the 256 x 256 pair tiles of the fp32, TF32 and half-precision kinds need 64 B per SM clock at full "
-                    "tensor rate, so their tensor-pipe utilisation cannot exceed the ratio"}
+            "note": "bulk copies L2 -> shared memory and nothing else, 128 KB in flight per SM, everything an L2 hit "
+                    "(b200_measure_l2_ingest); the 256 x 256 pair tiles of the fp32, TF32 and half-precision kinds need "
+                    "64 B per SM clock at full tensor rate and see a quarter of their sectors at HBM latency"}
     rig.barrier()
     if rank == 0 and world == 1 and not args.skip_cpu:
         extras["gpu_comparator"] = gpu_comparator(["batched_square", "fp16_broadcast"])

@@ -329,8 +329,8 @@ B200_API int b200_profile_read(b200_ctx *ctx, double ms[4], uint64_t launches[4]
  * 32 KB blocks of a 64 MB buffer into a four-stage shared-memory ring with bulk copies and does
  * nothing else; reported are bytes per SM clock (slowest SM) and GB/s per SM (CUDA events), about
  * two milliseconds of GPU time.  The tensor-core products need 64 bytes per SM clock at full
- * tensor rate with their 256 x 256 tiles, so (this rate) / 64 bounds their tensor-pipe utilisation;
- * the benchmark reports it beside the roofline.  Waits for `stream`. */
+ * tensor rate with their 256 x 256 tiles; the benchmark reports this figure beside their
+ * roofline.  Waits for `stream`. */
 B200_API int b200_measure_l2_ingest(b200_ctx *ctx, void *stream, double *bytes_per_clock_per_sm, double *gb_per_s_per_sm);
 
 /* Number of kernel launches this context has issued (all kernels of this library). */

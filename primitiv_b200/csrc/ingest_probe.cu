@@ -6,8 +6,8 @@
 // clock at full tensor rate.  This kernel does nothing but such copies: every SM streams 32 KB
 // blocks of a 64 MB buffer (it fits in L2) through a four-stage shared-memory ring, a producer
 // thread issuing bulk copies, a consumer thread releasing each stage as soon as it has landed.
-// The rate it reaches is the most any kernel with that much shared memory in flight can be fed;
-// tensor-pipe utilisation of a product cannot exceed (this rate) / (bytes it needs per clock).
+// The rate it reaches is what that much shared memory in flight can be fed when every block is an
+// L2 hit; a product whose operands partly come from HBM is fed less per byte in flight.
 #include <vector>
 
 #include "ctx.h"
