@@ -1128,9 +1128,14 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     MixPlanes lay[2];
     for (int o = 0; o < 2; ++o) {
       // (measured: an MN-major A costs nothing, an MN-major B 20 % of the main loop -- 3.84 against 3.16 ms
-      // on 8 x 4096^3 -- so a B operand that is MN-major in memory is still transposed into K-major planes)
+      // on 8 x 4096^3 -- so a B operand that is MN-major in memory is still transposed into K-major planes.
+      // Unless its flat planes are already cached and the product has few rows: transposing B costs
+      // 12 bytes per element of B whatever m is, a fifth of the main loop shrinks with m, and the two
+      // meet near m = 1800.  That is the weight gradient of a layer, gW = gZ . H^T over a large
+      // minibatch, whose H was split flat for the forward product.)
+      const bool b_mn = o == 1 && views[o]->mn_major;
       *flat[o] = !fixed_scratch && ctx->correction_policy == 0 && mix_flat_ok(*views[o]) &&
-                 !(o == 1 && views[o]->mn_major);
+                 (!b_mn || (g.m <= 1536u && mix_flat_cached(ctx, *views[o])));
       if (!*flat[o]) {
         lay[o] = mix_planes(*views[o]);
         repack_floats += lay[o].floats();

@@ -652,6 +652,15 @@ void plane_cache_drop_range(b200_ctx *ctx, const void *ptr, std::size_t bytes) {
   for (void *b : blocks) ctx->pool.free(b);   // stream-ordered reuse: queued products that read them run first
 }
 
+bool mix_flat_cached(const b200_ctx *ctx, const OperandView &v) {
+  const PlaneCache &pc = ctx->planes;
+  if (!pc.active()) return false;
+  const uint64_t n = static_cast<uint64_t>(v.nbatch > 1 ? v.nbatch : 1u) * v.mn * v.k;
+  for (const PlaneCache::Entry &e : pc.entries)
+    if (e.src == v.ptr && e.src_bytes == n * sizeof(float)) return true;
+  return false;
+}
+
 int mix_flat_planes(b200_ctx *ctx, cudaStream_t stream, const OperandView &v, const void *planes_out[3],
                     void **owned_block) {
   PlaneCache &pc = ctx->planes;

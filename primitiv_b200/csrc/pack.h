@@ -61,6 +61,8 @@ void pack_mix(b200_ctx *ctx, cudaStream_t stream, OperandView &v, float *dst, co
 // when the operand is dense and every stride is a multiple of 8 elements (TMA needs 16-byte rows in
 // the bf16 planes too).
 bool mix_flat_ok(const OperandView &v);
+// Whether the context's plane cache already holds the flat planes of this operand.
+bool mix_flat_cached(const b200_ctx *ctx, const OperandView &v);
 // Finds the operand's flat planes in the context's plane cache, or packs them (one elementwise
 // pass) and offers them to the cache.  planes_out = {hi, hi8, lo8}.  *owned_block is the block the
 // caller has to return to the pool after its launch, or null when the cache keeps it.
