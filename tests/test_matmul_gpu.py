@@ -430,6 +430,40 @@ def test_fused_host_entry_point(ctx, mode, batches, accumulate):
     assert ol.rel_err(ga.astype(np.float32), ga64) < tol and ol.rel_err(gb.astype(np.float32), gb64) < tol
 
 
+@pytest.mark.parametrize("accumulate", [True, False], ids=["prefill_0.5", "known_zero"])
+@pytest.mark.parametrize("mode", ["3xtf32", "fp16"])
+@pytest.mark.parametrize("outputs", ["all", "no_y", "no_gb", "no_ga"])
+def test_fused_host_entry_point_large_items(ctx, mode, accumulate, outputs):
+    """Items large enough that the call's pipeline runs one batch item per chunk (8 MiB and more per
+    operand item), pinned host buffers: same results as the oracle, whichever outputs are asked for."""
+    di, dj, dk, ba, bb = 1024, 1024, 2048, 3, 3
+    rng = np.random.default_rng(77)
+    half = mode == "fp16"
+    dt = np.float16 if half else np.float32
+    mk = lambda n, normal=False: (rng.standard_normal(n) if normal else rng.uniform(-1, 1, n)).astype(np.float32).astype(dt)
+    a, b, gy = mk(di * dj * ba), mk(dj * dk * bb), mk(di * dk * bb, True)
+    a32, b32, gy32 = (x.astype(np.float32) for x in (a, b, gy))
+    pin = lambda x: torch.from_numpy(x.copy()).pin_memory()
+    ta, tb, tgy = pin(a), pin(b), pin(gy)
+    ty = pin(np.full(di * dk * bb, 7.0, dt))
+    tga = pin(np.full(di * dj * ba, 0.5 if accumulate else 1e4, dt))
+    tgb = pin(np.full(dj * dk * bb, 0.5 if accumulate else 1e4, dt))
+    P = lambda t: t.data_ptr()
+    ctx.matmul_fw_bw_host(MODES[mode], P(ta), P(tb), P(tgy), None if outputs == "no_y" else P(ty),
+                          None if outputs == "no_ga" else P(tga), None if outputs == "no_gb" else P(tgb),
+                          di, dj, dk, ba, bb, accumulate_a=accumulate, accumulate_b=accumulate)
+    tol = 2e-3 if half else 1e-5
+    start = 0.5 if accumulate else 0.0
+    ga64, gb64 = ol.bw_f64(a32, b32, gy32, np.full(di * dj * ba, start, np.float32), np.full(dj * dk * bb, start, np.float32),
+                           di, dj, dk, ba, bb)
+    if outputs != "no_y":
+        assert ol.rel_err(ty.numpy().astype(np.float32), ol.fw_f64(a32, b32, di, dj, dk, ba, bb)) < tol
+    if outputs != "no_ga":
+        assert ol.rel_err(tga.numpy().astype(np.float32), ga64) < tol
+    if outputs != "no_gb":
+        assert ol.rel_err(tgb.numpy().astype(np.float32), gb64) < tol
+
+
 def test_fused_host_entry_point_optional_outputs(ctx):
     """Any of y / ga / gb may be left out; the plumbing workload with pinned host buffers."""
     c = ol.config1_inputs()
