@@ -224,6 +224,82 @@ __global__ void __launch_bounds__(256) binary_bw_mixed_kernel(const T *__restric
   }
 }
 
+// Vector form of binary_bw_mixed_kernel (volume a multiple of the vector width, every array 16-byte
+// aligned): a thread owns one 128-bit vector of the volume, and four batch items are loaded before
+// the first of them is stored, so that the stores (which may alias the loads as far as the
+// compiler knows) do not put one memory latency between every two items.  Only the operands the
+// derivative needs are read at all (none for + and -).
+template <typename T, int OP>
+__global__ void __launch_bounds__(256) binary_bw_mixed_vec_kernel(const T *__restrict__ a, const T *__restrict__ b,
+                                                                  const T *__restrict__ y, const T *__restrict__ gy,
+                                                                  T *ga, T *gb, float *partial, u64 volume,
+                                                                  uint32_t batch, uint32_t slice_len, int a_batched,
+                                                                  int acc_batched, int acc_summed) {
+  pdl_enter();
+  constexpr int N = Vec<T>::N;
+  constexpr unsigned U = 4;
+  constexpr bool kNeedA = OP == B200_OP_MULTIPLY || OP == B200_OP_POW;                        // db or da reads a
+  constexpr bool kNeedB = OP == B200_OP_MULTIPLY || OP == B200_OP_DIVIDE || OP == B200_OP_POW;
+  constexpr bool kNeedY = OP == B200_OP_DIVIDE || OP == B200_OP_POW;
+  __shared__ float buf[kSumLanes][32 * N];
+  T *g_batched = a_batched ? ga : gb, *g_summed = a_batched ? gb : ga;
+  const T *op_batched = a_batched ? a : b, *op_shared = a_batched ? b : a;
+  const bool need_batched = a_batched ? kNeedA : kNeedB, need_shared = a_batched ? kNeedB : kNeedA;
+  for (u64 tile = blockIdx.x; tile * (32ull * N) < volume; tile += gridDim.x) {
+    const u64 i = (tile * 32ull + threadIdx.x) * N;
+    const uint32_t lo = blockIdx.y * slice_len;
+    const uint32_t hi = lo + slice_len < batch ? lo + slice_len : batch;
+    float v[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) v[j] = 0.f;
+    if (i < volume) {
+      Vec<T> vs;
+      vs.raw = {};
+      if (need_shared) vs.load(op_shared + i);
+      for (uint32_t n = lo + threadIdx.y; n < hi; n += kSumLanes * U) {
+        Vec<T> vgy[U], vop[U], vy[U], vold[U];
+#pragma unroll
+        for (unsigned u = 0; u < U; ++u) {
+          vop[u].raw = {};
+          vy[u].raw = {};
+          vold[u].raw = {};
+          if (n + u * kSumLanes < hi) {
+            const u64 e = static_cast<u64>(n + u * kSumLanes) * volume + i;
+            vgy[u].load(gy + e);
+            if (need_batched) vop[u].load(op_batched + e);
+            if (kNeedY) vy[u].load(y + e);
+            if (acc_batched) vold[u].load(g_batched + e);
+          }
+        }
+#pragma unroll
+        for (unsigned u = 0; u < U; ++u) {
+          if (n + u * kSumLanes < hi) {
+            const u64 e = static_cast<u64>(n + u * kSumLanes) * volume + i;
+            Vec<T> out;
+#pragma unroll
+            for (int j = 0; j < N; ++j) {
+              const float av = a_batched ? vop[u].get(j) : vs.get(j), bv = a_batched ? vs.get(j) : vop[u].get(j);
+              float da, db;
+              binary_d<OP>(av, bv, vy[u].get(j), vgy[u].get(j), da, db);
+              out.set(j, (acc_batched ? vold[u].get(j) : 0.f) + (a_batched ? da : db));
+              v[j] += a_batched ? db : da;
+            }
+            out.store(g_batched + e);
+          }
+        }
+      }
+    }
+    combine_batch_lanes_vec<N>(v, buf);
+    if (threadIdx.y == 0 && i < volume) {
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        if (gridDim.y == 1) st(g_summed, i + j, (acc_summed ? ld(g_summed, i + j) : 0.f) + v[j]);
+        else partial[static_cast<u64>(blockIdx.y) * volume + i + j] = v[j];
+      }
+    }
+  }
+}
+
 // y[n][i] = x[n or 0][i] op k[n or 0]
 template <typename T, int OP>
 __global__ void __launch_bounds__(kBlock) scalar_fw_kernel(const T *__restrict__ x, const T *__restrict__ k,
@@ -372,23 +448,32 @@ int launch_binary_bw(b200_ctx *ctx, cudaStream_t s, int op, const void *a, const
     }
     return B200_OK;
   }
-  const BatchSlices bs = batch_slices(ctx, volume, batch);
+  constexpr unsigned N = Vec<T>::N;
+  const bool vec = volume % N == 0 && volume >= 32ull * N && aligned16(a) && aligned16(b) && aligned16(y) &&
+                   aligned16(gy) && aligned16(ga) && aligned16(gb);
+  const BatchSlices bs = batch_slices(ctx, volume, batch, vec ? 32u * N : 32u);
   void *partial = nullptr;
   if (bs.slices > 1) {
     const int rc = ctx->pool.alloc(static_cast<size_t>(bs.slices) * volume * sizeof(float), &partial, nullptr);
     if (rc != B200_OK) return rc;
   }
   const dim3 grid(bs.tiles, bs.slices), block(32, kSumLanes);
-  switch (op) {
-#define X(OP) case OP: b200::launch(ctx, binary_bw_mixed_kernel<T, OP>, dim3(grid), dim3(block), 0, s, 1u, pa, pb, py, pgy, pga, pgb, static_cast<float *>(partial), volume, batch, bs.slice_len, a_batched, a_batched ? acc_a : acc_b, a_batched ? acc_b : acc_a); break;
-    B200_BINARY_OPS(X)
+  if (vec) {
+    switch (op) {
+#define X(OP) case OP: b200::launch(ctx, binary_bw_mixed_vec_kernel<T, OP>, dim3(grid), dim3(block), 0, s, 1u, pa, pb, py, pgy, pga, pgb, static_cast<float *>(partial), volume, batch, bs.slice_len, a_batched, a_batched ? acc_a : acc_b, a_batched ? acc_b : acc_a); break;
+      B200_BINARY_OPS(X)
 #undef X
+    }
+  } else {
+    switch (op) {
+#define X(OP) case OP: b200::launch(ctx, binary_bw_mixed_kernel<T, OP>, dim3(grid), dim3(block), 0, s, 1u, pa, pb, py, pgy, pga, pgb, static_cast<float *>(partial), volume, batch, bs.slice_len, a_batched, a_batched ? acc_a : acc_b, a_batched ? acc_b : acc_a); break;
+      B200_BINARY_OPS(X)
+#undef X
+    }
   }
   if (bs.slices > 1) {
-    b200::launch(ctx, batch_final_kernel<T>, dim3(grid_for(ctx, volume, 256)), dim3(256), 0, s, 1u, static_cast<const float *>(partial),
-                                                                     a_batched ? pgb : pga, volume, bs.slices, 1.f,
-                                                                     a_batched ? acc_b : acc_a);
-    ++ctx->launches;
+    launch_batch_final<T>(ctx, s, static_cast<const float *>(partial), a_batched ? pgb : pga, volume, bs.slices, 1.f,
+                          a_batched ? acc_b : acc_a);
     ctx->pool.free(partial);  // stream-ordered reuse
   }
   return B200_OK;

@@ -66,9 +66,10 @@ struct BatchSlices {
   uint32_t slice_len;  // batch items per slice
 };
 
-inline BatchSlices batch_slices(const b200_ctx *ctx, u64 volume, uint32_t batch) {
+// tile_elems: consecutive elements of the volume per CTA (32, or 32 vectors of 4 / 8 in the vector forms)
+inline BatchSlices batch_slices(const b200_ctx *ctx, u64 volume, uint32_t batch, unsigned tile_elems = 32u) {
   BatchSlices r;
-  const u64 tiles = (volume + 31ull) / 32ull;
+  const u64 tiles = (volume + tile_elems - 1ull) / tile_elems;
   r.tiles = static_cast<unsigned>(tiles < 0x7fffffffull ? tiles : 0x7fffffffull);
   u64 want = (2ull * static_cast<u64>(ctx->sm_count) + tiles - 1) / tiles;  // about two CTAs per SM
   const u64 most = batch / (4u * kSumLanes) ? batch / (4u * kSumLanes) : 1;  // >= 32 items per slice
@@ -106,6 +107,38 @@ __global__ void __launch_bounds__(256) batch_final_kernel(const float *__restric
   }
 }
 
+// The same for a few outputs with many slices (a scalar loss over 65536 items: one output, 300
+// slices): a warp per output, lane l adds slices l, l + 32, ... in order, and the lanes are
+// combined by a fixed shuffle tree.  One thread per output would walk the slices as a chain of
+// dependent loads.
+template <typename T>
+__global__ void __launch_bounds__(256) batch_final_warp_kernel(const float *__restrict__ partial, T *y, u64 volume,
+                                                               unsigned slices, float scale, int accumulate) {
+  pdl_enter();
+  const unsigned lane = threadIdx.x & 31u;
+  const u64 warps = (static_cast<u64>(gridDim.x) * blockDim.x) >> 5;
+  for (u64 i = (static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; i < volume; i += warps) {
+    float t = 0.f;
+    for (unsigned sl = lane; sl < slices; sl += 32u) t += partial[static_cast<u64>(sl) * volume + i];
+#pragma unroll
+    for (unsigned d = 16u; d > 0u; d >>= 1) t += __shfl_xor_sync(0xffffffffu, t, d);
+    if (lane == 0) st(y, i, (accumulate ? ld(y, i) : 0.f) + scale * t);
+  }
+}
+
+// Picks the form of the final pass: many slices of few outputs go to the warp form.
+template <typename T>
+inline void launch_batch_final(b200_ctx *ctx, cudaStream_t s, const float *partial, T *y, u64 volume, unsigned slices,
+                               float scale, int accumulate) {
+  if (slices >= 64u && volume <= 4096ull)
+    b200::launch(ctx, batch_final_warp_kernel<T>, dim3(grid_for(ctx, volume * 32ull, 256)), dim3(256), 0, s, 1u, partial, y,
+                 volume, slices, scale, accumulate);
+  else
+    b200::launch(ctx, batch_final_kernel<T>, dim3(grid_for(ctx, volume, 256)), dim3(256), 0, s, 1u, partial, y, volume,
+                 slices, scale, accumulate);
+  ++ctx->launches;
+}
+
 // y[i] = (accumulate ? y[i] : 0) + scale * sum_n x[n][i]; with more than one slice the CTA's
 // sum goes to partial[slice][i] instead.
 template <typename T>
@@ -129,23 +162,86 @@ __global__ void __launch_bounds__(256) batch_sum_tile_kernel(const T *__restrict
   }
 }
 
-// Host side of the two kernels above.  Returns a CUDA / library status.
+// Combines the 8 batch lanes of a CTA for the N values each thread holds (vector forms).
+template <int N>
+__device__ __forceinline__ void combine_batch_lanes_vec(float (&v)[N], float (*buf)[32 * N]) {
+#pragma unroll
+  for (int j = 0; j < N; ++j) buf[threadIdx.y][threadIdx.x * N + j] = v[j];
+  __syncthreads();
+  if (threadIdx.y == 0) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      float t = 0.f;
+#pragma unroll
+      for (unsigned l = 0; l < kSumLanes; ++l) t += buf[l][threadIdx.x * N + j];
+      v[j] = t;
+    }
+  }
+  __syncthreads();
+}
+
+// Vector form of batch_sum_tile_kernel (volume a multiple of the vector width, 16-byte aligned
+// arrays): a thread owns one 128-bit vector of the volume and keeps four items in flight.
+template <typename T>
+__global__ void __launch_bounds__(256) batch_sum_tile_vec_kernel(const T *__restrict__ x, T *y, float *partial,
+                                                                 u64 volume, uint32_t batch, uint32_t slice_len,
+                                                                 float scale, int accumulate) {
+  pdl_enter();
+  constexpr int N = Vec<T>::N;
+  constexpr unsigned U = 4;
+  __shared__ float buf[kSumLanes][32 * N];
+  for (u64 tile = blockIdx.x; tile * (32ull * N) < volume; tile += gridDim.x) {
+    const u64 i = (tile * 32ull + threadIdx.x) * N;
+    const uint32_t lo = blockIdx.y * slice_len;
+    const uint32_t hi = lo + slice_len < batch ? lo + slice_len : batch;
+    float v[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) v[j] = 0.f;
+    if (i < volume) {
+      for (uint32_t n = lo + threadIdx.y; n < hi; n += kSumLanes * U) {
+        Vec<T> vx[U];
+#pragma unroll
+        for (unsigned u = 0; u < U; ++u)
+          if (n + u * kSumLanes < hi) vx[u].load(x + static_cast<u64>(n + u * kSumLanes) * volume + i);
+#pragma unroll
+        for (unsigned u = 0; u < U; ++u)
+          if (n + u * kSumLanes < hi) {
+#pragma unroll
+            for (int j = 0; j < N; ++j) v[j] += vx[u].get(j);
+          }
+      }
+    }
+    combine_batch_lanes_vec<N>(v, buf);
+    if (threadIdx.y == 0 && i < volume) {
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        if (gridDim.y == 1) st(y, i + j, (accumulate ? ld(y, i + j) : 0.f) + scale * v[j]);
+        else partial[static_cast<u64>(blockIdx.y) * volume + i + j] = v[j];
+      }
+    }
+  }
+}
+
+// Host side of the kernels above.  Returns a CUDA / library status.
 template <typename T>
 int launch_batch_sum(b200_ctx *ctx, cudaStream_t s, const void *x, void *y, u64 volume, uint32_t batch,
                      float scale, int accumulate) {
-  const BatchSlices bs = batch_slices(ctx, volume, batch);
+  constexpr unsigned N = Vec<T>::N;
+  const bool vec = volume % N == 0 && volume >= 32ull * N && aligned16(x);
+  const BatchSlices bs = batch_slices(ctx, volume, batch, vec ? 32u * N : 32u);
   void *partial = nullptr;
   if (bs.slices > 1) {
     const int rc = ctx->pool.alloc(static_cast<size_t>(bs.slices) * volume * sizeof(float), &partial, nullptr);
     if (rc != B200_OK) return rc;
   }
-  b200::launch(ctx, batch_sum_tile_kernel<T>, dim3(bs.tiles, bs.slices), dim3(32, kSumLanes), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y), static_cast<float *>(partial), volume, batch, bs.slice_len,
-      scale, accumulate);
+  if (vec)
+    b200::launch(ctx, batch_sum_tile_vec_kernel<T>, dim3(bs.tiles, bs.slices), dim3(32, kSumLanes), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y), static_cast<float *>(partial), volume, batch, bs.slice_len,
+        scale, accumulate);
+  else
+    b200::launch(ctx, batch_sum_tile_kernel<T>, dim3(bs.tiles, bs.slices), dim3(32, kSumLanes), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y), static_cast<float *>(partial), volume, batch, bs.slice_len,
+        scale, accumulate);
   if (bs.slices > 1) {
-    b200::launch(ctx, batch_final_kernel<T>, dim3(grid_for(ctx, volume, 256)), dim3(256), 0, s, 1u, static_cast<const float *>(partial),
-                                                                     static_cast<T *>(y), volume, bs.slices, scale,
-                                                                     accumulate);
-    ++ctx->launches;
+    launch_batch_final<T>(ctx, s, static_cast<const float *>(partial), static_cast<T *>(y), volume, bs.slices, scale, accumulate);
     ctx->pool.free(partial);  // stream-ordered reuse
   }
   return B200_OK;

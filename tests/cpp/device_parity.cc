@@ -506,6 +506,60 @@ void test_batch_ops_and_inplace(Pair &p) {
   }
 }
 
+// Sums over the batch in their large forms: volumes that take the 128-bit vector kernels (a multiple
+// of 8 elements, at least 256), ragged ones that do not, batches long enough to be cut into slices,
+// and a tiny volume under a very long batch (hundreds of slices, combined by the warp form of the
+// final pass).  Binary operators with one broadcast operand, batch::sum, and in-place addition
+// into a batch-1 tensor all go through them.
+void test_large_batch_sums(Pair &p) {
+  Device *devs[2] = {&p.naive, &p.dev};
+  struct BCase { const char *name; FwXS fw; BwAB bw; float lo, hi; };
+  const BCase binaries[] = {
+    {"add", &Device::add_fw, &Device::add_bw, -2, 2}, {"subtract", &Device::subtract_fw, &Device::subtract_bw, -2, 2},
+    {"multiply", &Device::multiply_fw, &Device::multiply_bw, -2, 2},
+    {"divide", &Device::divide_fw, &Device::divide_bw, .5f, 2}, {"pow", &Device::pow_fw, &Device::pow_bw, .5f, 2},
+  };
+  struct Dim { std::uint32_t rows, cols, batch; };
+  const Dim dims[] = {{40, 8, 70}, {33, 5, 70}, {64, 16, 300}, {8, 1, 4096}};
+  for (const Dim &dm : dims) {
+    for (int which = 0; which < 2; ++which) {   // which operand is broadcast
+      const Shape sa({dm.rows, dm.cols}, which == 0 ? 1 : dm.batch), sb({dm.rows, dm.cols}, which == 0 ? dm.batch : 1);
+      const Shape sy({dm.rows, dm.cols}, dm.batch);
+      const std::string tag = " " + std::to_string(dm.rows) + "x" + std::to_string(dm.cols) + " batch " +
+                              std::to_string(dm.batch) + (which == 0 ? " (a broadcast)" : " (b broadcast)");
+      for (const BCase &c : binaries) {
+        const vector<float> av = on_grid(rnd(sa.size(), c.lo, c.hi)), bv = on_grid(rnd(sb.size(), c.lo, c.hi));
+        const vector<float> gv = on_grid(rnd(sy.size()));
+        vector<float> gas[2], gbs[2];
+        for (int d = 0; d < 2; ++d) {
+          Tensor a = p.on(*devs[d], sa, av), b = p.on(*devs[d], sb, bv), gy = p.on(*devs[d], sy, gv);
+          Tensor y = (devs[d]->*c.fw)(a, b);
+          Tensor ga = devs[d]->new_tensor_by_constant(sa, 0.5f), gb = devs[d]->new_tensor_by_constant(sb, 0.5f);
+          (devs[d]->*c.bw)(a, b, y, gy, ga, gb);
+          gas[d] = ga.to_vector(); gbs[d] = gb.to_vector();
+        }
+        // a sum of `batch` terms: the tolerance grows with its square root
+        const float t = g_tol * 8 * std::sqrt(static_cast<float>(dm.batch));
+        expect_normwise(gas[0], gas[1], std::string(c.name) + "_bw ga" + tag, t);
+        expect_normwise(gbs[0], gbs[1], std::string(c.name) + "_bw gb" + tag, t);
+      }
+    }
+    const Shape s({dm.rows, dm.cols}, dm.batch), s1({dm.rows, dm.cols}, 1);
+    const vector<float> xv = on_grid(rnd(s.size())), zv = on_grid(rnd(s1.size()));
+    vector<float> sums[2], adds[2];
+    for (int d = 0; d < 2; ++d) {
+      Tensor x = p.on(*devs[d], s, xv), z = p.on(*devs[d], s1, zv);
+      sums[d] = devs[d]->batch_sum_fw(x).to_vector();
+      z.inplace_add(x);
+      adds[d] = z.to_vector();
+    }
+    const float t = g_tol * 8 * std::sqrt(static_cast<float>(dm.batch));
+    const std::string tag = " " + std::to_string(dm.rows) + "x" + std::to_string(dm.cols) + " batch " + std::to_string(dm.batch);
+    expect_normwise(sums[0], sums[1], "batch_sum_fw" + tag, t);
+    expect_normwise(adds[0], adds[1], "inplace_add into batch 1" + tag, t);
+  }
+}
+
 void test_random(Pair &p) {
   const Shape s({1000, 100});
   const vector<float> u = p.dev.random_uniform(s, -2.f, 3.f).to_vector();
@@ -858,6 +912,7 @@ int main(int argc, char **argv) {
     test_matmul(p);
     test_movement(p);
     test_batch_ops_and_inplace(p);
+    test_large_batch_sums(p);
     test_random(p);
     test_conv_and_pool(p);
     test_zero_gradients(p);
