@@ -72,7 +72,8 @@ inline BatchSlices batch_slices(const b200_ctx *ctx, u64 volume, uint32_t batch,
   const u64 tiles = (volume + tile_elems - 1ull) / tile_elems;
   r.tiles = static_cast<unsigned>(tiles < 0x7fffffffull ? tiles : 0x7fffffffull);
   u64 want = (2ull * static_cast<u64>(ctx->sm_count) + tiles - 1) / tiles;  // about two CTAs per SM
-  const u64 most = batch / (4u * kSumLanes) ? batch / (4u * kSumLanes) : 1;  // >= 32 items per slice
+  // at least 128 items per slice: a short batch (a recurrent step's 64 items) is one slice and one launch
+  const u64 most = batch / (16u * kSumLanes) ? batch / (16u * kSumLanes) : 1;
   if (want > most) want = most;
   if (want > 65535ull) want = 65535ull;
   if (want < 1) want = 1;
