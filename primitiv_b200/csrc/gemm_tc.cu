@@ -1115,6 +1115,10 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   };
   // kind 4 bookkeeping: the plane pointers of each operand and whether they are flat copies
   bool a_flat = false, b_flat = false;
+  // ... and the one mixed case: B's TF32 plane transposed into K-major scratch, its bf16 planes taken
+  // flat (MN-major) from the cache.  vb8 is then the view of those bf16 planes.
+  bool b_hybrid = false;
+  OperandView vb8;
   if (mix) {
     // An operand that is dense and 32-byte aligned in every stride is packed "flat": the three
     // planes repeat the caller's layout element for element (the kernel reads either
@@ -1134,11 +1138,16 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
       // meet near m = 1800.  That is the weight gradient of a layer, gW = gZ . H^T over a large
       // minibatch, whose H was split flat for the forward product.)
       const bool b_mn = o == 1 && views[o]->mn_major;
-      *flat[o] = !fixed_scratch && ctx->correction_policy == 0 && mix_flat_ok(*views[o]) &&
-                 (!b_mn || (g.m <= 1536u && mix_flat_cached(ctx, *views[o])));
+      const bool flat_possible = !fixed_scratch && ctx->correction_policy == 0 && mix_flat_ok(*views[o]);
+      const bool cached = flat_possible && b_mn && mix_flat_cached(ctx, *views[o]);
+      *flat[o] = flat_possible && (!b_mn || (g.m <= 1536u && cached));
+      // Only the TF32 plane of an MN-major B is slow to read; its bf16 planes are not.  With the flat
+      // planes already cached, the transposing pre-pass therefore writes the TF32 plane alone (8
+      // instead of 12 bytes per element) and the correction passes read the cached bf16 planes.
+      if (b_mn && !*flat[o] && cached) b_hybrid = true;
       if (!*flat[o]) {
         lay[o] = mix_planes(*views[o]);
-        repack_floats += lay[o].floats();
+        repack_floats += (o == 1 && b_hybrid) ? lay[o].hi_elems : lay[o].floats();
       }
     }
     float *cursor = nullptr;
@@ -1157,6 +1166,20 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
           release();
           return rc;
         }
+      } else if (o == 1 && b_hybrid) {
+        vb8 = vb;   // the caller's layout: what the cached bf16 planes repeat
+        const void *flat_planes[3];
+        void *unused = nullptr;
+        const int rc = mix_flat_planes(ctx, stream, vb, flat_planes, &unused);   // a cache hit: nothing is packed
+        if (rc != B200_OK || unused) {
+          if (unused) ctx->pool.free(unused);
+          release();
+          return rc != B200_OK ? rc : B200_ERR_INVALID_ARG;
+        }
+        pack_mix(ctx, stream, vb, cursor, lay[o], outs[o], /*hi_only=*/true);
+        cursor += lay[o].hi_elems;
+        b_mix[1] = flat_planes[1];
+        b_mix[2] = flat_planes[2];
       } else {
         pack_mix(ctx, stream, *views[o], cursor, lay[o], outs[o]);
         cursor += lay[o].floats();
@@ -1297,7 +1320,8 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (p.a_mn_major << 15) | (p.b_mn_major << 16) |
             ((mma_n >> 3) << 17) | ((tile_m >> 4) << 24);
   // bf16 x bf16 -> fp32 (kind::f16 with format 1 = BF16), same operand major-ness as the TF32 pass
-  p.idesc8 = (1u << 4) | (1u << 7) | (1u << 10) | (p.a_mn_major << 15) | (p.b_mn_major << 16) |
+  const bool b8_mn = b_hybrid ? true : vb.mn_major;   // major-ness of B's bf16 planes
+  p.idesc8 = (1u << 4) | (1u << 7) | (1u << 10) | (p.a_mn_major << 15) | ((b8_mn ? 1u : 0u) << 16) |
              ((p.bn >> 3) << 17) | ((tile_m >> 4) << 24);
   if (mix) {
     // Descriptor fields per plane kind.  K-major: rows of 128 bytes (TF32, 128-byte swizzle, 8-row groups
@@ -1318,16 +1342,16 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     p.mix_a[0] = desc(va.mn_major, true);
     p.mix_a[1] = desc(va.mn_major, false);
     p.mix_b[0] = desc(vb.mn_major, true);
-    p.mix_b[1] = desc(vb.mn_major, false);
+    p.mix_b[1] = desc(b8_mn, false);
     // TMA boxes of one stage: [A hi | A hi8 | A lo8 | B hi | B hi8 | B lo8]; a K-major plane is one box,
     // an MN-major plane one box per 128 bytes of mn (32 floats, 64 bf16)
     uint32_t nb = 0;
     for (uint32_t o = 0; o < 2u; ++o) {
-      const bool mn = o ? vb.mn_major : va.mn_major;
       const uint32_t rows = o ? b_rows : kBM;
       const uint32_t plane32 = o ? p.b_stage_bytes : p.a_stage_bytes, plane8 = o ? p.b8_bytes : p.a8_bytes;
       const uint32_t base = o ? 2u * p.a_stage_bytes : 0u;
       for (uint32_t t = 0; t < 3u; ++t) {
+        const bool mn = o ? (t == 0 ? vb.mn_major : b8_mn) : va.mn_major;
         const uint32_t off = base + (t == 0 ? 0u : plane32 + (t - 1u) * plane8);
         const uint32_t map = t == 0 ? (o ? 2u : 0u) : (o ? 6u : 4u) + (t - 1u);
         const uint32_t per = t == 0 ? 32u : 64u;   // mn elements per 128-byte chunk
@@ -1419,8 +1443,8 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
     rc = encode_map(ctx, &p.mapA8[i], a_mix[1 + i], va, 2, va.mn_major ? 64u : kBM, p.bk,
                     va.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, true);
     if (rc == B200_OK)
-      rc = encode_map(ctx, &p.mapB8[i], b_mix[1 + i], vb, 2, vb.mn_major ? 64u : b_rows, p.bk,
-                      vb.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, true);
+      rc = encode_map(ctx, &p.mapB8[i], b_mix[1 + i], b_hybrid ? vb8 : vb, 2, b8_mn ? 64u : b_rows, p.bk,
+                      b8_mn ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, true);
   }
   if (rc == B200_OK && !ctx->tc_smem_configured) {
     const int max_dyn = static_cast<int>(ctx->smem_optin - 512);

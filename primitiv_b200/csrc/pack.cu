@@ -467,8 +467,10 @@ __global__ void __launch_bounds__(256) pack_mix_transpose64_kernel(const float *
         const unsigned long long o = dst_b + static_cast<unsigned long long>(i0 + im) * k + p0 + pk;
         *reinterpret_cast<float4 *>(hi + o) = m.h0;
         *reinterpret_cast<float4 *>(hi + o + 4) = m.h1;
-        *reinterpret_cast<uint4 *>(h8 + o) = m.h8;
-        *reinterpret_cast<uint4 *>(l8 + o) = m.l8;
+        if (h8) {
+          *reinterpret_cast<uint4 *>(h8 + o) = m.h8;
+          *reinterpret_cast<uint4 *>(l8 + o) = m.l8;
+        }
       }
     }
     __syncthreads();
@@ -509,8 +511,10 @@ __global__ void __launch_bounds__(256) pack_mix_kernel(const float *__restrict__
         const float h = rn_tf32(x);
         const unsigned long long o = dst_b + static_cast<unsigned long long>(i) * k_pad + pp;
         hi[o] = h;
-        h8[o] = __float2bfloat16_rn(x);
-        l8[o] = __float2bfloat16_rn(x - h);
+        if (h8) {
+          h8[o] = __float2bfloat16_rn(x);
+          l8[o] = __float2bfloat16_rn(x - h);
+        }
       }
     }
     if (kTranspose) __syncthreads();
@@ -577,17 +581,18 @@ MixPlanes mix_planes(const OperandView &v) {
 }
 
 void pack_mix(b200_ctx *ctx, cudaStream_t stream, OperandView &v, float *dst, const MixPlanes &lay,
-              const void *planes_out[3]) {
+              const void *planes_out[3], bool hi_only) {
   float *hi = dst;
-  __nv_bfloat16 *h8 = reinterpret_cast<__nv_bfloat16 *>(dst + lay.hi_elems);
-  __nv_bfloat16 *l8 = h8 + lay.h8_elems;
+  // (the kernels below skip the bf16 planes when their pointers are null)
+  __nv_bfloat16 *h8 = hi_only ? nullptr : reinterpret_cast<__nv_bfloat16 *>(dst + lay.hi_elems);
+  __nv_bfloat16 *l8 = hi_only ? nullptr : h8 + lay.h8_elems;
   const bool src_ok = (reinterpret_cast<uintptr_t>(v.ptr) & 15u) == 0 && v.k % 8u == 0 &&
                       (v.nbatch <= 1 || v.batch_stride % 4u == 0);
   const bool dense = v.nbatch <= 1 || v.batch_stride == static_cast<uint64_t>(v.mn) * v.k;
   const float *src = static_cast<const float *>(v.ptr);
   {
     ProfScope prof(ctx, kProfPack, stream);
-    if (!v.mn_major && src_ok && dense && v.ld == v.k) {
+    if (!hi_only && !v.mn_major && src_ok && dense && v.ld == v.k) {
       const unsigned long long n4 = static_cast<unsigned long long>(v.nbatch) * v.mn * v.k / 4ull;
       const unsigned long long cap = static_cast<unsigned long long>(ctx->sm_count) * 16ull;
       const unsigned long long need = (n4 + 1023ull) / 1024ull;

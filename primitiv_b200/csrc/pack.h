@@ -53,8 +53,9 @@ struct MixPlanes {
 };
 MixPlanes mix_planes(const OperandView &v);
 // planes_out = {hi, hi8, lo8}; v is rewritten to describe the packed operand (K-major, ld = kpad).
+// With hi_only the TF32 plane alone is written (dst holds lay.hi_elems floats; planes_out[1], [2] are null).
 void pack_mix(b200_ctx *ctx, cudaStream_t stream, OperandView &v, float *dst, const MixPlanes &lay,
-              const void *planes_out[3]);
+              const void *planes_out[3], bool hi_only = false);
 
 // Flat form of the same three planes: element e of the caller's array <-> element e of each plane,
 // so the planes keep the operand's major-ness and serve any later use of the same array.  Possible
