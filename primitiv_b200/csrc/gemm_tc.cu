@@ -1215,7 +1215,9 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
       // (single pass: an MN-major B is the one layout the kernel reads slowly, a fifth of the main
       // loop; from about 2600 output rows up that costs more than transposing B once into K-major
       // scratch, 8 bytes of traffic per element)
-      const bool slow_b = passes == 1 && o == 1 && v.mn_major && g.m >= 2560u && !fixed_scratch;
+      // (and only for a B of 4 Mi elements or more: for a small product the extra launch costs more)
+      const bool slow_b = passes == 1 && o == 1 && v.mn_major && g.m >= 2560u && !fixed_scratch &&
+                          static_cast<uint64_t>(v.mn) * v.k * (v.nbatch ? v.nbatch : 1u) >= (1ull << 22);
       pack[o] = passes == 3 || slow_b || !direct_ok(v.ptr, v.ld, v.batch_stride, v.nbatch, 4);
       lay[o] = tf32_planes(v);
       if (pack[o]) total += planes * lay[o].plane_elems;
