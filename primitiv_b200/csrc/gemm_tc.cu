@@ -1140,7 +1140,10 @@ int gemm_tc_run(b200_ctx *ctx, const GemmArgs &g, cudaStream_t stream, float *fi
       const bool b_mn = o == 1 && views[o]->mn_major;
       const bool flat_possible = !fixed_scratch && ctx->correction_policy == 0 && mix_flat_ok(*views[o]);
       const bool cached = flat_possible && b_mn && mix_flat_cached(ctx, *views[o]);
-      *flat[o] = flat_possible && (!b_mn || (g.m <= 1536u && cached));
+      // (a small B as well, whatever m: its transposing pre-pass would be one more launch in a chain of
+      // few-microsecond kernels, more than a fifth of such a product's main loop)
+      const bool small_b = static_cast<uint64_t>(views[o]->mn) * views[o]->k * (views[o]->nbatch ? views[o]->nbatch : 1u) < (1ull << 20);
+      *flat[o] = flat_possible && (!b_mn || ((g.m <= 1536u || small_b) && cached));
       // Only the TF32 plane of an MN-major B is slow to read; its bf16 planes are not.  With the flat
       // planes already cached, the transposing pre-pass therefore writes the TF32 plane alone (8
       // instead of 12 bytes per element) and the correction passes read the cached bf16 planes.

@@ -161,9 +161,10 @@ def test_operand_cache_shares_planes_between_forward_and_backward(ctx, batches, 
     misses) and the second use of each finds those planes (three hits).  b's second use is as an
     MN-major B operand, whose TF32 plane the kernel reads slowly: with few output rows (di = 384)
     that product still takes all of b's cached planes (transposing b would cost more than the slower
-    main loop), with many (di = 1664) it takes the cached bf16 planes and transposes the TF32 plane
-    alone into scratch.  The results are the oracle's."""
-    dj, dk = 256, 512
+    main loop; a b of under a million elements does the same whatever di), with many (di = 1664, b of
+    a million elements) it takes the cached bf16 planes and transposes the TF32 plane alone into
+    scratch.  The results are the oracle's."""
+    dj, dk = (256, 512) if di == 384 else (1024, 1024)
     ba, bb = batches
     bs = max(ba, bb)
     rng = np.random.default_rng(31 + ba * 10 + bb)
