@@ -120,6 +120,11 @@ B200_API int b200_slice_fw(b200_ctx *ctx, int mode, const void *x, void *y, uint
 B200_API int b200_slice_bw(b200_ctx *ctx, int mode, const void *gy, void *gx, uint64_t base,
                            uint32_t x_dim, uint32_t y_dim, uint32_t offset, uint64_t repeat,
                            uint32_t bx, uint32_t by, void *stream);
+/* The same with an `accumulate` flag: 0 for a gx that holds nothing yet (a gradient whose zero-fill
+ * the caller has deferred): every element of gx is stored, the slice from gy, the rest as zeros. */
+B200_API int b200_slice_bw_ex(b200_ctx *ctx, int mode, const void *gy, void *gx, uint64_t base,
+                              uint32_t x_dim, uint32_t y_dim, uint32_t offset, uint64_t repeat,
+                              uint32_t bx, uint32_t by, int accumulate, void *stream);
 /* concat.cc, one input at a time: y[b][.., offset + j, ..] = x[b or 0][.., j, ..] (x_dim rows of y_dim). */
 B200_API int b200_concat_part(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t base,
                               uint32_t x_dim, uint32_t y_dim, uint32_t offset, uint64_t repeat,

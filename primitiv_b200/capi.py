@@ -78,6 +78,7 @@ SIGNATURES = {
     "b200_copy": (_int, [_vp, _int, _vp, _int, _vp, _u64, _vp]),
     "b200_slice_fw": (_int, [_vp, _int, _vp, _vp, _u64, _u32, _u32, _u32, _u64, _vp]),
     "b200_slice_bw": (_int, [_vp, _int, _vp, _vp, _u64, _u32, _u32, _u32, _u64, _u32, _u32, _vp]),
+    "b200_slice_bw_ex": (_int, [_vp, _int, _vp, _vp, _u64, _u32, _u32, _u32, _u64, _u32, _u32, _int, _vp]),
     "b200_concat_part": (_int, [_vp, _int, _vp, _vp, _u64, _u32, _u32, _u32, _u64, _u32, _int, _vp]),
     "b200_pick_fw": (_int, [_vp, _int, _vp, _vp, _u32, _vp, _u64, _u32, _u64, _u32, _int, _vp]),
     "b200_pick_bw": (_int, [_vp, _int, _vp, _vp, _u32, _vp, _u64, _u32, _u64, _u32, _int, _vp]),

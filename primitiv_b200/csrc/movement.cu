@@ -41,6 +41,26 @@ __global__ void __launch_bounds__(kBlock) slice_bw_flat_kernel(const T *__restri
   }
 }
 
+// The same when gx is known to hold zeros that were never written (a fresh gradient): every element of
+// gx is stored, the slice from gy and the rest as zero, in place of a zero-fill followed by an add.
+template <typename T>
+__global__ void __launch_bounds__(kBlock) slice_bw_store_kernel(const T *__restrict__ gy, T *__restrict__ gx, u64 span,
+                                                                u64 skip, u64 off, u64 per_batch, u64 x_volume,
+                                                                u64 total_x, int gy_batched) {
+  pdl_enter();
+  const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
+  for (u64 d = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x; d < total_x; d += stride) {
+    const u64 n = d / x_volume, rem = d - n * x_volume;
+    const u64 r = rem / skip, jj = rem - r * skip;
+    float v = 0.f;
+    if (jj >= off && jj < off + span) {
+      const u64 e = r * span + (jj - off);
+      v = ld(gy, gy_batched ? n * per_batch + e : e);
+    }
+    st(gx, d, v);
+  }
+}
+
 // gx[0][r][offset + j][i] += sum_n gy[n][r][j][i]: a batch-1 destination of a batched gradient
 // (32 x 8 CTAs over elements x batch lanes, lanes combined in order: deterministic)
 template <typename T>
@@ -276,13 +296,30 @@ int b200_slice_fw(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t base
 
 int b200_slice_bw(b200_ctx *ctx, int mode, const void *gy, void *gx, uint64_t base, uint32_t x_dim,
                   uint32_t y_dim, uint32_t offset, uint64_t repeat, uint32_t bx, uint32_t by, void *stream) {
+  return b200_slice_bw_ex(ctx, mode, gy, gx, base, x_dim, y_dim, offset, repeat, bx, by, 1, stream);
+}
+
+int b200_slice_bw_ex(b200_ctx *ctx, int mode, const void *gy, void *gx, uint64_t base, uint32_t x_dim,
+                     uint32_t y_dim, uint32_t offset, uint64_t repeat, uint32_t bx, uint32_t by, int accumulate,
+                     void *stream) {
   B200_OPS_PROLOGUE(ctx);
   const u64 span = base * y_dim, skip = base * x_dim, per_batch = span * repeat;
-  if (per_batch == 0 || bx == 0 || by == 0) return B200_OK;
-  if (!gx || !gy || offset + y_dim > x_dim) return B200_ERR_INVALID_ARG;
+  if (bx == 0 || by == 0 || skip * repeat == 0) return B200_OK;
+  if (!gx || (per_batch && !gy) || offset + y_dim > x_dim) return B200_ERR_INVALID_ARG;
+  if (!accumulate && !(bx > 1 || by == 1)) {
+    // a batch-1 destination of a batched gradient: zeros first, then the summing form
+    const int rc = b200_fill(ctx, mode, gx, skip * repeat * bx, 0.f, stream);
+    if (rc != B200_OK) return rc;
+    accumulate = 1;
+  }
+  if (per_batch == 0 && accumulate) return B200_OK;
   ProfScope prof(ctx, kProfElementwise, s);
   B200_DISPATCH_MODE(mode, {
-    if (bx > 1 || by == 1) {
+    if (!accumulate) {
+      const u64 total_x = skip * repeat * bx;
+      b200::launch(ctx, slice_bw_store_kernel<T>, dim3(grid_for(ctx, total_x, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(gy), static_cast<T *>(gx), span, skip, base * offset, per_batch, skip * repeat,
+          total_x, by > 1);
+    } else if (bx > 1 || by == 1) {
       const u64 total = per_batch * bx;
       b200::launch(ctx, slice_bw_flat_kernel<T>, dim3(grid_for(ctx, total, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(gy), static_cast<T *>(gx), span, skip, base * offset, per_batch, skip * repeat,
           total, by > 1);

@@ -380,8 +380,11 @@ void B200::slice_bw_impl(const Tensor &gy, std::uint32_t dim, std::uint32_t offs
   const Shape &sx = gx.shape();
   const std::uint64_t base = sx.lower_volume(dim);
   const std::uint32_t x_dim = sx[dim];
-  B200_CALL(::b200_slice_bw(state_->ctx, imode(), CDATA(gy), MDATA(gx), base, x_dim, gy.shape()[dim], offset,
-                            sx.volume() / (base * x_dim), sx.batch(), gy.shape().batch(), nullptr));
+  // a gradient whose zero-fill is still pending is stored as a whole (slice from gy, zeros elsewhere)
+  int accumulate = 1;
+  void *dst = out_acc(gx, &accumulate);
+  B200_CALL(::b200_slice_bw_ex(state_->ctx, imode(), CDATA(gy), dst, base, x_dim, gy.shape()[dim], offset,
+                               sx.volume() / (base * x_dim), sx.batch(), gy.shape().batch(), accumulate, nullptr));
 }
 
 void B200::concat_fw_impl(const std::vector<const Tensor *> &xs, std::uint32_t dim, Tensor &y) {

@@ -752,6 +752,25 @@ void test_zero_gradients(Pair &p) {
     expect_close(r[0][1], r[1][1], "prelu_bw after it", tol);
     expect_close(r[0][2], r[1][2], "zeros read back", 0.f);
     expect_close(r[0][3], r[1][3], "slice_bw into zeros", tol);
+    // ... along either axis, with every batch combination, followed by a second slice that must be added
+    for (std::uint32_t dim = 0; dim < 2; ++dim) {
+      for (const auto &bb : kBatches) {
+        const Shape sx({7, 5}, bb[0]);
+        const Shape sg(dim == 0 ? std::vector<std::uint32_t>{3, 5} : std::vector<std::uint32_t>{7, 2}, bb[1]);
+        if (bb[0] > 1 && bb[1] > 1 && bb[0] != bb[1]) continue;
+        const vector<float> g1 = on_grid(rnd(sg.size())), g2 = on_grid(rnd(sg.size()));
+        vector<float> got[2];
+        for (int d = 0; d < 2; ++d) {
+          Device &dev = *devs[d];
+          Tensor gx = dev.new_tensor_by_constant(sx, 0);
+          dev.slice_bw(p.on(dev, sg, g1), dim, 1, gx);
+          dev.slice_bw(p.on(dev, sg, g2), dim, 2, gx);
+          got[d] = gx.to_vector();
+        }
+        expect_close(got[0], got[1], "slice_bw twice into zeros, dim " + std::to_string(dim) + " batches " +
+                     std::to_string(bb[0]) + "," + std::to_string(bb[1]), tol * 4);
+      }
+    }
     expect_close(r[0][4], r[1][4], "multiply_bw with ga == gb into zeros", tol);
     expect_close(r[0][5], r[1][5], "reset(0) of a live tensor, then inplace_add", tol);
     expect_close(r[0][6], r[1][6], "a block reused after a dropped pending fill", 0.f);
