@@ -95,6 +95,10 @@ B200_API int b200_binary_bw(b200_ctx *ctx, int mode, int op, const void *a, cons
 /* inplace_add.cc / inplace_subtract.cc: y[b or 0] += sign * x[b or 0] over max(bx, by) batches. */
 B200_API int b200_inplace_add(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t volume,
                               uint32_t bx, uint32_t by, float sign, void *stream);
+/* The same with an `accumulate` flag: 0 for a y that holds nothing yet (a gradient whose zero-fill
+ * the caller has deferred): y[n or 0] = sign * x[n or 0], summed over the batch for a batch-1 y. */
+B200_API int b200_inplace_add_ex(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t volume,
+                                 uint32_t bx, uint32_t by, float sign, int accumulate, void *stream);
 /* inplace_multiply_const.cc, reset_tensor.cc, identity.cc */
 B200_API int b200_inplace_multiply_const(b200_ctx *ctx, int mode, void *x, uint64_t n, float k, void *stream);
 B200_API int b200_fill(b200_ctx *ctx, int mode, void *y, uint64_t n, float value, void *stream);

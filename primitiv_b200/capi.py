@@ -66,6 +66,7 @@ SIGNATURES = {
     "b200_binary_fw": (_int, [_vp, _int, _int, _vp, _vp, _vp, _u64, _u32, _int, _int, _vp]),
     "b200_binary_bw": (_int, [_vp, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _u32, _int, _int, _int, _int, _vp]),
     "b200_inplace_add": (_int, [_vp, _int, _vp, _vp, _u64, _u32, _u32, ctypes.c_float, _vp]),
+    "b200_inplace_add_ex": (_int, [_vp, _int, _vp, _vp, _u64, _u32, _u32, ctypes.c_float, _int, _vp]),
     "b200_inplace_multiply_const": (_int, [_vp, _int, _vp, _u64, ctypes.c_float, _vp]),
     "b200_fill": (_int, [_vp, _int, _vp, _u64, ctypes.c_float, _vp]),
     "b200_identity": (_int, [_vp, _int, _vp, _u32, _vp]),

@@ -317,27 +317,28 @@ __global__ void __launch_bounds__(kBlock) scalar_fw_kernel(const T *__restrict__
 template <typename T>
 __global__ void __launch_bounds__(kBlock) inplace_add_kernel(const T *__restrict__ x, T *__restrict__ y,
                                                              u64 volume, uint32_t bx, uint32_t by, float sign,
-                                                             int vec) {
+                                                             int vec, int accumulate) {
   pdl_enter();
   const u64 tid = static_cast<u64>(blockIdx.x) * blockDim.x + threadIdx.x;
   const u64 stride = static_cast<u64>(gridDim.x) * blockDim.x;
   constexpr int N = Vec<T>::N;
   {
     // every destination element gets exactly one source element: flat and vectorised
-    // (a batch-1 destination of a batched source is a batch sum: launch_batch_sum)
+    // (a batch-1 destination of a batched source is a batch sum: launch_batch_sum);
+    // accumulate == 0: y holds nothing yet and is stored, not added to
     const u64 total = volume * by;
     const u64 nv = vec ? total / N : 0;
     for (u64 i = tid; i < nv; i += stride) {
       const u64 e = i * N;
       Vec<T> vx, vy;
       vx.load(x + (bx > 1 ? e : e % volume));
-      vy.load(y + e);
+      if (accumulate) vy.load(y + e);
 #pragma unroll
-      for (int j = 0; j < N; ++j) vy.set(j, vy.get(j) + sign * vx.get(j));
+      for (int j = 0; j < N; ++j) vy.set(j, (accumulate ? vy.get(j) : 0.f) + sign * vx.get(j));
       vy.store(y + e);
     }
     for (u64 e = nv * N + tid; e < total; e += stride)
-      st(y, e, ld(y, e) + sign * ld(x, bx > 1 ? e : e % volume));
+      st(y, e, (accumulate ? ld(y, e) : 0.f) + sign * ld(x, bx > 1 ? e : e % volume));
   }
 }
 
@@ -547,6 +548,11 @@ int b200_binary_bw(b200_ctx *ctx, int mode, int op, const void *a, const void *b
 
 int b200_inplace_add(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t volume, uint32_t bx,
                      uint32_t by, float sign, void *stream) {
+  return b200_inplace_add_ex(ctx, mode, x, y, volume, bx, by, sign, 1, stream);
+}
+
+int b200_inplace_add_ex(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t volume, uint32_t bx,
+                        uint32_t by, float sign, int accumulate, void *stream) {
   B200_OPS_PROLOGUE(ctx);
   if (volume == 0 || bx == 0 || by == 0) return B200_OK;
   if (!x || !y || (bx != by && bx != 1 && by != 1)) return B200_ERR_INVALID_ARG;
@@ -554,12 +560,12 @@ int b200_inplace_add(b200_ctx *ctx, int mode, const void *x, void *y, uint64_t v
   B200_DISPATCH_MODE(mode, {
     if (by == 1 && bx > 1) {
       // the destination receives the sum over the batch
-      const int rc = launch_batch_sum<T>(ctx, s, x, y, volume, bx, sign, 1);
+      const int rc = launch_batch_sum<T>(ctx, s, x, y, volume, bx, sign, accumulate ? 1 : 0);
       if (rc != B200_OK) return rc;
     } else {
       const int vec = aligned16(x) && aligned16(y) && volume % Vec<T>::N == 0;
       const u64 work = volume * by / (vec ? Vec<T>::N : 1) + 1;
-      b200::launch(ctx, inplace_add_kernel<T>, dim3(grid_for(ctx, work, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y), volume, bx, by, sign, vec);
+      b200::launch(ctx, inplace_add_kernel<T>, dim3(grid_for(ctx, work, kBlock)), dim3(kBlock), 0, s, 1u, static_cast<const T *>(x), static_cast<T *>(y), volume, bx, by, sign, vec, accumulate ? 1 : 0);
     }
   });
   B200_OPS_EPILOGUE(ctx);

@@ -704,22 +704,16 @@ void B200::inplace_multiply_const_impl(float k, Tensor &x) {
 void B200::inplace_add_impl(const Tensor &x, Tensor &y) {
   const void *px = in(x);
   int acc = 1;
-  void *py = out_acc(y, &acc);
-  const std::uint32_t bx = x.shape().batch(), by = y.shape().batch();
-  if (!acc && bx == by) {
-    // y held (deferred) zeros: y = x
-    B200_CALL(::b200_copy(state_->ctx, imode(), px, imode(), py, y.shape().size(), nullptr));
-  } else if (!acc && by == 1) {
-    // y = sum over the batch of x
-    B200_CALL(::b200_batch_sum_fw(state_->ctx, imode(), px, py, y.shape().volume(), bx, nullptr));
-  } else {
-    if (!acc) B200_CALL(::b200_fill(state_->ctx, imode(), py, y.shape().size(), 0.f, nullptr));
-    B200_CALL(::b200_inplace_add(state_->ctx, imode(), px, py, y.shape().volume(), bx, by, 1.f, nullptr));
-  }
+  void *py = out_acc(y, &acc);   // acc == 0: y held (deferred) zeros and is stored, not added to
+  B200_CALL(::b200_inplace_add_ex(state_->ctx, imode(), px, py, y.shape().volume(), x.shape().batch(), y.shape().batch(),
+                                  1.f, acc, nullptr));
 }
 void B200::inplace_subtract_impl(const Tensor &x, Tensor &y) {
-  B200_CALL(::b200_inplace_add(state_->ctx, imode(), CDATA(x), MDATA(y), y.shape().volume(), x.shape().batch(),
-                               y.shape().batch(), -1.f, nullptr));
+  const void *px = in(x);
+  int acc = 1;
+  void *py = out_acc(y, &acc);
+  B200_CALL(::b200_inplace_add_ex(state_->ctx, imode(), px, py, y.shape().volume(), x.shape().batch(), y.shape().batch(),
+                                  -1.f, acc, nullptr));
 }
 
 }  // namespace devices
